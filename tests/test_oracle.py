@@ -1,0 +1,106 @@
+"""The CPU oracle against fixtures produced by the reference's own test code."""
+
+import torch
+
+import oracle
+
+
+def _operand(case, which):
+    data, sf = case[which], case['sf' + which]
+    is_fp4 = case.get(f'{which}_is_fp4', False)
+    major = case.get(f'{which}_major', 'K')
+    if is_fp4:
+        # two codes per byte along the operand's contiguous axis: K for a K-major
+        # operand ([MN, K/2]), MN for an MN-major one (logical [MN/2, K])
+        vals = oracle.decode_e2m1_packed(data, axis=-2 if major == 'MN' else -1)
+    else:
+        vals = oracle.decode_e4m3(data)
+    return vals, sf
+
+
+def test_dense_cases_match_reference_oracle(golden):
+    names = [n for n in golden if n.startswith('dense_')]
+    assert len(names) >= 8
+    for name in names:
+        c = golden[name]
+        gm, gn, gk = c['recipe']
+        a_vals, sfa = _operand(c, 'a')
+        b_vals, sfb = _operand(c, 'b')
+        a = oracle.dequantize(a_vals, sfa, gm, gk)
+        b = oracle.dequantize(b_vals, sfb, gn, gk)
+        d = oracle.gemm_ref(a, b, c['d'].dtype,
+                            c=c['c'] if c['accumulate'] else None,
+                            bias=c['c'] if c['with_bias'] else None,
+                            alpha=c['alpha'])
+        assert torch.equal(d, c['d']), name
+
+
+def test_m_grouped_matches_reference_oracle(golden):
+    for name in ('mgrouped_fp8_nt', 'mgrouped_fp8_nn'):
+        c = golden[name]
+        a = oracle.dequantize(oracle.decode_e4m3(c['a']), c['sfa'], 1, 32)
+        # scale rows in the group padding hold garbage on purpose; A is zero there
+        a = torch.nan_to_num(a, nan=0.0, posinf=0.0, neginf=0.0)
+        b = oracle.dequantize(oracle.decode_e4m3(c['b']), c['sfb'], 1, 32)
+        d = oracle.m_grouped_psum_ref(a, b, c['psum'], torch.bfloat16)
+        assert torch.equal(d, c['d']), name
+
+
+def test_psum_layout(golden):
+    c = golden['psum_layout']
+    sizes, last = [], 0
+    for p in c['psum']:
+        sizes.append(p - last)
+        last = oracle.align(p, 256)
+    total, psum = oracle.make_psum_layout(sizes, 256)
+    assert total == c['total'] and psum == c['psum']
+    assert [(s.start, s.stop) for s in oracle.psum_valid_spans(psum)] == c['valid']
+    assert [(s.start, s.stop) for s in oracle.psum_padding_spans(psum)] == c['pad']
+
+
+def test_quantizers(golden):
+    for name, gran in (('quant_fp8_1x128', (1, 128)), ('quant_fp8_128x128', (128, 128))):
+        c = golden[name]
+        q, sf, rep = oracle.quantize_e4m3(c['x'], gran)
+        assert torch.equal(q.view(torch.uint8), c['q'])
+        assert torch.equal(sf, c['sf']) and torch.equal(rep, c['repr'])
+    c = golden['quant_fp4_1x32']
+    q, sf, rep = oracle.quantize_e2m1(c['x'], (1, 32))
+    assert torch.equal(q.contiguous(), c['q']) and torch.equal(sf, c['sf']) and torch.equal(rep, c['repr'])
+    assert torch.equal(oracle.dequantize(oracle.decode_e2m1_packed(q), sf, 1, 32), rep)
+
+
+def test_sf_layout_model(golden):
+    cases = golden['sf_layout']
+    assert len(cases) == 12
+    for name, c in cases.items():
+        out = oracle.required_sf_layout(c['sf'], c['mn'], c['k'], c['gran'])
+        assert out.dtype == torch.int16 and out.shape == c['expected'].shape, name
+        assert out.stride(-2) == 1 and out.stride(-1) == out.size(-2), name
+        assert torch.equal(out, c['expected']), name
+
+
+def test_sf_gran_k_128_is_replication():
+    torch.manual_seed(0)
+    mn, k = 24, 640
+    e = torch.randint(100, 140, (mn, 5), dtype=torch.int32)
+    sf128 = (e << 23).view(torch.float32)
+    sf32 = sf128.repeat_interleave(4, dim=1)
+    a = oracle.required_sf_layout(sf128, mn, k, 1, gran_k=128)
+    b = oracle.required_sf_layout(sf32, mn, k, 1, gran_k=32)
+    assert torch.equal(a, b)
+    assert torch.equal(oracle.unpack_required_sf(a, k), sf32)
+
+
+def test_e2m1_to_e4m3_map_is_exact():
+    for code in range(16):
+        byte = oracle.e2m1_to_e4m3_byte(code)
+        val = torch.tensor([byte], dtype=torch.uint8).view(torch.float8_e4m3fn).float().item()
+        assert val == oracle.E2M1_VALUES[code] and (val != 0 or code in (0, 8))
+
+
+def test_metrics():
+    x = torch.randn(64, 64)
+    assert oracle.calc_diff(x, x) == 0.0
+    assert oracle.max_rel_err(x, x) == 0.0
+    assert oracle.calc_diff(x, -x) > 1.9
