@@ -1,0 +1,484 @@
+// C ABI of libdg_b200.so: validation, the B200 tiling heuristic, TMA descriptor construction, launch.
+//
+// Host-side counterpart of the reference's launchers (csrc/jit_kernels/fp8_gemm.hpp:11-151,
+// fp8_dequant_gemm.hpp:24-95), of its tiling search (csrc/jit_kernels/heuristics.hpp:592-755) and of the
+// runtime knobs (csrc/jit/jit.hpp:18-76). Nothing here allocates device memory or synchronises.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "host_common.h"
+#include "launch.h"
+
+namespace dg {
+
+// ------------------------------------------------------------------------------------------------
+// Errors
+// ------------------------------------------------------------------------------------------------
+static thread_local char tls_error[512] = "";
+
+void set_last_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(tls_error, sizeof(tls_error), fmt, ap);
+    va_end(ap);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Runtime knobs
+// ------------------------------------------------------------------------------------------------
+static std::atomic<int> g_num_sms{0};   // 0 = not set: use the device's SM count
+
+static int device_sm_count() {
+    static std::atomic<int> cached{0};
+    int v = cached.load();
+    if (v > 0) return v;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) {
+        cached.store(sms);
+        return sms;
+    }
+    (void)cudaGetLastError();
+    return 148;    // B200; used when planning without a device (dry run)
+}
+
+static uint32_t effective_num_sms(const dg_gemm_desc_t& d) {
+    int n = d.num_sms ? (int)d.num_sms : (g_num_sms.load() > 0 ? g_num_sms.load() : device_sm_count());
+    return (uint32_t)(n < 1 ? 1 : n);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Small helpers
+// ------------------------------------------------------------------------------------------------
+static inline uint32_t ceil_div_u32(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+static inline uint64_t align_u64(uint64_t a, uint64_t b) { return (a + b - 1) / b * b; }
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+static inline uint32_t elem_size(int dtype) { return dtype == DG_F32 ? 4u : dtype == DG_BF16 ? 2u : 1u; }
+
+static bool is_grouped(int t) { return t == DG_GEMM_M_GROUPED_PSUM || t == DG_GEMM_M_GROUPED_MASKED; }
+
+// Can D (or the split-K workspace) be written through TMA?
+static bool tma_store_ok(const dg_gemm_desc_t& d) {
+    const uint32_t es = elem_size(d.d_dtype);
+    return aligned16(d.d) && (d.outer_stride_d * es) % 16 == 0 &&
+           (d.gemm_type != DG_GEMM_M_GROUPED_MASKED || (d.group_stride_d * es) % 16 == 0);
+}
+
+static int validate(const dg_gemm_desc_t& d) {
+    DG_CHECK_ARG(d.gemm_type == DG_GEMM_NORMAL || is_grouped(d.gemm_type) ||
+                 d.gemm_type == DG_GEMM_K_GROUPED_PSUM || d.gemm_type == DG_GEMM_BATCHED, "Unknown gemm type %d", d.gemm_type);
+    DG_UNSUPPORTED(d.gemm_type == DG_GEMM_K_GROUPED_PSUM || d.gemm_type == DG_GEMM_BATCHED,
+                   "K-grouped and batched GEMM are not built in this library");
+    DG_CHECK_ARG(d.a_dtype == DG_E4M3 || d.a_dtype == DG_E2M1X2, "Unsupported operand dtypes");
+    DG_CHECK_ARG(d.b_dtype == DG_E4M3 || d.b_dtype == DG_E2M1X2, "Unsupported operand dtypes");
+    DG_CHECK_ARG(!(d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E4M3), "Unsupported operand dtypes");
+    DG_UNSUPPORTED(d.a_dtype == DG_E2M1X2, "FP4 x FP4 GEMM is not built in this library");
+    DG_UNSUPPORTED(d.b_dtype == DG_E2M1X2, "FP8 x FP4 GEMM is not built yet");
+    DG_CHECK_ARG(d.d_dtype == DG_BF16 || d.d_dtype == DG_F32, "D must be bf16 or fp32");
+    DG_CHECK_ARG(d.major_a == DG_MAJOR_K || d.major_a == DG_MAJOR_MN, "bad major_a");
+    DG_CHECK_ARG(d.major_b == DG_MAJOR_K || d.major_b == DG_MAJOR_MN, "bad major_b");
+    DG_CHECK_ARG(d.m > 0 && d.n > 0 && d.k > 0, "empty problems are handled by the caller (m, n, k must be > 0)");
+    DG_CHECK_ARG(d.a && d.b && d.d && d.sfa && d.sfb, "null operand pointer");
+    DG_CHECK_ARG(d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_ALPHA || d.epilogue == DG_EPILOGUE_BIAS,
+                 "unknown epilogue");
+    DG_CHECK_ARG(!(d.epilogue == DG_EPILOGUE_BIAS && d.bias == nullptr), "bias epilogue without a bias pointer");
+    DG_CHECK_ARG(!(d.epilogue == DG_EPILOGUE_BIAS && d.accumulate), "bias and accumulation cannot be used together");
+    if (is_grouped(d.gemm_type)) {
+        DG_CHECK_ARG(d.grouped_layout != nullptr && d.num_groups > 0, "grouped GEMM needs grouped_layout and num_groups");
+        DG_CHECK_ARG(d.major_a == DG_MAJOR_K, "A must be K-major for m-grouped GEMM");
+        DG_CHECK_ARG(!d.accumulate, "grouped matmul doesn't support accumulation");
+        DG_CHECK_ARG(d.epilogue != DG_EPILOGUE_BIAS, "grouped matmul doesn't support bias");
+    }
+    if (d.gemm_type == DG_GEMM_M_GROUPED_PSUM)
+        DG_CHECK_ARG(d.m % 256 == 0, "m-grouped psum layout: total rows must be a multiple of the 256-row alignment");
+
+    // What TMA needs from the operands. The caller repacks (dg_pad_rows_launch) when these fail.
+    DG_UNSUPPORTED(!aligned16(d.a) || d.outer_stride_a % 16 != 0 || d.group_stride_a % 16 != 0,
+                   "A: base and strides must be multiples of 16 bytes");
+    DG_UNSUPPORTED(!aligned16(d.b) || d.outer_stride_b % 16 != 0 || d.group_stride_b % 16 != 0,
+                   "B: base and strides must be multiples of 16 bytes");
+    DG_UNSUPPORTED(!aligned16(d.sfa) || d.sfa_stride % 8 != 0 || d.sfa_group_stride % 8 != 0,
+                   "SFA: base and strides must be multiples of 16 bytes");
+    DG_UNSUPPORTED(!aligned16(d.sfb) || d.sfb_stride % 8 != 0 || d.sfb_group_stride % 8 != 0,
+                   "SFB: base and strides must be multiples of 16 bytes");
+    return DG_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Heuristic
+// ------------------------------------------------------------------------------------------------
+static uint32_t tmem_cols_for(uint32_t block_n, uint32_t accum_stages) {
+    const uint32_t need = accum_stages * block_n + 4 + 4 * (sfb_rows(block_n) / 128);
+    uint32_t cols = 32;
+    while (cols < need) cols *= 2;
+    return cols;
+}
+
+static uint32_t max_stages_for(uint32_t block_n, uint32_t cta_group) {
+    constexpr uint32_t kSmemCap = 227 * 1024;
+    uint32_t best = 0;
+    for (uint32_t s = 1; s <= kMaxStages; ++s)
+        if (make_smem_layout(block_n, s, cta_group).total <= kSmemCap) best = s;
+    return best;
+}
+
+// Fill the derived fields of a configuration whose block_n / cta_group / split_k are set.
+static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
+    const uint32_t num_sms = effective_num_sms(d);
+    c.block_m = kBlockM * c.cta_group;
+    c.block_k = kBlockK;
+    const bool d_fp32 = d.d_dtype == DG_F32;
+    const bool split = c.split_k > 1;
+    const bool tma_ok = split || tma_store_ok(d);
+    if (split) c.epilogue_mode = kEpiTmaReduce;
+    else if (d.accumulate) c.epilogue_mode = tma_ok ? kEpiTmaReduce : kEpiPlainAtomic;
+    else c.epilogue_mode = tma_ok ? kEpiTmaStore : kEpiPlainStore;
+
+    const bool out_fp32 = split || d_fp32;
+    const uint32_t gran = (c.epilogue_mode <= kEpiTmaReduce && !out_fp32) ? 64u : 32u;
+    DG_CHECK_ARG(c.cta_group == 1 || c.cta_group == 2, "cta_group must be 1 or 2");
+    DG_CHECK_ARG(c.block_n >= gran && c.block_n <= 256 && c.block_n % gran == 0,
+                 "block_n must be a multiple of %u in [%u, 256]", gran, gran);
+    DG_CHECK_ARG(c.block_n % (16 * c.cta_group) == 0, "block_n not valid for this cta_group");
+    if (d.major_b == DG_MAJOR_MN)
+        DG_CHECK_ARG((c.block_n / c.cta_group) % 128 == 0, "MN-major B needs block_n / cta_group to be a multiple of 128");
+    DG_CHECK_ARG(c.cta_group == 1 || d.gemm_type != DG_GEMM_M_GROUPED_MASKED, "masked grouped GEMM uses cta_group 1");
+    DG_CHECK_ARG(!split || d.gemm_type == DG_GEMM_NORMAL, "split-K is only available for the dense GEMM");
+
+    const uint32_t accum_stages = (2 * c.block_n + 4 + 4 * (sfb_rows(c.block_n) / 128) <= 512) ? 2u : 1u;
+    c.tmem_cols = tmem_cols_for(c.block_n, accum_stages);
+    c.reserved[0] = accum_stages;
+    const uint32_t max_stages = max_stages_for(c.block_n, c.cta_group);
+    if (c.num_stages == 0 || c.num_stages > max_stages) c.num_stages = max_stages;
+    DG_CHECK_ARG(c.num_stages >= 1, "tile does not fit in shared memory");
+    const uint32_t nkb = ceil_div_u32(d.k, kBlockK);
+    if (c.num_stages > nkb * 4 && c.num_stages > 2) c.num_stages = nkb * 4 > 2 ? nkb * 4 : 2;
+    if (c.num_stages > max_stages) c.num_stages = max_stages;
+    if (split) {
+        DG_CHECK_ARG(c.split_k <= nkb, "split_k larger than the number of K blocks");
+        // every split must own at least one K block
+        const uint32_t per = ceil_div_u32(nkb, c.split_k);
+        c.split_k = ceil_div_u32(nkb, per);
+    }
+    // one CTA per SM: keep the dynamic shared memory above half of the SM's capacity
+    const uint32_t need = make_smem_layout(c.block_n, c.num_stages, c.cta_group).total;
+    c.smem_bytes = need < 120u * 1024 ? 120u * 1024 : need;
+
+    uint32_t grid_units;
+    const uint32_t max_units = num_sms / c.cta_group;
+    if (d.gemm_type == DG_GEMM_NORMAL) {
+        const uint64_t tiles = (uint64_t)ceil_div_u32(d.m, c.block_m) * ceil_div_u32(d.n, c.block_n) * c.split_k;
+        grid_units = (uint32_t)(tiles < max_units ? tiles : max_units);
+    } else {
+        uint64_t bound;   // an upper bound on the tile count; the real count is only known on device
+        if (d.gemm_type == DG_GEMM_M_GROUPED_PSUM) bound = (uint64_t)(d.m / c.block_m) * ceil_div_u32(d.n, c.block_n);
+        else bound = (uint64_t)d.num_groups * ceil_div_u32(d.m, c.block_m) * ceil_div_u32(d.n, c.block_n);
+        grid_units = (uint32_t)(bound < max_units ? bound : max_units);
+    }
+    if (grid_units == 0) grid_units = 1;
+    c.num_ctas = grid_units * c.cta_group;
+    return DG_OK;
+}
+
+static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
+    memset(&c, 0, sizeof(c));
+    const uint32_t num_sms = effective_num_sms(d);
+    const bool d_fp32 = d.d_dtype == DG_F32;
+    const bool tma_ok = tma_store_ok(d);
+    const uint32_t nkb = ceil_div_u32(d.k, kBlockK);
+    c.cta_group = 1;
+
+    // Rows one CTA wave has to cover per tile column, used to cost a candidate block_n.
+    const uint32_t m_blocks = d.gemm_type == DG_GEMM_NORMAL ? ceil_div_u32(d.m, kBlockM)
+                            : d.gemm_type == DG_GEMM_M_GROUPED_PSUM ? d.m / kBlockM
+                            : d.num_groups * ceil_div_u32(d.expected_m ? (d.expected_m < d.m ? d.expected_m : d.m) : d.m, kBlockM);
+
+    double best_cost = 1e30;
+    uint32_t best_bn = 0, best_split = 1;
+    for (uint32_t split = 1; split <= 16; ++split) {
+        if (split > 1 && (d.gemm_type != DG_GEMM_NORMAL || nkb / split < 4)) break;
+        const bool out_fp32 = d_fp32 || split > 1;
+        const uint32_t gran = ((tma_ok || split > 1) && !out_fp32) ? 64u : 32u;
+        for (uint32_t bn = gran; bn <= 256; bn += gran) {
+            if (d.major_b == DG_MAJOR_MN && bn % 128 != 0) continue;
+            if (bn > 64 && bn - gran >= d.n) continue;           // wider than the problem: no gain
+            const uint32_t n_blocks = ceil_div_u32(d.n, bn);
+            const uint64_t tiles = (uint64_t)m_blocks * n_blocks * split;
+            const uint64_t waves = (tiles + num_sms - 1) / num_sms;
+            const uint32_t kb_per = ceil_div_u32(nkb, split);
+            const bool single_accum = 2 * bn + 4 + 4 * (sfb_rows(bn) / 128) > 512;
+            // Time per K block of one tile, ns: tensor pipe (128 x bn x 128 at ~30 TFLOP/s per SM) against
+            // the operand bytes over this SM's share of L2 bandwidth.
+            const double t_mma = bn * 1.1;
+            const double t_load = (128.0 + bn) * 128.0 / 90.0;
+            const double t_epi = bn * (out_fp32 ? 9.0 : 7.0);
+            const double t_tile = kb_per * (t_mma > t_load ? t_mma : t_load) + (single_accum || waves == 1 ? t_epi : 0.0) + 300.0;
+            double cost = (double)waves * t_tile;
+            if (split > 1) cost += 2500.0 + 0.002 * d.m * d.n;        // finalisation pass
+            // HBM floor: every operand byte is read once
+            const double bytes = (double)d.m * d.k + (double)d.n * d.k * (is_grouped(d.gemm_type) ? d.num_groups : 1) +
+                                 (double)d.m * d.n * elem_size(d.d_dtype);
+            const double t_hbm = bytes / 6400.0;
+            if (cost < t_hbm) cost = t_hbm + 1e-3 * waves;             // prefer fewer waves when HBM-bound
+            if (cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && bn > best_bn)) {
+                best_cost = cost; best_bn = bn; best_split = split;
+            }
+        }
+    }
+    DG_CHECK_ARG(best_bn != 0, "no legal tiling for this problem");
+    c.block_n = best_bn;
+    c.split_k = best_split;
+    return complete_config(d, c);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Tensor maps
+// ------------------------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+    static std::atomic<void*> cached{nullptr};
+    void* fn = cached.load();
+    if (fn == nullptr) {
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return nullptr;
+        cached.store(fn);
+    }
+    return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+}
+
+// dims / box innermost first; strides_bytes has rank-1 entries (innermost is contiguous).
+static int encode_map(CUtensorMap* out, CUtensorMapDataType dtype, uint32_t rank, const void* base,
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                      CUtensorMapSwizzle swizzle, const char* what) {
+    auto fn = get_encode_fn();
+    if (fn == nullptr) { set_last_error("cuTensorMapEncodeTiled is not available from this driver"); return DG_ERR_CUDA; }
+    cuuint64_t gdim[5]; cuuint64_t gstr[4]; cuuint32_t bdim[5]; cuuint32_t estr[5];
+    for (uint32_t i = 0; i < rank; ++i) { gdim[i] = dims[i]; bdim[i] = box[i]; estr[i] = 1; }
+    for (uint32_t i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+    CUresult r = fn(out, dtype, rank, const_cast<void*>(base), gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error("cuTensorMapEncodeTiled failed for %s with code %d (dims %llu x %llu x %llu, strides %llu, %llu, box %u x %u x %u)",
+                       what, (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)(rank > 2 ? dims[2] : 1),
+                       (unsigned long long)strides_bytes[0], (unsigned long long)(rank > 2 ? strides_bytes[1] : 0), box[0], box[1], rank > 2 ? box[2] : 1);
+        return DG_ERR_CUDA;
+    }
+    return DG_OK;
+}
+
+static uint64_t nonzero_stride(uint64_t s, uint64_t fallback) { return s ? s : fallback; }
+
+static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* workspace, size_t workspace_bytes,
+                      bool encode, LaunchPlan& plan) {
+    memset(&plan, 0, sizeof(plan));
+    GemmKernelArgs& a = plan.args;
+    const bool masked = d.gemm_type == DG_GEMM_M_GROUPED_MASKED;
+    const bool grouped = is_grouped(d.gemm_type);
+    const bool split = c.split_k > 1;
+    const uint32_t accum_stages = c.reserved[0];
+    const uint32_t groups = grouped ? d.num_groups : 1;
+
+    a.m = d.m; a.n = d.n; a.k = d.k;
+    a.block_n = c.block_n;
+    a.num_stages = c.num_stages;
+    a.num_k_blocks = ceil_div_u32(d.k, kBlockK);
+    a.num_m_blocks = ceil_div_u32(d.m, c.block_m);
+    a.num_n_blocks = ceil_div_u32(d.n, c.block_n);
+    a.gemm_type = (uint32_t)d.gemm_type;
+    a.num_groups = groups;
+    a.grouped_layout = d.grouped_layout;
+    a.split_k = c.split_k;
+    a.k_blocks_per_split = ceil_div_u32(a.num_k_blocks, c.split_k);
+    a.raster_group = 8;
+    a.epilogue_mode = c.epilogue_mode;
+    a.d_is_fp32 = (split || d.d_dtype == DG_F32) ? 1u : 0u;
+    a.has_alpha = d.epilogue == DG_EPILOGUE_ALPHA ? 1u : 0u;
+    a.alpha = d.alpha;
+    a.has_bias = (d.epilogue == DG_EPILOGUE_BIAS && !split) ? 1u : 0u;
+    a.bias = d.bias;
+    a.d = d.d;
+    a.d_stride = d.outer_stride_d;
+    a.d_group_stride = d.group_stride_d;
+    a.tmem_cols = c.tmem_cols;
+    a.accum_stages = accum_stages;
+    // Instruction descriptor (block-scaled, kind::mxf8f6f4): E4M3 x E4M3, UE8M0 scales, FP32 accumulate.
+    a.idesc = ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) | ((c.block_n >> 3) << 17) | (1u << 23) |
+              (((kBlockM * c.cta_group) >> 4) << 24);
+
+    plan.cta_group = (int)c.cta_group;
+    plan.major_a = d.major_a;
+    plan.major_b = d.major_b;
+    plan.num_ctas = c.num_ctas;
+    plan.smem_bytes = c.smem_bytes;
+
+    const uint32_t ws_stride = (uint32_t)align_u64(d.n, 4);
+    if (split) {
+        const size_t need = (size_t)d.m * ws_stride * sizeof(float);
+        if (encode && (workspace == nullptr || workspace_bytes < need || !aligned16(workspace))) {
+            set_last_error("split-K needs %zu bytes of zeroed, 16-byte aligned workspace", need);
+            return DG_ERR_WORKSPACE;
+        }
+        plan.finalize = true;
+        plan.ws = static_cast<float*>(workspace);
+        plan.ws_stride = ws_stride;
+        plan.final_d = d.d;
+        plan.final_d_stride = d.outer_stride_d;
+        plan.final_d_is_fp32 = d.d_dtype == DG_F32;
+        plan.final_accumulate = d.accumulate ? 1u : 0u;
+        plan.final_bias = d.epilogue == DG_EPILOGUE_BIAS ? d.bias : nullptr;
+    }
+    if (!encode) return DG_OK;
+
+    const uint32_t load_n = c.block_n / c.cta_group;
+    const uint64_t k64 = (d.k + 63) / 64;
+    const uint64_t rows_a = d.m;      // rows per group for masked, all rows otherwise
+    // ---- A
+    {
+        const uint64_t gs = nonzero_stride(d.group_stride_a, rows_a * d.outer_stride_a);
+        if (d.major_a == DG_MAJOR_K) {
+            const uint64_t dims[3] = {d.k, rows_a, masked ? groups : 1};
+            const uint64_t str[2] = {d.outer_stride_a, gs};
+            const uint32_t box[3] = {kBlockK, kBlockM, 1};
+            if (int rc = encode_map(&plan.tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "A")) return rc;
+        } else {
+            const uint64_t dims[3] = {rows_a, d.k, 1};
+            const uint64_t str[2] = {d.outer_stride_a, align_u64((uint64_t)d.k * d.outer_stride_a, 16)};
+            const uint32_t box[3] = {kBlockM, kBlockK, 1};
+            if (int rc = encode_map(&plan.tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "A")) return rc;
+        }
+    }
+    // ---- B
+    {
+        if (d.major_b == DG_MAJOR_K) {
+            const uint64_t gs = nonzero_stride(d.group_stride_b, (uint64_t)d.n * d.outer_stride_b);
+            const uint64_t dims[3] = {d.k, d.n, groups};
+            const uint64_t str[2] = {d.outer_stride_b, gs};
+            const uint32_t box[3] = {kBlockK, load_n, 1};
+            if (int rc = encode_map(&plan.tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "B")) return rc;
+        } else {
+            const uint64_t gs = nonzero_stride(d.group_stride_b, (uint64_t)d.k * d.outer_stride_b);
+            const uint64_t dims[3] = {d.n, d.k, groups};
+            const uint64_t str[2] = {d.outer_stride_b, gs};
+            const uint32_t box[3] = {128, kBlockK, 1};
+            if (int rc = encode_map(&plan.tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "B")) return rc;
+        }
+    }
+    // ---- scale factors: int16 [rows (contiguous), K64, groups]
+    {
+        const uint64_t gs = nonzero_stride(d.sfa_group_stride, k64 * d.sfa_stride);
+        const uint64_t dims[3] = {rows_a, k64, masked ? groups : 1};
+        const uint64_t str[2] = {d.sfa_stride * 2, gs * 2};
+        const uint32_t box[3] = {128, 2, 1};
+        if (int rc = encode_map(&plan.tm_sfa, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.sfa, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE, "SFA")) return rc;
+    }
+    {
+        const uint64_t gs = nonzero_stride(d.sfb_group_stride, k64 * d.sfb_stride);
+        const uint64_t dims[3] = {d.n, k64, groups};
+        const uint64_t str[2] = {d.sfb_stride * 2, gs * 2};
+        const uint32_t box[3] = {sfb_rows(c.block_n), 2, 1};
+        if (int rc = encode_map(&plan.tm_sfb, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.sfb, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE, "SFB")) return rc;
+    }
+    // ---- D (or the split-K workspace)
+    if (c.epilogue_mode <= kEpiTmaReduce) {
+        if (split) {
+            const uint64_t dims[3] = {d.n, d.m, 1};
+            const uint64_t str[2] = {(uint64_t)ws_stride * 4, align_u64((uint64_t)d.m * ws_stride * 4, 16)};
+            const uint32_t box[3] = {32, kStoreBoxRows, 1};
+            if (int rc = encode_map(&plan.tm_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, workspace, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "workspace")) return rc;
+        } else {
+            const uint32_t es = elem_size(d.d_dtype);
+            const uint64_t gs = nonzero_stride(d.group_stride_d, (uint64_t)d.m * d.outer_stride_d);
+            const uint64_t dims[3] = {d.n, d.m, masked ? groups : 1};
+            const uint64_t str[2] = {d.outer_stride_d * es, align_u64(gs * es, 16)};
+            const uint32_t box[3] = {es == 4 ? 32u : 64u, kStoreBoxRows, 1};
+            if (int rc = encode_map(&plan.tm_d, es == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                                    d.d, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "D")) return rc;
+        }
+    } else {
+        plan.tm_d = plan.tm_a;    // unused by the plain-store epilogue, but must be a valid descriptor
+    }
+    return DG_OK;
+}
+
+static void maybe_print_config(const dg_gemm_desc_t& d, const dg_gemm_config_t& c) {
+    // One line per launch when DG_PRINT_CONFIGS is set (csrc/jit_kernels/heuristics.hpp:749-753).
+    static const bool enabled = [] { const char* e = getenv("DG_PRINT_CONFIGS"); return e && atoi(e) != 0; }();
+    if (!enabled) return;
+    fprintf(stderr, "[dg_b200] type=%d m=%u n=%u k=%u majors=%d%d d=%s acc=%d groups=%u -> block=%ux%ux%u stages=%u cta_group=%u "
+            "split_k=%u ctas=%u tmem=%u smem=%u epilogue=%u\n",
+            d.gemm_type, d.m, d.n, d.k, d.major_a, d.major_b, d.d_dtype == DG_F32 ? "f32" : "bf16", d.accumulate, d.num_groups,
+            c.block_m, c.block_n, c.block_k, c.num_stages, c.cta_group, c.split_k, c.num_ctas, c.tmem_cols, c.smem_bytes, c.epilogue_mode);
+}
+
+static int resolve_config(const dg_gemm_desc_t& d, const dg_gemm_config_t* in, dg_gemm_config_t& out) {
+    if (in == nullptr) return select_config(d, out);
+    out = *in;
+    if (out.cta_group == 0) out.cta_group = 1;
+    if (out.split_k == 0) out.split_k = 1;
+    return complete_config(d, out);
+}
+
+}  // namespace dg
+
+using namespace dg;
+
+extern "C" {
+
+const char* dg_last_error(void) { return tls_error; }
+int dg_abi_version(void) { return DG_B200_ABI_VERSION; }
+
+int dg_get_num_sms(void) { return g_num_sms.load() > 0 ? g_num_sms.load() : device_sm_count(); }
+int dg_set_num_sms(int num_sms) {
+    DG_CHECK_ARG(num_sms >= 0 && num_sms <= 1024, "num_sms out of range");
+    g_num_sms.store(num_sms);
+    return DG_OK;
+}
+int dg_get_mk_alignment_for_contiguous_layout(void) { return 256; }
+
+int dg_select_config(const dg_gemm_desc_t* desc, dg_gemm_config_t* out) {
+    DG_CHECK_ARG(desc != nullptr && out != nullptr, "dg_select_config: null argument");
+    if (int rc = validate(*desc)) return rc;
+    return select_config(*desc, *out);
+}
+
+size_t dg_gemm_workspace_bytes(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config) {
+    if (desc == nullptr) return 0;
+    dg_gemm_config_t c;
+    if (validate(*desc) != DG_OK || resolve_config(*desc, config, c) != DG_OK) return 0;
+    if (c.split_k <= 1) return 0;
+    return (size_t)desc->m * align_u64(desc->n, 4) * sizeof(float);
+}
+
+int dg_gemm_dry_run(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config) {
+    DG_CHECK_ARG(desc != nullptr, "dg_gemm_dry_run: null descriptor");
+    if (int rc = validate(*desc)) return rc;
+    dg_gemm_config_t c;
+    if (int rc = resolve_config(*desc, config, c)) return rc;
+    LaunchPlan plan;
+    if (int rc = build_plan(*desc, c, nullptr, 0, /*encode=*/false, plan)) return rc;
+    maybe_print_config(*desc, c);
+    return DG_OK;
+}
+
+int dg_gemm_launch(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config,
+                   void* workspace, size_t workspace_bytes, void* stream) {
+    DG_CHECK_ARG(desc != nullptr, "dg_gemm_launch: null descriptor");
+    if (int rc = validate(*desc)) return rc;
+    dg_gemm_config_t c;
+    if (int rc = resolve_config(*desc, config, c)) return rc;
+    LaunchPlan plan;
+    if (int rc = build_plan(*desc, c, workspace, workspace_bytes, /*encode=*/true, plan)) return rc;
+    maybe_print_config(*desc, c);
+    return launch_gemm_kernel(plan, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,29 @@
+// The launch plan: everything the host derives from (descriptor, configuration) before enqueueing.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "mx_gemm.cuh"
+
+namespace dg {
+
+struct LaunchPlan {
+    GemmKernelArgs args;
+    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d;
+    int cta_group, major_a, major_b;
+    uint32_t num_ctas, smem_bytes;
+    // split-K finalisation (workspace -> D)
+    bool finalize;
+    float* ws;
+    uint64_t ws_stride;
+    void* final_d;
+    uint64_t final_d_stride;
+    uint32_t final_d_is_fp32, final_accumulate;
+    const void* final_bias;
+};
+
+int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream);
+int get_status_pointer(int32_t** out);
+
+}  // namespace dg

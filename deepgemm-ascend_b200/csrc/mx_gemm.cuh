@@ -1,0 +1,562 @@
+// Block-scaled FP8 / FP8xFP4 GEMM for sm_100a: D = A * B^T with one UE8M0 scale per row per 32 K.
+//
+// Replaces the device kernels of the reference, deep_gemm/include/deep_gemm/fp8_gemm.hpp:36-287
+// (fp8_gemm_impl) and fp8_dequant_gemm.hpp:113-443 (fp8_dequant_gemm_impl), the tile scheduler
+// scheduler.hpp:42-249 and the epilogue epilogue.hpp:15-142 + epilogue/operators.hpp:119-221.
+//
+// One persistent CTA per SM (or one CTA pair per two SMs), 256 threads, warp-specialised:
+//   warp 0      TMA producer: A, B tiles (128B-swizzled) and the two scale-factor slabs per K block
+//   warp 1      MMA issuer: tcgen05.cp of the scales into TMEM, then 4 x tcgen05.mma (K = 32 each)
+//   warp 2      scale-factor packer: int16-pair columns -> the 32x16B atom tcgen05.cp expects;
+//               also owns TMEM allocation
+//   warp 3      FP4 -> E4M3 decoder helper (mixed FP8xFP4 with MN-major packed B), idle otherwise
+//   warps 4..7  epilogue: tcgen05.ld, alpha / bias, cast, swizzled smem staging, TMA store or
+//               TMA reduce-add (accumulate, split-K), or bounds-checked plain stores / atomics
+// The accumulator is double-buffered in TMEM so that the epilogue of tile i overlaps the main loop
+// of tile i+1. Every wait is bounded: a wait that gives up records a code in the device status word,
+// raises the CTA's abort flag and lets all roles drain and free TMEM.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+
+#include "ptx.cuh"
+
+namespace dg {
+
+constexpr uint32_t kBlockM = 128;        // rows of A per CTA
+constexpr uint32_t kBlockK = 128;        // K elements (bytes of FP8) per pipeline stage
+constexpr uint32_t kUmmaK = 32;          // K per tcgen05.mma for 8-bit operands
+constexpr uint32_t kNumThreads = 256;
+constexpr uint32_t kNumEpilogueWarps = 4;
+constexpr uint32_t kStoreBoxRows = 32;   // each epilogue warp stores its own 32 rows
+constexpr uint32_t kStoreBufBytes = kStoreBoxRows * 128;  // one 128B-swizzled box
+constexpr uint32_t kNumStoreBufs = 2;    // per epilogue warp
+constexpr uint32_t kMaxStages = 12;
+constexpr uint64_t kWaitTimeoutNs = 2000000000ull;  // 2 s
+
+enum GemmTypeDev : uint32_t { kNormal = 0, kMGroupedPsum = 1, kMGroupedMasked = 4 };
+enum EpilogueMode : uint32_t { kEpiTmaStore = 0, kEpiTmaReduce = 1, kEpiPlainStore = 2, kEpiPlainAtomic = 3 };
+enum StatusCode : int32_t {
+    kStatusOk = 0,
+    kStatusTimeoutProducer = 101, kStatusTimeoutPacker = 102, kStatusTimeoutMma = 103,
+    kStatusTimeoutEpilogue = 104, kStatusTimeoutDrain = 105, kStatusTimeoutDecoder = 106,
+};
+
+struct GemmKernelArgs {
+    uint32_t m, n, k;                 // m: rows of D (normal), total rows (psum), max_m (masked)
+    uint32_t block_n;                 // multiple of 32, <= 256
+    uint32_t num_stages;
+    uint32_t num_k_blocks;            // ceil(k / 128)
+    uint32_t num_m_blocks, num_n_blocks;
+    uint32_t gemm_type;
+    uint32_t num_groups;
+    const int32_t* grouped_layout;    // psum[G] or masked_m[G]
+    uint32_t split_k, k_blocks_per_split;
+    uint32_t raster_group;            // m-blocks per rasterisation group (L2 reuse of B)
+    uint32_t epilogue_mode;
+    uint32_t d_is_fp32;
+    uint32_t has_bias, has_alpha;
+    float alpha;
+    const void* bias;
+    void* d;                          // plain-store modes only
+    uint64_t d_stride, d_group_stride;  // elements
+    uint32_t idesc;                   // tcgen05 instruction descriptor without the scale ids
+    uint32_t tmem_cols, accum_stages;
+    int32_t* status;
+};
+
+// ------------------------------------------------------------------------------------------------
+// Bounded waits
+// ------------------------------------------------------------------------------------------------
+struct AbortFlag {
+    volatile uint32_t* flag;   // shared memory
+    int32_t* status;           // global memory
+    __device__ __forceinline__ bool raised() const { return *flag != 0; }
+    __device__ __forceinline__ void raise(int32_t code) const {
+        *flag = 1;
+        atomicCAS(status, 0, code);
+    }
+};
+
+// Returns false when the wait gave up or the CTA is aborting.
+__device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, const AbortFlag& ab, int32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0xff) == 0) {
+            if (ab.raised()) return false;
+            if (global_timer_ns() - t0 > kWaitTimeoutNs) { ab.raise(code); return false; }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ bool wait_barrier_cluster(uint32_t bar, uint32_t parity, const AbortFlag& ab, int32_t code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if ((++spins & 0xff) == 0) {
+            if (ab.raised()) return false;
+            if (global_timer_ns() - t0 > kWaitTimeoutNs) { ab.raise(code); return false; }
+        }
+    }
+    return true;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Tile scheduler (every role runs its own copy; the sequence is a pure function of the arguments)
+// ------------------------------------------------------------------------------------------------
+struct Tile {
+    uint32_t row0;        // first row of this CTA in A / SFA / D (within the group for masked)
+    uint32_t row_z;       // third TMA coordinate of A / SFA / D (group for masked, else 0)
+    uint32_t n0;          // first column of D == first row of B
+    uint32_t b_z;         // third TMA coordinate of B / SFB (group)
+    uint32_t kb_begin, kb_end;
+};
+
+template <int kCtaGroup>
+struct Scheduler {
+    const GemmKernelArgs& p;
+    uint32_t tile, stride;
+    uint32_t cur_group = 0, cur_first = 0, cur_blocks = 0, cur_row0 = 0;
+    bool group_loaded = false;
+
+    __device__ Scheduler(const GemmKernelArgs& args) : p(args) {
+        tile = blockIdx.x / kCtaGroup;
+        stride = gridDim.x / kCtaGroup;
+    }
+
+    // m-blocks are counted in units of (128 * kCtaGroup) rows.
+    __device__ __forceinline__ void load_group() {
+        if (p.gemm_type == kMGroupedPsum) {
+            // scheduler.hpp:147-162: group g owns rows [align(psum[g-1],256), psum[g]) and the
+            // kernel computes whole 256-row blocks of it.
+            const uint32_t start = cur_group == 0 ? 0u : ((uint32_t)__ldg(p.grouped_layout + cur_group - 1) + 255u) / 256u * 256u;
+            const uint32_t end = (uint32_t)__ldg(p.grouped_layout + cur_group);
+            const uint32_t rows = end > start ? end - start : 0u;
+            cur_row0 = start;
+            cur_blocks = (rows + 255u) / 256u * (256u / (kBlockM * kCtaGroup));
+        } else {
+            const uint32_t rows = min((uint32_t)max(__ldg(p.grouped_layout + cur_group), 0), p.m);
+            cur_row0 = 0;
+            cur_blocks = (rows + kBlockM * kCtaGroup - 1) / (kBlockM * kCtaGroup);
+        }
+        group_loaded = true;
+    }
+
+    __device__ bool next(Tile& t) {
+        const uint32_t rank = kCtaGroup == 2 ? (blockIdx.x & 1u) : 0u;
+        if (p.gemm_type == kNormal) {
+            const uint32_t total = p.num_m_blocks * p.num_n_blocks * p.split_k;
+            if (tile >= total) return false;
+            const uint32_t ks = tile % p.split_k, mn = tile / p.split_k;
+            const uint32_t per_group = p.raster_group * p.num_n_blocks;
+            const uint32_t gi = mn / per_group, in_group = mn - gi * per_group;
+            const uint32_t first_m = gi * p.raster_group;
+            const uint32_t rows = min(p.raster_group, p.num_m_blocks - first_m);
+            const uint32_t mb = first_m + in_group % rows, nb = in_group / rows;
+            t.row0 = (mb * kCtaGroup + rank) * kBlockM;
+            t.row_z = 0;
+            t.n0 = nb * p.block_n;
+            t.b_z = 0;
+            t.kb_begin = ks * p.k_blocks_per_split;
+            t.kb_end = min(t.kb_begin + p.k_blocks_per_split, p.num_k_blocks);
+        } else {
+            const uint32_t mb_lin = tile / p.num_n_blocks, nb = tile - mb_lin * p.num_n_blocks;
+            while (true) {
+                if (cur_group >= p.num_groups) return false;
+                if (!group_loaded) load_group();
+                if (mb_lin < cur_first + cur_blocks) break;
+                cur_first += cur_blocks;
+                cur_group += 1;
+                group_loaded = false;
+            }
+            const uint32_t mb = mb_lin - cur_first;
+            t.row0 = cur_row0 + (mb * kCtaGroup + rank) * kBlockM;
+            t.row_z = p.gemm_type == kMGroupedMasked ? cur_group : 0u;
+            t.n0 = nb * p.block_n;
+            t.b_z = cur_group;
+            t.kb_begin = 0;
+            t.kb_end = p.num_k_blocks;
+        }
+        tile += stride;
+        return true;
+    }
+};
+
+// ------------------------------------------------------------------------------------------------
+// Descriptors
+// ------------------------------------------------------------------------------------------------
+// K-major operand tile, 128-byte rows, 128B swizzle: 8-row groups are 1024 B apart.
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+    d |= (uint64_t)1 << 16;                    // leading byte offset: unused for swizzled K-major
+    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
+    d |= (uint64_t)1 << 46;                    // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+    return d;
+}
+// MN-major operand tile: [mn atoms of 128 B][block_k rows][128 B], 128B swizzle over 8 K rows.
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, uint32_t atom_stride_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+    d |= (uint64_t)((atom_stride_bytes >> 4) & 0x3fff) << 16;   // leading: next 128-B atom along MN
+    d |= (uint64_t)(1024 >> 4) << 32;                           // stride: next 8 rows along K
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Scale-factor atom for tcgen05.cp 32x128b: 32 rows of 16 B, no swizzle, 8-row groups 128 B apart.
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+    d |= (uint64_t)(128 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+
+__host__ __device__ __forceinline__ uint32_t sfb_rows(uint32_t block_n) { return (block_n + 127u) / 128u * 128u; }
+
+// Shared-memory carve-up, computed identically on host and device.
+struct SmemLayout {
+    uint32_t store_bufs, a, b, sf_raw_a, sf_raw_b, sf_pack_a, sf_pack_b, barriers, total;
+    uint32_t a_stage, b_stage, sfa_stage, sfb_stage;
+};
+__host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_t num_stages, uint32_t cta_group) {
+    SmemLayout L;
+    L.a_stage = kBlockM * kBlockK;
+    L.b_stage = (block_n / cta_group) * kBlockK;
+    L.sfa_stage = 128 * 4;
+    L.sfb_stage = sfb_rows(block_n) * 4;
+    uint32_t off = 0;
+    L.store_bufs = off; off += kNumEpilogueWarps * kNumStoreBufs * kStoreBufBytes;
+    L.a = off; off += num_stages * L.a_stage;
+    L.b = off; off += num_stages * L.b_stage;
+    off = (off + 1023u) & ~1023u;
+    L.sf_raw_a = off; off += num_stages * L.sfa_stage;
+    L.sf_raw_b = off; off += num_stages * L.sfb_stage;
+    L.sf_pack_a = off; off += num_stages * L.sfa_stage;
+    L.sf_pack_b = off; off += num_stages * L.sfb_stage;
+    L.barriers = off; off += (3 * kMaxStages + 4) * 8 + 16;
+    L.total = off + 1024;    // slack for the manual 1024-B alignment of the dynamic base
+    return L;
+}
+
+// ------------------------------------------------------------------------------------------------
+// The kernel
+// ------------------------------------------------------------------------------------------------
+// kMajorA / kMajorB: 0 = K-major, 1 = MN-major operand in global memory.
+template <int kCtaGroup, int kMajorA, int kMajorB>
+__global__ void __launch_bounds__(kNumThreads, 1)
+mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+               const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
+               const __grid_constant__ CUtensorMap tm_d, const GemmKernelArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const SmemLayout L = make_smem_layout(p.block_n, p.num_stages, kCtaGroup);
+
+    const uint32_t warp = threadIdx.x / 32, lane = lane_id();
+    const uint32_t cta_rank = kCtaGroup == 2 ? cluster_ctarank() : 0u;
+    const bool is_leader = cta_rank == 0;
+
+    // Barrier block: full[s], sf_full[s], empty[s], tmem_full[2], tmem_empty[2], tmem ptr, abort flag
+    const uint32_t bar_base = smem_base + L.barriers;
+    auto full_bar = [&](uint32_t s) { return bar_base + s * 8; };
+    auto sf_full_bar = [&](uint32_t s) { return bar_base + (kMaxStages + s) * 8; };
+    auto empty_bar = [&](uint32_t s) { return bar_base + (2 * kMaxStages + s) * 8; };
+    auto tmem_full_bar = [&](uint32_t e) { return bar_base + (3 * kMaxStages + e) * 8; };
+    auto tmem_empty_bar = [&](uint32_t e) { return bar_base + (3 * kMaxStages + 2 + e) * 8; };
+    volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + L.barriers + (3 * kMaxStages + 4) * 8);
+    const AbortFlag ab{tmem_ptr_smem + 1, p.status};
+
+    const uint32_t num_stages = p.num_stages;
+    const uint32_t load_n = p.block_n / kCtaGroup;            // rows of B this CTA fetches
+    const uint32_t sfb_slabs = sfb_rows(p.block_n) / 128;
+
+    if (threadIdx.x == 0) {
+        tmem_ptr_smem[1] = 0;
+        for (uint32_t s = 0; s < num_stages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(sf_full_bar(s), 32 * kCtaGroup);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (uint32_t e = 0; e < 2; ++e) {
+            mbar_init(tmem_full_bar(e), 1);
+            mbar_init(tmem_empty_bar(e), kNumEpilogueWarps * 32 * kCtaGroup);
+        }
+        fence_mbar_init();
+        tma_prefetch_desc(&tm_a); tma_prefetch_desc(&tm_b);
+        tma_prefetch_desc(&tm_sfa); tma_prefetch_desc(&tm_sfb);
+        tma_prefetch_desc(&tm_d);
+    }
+    if (warp == 2) {
+        tmem_alloc<kCtaGroup>(smem_u32((const void*)tmem_ptr_smem), p.tmem_cols);
+        tmem_relinquish<kCtaGroup>();
+    }
+    tc_fence_before_sync();
+    if constexpr (kCtaGroup == 2) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_ptr_smem[0];
+    // TMEM columns: accumulators first, then the scale factors of A and of B.
+    const uint32_t tmem_sfa = tmem_base + p.accum_stages * p.block_n;
+    const uint32_t tmem_sfb = tmem_sfa + 4;
+
+    if (warp == 0) {
+        // ======================================================================== TMA producer
+        if (elect_one()) {
+            Scheduler<kCtaGroup> sched(p);
+            Tile t;
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            while (ok && sched.next(t)) {
+                for (uint32_t kb = t.kb_begin; kb < t.kb_end; ++kb) {
+                    if (!(ok = wait_barrier(empty_bar(stage), phase ^ 1, ab, kStatusTimeoutProducer))) break;
+                    const uint32_t bar = full_bar(stage);
+                    const uint32_t bytes = L.a_stage + load_n * kBlockK + L.sfa_stage + L.sfb_stage;
+                    mbar_arrive_expect_tx(bar, bytes);
+                    const uint32_t sa = smem_base + L.a + stage * L.a_stage;
+                    const uint32_t sb = smem_base + L.b + stage * L.b_stage;
+                    const int32_t k0 = (int32_t)(kb * kBlockK);
+                    if constexpr (kMajorA == 0) {
+                        tma_load_3d(sa, &tm_a, bar, k0, (int32_t)t.row0, (int32_t)t.row_z);
+                    } else {
+                        tma_load_3d(sa, &tm_a, bar, (int32_t)t.row0, k0, (int32_t)t.row_z);
+                    }
+                    const uint32_t bn0 = t.n0 + cta_rank * load_n;
+                    if constexpr (kMajorB == 0) {
+                        tma_load_3d(sb, &tm_b, bar, k0, (int32_t)bn0, (int32_t)t.b_z);
+                    } else {
+                        // one box per 128-column atom: [atom][block_k rows][128 B]
+                        for (uint32_t a0 = 0; a0 < load_n; a0 += 128)
+                            tma_load_3d(sb + a0 * kBlockK, &tm_b, bar, (int32_t)(bn0 + a0), k0, (int32_t)t.b_z);
+                    }
+                    tma_load_3d(smem_base + L.sf_raw_a + stage * L.sfa_stage, &tm_sfa, bar,
+                                (int32_t)t.row0, (int32_t)(kb * 2), (int32_t)t.row_z);
+                    tma_load_3d(smem_base + L.sf_raw_b + stage * L.sfb_stage, &tm_sfb, bar,
+                                (int32_t)t.n0, (int32_t)(kb * 2), (int32_t)t.b_z);
+                    if (++stage == num_stages) { stage = 0; phase ^= 1; }
+                }
+            }
+            // Before leaving, make sure nothing this thread issued is still writing into shared memory:
+            // the consumers release a stage only after its bytes have landed, so draining the ring is enough.
+            for (uint32_t i = 0; i < num_stages && !ab.raised(); ++i) {
+                if (!wait_barrier(empty_bar(stage), phase ^ 1, ab, kStatusTimeoutDrain)) break;
+                if (++stage == num_stages) { stage = 0; phase ^= 1; }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ======================================================================== MMA issuer
+        if (is_leader && elect_one()) {
+            Scheduler<kCtaGroup> sched(p);
+            Tile t;
+            uint32_t stage = 0, phase = 0, tile_iter = 0;
+            bool ok = true;
+            while (ok && sched.next(t)) {
+                const uint32_t e = p.accum_stages == 2 ? (tile_iter & 1u) : 0u;
+                const uint32_t e_phase = p.accum_stages == 2 ? ((tile_iter >> 1) & 1u) : (tile_iter & 1u);
+                // the epilogue(s) must have drained this accumulator
+                if (kCtaGroup == 2) ok = wait_barrier_cluster(tmem_empty_bar(e), e_phase ^ 1, ab, kStatusTimeoutMma);
+                else ok = wait_barrier(tmem_empty_bar(e), e_phase ^ 1, ab, kStatusTimeoutMma);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + e * p.block_n;
+                for (uint32_t kb = t.kb_begin; kb < t.kb_end; ++kb) {
+                    if (kCtaGroup == 2) ok = wait_barrier_cluster(sf_full_bar(stage), phase, ab, kStatusTimeoutMma);
+                    else ok = wait_barrier(sf_full_bar(stage), phase, ab, kStatusTimeoutMma);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    // scales: smem -> TMEM (A: 128 rows = one slab; B: one slab per 128 columns)
+                    utccp_32x128b_warpx4<kCtaGroup>(tmem_sfa, make_sf_desc(smem_base + L.sf_pack_a + stage * L.sfa_stage));
+                    for (uint32_t i = 0; i < sfb_slabs; ++i)
+                        utccp_32x128b_warpx4<kCtaGroup>(tmem_sfb + i * 4,
+                                                        make_sf_desc(smem_base + L.sf_pack_b + stage * L.sfb_stage + i * 512));
+                    const uint32_t sa = smem_base + L.a + stage * L.a_stage;
+                    const uint32_t sb = smem_base + L.b + stage * L.b_stage;
+                    #pragma unroll
+                    for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k) {
+                        uint64_t da, db;
+                        if constexpr (kMajorA == 0) da = make_kmajor_sw128_desc(sa + k * kUmmaK);
+                        else da = make_mnmajor_sw128_desc(sa + k * kUmmaK * 128, kBlockK * 128);
+                        if constexpr (kMajorB == 0) db = make_kmajor_sw128_desc(sb + k * kUmmaK);
+                        else db = make_mnmajor_sw128_desc(sb + k * kUmmaK * 128, kBlockK * 128);
+                        const uint32_t idesc = p.idesc | (k << 4) | (k << 29);   // scale ids of B and of A
+                        umma_mxf8f6f4<kCtaGroup>(tmem_d, da, db, idesc, tmem_sfa, tmem_sfb,
+                                                 (kb > t.kb_begin || k > 0) ? 1u : 0u);
+                    }
+                    // release the stage once these MMAs have read it
+                    if constexpr (kCtaGroup == 2) umma_commit_2cta(empty_bar(stage), 3);
+                    else umma_commit_1cta(empty_bar(stage));
+                    if (++stage == num_stages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                if constexpr (kCtaGroup == 2) umma_commit_2cta(tmem_full_bar(e), 3);
+                else umma_commit_1cta(tmem_full_bar(e));
+                ++tile_iter;
+            }
+        }
+        __syncwarp();
+    } else if (warp == 2) {
+        // ======================================================================== scale-factor packer
+        // raw slab (TMA): [2 K64 columns][rows] int16  ->  packed: [32][4] uint32, entry [l][j] = the four
+        // UE8M0 bytes (K blocks 0..3 of this stage) of row j*32+l.
+        Scheduler<kCtaGroup> sched(p);
+        Tile t;
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        const uint32_t leader_sf_full0 = kCtaGroup == 2 ? mapa_shared(sf_full_bar(0), 0) : sf_full_bar(0);
+        while (ok && sched.next(t)) {
+            for (uint32_t kb = t.kb_begin; kb < t.kb_end; ++kb) {
+                if (!(ok = wait_barrier(full_bar(stage), phase, ab, kStatusTimeoutPacker))) break;
+                const uint16_t* raw_a = reinterpret_cast<const uint16_t*>(smem_gen + L.sf_raw_a + stage * L.sfa_stage);
+                uint4* pack_a = reinterpret_cast<uint4*>(smem_gen + L.sf_pack_a + stage * L.sfa_stage);
+                {
+                    uint32_t v[4];
+                    #pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j)
+                        v[j] = (uint32_t)raw_a[j * 32 + lane] | ((uint32_t)raw_a[128 + j * 32 + lane] << 16);
+                    pack_a[lane] = make_uint4(v[0], v[1], v[2], v[3]);
+                }
+                const uint32_t rows_b = sfb_slabs * 128;
+                const uint16_t* raw_b = reinterpret_cast<const uint16_t*>(smem_gen + L.sf_raw_b + stage * L.sfb_stage);
+                uint4* pack_b = reinterpret_cast<uint4*>(smem_gen + L.sf_pack_b + stage * L.sfb_stage);
+                for (uint32_t i = 0; i < sfb_slabs; ++i) {
+                    uint32_t v[4];
+                    #pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j) {
+                        const uint32_t r = i * 128 + j * 32 + lane;
+                        v[j] = (uint32_t)raw_b[r] | ((uint32_t)raw_b[rows_b + r] << 16);
+                    }
+                    pack_b[i * 32 + lane] = make_uint4(v[0], v[1], v[2], v[3]);
+                }
+                fence_proxy_async_smem();
+                if constexpr (kCtaGroup == 2) mbar_arrive_cluster(leader_sf_full0 + stage * 8);
+                else mbar_arrive(sf_full_bar(stage));
+                if (++stage == num_stages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp >= 4) {
+        // ======================================================================== epilogue
+        const uint32_t q = warp - 4;                         // TMEM lane quadrant == warp index % 4
+        Scheduler<kCtaGroup> sched(p);
+        Tile t;
+        uint32_t tile_iter = 0, buf = 0;
+        bool ok = true;
+        const uint32_t store_base = smem_base + L.store_bufs + q * kNumStoreBufs * kStoreBufBytes;
+        uint8_t* store_gen = smem_gen + L.store_bufs + q * kNumStoreBufs * kStoreBufBytes;
+        const uint32_t cols_per_box = p.d_is_fp32 ? 32u : 64u;
+        const uint32_t leader_tmem_empty0 = kCtaGroup == 2 ? mapa_shared(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+        while (ok && sched.next(t)) {
+            const uint32_t e = p.accum_stages == 2 ? (tile_iter & 1u) : 0u;
+            const uint32_t e_phase = p.accum_stages == 2 ? ((tile_iter >> 1) & 1u) : (tile_iter & 1u);
+            if (!(ok = wait_barrier(tmem_full_bar(e), e_phase, ab, kStatusTimeoutEpilogue))) break;
+            tc_fence_after_sync();
+            const uint32_t row = t.row0 + q * 32 + lane;       // row of D held by this thread
+            const uint32_t taddr = tmem_base + ((q * 32u) << 16) + e * p.block_n;
+            for (uint32_t c0 = 0; c0 < p.block_n; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(taddr + c0, v);
+                tmem_ld_wait();
+                const uint32_t col0 = t.n0 + c0;
+                if (p.has_alpha) {
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * p.alpha);
+                }
+                if (p.has_bias) {
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float bv = 0.f;
+                        if (col0 + i < p.n)
+                            bv = p.d_is_fp32 ? __ldg(reinterpret_cast<const float*>(p.bias) + col0 + i)
+                                             : __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0 + i));
+                        v[i] = __float_as_uint(__uint_as_float(v[i]) + bv);
+                    }
+                }
+                if (p.epilogue_mode <= kEpiTmaReduce) {
+                    // stage a [32 rows x 128 B] box, 16-byte chunk c of row r at chunk (c ^ (r & 7))
+                    const uint32_t half = p.d_is_fp32 ? 0u : ((c0 / 32) & 1u);   // bf16: two 32-col groups per box
+                    if (half == 0) {
+                        // the buffer may still be read by the store issued two boxes ago
+                        tma_store_wait_read<kNumStoreBufs - 1>();
+                        __syncwarp();
+                    }
+                    uint8_t* rowp = store_gen + buf * kStoreBufBytes + lane * 128;
+                    if (p.d_is_fp32) {
+                        #pragma unroll
+                        for (uint32_t c = 0; c < 8; ++c)
+                            *reinterpret_cast<uint4*>(rowp + ((c ^ (lane & 7u)) * 16)) =
+                                make_uint4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+                    } else {
+                        #pragma unroll
+                        for (uint32_t c = 0; c < 4; ++c) {
+                            uint32_t w[4];
+                            #pragma unroll
+                            for (uint32_t i = 0; i < 4; ++i) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[c * 8 + i * 2]),
+                                                                         __uint_as_float(v[c * 8 + i * 2 + 1]));
+                                w[i] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                            const uint32_t chunk = half * 4 + c;
+                            *reinterpret_cast<uint4*>(rowp + ((chunk ^ (lane & 7u)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                    const bool box_done = p.d_is_fp32 || half == 1 || c0 + 32 >= p.block_n;
+                    if (box_done) {
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            const int32_t x = (int32_t)(t.n0 + (c0 / cols_per_box) * cols_per_box);
+                            const int32_t y = (int32_t)(t.row0 + q * 32);
+                            if (p.epilogue_mode == kEpiTmaStore)
+                                tma_store_3d(&tm_d, store_base + buf * kStoreBufBytes, x, y, (int32_t)t.row_z);
+                            else
+                                tma_reduce_add_3d(&tm_d, store_base + buf * kStoreBufBytes, x, y, (int32_t)t.row_z);
+                            tma_store_commit();
+                        }
+                        buf ^= 1;
+                    }
+                } else {
+                    // plain path: bounds-checked element stores / atomics, any N and any stride
+                    const bool row_ok = row < p.m;
+                    const uint64_t base = (uint64_t)t.row_z * p.d_group_stride + (uint64_t)row * p.d_stride;
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (row_ok && col0 + i < p.n) {
+                            const float f = __uint_as_float(v[i]);
+                            if (p.d_is_fp32) {
+                                float* dst = reinterpret_cast<float*>(p.d) + base + col0 + i;
+                                if (p.epilogue_mode == kEpiPlainAtomic) atomicAdd(dst, f); else *dst = f;
+                            } else {
+                                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + base + col0 + i;
+                                if (p.epilogue_mode == kEpiPlainAtomic) atomicAdd(dst, __float2bfloat16_rn(f));
+                                else *dst = __float2bfloat16_rn(f);
+                            }
+                        }
+                    }
+                }
+            }
+            // this accumulator may be overwritten by the next-but-one tile
+            tc_fence_before_sync();
+            if constexpr (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty0 + e * 8);
+            else mbar_arrive(tmem_empty_bar(e));
+            ++tile_iter;
+        }
+        // shared memory must outlive the bulk stores that read it
+        tma_store_wait_all<0>();
+    }
+
+    // ============================================================================ teardown
+    tc_fence_before_sync();
+    if constexpr (kCtaGroup == 2) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
+    if (warp == 2) {
+        tc_fence_after_sync();
+        tmem_dealloc<kCtaGroup>(tmem_base, p.tmem_cols);
+    }
+}
+
+}  // namespace dg

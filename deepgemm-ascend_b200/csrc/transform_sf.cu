@@ -1,0 +1,208 @@
+// Scale-factor relayout into the layout the GEMM kernel reads: int16 [MN, ceil(K/64)], MN-major,
+// two UE8M0 bytes per element (low byte = even 32-wide K block).
+//
+// Replaces the reference's transform_sf kernel, deep_gemm/include/deep_gemm/transform_sf.hpp:447-639:
+// exponent extraction and validation (:13-21), pair packing (:276-279), K-major -> MN-major transpose,
+// replication over gran_mn rows (:616-619) and zeroing of the rows in a group's padding (:374-445).
+// Added here: k_repeat = 4 expands a per-128-K scale over the four 32-wide blocks it covers.
+//
+// HBM-bound streaming kernel. Each CTA produces a [128 rows x 32 int16 columns] output tile: the
+// source region it needs (at most 128 rows x 64 scales) is read coalesced along whichever source
+// axis is contiguous, reduced to bytes in shared memory, and written back coalesced along MN.
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "host_common.h"
+
+namespace dg {
+
+constexpr uint32_t kTileRows = 128;      // output rows per CTA
+constexpr uint32_t kTileCols = 32;       // output int16 columns per CTA (= 64 K blocks)
+constexpr uint32_t kTsfThreads = 256;
+
+struct TransformSfArgs {
+    const void* src;
+    int16_t* dst;
+    uint64_t src_row_stride, src_col_stride, src_batch_stride;
+    uint64_t dst_col_stride, dst_batch_stride;
+    uint32_t src_rows, src_cols;
+    uint32_t dst_mn, dst_cols, k32_blocks;
+    uint32_t gran_mn, k_repeat;
+    uint32_t src_is_fp32;
+    const int32_t* psum;
+    uint32_t num_groups, alignment;
+    int32_t* invalid_flag;
+    uint32_t tiles_m, tiles_c;
+};
+
+// Is source row r (in units of gran_mn rows) inside the padding of some group?  Group g pads the
+// source rows [ceil(psum[g]/gran), align(psum[g], alignment)/gran).
+__device__ __forceinline__ bool row_in_group_padding(const TransformSfArgs& a, uint32_t r) {
+    uint32_t lo = 0, hi = a.num_groups;          // first g with align(psum[g])/gran > r
+    while (lo < hi) {
+        const uint32_t mid = (lo + hi) / 2;
+        const uint32_t p = (uint32_t)__ldg(a.psum + mid);
+        const uint32_t end = (p + a.alignment - 1) / a.alignment * a.alignment / a.gran_mn;
+        if (end > r) hi = mid; else lo = mid + 1;
+    }
+    if (lo >= a.num_groups) return true;         // beyond the last group: nothing valid lives there
+    const uint32_t p = (uint32_t)__ldg(a.psum + lo);
+    return r >= (p + a.gran_mn - 1) / a.gran_mn;
+}
+
+__global__ void __launch_bounds__(kTsfThreads) transform_sf_kernel(const TransformSfArgs a) {
+    __shared__ uint8_t bytes[kTileRows][64 + 4];    // [source row][source scale], as UE8M0 bytes
+    __shared__ uint8_t padded[kTileRows];
+
+    const uint32_t tiles_per_batch = a.tiles_m * a.tiles_c;
+    for (uint32_t tile = blockIdx.x; tile < tiles_per_batch; tile += gridDim.x) {
+        const uint32_t batch = blockIdx.y;
+        const uint32_t tm = tile % a.tiles_m, tc = tile / a.tiles_m;
+        const uint32_t mn0 = tm * kTileRows, c0 = tc * kTileCols;
+        const uint32_t r0 = mn0 / a.gran_mn;
+        const uint32_t rows = min((kTileRows + a.gran_mn - 1) / a.gran_mn, a.src_rows > r0 ? a.src_rows - r0 : 0u);
+        // source scales covering K blocks [2*c0, 2*c0 + 64)
+        const uint32_t s0 = 2 * c0 / a.k_repeat;
+        const uint32_t scales = 64 / a.k_repeat;
+
+        __syncthreads();                       // previous tile's readers are done with shared memory
+        if (threadIdx.x < kTileRows)
+            padded[threadIdx.x] = (a.psum != nullptr && threadIdx.x < rows) ? row_in_group_padding(a, r0 + threadIdx.x) : 0;
+        __syncthreads();
+
+        const uint8_t* src_base = reinterpret_cast<const uint8_t*>(a.src);
+        if (a.src_is_fp32) {
+            const uint32_t total = rows * scales;
+            const bool row_fast = a.src_row_stride == 1 && a.src_col_stride != 1;
+            bool bad = false;
+            for (uint32_t i = threadIdx.x; i < total; i += kTsfThreads) {
+                const uint32_t r = row_fast ? i % rows : i / scales;
+                const uint32_t s = row_fast ? i / rows : i % scales;
+                uint8_t e = 0;
+                if (s0 + s < a.src_cols && !padded[r]) {
+                    const uint64_t off = batch * a.src_batch_stride + (uint64_t)(r0 + r) * a.src_row_stride + (uint64_t)(s0 + s) * a.src_col_stride;
+                    const uint32_t bits = __ldg(reinterpret_cast<const uint32_t*>(src_base) + off);
+                    e = (uint8_t)((bits >> 23) & 0xff);
+                    bad |= (bits & 0x807fffffu) != 0;      // negative, or not a power of two
+                }
+                bytes[r][s] = e;
+            }
+            if (bad && a.invalid_flag != nullptr) atomicExch(a.invalid_flag, 1);
+        } else {
+            // int16 source: each element already holds two bytes (two consecutive source scales)
+            const uint32_t words = scales / 2 > 0 ? scales / 2 : 1;
+            const uint32_t w0 = s0 / 2;
+            const uint32_t total = rows * words;
+            const bool row_fast = a.src_row_stride == 1 && a.src_col_stride != 1;
+            for (uint32_t i = threadIdx.x; i < total; i += kTsfThreads) {
+                const uint32_t r = row_fast ? i % rows : i / words;
+                const uint32_t w = row_fast ? i / rows : i % words;
+                uint16_t v = 0;
+                if (w0 + w < a.src_cols && !padded[r]) {
+                    const uint64_t off = batch * a.src_batch_stride + (uint64_t)(r0 + r) * a.src_row_stride + (uint64_t)(w0 + w) * a.src_col_stride;
+                    v = __ldg(reinterpret_cast<const uint16_t*>(src_base) + off);
+                }
+                bytes[r][2 * w] = (uint8_t)(v & 0xff);
+                bytes[r][2 * w + 1] = (uint8_t)(v >> 8);
+            }
+        }
+        __syncthreads();
+
+        // Packed int16 input at gran_k = 32 passes its bytes through untouched, including the high
+        // byte of a last odd block (tests/test_layout.py:39-50); every other input leaves K blocks
+        // that do not exist at 0.
+        const bool passthrough = !a.src_is_fp32 && a.k_repeat == 1;
+        for (uint32_t i = threadIdx.x; i < kTileRows * kTileCols; i += kTsfThreads) {
+            const uint32_t ml = i % kTileRows, c = i / kTileRows;
+            const uint32_t mn = mn0 + ml, col = c0 + c;
+            if (mn >= a.dst_mn || col >= a.dst_cols) continue;
+            const uint32_t r = ml / a.gran_mn;
+            uint32_t lo = 0, hi = 0;
+            if (r < rows) {
+                const uint32_t kb = 2 * col;
+                // when k_repeat = 4 and s0 was rounded down, index relative to the K blocks of s0
+                const uint32_t rel0 = kb / a.k_repeat - s0, rel1 = (kb + 1) / a.k_repeat - s0;
+                if (passthrough || kb < a.k32_blocks) lo = bytes[r][rel0];
+                if (passthrough || kb + 1 < a.k32_blocks) hi = bytes[r][rel1];
+            }
+            a.dst[batch * a.dst_batch_stride + (uint64_t)col * a.dst_col_stride + mn] = (int16_t)(lo | (hi << 8));
+        }
+    }
+}
+
+__global__ void pad_rows_kernel(const uint8_t* __restrict__ src, uint64_t src_pitch, uint8_t* __restrict__ dst,
+                                uint64_t dst_pitch, uint64_t rows, uint64_t row_bytes) {
+    const uint64_t total = rows * dst_pitch;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t r = i / dst_pitch, c = i - r * dst_pitch;
+        dst[i] = c < row_bytes ? src[r * src_pitch + c] : 0;
+    }
+}
+
+__global__ void l2_flush_kernel(uint4* __restrict__ buf, size_t n16) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
+        buf[i] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+}  // namespace dg
+
+using namespace dg;
+
+extern "C" int dg_transform_sf_launch(const void* src, int src_is_fp32,
+                                      uint64_t src_row_stride, uint64_t src_col_stride, uint64_t src_batch_stride,
+                                      uint32_t src_rows, uint32_t src_cols,
+                                      int16_t* dst, uint64_t dst_col_stride, uint64_t dst_batch_stride,
+                                      uint32_t dst_mn, uint32_t k32_blocks, uint32_t gran_mn, uint32_t k_repeat,
+                                      uint32_t num_batches, const int32_t* psum, uint32_t num_groups,
+                                      uint32_t alignment, int32_t* invalid_flag, void* stream) {
+    DG_CHECK_ARG(src != nullptr && dst != nullptr, "transform_sf: null pointer");
+    DG_CHECK_ARG(gran_mn >= 1 && gran_mn <= 128 && (gran_mn & (gran_mn - 1)) == 0,
+                 "gran_mn only support a power of two in [1, 128]");
+    DG_CHECK_ARG(k_repeat == 1 || k_repeat == 4, "transform_sf: gran_k must be 32 or 128");
+    DG_CHECK_ARG(psum == nullptr || (num_groups > 0 && num_batches == 1),
+                 "Grouped transform SF requires one logical batch and grouped_layout");
+    DG_CHECK_ARG(alignment > 0 && alignment % gran_mn == 0, "transform_sf: alignment must be a multiple of gran_mn");
+    DG_CHECK_ARG(num_batches >= 1 && num_batches <= 65535, "transform_sf: num_batches out of range");
+    if (dst_mn == 0 || k32_blocks == 0) return DG_OK;
+
+    TransformSfArgs a{};
+    a.src = src; a.dst = dst;
+    a.src_row_stride = src_row_stride; a.src_col_stride = src_col_stride; a.src_batch_stride = src_batch_stride;
+    a.dst_col_stride = dst_col_stride; a.dst_batch_stride = dst_batch_stride;
+    a.src_rows = src_rows; a.src_cols = src_cols;
+    a.dst_mn = dst_mn; a.k32_blocks = k32_blocks;
+    a.dst_cols = (k32_blocks + 1) / 2;
+    if (!src_is_fp32 && k_repeat == 1) a.dst_cols = src_cols;    // pass-through keeps the source's column count
+    a.gran_mn = gran_mn; a.k_repeat = k_repeat; a.src_is_fp32 = src_is_fp32 ? 1 : 0;
+    a.psum = psum; a.num_groups = num_groups; a.alignment = alignment;
+    a.invalid_flag = invalid_flag;
+    a.tiles_m = (dst_mn + kTileRows - 1) / kTileRows;
+    a.tiles_c = (a.dst_cols + kTileCols - 1) / kTileCols;
+    const uint64_t tiles = (uint64_t)a.tiles_m * a.tiles_c;
+    const uint32_t grid_x = (uint32_t)(tiles < 148ull * 16 ? tiles : 148ull * 16);
+    transform_sf_kernel<<<dim3(grid_x, num_batches), kTsfThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    DG_CHECK_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+extern "C" int dg_pad_rows_launch(const void* src, uint64_t src_pitch_bytes, void* dst, uint64_t dst_pitch_bytes,
+                                  uint64_t rows, uint64_t row_bytes, void* stream) {
+    DG_CHECK_ARG(src != nullptr && dst != nullptr, "pad_rows: null pointer");
+    DG_CHECK_ARG(dst_pitch_bytes >= row_bytes, "pad_rows: destination pitch smaller than a row");
+    if (rows == 0 || dst_pitch_bytes == 0) return DG_OK;
+    const uint64_t total = rows * dst_pitch_bytes;
+    const uint32_t grid = (uint32_t)((total + 255) / 256 < 148ull * 32 ? (total + 255) / 256 : 148ull * 32);
+    pad_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(src), src_pitch_bytes, static_cast<uint8_t*>(dst), dst_pitch_bytes, rows, row_bytes);
+    DG_CHECK_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+extern "C" int dg_l2_flush_launch(void* buffer, size_t bytes, void* stream) {
+    DG_CHECK_ARG(buffer != nullptr && (reinterpret_cast<uintptr_t>(buffer) & 15) == 0, "l2_flush: buffer must be 16-byte aligned");
+    const size_t n16 = bytes / 16;
+    if (n16 == 0) return DG_OK;
+    l2_flush_kernel<<<148 * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(buffer), n16);
+    DG_CHECK_CUDA(cudaGetLastError());
+    return DG_OK;
+}

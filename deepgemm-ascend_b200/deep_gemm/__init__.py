@@ -1,0 +1,53 @@
+"""deep_gemm for NVIDIA B200: block-scaled FP8 / FP8xFP4 GEMM behind the DeepGEMM-Ascend Python API.
+
+The names, arguments and error text of the hot path follow the reference's `deep_gemm/__init__.py:25-81`;
+everything else of the reference (attention, MegaMoE, einsum, BF16 GEMM, ACLNN wrappers) is out of scope
+and not exported. Importing this package never initialises a CUDA context.
+"""
+
+__version__ = '0.1.1'
+
+from . import epilogue, locality_domain, testing  # noqa: F401
+from ._api import (  # noqa: F401
+    device_status,
+    fp8_fp4_gemm_nn,
+    fp8_fp4_gemm_nt,
+    fp8_fp4_gemm_tn,
+    fp8_fp4_gemm_tt,
+    fp8_gemm_nn,
+    fp8_gemm_nt,
+    fp8_gemm_tn,
+    fp8_gemm_tt,
+    get_deterministic_algorithms,
+    get_dry_run,
+    get_mk_alignment_for_contiguous_layout,
+    get_npu_arch,
+    get_num_sms,
+    get_recipe,
+    get_theoretical_mk_alignment_for_contiguous_layout,
+    init,
+    m_grouped_fp8_fp4_gemm_nn_contiguous,
+    m_grouped_fp8_fp4_gemm_nt_contiguous,
+    m_grouped_fp8_fp4_gemm_nt_masked,
+    m_grouped_fp8_gemm_nn_contiguous,
+    m_grouped_fp8_gemm_nt_contiguous,
+    m_grouped_fp8_gemm_nt_masked,
+    set_dry_run,
+    set_mk_alignment_for_contiguous_layout,
+    set_npu_arch,
+    set_num_sms,
+    transform_sf_into_required_layout,
+    use_deterministic_algorithms,
+)
+from .locality_domain import (  # noqa: F401
+    destroy_localizer,
+    get_num_locality_domains,
+    is_localization_available,
+    is_localized,
+    localize,
+)
+
+
+def get_library_root_path() -> str:
+    import os
+    return os.path.dirname(os.path.realpath(__file__))

@@ -1,0 +1,179 @@
+/*
+ * dg_b200.h — C ABI of libdg_b200.so: block-scaled FP8 / FP8xFP4 GEMM for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a DeepGEMM-Ascend host layer binds instead of its bisheng JIT: every entry
+ * point replaces one `jit->compile(...)` + `jit->launch(...)` pair of the reference, or one host
+ * helper directly in front of it. Plain C: pointers, sizes and enums only; no torch types.
+ *
+ * Conventions
+ *   - every function returns 0 on success and a negative DG_ERR_* code otherwise; the message of the
+ *     last failure on the calling thread is returned by dg_last_error();
+ *   - nothing here synchronises the device or allocates device memory; all work is enqueued on the
+ *     `stream` argument (a cudaStream_t passed as void*; NULL is the legacy default stream);
+ *   - device pointers must belong to the device that is current on the calling thread;
+ *   - functions are thread-safe (the reference pre-compiles from a thread pool).
+ */
+#ifndef DG_B200_H_
+#define DG_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DG_B200_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+enum {
+    DG_OK = 0,
+    DG_ERR_INVALID = -1,      /* argument rejected by validation (message says which) */
+    DG_ERR_UNSUPPORTED = -2,  /* legal in the reference's API but not built here */
+    DG_ERR_CUDA = -3,         /* a CUDA runtime / driver call failed */
+    DG_ERR_WORKSPACE = -4     /* workspace missing or too small */
+};
+
+/* deep_gemm/include/deep_gemm/common.hpp:82 (Major) */
+typedef enum { DG_MAJOR_K = 0, DG_MAJOR_MN = 1 } dg_major_t;
+
+/* deep_gemm/include/deep_gemm/common.hpp:87-92 (GemmType); MASKED is the entry point the reference
+ * only names (csrc/apis/gemm.hpp:606,630). */
+typedef enum {
+    DG_GEMM_NORMAL = 0,
+    DG_GEMM_M_GROUPED_PSUM = 1,
+    DG_GEMM_K_GROUPED_PSUM = 2, /* not built */
+    DG_GEMM_BATCHED = 3,        /* not built */
+    DG_GEMM_M_GROUPED_MASKED = 4
+} dg_gemm_type_t;
+
+/* csrc/utils/dtype.hpp:9 (packed FP4 is stored as int8, two E2M1 codes per byte, low nibble first) */
+typedef enum { DG_E4M3 = 0, DG_E2M1X2 = 1, DG_BF16 = 2, DG_F32 = 3 } dg_dtype_t;
+
+/* csrc/jit_kernels/epilogue_class.hpp:29-66 (Identity / ScaleByAlpha / AddBias) */
+typedef enum { DG_EPILOGUE_IDENTITY = 0, DG_EPILOGUE_ALPHA = 1, DG_EPILOGUE_BIAS = 2 } dg_epilogue_t;
+
+/*
+ * Problem descriptor. Mirrors GemmDesc, csrc/jit_kernels/gemm_config.hpp:39-95, plus the
+ * epilogue::Args of deep_gemm/include/deep_gemm/common.hpp:96-102.
+ *
+ *   Normal            A [M,K]          B [N,K]        D [M,N]
+ *   M-grouped psum    A [M_total,K]    B [G,N,K]      D [M_total,N]     grouped_layout = psum int32[G]
+ *   M-grouped masked  A [G,max_m,K]    B [G,N,K]      D [G,max_m,N]     grouped_layout = masked_m int32[G], m = max_m
+ *
+ * "[MN,K]" is the logical shape; `major_*` says which axis is contiguous in memory and
+ * `outer_stride_*` is the stride of the other axis in ELEMENTS (bytes for packed FP4 operands:
+ * the stride counts int8 storage elements). sfa / sfb are in the required layout
+ * (int16 [MN, ceil(K/64)], MN-major, csrc/apis/layout.hpp:19-36); `sf*_stride` is the distance in
+ * int16 elements between consecutive K64 columns (== MN for a dense tensor) and must be a multiple
+ * of 8; sf*_group_stride is the distance between groups of scales in int16 elements.
+ */
+typedef struct {
+    const void* a;
+    const void* b;
+    void* d;
+    const int16_t* sfa;
+    const int16_t* sfb;
+    int32_t a_dtype, b_dtype, d_dtype;        /* dg_dtype_t */
+    uint32_t m, n, k;
+    int32_t major_a, major_b;                 /* dg_major_t */
+    uint64_t outer_stride_a, outer_stride_b, outer_stride_d;
+    uint64_t group_stride_a, group_stride_b, group_stride_d; /* elements between groups (B always; A, D: masked) */
+    uint64_t sfa_stride, sfb_stride;
+    uint64_t sfa_group_stride, sfb_group_stride;             /* int16 elements between groups of scales */
+    int32_t accumulate;                       /* D += A B^T (csrc/apis/gemm.hpp:106-112,180) */
+    int32_t gemm_type;                        /* dg_gemm_type_t */
+    const int32_t* grouped_layout;            /* device pointer, read on device only */
+    uint32_t num_groups;
+    uint32_t expected_m;                      /* heuristic hint (gemm_config.hpp:59) */
+    int32_t epilogue;                         /* dg_epilogue_t */
+    float alpha;
+    const void* bias;                         /* [1,N], D's dtype */
+    uint32_t num_sms;                         /* cap of the persistent grid; 0 = all SMs */
+} dg_gemm_desc_t;
+
+/* Tiling chosen for a problem. Replaces GemmConfig, csrc/jit_kernels/gemm_config.hpp:98-121. */
+typedef struct {
+    uint32_t block_m, block_n, block_k;
+    uint32_t num_stages;
+    uint32_t cta_group;       /* 1, or 2 = two CTAs of a cluster share one 256-row UMMA */
+    uint32_t split_k;         /* >1: partial sums reduced in FP32 through the workspace */
+    uint32_t num_ctas;        /* persistent grid size */
+    uint32_t tmem_cols;
+    uint32_t smem_bytes;
+    uint32_t epilogue_mode;   /* 0 TMA store, 1 TMA reduce-add, 2 plain stores, 3 plain atomics */
+    uint32_t reserved[6];
+} dg_gemm_config_t;
+
+/* The B200 tiling heuristic. Replaces select_gemm_config, csrc/jit_kernels/heuristics.hpp:592-755. */
+int dg_select_config(const dg_gemm_desc_t* desc, dg_gemm_config_t* out);
+
+/* Bytes of zero-initialised device scratch dg_gemm_launch needs for (desc, config); 0 when none.
+ * The library keeps the scratch zero between calls once the caller has zeroed it once. */
+size_t dg_gemm_workspace_bytes(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config);
+
+/* Enqueue the GEMM. Replaces launch_fp8_gemm / launch_fp4_gemm / launch_fp8_dequant_gemm,
+ * csrc/jit_kernels/fp8_gemm.hpp:11-79,83-151 and csrc/jit_kernels/fp8_dequant_gemm.hpp:24-95.
+ * `config` may be NULL (the heuristic is used). */
+int dg_gemm_launch(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
+/* Validate (desc, config) and build the launch plan without touching the device: the counterpart
+ * of the reference's dry-run compile, csrc/jit_kernels/fp8_gemm.hpp:67-70. */
+int dg_gemm_dry_run(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config);
+
+/*
+ * Scale-factor relayout into the required layout. Replaces launch_transform_sf,
+ * csrc/jit_kernels/transform_sf.hpp:15-105, and the device kernel
+ * deep_gemm/include/deep_gemm/transform_sf.hpp:447-639.
+ *
+ *   src            fp32 [B, src_rows, src_cols] (src_is_fp32) or int16 with two UE8M0 bytes per element
+ *   src_row_stride / src_col_stride / src_batch_stride   in source elements (either major is fine)
+ *   dst            int16, element (b, mn, c) at dst[b*dst_batch_stride + c*dst_col_stride + mn]
+ *   dst_mn         rows of the result; row mn reads source row mn / gran_mn
+ *   k32_blocks     number of 32-wide K blocks of the operand, ceil(K/32)
+ *   k_repeat       1 (gran_k = 32) or 4 (gran_k = 128: each source scale covers four blocks)
+ *   psum           NULL, or int32[num_groups] psum layout: rows in a group's padding get scale byte 0
+ *   invalid_flag   NULL, or a device int32 set to 1 when an fp32 scale is negative or has mantissa bits
+ *                  (the reference asserts on device, transform_sf.hpp:13-21; this library never traps)
+ */
+int dg_transform_sf_launch(const void* src, int src_is_fp32,
+                           uint64_t src_row_stride, uint64_t src_col_stride, uint64_t src_batch_stride,
+                           uint32_t src_rows, uint32_t src_cols,
+                           int16_t* dst, uint64_t dst_col_stride, uint64_t dst_batch_stride,
+                           uint32_t dst_mn, uint32_t k32_blocks, uint32_t gran_mn, uint32_t k_repeat,
+                           uint32_t num_batches, const int32_t* psum, uint32_t num_groups,
+                           uint32_t alignment, int32_t* invalid_flag, void* stream);
+
+/* Copy a 2-D byte matrix into a buffer whose row pitch satisfies the 16-byte rule of TMA, zero
+ * filling the tail of each row. Used for operands whose contiguous extent is not a multiple of 16
+ * bytes (the unaligned-K / unaligned-MN cases of tests/generators.py:491-541). */
+int dg_pad_rows_launch(const void* src, uint64_t src_pitch_bytes, void* dst, uint64_t dst_pitch_bytes,
+                       uint64_t rows, uint64_t row_bytes, void* stream);
+
+/* Writes a buffer larger than L2 so that the next kernel starts cold (deep_gemm/testing/bench.py:263-268). */
+int dg_l2_flush_launch(void* buffer, size_t bytes, void* stream);
+
+/* Device-side status word of the most recent kernels on this device: 0, or a code recorded by a
+ * bounded wait that gave up. Reading it synchronises the device. */
+int dg_device_status(int32_t* out_status);
+
+/* Runtime knobs, csrc/apis/runtime.hpp:12-62 / csrc/jit/jit.hpp:18-76. */
+int dg_get_num_sms(void);
+int dg_set_num_sms(int num_sms);
+int dg_get_mk_alignment_for_contiguous_layout(void); /* fixed at 256, csrc/jit/jit.hpp:59-73 */
+
+const char* dg_last_error(void);
+int dg_abi_version(void);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DG_B200_H_ */

@@ -1,0 +1,65 @@
+"""Seeded input generators and comparison helpers shared by the parity tests.
+
+Inputs follow the two distributions the reference uses (tests/generators.py:124-166 uniform codes with
+power-of-two scales; :61-95 N(0,1) block quantisation) and are built on the CPU so that the oracle and the
+CUDA path see identical bytes.
+"""
+
+from __future__ import annotations
+
+import random
+
+import torch
+
+import oracle
+
+# Tolerances on BF16 / FP32 output: 1 - cosine <= 1e-3 and max relative error <= 2e-2.
+COS_TOL = 1e-3
+REL_TOL = 2e-2
+
+
+def seed_all(seed: int = 0) -> None:
+    random.seed(seed)
+    torch.manual_seed(seed)
+
+
+def uniform_fp8(shape, gran, sf_choices=(2.0 ** -9, 2.0 ** -8, 2.0 ** -7)):
+    """Every non-NaN E4M3 code equally likely; scales drawn from three powers of two.
+    Returns (data float8 [..., MN, K], sf fp32, dequantised fp32)."""
+    raw = torch.randint(0, 254, shape, dtype=torch.uint8)
+    raw += (raw >= 0x7F).to(torch.uint8)
+    raw[raw == 0xFF] = 0xFE
+    data = raw.view(torch.float8_e4m3fn)
+    sf_shape = (*shape[:-2], oracle.ceil_div(shape[-2], gran[0]), oracle.ceil_div(shape[-1], gran[1]))
+    table = torch.tensor(sf_choices, dtype=torch.float32)
+    sf = table[torch.randint(0, len(sf_choices), sf_shape)].contiguous()
+    return data, sf, oracle.dequantize(data.float(), sf, gran[0], gran[1])
+
+
+def normal_fp8(shape, gran):
+    x = torch.randn(shape, dtype=torch.float32)
+    if x.dim() == 2:
+        return oracle.quantize_e4m3(x, gran)
+    parts = [oracle.quantize_e4m3(x[i], gran) for i in range(x.size(0))]
+    return (torch.stack([p[0].view(torch.uint8) for p in parts]).view(torch.float8_e4m3fn),
+            torch.stack([p[1] for p in parts]), torch.stack([p[2] for p in parts]))
+
+
+def with_major(t: torch.Tensor, mn_major: bool) -> torch.Tensor:
+    """Same logical [..., MN, K] tensor, stored with MN contiguous when `mn_major`."""
+    if not mn_major:
+        return t.contiguous()
+    if t.dtype == torch.float8_e4m3fn:
+        return t.view(torch.uint8).transpose(-2, -1).contiguous().transpose(-2, -1).view(torch.float8_e4m3fn)
+    return t.transpose(-2, -1).contiguous().transpose(-2, -1)
+
+
+def assert_close(out: torch.Tensor, ref: torch.Tensor, what: str = '') -> tuple[float, float]:
+    out, ref = out.detach().cpu(), ref.detach().cpu()
+    assert out.shape == ref.shape, f'{what}: shape {out.shape} vs {ref.shape}'
+    assert torch.isfinite(out.float()).all(), f'{what}: non-finite output'
+    diff = oracle.calc_diff(out, ref)
+    rel = oracle.max_rel_err(out, ref)
+    assert diff <= COS_TOL, f'{what}: 1-cos = {diff:.3e}'
+    assert rel <= REL_TOL, f'{what}: max rel err = {rel:.3e}'
+    return diff, rel

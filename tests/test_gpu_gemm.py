@@ -1,0 +1,176 @@
+"""Parity of the CUDA GEMM path (through the Python API and the C ABI) with the CPU oracle.
+
+Tolerance on the output: 1 - cosine <= 1e-3 and max relative error <= 2e-2 (see tests/helpers.py); padding rows,
+group handling and scale-factor layouts are compared bit-exactly.
+"""
+
+import pytest
+import torch
+
+import deep_gemm
+import oracle
+from helpers import assert_close, normal_fp8, seed_all, uniform_fp8, with_major
+
+pytestmark = pytest.mark.gpu
+
+
+def _dense(m, n, k, *, trans='nt', recipe=(1, 1, 32), dist='uniform', out=torch.bfloat16, acc=False, bias=False,
+           alpha=None, config=None, seed=0):
+    seed_all(seed)
+    gm, gn, gk = recipe
+    gen = uniform_fp8 if dist == 'uniform' else normal_fp8
+    a, sfa, a_ref = gen((m, k), (gm, gk))
+    b, sfb, b_ref = gen((n, k), (gn, gk))
+    c = torch.randn(1 if bias else m, n).to(out) if (acc or bias) else None
+    ref = oracle.gemm_ref(a_ref, b_ref, out, c=c if acc else None, bias=c if bias else None, alpha=alpha)
+    a_dev = with_major(a, trans[0] == 't').cuda()
+    b_dev = with_major(b, trans[1] == 'n').cuda()
+    a_arg = (a_dev.transpose(0, 1), sfa.cuda().transpose(0, 1)) if trans[0] == 't' else (a_dev, sfa.cuda())
+    b_arg = (b_dev.transpose(0, 1), sfb.cuda().transpose(0, 1)) if trans[1] == 'n' else (b_dev, sfb.cuda())
+    d = torch.full((m, n), float('nan'), dtype=out, device='cuda')
+    kwargs = {}
+    if acc:
+        d.copy_(c)
+        kwargs['c'] = d
+    elif bias:
+        kwargs['c'] = c.cuda()
+    getattr(deep_gemm, f'fp8_gemm_{trans}')(a_arg, b_arg, d, recipe=recipe, alpha=alpha, config=config, **kwargs)
+    assert deep_gemm.device_status() == 0
+    return assert_close(d, ref, f'{trans} {m}x{n}x{k} recipe={recipe} {dist} out={out} acc={acc} bias={bias} alpha={alpha}')
+
+
+@pytest.mark.parametrize('m,n,k', [(128, 128, 128), (128, 256, 512), (256, 192, 1024), (64, 2112, 7168),
+                                   (1, 576, 512), (384, 7168, 256)])
+def test_dense_nt_bf16(m, n, k):
+    _dense(m, n, k)
+
+
+def test_dense_nt_baseline_distribution_and_recipe():
+    """N(0,1) data, per-1x128 scales on A and 128x128 on B: the distribution the benchmark uses."""
+    _dense(128, 2112, 7168, recipe=(1, 128, 128), dist='normal')
+    _dense(320, 512, 1024, recipe=(1, 128, 128), dist='normal', out=torch.float32)
+
+
+@pytest.mark.parametrize('recipe', [(1, 32, 32), (32, 1, 32), (32, 32, 32), (128, 128, 32)])
+def test_dense_recipes(recipe):
+    _dense(200, 328, 640, recipe=recipe, out=torch.float32, acc=True)
+
+
+@pytest.mark.parametrize('m,n,k', [(4, 4, 64), (17, 512, 1024), (512, 17, 1024), (15, 1024, 512), (130, 257, 2048),
+                                   (513, 257, 1024)])
+def test_dense_unaligned_mn(m, n, k):
+    _dense(m, n, k, out=torch.float32, acc=True)
+    _dense(m, n, k, out=torch.bfloat16)
+
+
+@pytest.mark.parametrize('m,n,k', [(64, 64, 4), (256, 512, 17), (512, 256, 15), (128, 128, 234), (256, 384, 4095)])
+def test_dense_unaligned_k(m, n, k):
+    _dense(m, n, k, out=torch.float32, acc=True)
+
+
+@pytest.mark.parametrize('out', [torch.bfloat16, torch.float32])
+def test_dense_epilogues(out):
+    _dense(256, 384, 512, out=out, bias=True)
+    _dense(256, 384, 512, out=out, alpha=-0.375)
+    _dense(256, 384, 512, out=out, acc=True)
+    _dense(256, 384, 512, out=out, acc=True, alpha=0.625)
+
+
+@pytest.mark.parametrize('trans', ['nn', 'tn', 'tt'])
+def test_dense_majors(trans):
+    _dense(256, 384, 512, trans=trans)
+    _dense(384, 256, 1024, trans=trans, out=torch.float32, acc=True)
+
+
+def test_dense_forced_tilings():
+    for bn in (64, 128, 192, 256):
+        _dense(384, 768, 1024, config={'block_n': bn})
+    for stages in (1, 2, 3):
+        _dense(256, 256, 2048, config={'block_n': 128, 'num_stages': stages})
+    for split in (2, 4, 7):
+        _dense(128, 512, 4096, config={'block_n': 128, 'split_k': split})
+        _dense(128, 512, 4096, config={'block_n': 128, 'split_k': split}, bias=True)
+        _dense(100, 500, 4096, config={'block_n': 96, 'split_k': split}, out=torch.float32, acc=True)
+    # a second split-K launch must find the workspace zeroed by the first one
+    _dense(128, 512, 4096, config={'block_n': 128, 'split_k': 4}, seed=1)
+
+
+def test_golden_fixtures_through_the_api(golden):
+    for name in ('dense_fp8_nt_bf16', 'dense_fp8_nt_acc_f32', 'dense_fp8_unaligned_k', 'dense_fp8_recipe_32_32',
+                 'dense_fp8_nn_bias', 'dense_fp8_tn_alpha'):
+        c = golden[name]
+        a = c['a'].view(torch.float8_e4m3fn)
+        b = c['b'].view(torch.float8_e4m3fn)
+        a_dev = with_major(a, c['a_major'] == 'MN').cuda()
+        b_dev = with_major(b, c['b_major'] == 'MN').cuda()
+        d = torch.zeros_like(c['d']).cuda()
+        kwargs = {}
+        if c['accumulate']:
+            d.copy_(c['c'])
+            kwargs['c'] = d
+        elif c['with_bias']:
+            kwargs['c'] = c['c'].cuda()
+        gm, gn, gk = c['recipe']
+        deep_gemm.fp8_gemm_nt((a_dev, c['sfa'].cuda()), (b_dev, c['sfb'].cuda()), d, recipe_a=(gm, gk),
+                              recipe_b=(gn, gk), alpha=c['alpha'], **kwargs)
+        assert_close(d, c['d'], name)
+
+
+def _grouped_case(sizes, n, k, trans_b=False, out=torch.bfloat16, seed=0):
+    seed_all(seed)
+    total, psum = oracle.make_psum_layout(sizes, 256)
+    g = len(sizes)
+    a, sfa, a_ref = uniform_fp8((total, k), (1, 32))
+    b, sfb, b_ref = uniform_fp8((g, n, k), (1, 32))
+    for span in oracle.psum_padding_spans(psum, 256):
+        a.view(torch.uint8)[span] = 0
+        a_ref[span] = 0
+        sfa[span] = torch.randn_like(sfa[span])          # garbage on purpose (tests/generators.py:342-346)
+    ref = oracle.m_grouped_psum_ref(a_ref, b_ref, psum, out)
+    b_dev = with_major(b, trans_b).cuda()
+    b_arg = (b_dev.transpose(1, 2), sfb.cuda().transpose(1, 2)) if trans_b else (b_dev, sfb.cuda())
+    d = torch.full((total, n), float('nan'), dtype=out, device='cuda')
+    layout = torch.tensor(psum, dtype=torch.int32, device='cuda')
+    fn = deep_gemm.m_grouped_fp8_gemm_nn_contiguous if trans_b else deep_gemm.m_grouped_fp8_gemm_nt_contiguous
+    fn((a.cuda(), sfa.cuda()), b_arg, d, layout)
+    assert deep_gemm.device_status() == 0
+    assert_close(d, ref, f'm-grouped sizes={sizes} n={n} k={k} trans_b={trans_b}')
+    # padding rows are computed from zero rows of A and must be exactly zero
+    for span in oracle.psum_padding_spans(psum, 256):
+        assert (d[span] == 0).all(), 'padding rows of D must be exactly zero'
+
+
+@pytest.mark.parametrize('sizes', [[300, 200, 513], [1, 0, 255, 256, 257], [700]])
+def test_m_grouped_contiguous(sizes):
+    _grouped_case(sizes, 384, 512)
+    _grouped_case(sizes, 256, 768, trans_b=True, out=torch.float32)
+
+
+def test_m_grouped_golden(golden):
+    for name, trans_b in (('mgrouped_fp8_nt', False), ('mgrouped_fp8_nn', True)):
+        c = golden[name]
+        a = c['a'].view(torch.float8_e4m3fn).cuda()
+        b = with_major(c['b'].view(torch.float8_e4m3fn), trans_b).cuda()
+        sfb = c['sfb'].cuda()
+        b_arg = (b.transpose(1, 2), sfb.transpose(1, 2)) if trans_b else (b, sfb)
+        d = torch.full(tuple(c['d'].shape), float('nan'), dtype=torch.bfloat16, device='cuda')
+        layout = torch.tensor(c['psum'], dtype=torch.int32, device='cuda')
+        fn = deep_gemm.m_grouped_fp8_gemm_nn_contiguous if trans_b else deep_gemm.m_grouped_fp8_gemm_nt_contiguous
+        fn((a, c['sfa'].cuda()), b_arg, d, layout)
+        assert_close(d, c['d'], name)
+
+
+@pytest.mark.parametrize('max_m,masked', [(256, [0, 256, 1, 130, 77]), (128, [128, 5, 0]), (200, [200, 13, 129])])
+def test_m_grouped_masked(max_m, masked):
+    seed_all(7)
+    g, n, k = len(masked), 384, 640
+    a, sfa, a_ref = uniform_fp8((g, max_m, k), (1, 32))
+    b, sfb, b_ref = uniform_fp8((g, n, k), (1, 32))
+    ref = oracle.m_grouped_masked_ref(a_ref, b_ref, masked, torch.bfloat16)
+    d = torch.full((g, max_m, n), float('nan'), dtype=torch.bfloat16, device='cuda')
+    mask = torch.tensor(masked, dtype=torch.int32, device='cuda')
+    deep_gemm.m_grouped_fp8_gemm_nt_masked((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d, mask, max(masked))
+    assert deep_gemm.device_status() == 0
+    for i, mg in enumerate(masked):
+        if mg:
+            assert_close(d[i, :mg], ref[i, :mg], f'masked group {i} rows {mg}')

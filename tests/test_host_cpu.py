@@ -1,0 +1,176 @@
+"""Host-side behaviour that needs no GPU: the C ABI loads and exports what include/dg_b200.h declares,
+argument validation, shape / major inference, the tiling heuristic and the dry-run path on meta tensors."""
+
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+import deep_gemm
+from deep_gemm import _lib as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _meta_pair(rows, k, gran=(1, 32), dtype=torch.float8_e4m3fn, mn_major=False):
+    data = torch.empty((k, rows) if mn_major else (rows, k), dtype=dtype, device='meta')
+    if mn_major:
+        data = data.transpose(0, 1)
+    sf = torch.empty((rows + gran[0] - 1) // gran[0], (k + gran[1] - 1) // gran[1], dtype=torch.float32, device='meta')
+    return data, sf
+
+
+@pytest.fixture(autouse=True)
+def dry_run():
+    deep_gemm.set_dry_run(True)
+    yield
+    deep_gemm.set_dry_run(False)
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, 'include', 'dg_b200.h')).read()
+    declared = set(re.findall(r'\b(dg_[a-z0-9_]+)\s*\(', header))
+    assert declared, 'no declarations found'
+    handle = ctypes.CDLL(L.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(handle, name), f'{name} is declared but not exported'
+    assert declared == set(L.EXPORTED_SYMBOLS)
+    assert L.lib().dg_abi_version() == 1
+
+
+def test_struct_sizes_match_the_header():
+    # 5 pointers, 8 x 4-byte, 10 x 8-byte, 2 x 4, pointer, 2 x 4, 2 x 4, pointer, 4 (+4 padding)
+    assert ctypes.sizeof(L.GemmDesc) == 200
+    assert ctypes.sizeof(L.GemmConfig) == 64
+
+
+def test_public_names_of_the_hot_path_exist():
+    for name in ('fp8_gemm_nt', 'fp8_gemm_nn', 'fp8_gemm_tn', 'fp8_gemm_tt',
+                 'fp8_fp4_gemm_nt', 'fp8_fp4_gemm_nn', 'fp8_fp4_gemm_tn', 'fp8_fp4_gemm_tt',
+                 'm_grouped_fp8_gemm_nt_contiguous', 'm_grouped_fp8_gemm_nn_contiguous',
+                 'm_grouped_fp8_fp4_gemm_nt_contiguous', 'm_grouped_fp8_fp4_gemm_nn_contiguous',
+                 'm_grouped_fp8_gemm_nt_masked', 'm_grouped_fp8_fp4_gemm_nt_masked',
+                 'transform_sf_into_required_layout', 'get_num_sms', 'set_num_sms',
+                 'get_mk_alignment_for_contiguous_layout', 'use_deterministic_algorithms', 'set_dry_run'):
+        assert callable(getattr(deep_gemm, name)), name
+    assert deep_gemm.fp8_gemm_nt is deep_gemm.fp8_fp4_gemm_nt
+    assert deep_gemm.get_mk_alignment_for_contiguous_layout() == 256
+    deep_gemm.epilogue.Identity(), deep_gemm.epilogue.Alpha(0.5)
+
+
+def test_num_sms_knob_round_trips():
+    deep_gemm.set_num_sms(132)
+    assert deep_gemm.get_num_sms() == 132
+    deep_gemm.set_num_sms(0)
+    assert deep_gemm.get_num_sms() >= 1
+
+
+def test_dry_run_on_meta_tensors_all_spellings():
+    m, n, k = 256, 384, 512
+    d = torch.empty(m, n, dtype=torch.bfloat16, device='meta')
+    for name, ta, tb in (('nt', False, False), ('nn', False, True), ('tn', True, True), ('tt', True, False)):
+        a, sfa = _meta_pair(m, k, mn_major=ta)
+        b, sfb = _meta_pair(n, k, mn_major=tb)
+        a_arg = (a.transpose(0, 1), sfa.transpose(0, 1)) if ta else (a, sfa)
+        b_arg = (b.transpose(0, 1), sfb.transpose(0, 1)) if tb else (b, sfb)
+        getattr(deep_gemm, f'fp8_gemm_{name}')(a_arg, b_arg, d)
+
+
+def test_alpha_and_bias_are_exclusive():
+    a, b = _meta_pair(128, 256), _meta_pair(64, 256)
+    d = torch.empty(128, 64, dtype=torch.bfloat16, device='meta')
+    bias = torch.empty(1, 64, dtype=torch.bfloat16, device='meta')
+    with pytest.raises(RuntimeError, match='alpha and bias cannot be used together'):
+        deep_gemm.fp8_gemm_nt(a, b, d, c=bias, alpha=0.5)
+    deep_gemm.fp8_gemm_nt(a, b, d, c=bias)
+    deep_gemm.fp8_gemm_nt(a, b, d, alpha=0.5)
+    with pytest.raises(RuntimeError, match='exclusive'):
+        deep_gemm.fp8_gemm_nt(a, b, d, alpha=0.5, epilogue=deep_gemm.epilogue.Identity())
+
+
+def test_shape_conflicts_and_bad_c_are_reported():
+    a, b = _meta_pair(128, 256), _meta_pair(64, 128)
+    d = torch.empty(128, 64, dtype=torch.bfloat16, device='meta')
+    with pytest.raises(RuntimeError, match="Conflicting shape dimension 'k'"):
+        deep_gemm.fp8_gemm_nt(a, b, d)
+    b = _meta_pair(64, 256)
+    with pytest.raises(RuntimeError, match="C must match D's pointer and shape"):
+        deep_gemm.fp8_gemm_nt(a, b, d, c=torch.empty(2, 64, dtype=torch.bfloat16, device='meta'))
+    with pytest.raises(RuntimeError, match='bf16 or fp32'):
+        deep_gemm.fp8_gemm_nt(a, b, torch.empty(128, 64, dtype=torch.float16, device='meta'))
+
+
+def test_recipe_rules():
+    assert deep_gemm.get_recipe(None, None, None) == (1, 1, 32, 32)
+    assert deep_gemm.get_recipe((1, 128, 128), None, None) == (1, 128, 128, 128)
+    assert deep_gemm.get_recipe(None, (1, 128), (1, 32)) == (1, 1, 128, 32)
+    with pytest.raises(RuntimeError, match='mutually exclusive'):
+        deep_gemm.get_recipe((1, 1, 32), (1, 32), None)
+
+
+def test_sf_fast_path_returns_the_same_tensor():
+    mn, k = 64, 256
+    sf = torch.empty(k // 64, mn, dtype=torch.int16, device='meta').transpose(0, 1)
+    assert deep_gemm.transform_sf_into_required_layout(sf, mn, k, (1, 1, 32), is_sfa=True) is sf
+    sf32 = torch.empty(mn, k // 32, dtype=torch.float32, device='meta')
+    out = deep_gemm.transform_sf_into_required_layout(sf32, mn, k, (1, 1, 32), is_sfa=True)
+    assert out.dtype == torch.int16 and tuple(out.shape) == (mn, k // 64)
+    assert out.stride(-2) == 1 and out.stride(-1) == mn
+    with pytest.raises(RuntimeError, match='disable_ue8m0_cast'):
+        deep_gemm.transform_sf_into_required_layout(sf32, mn, k, (1, 1, 32), is_sfa=True, disable_ue8m0_cast=True)
+    with pytest.raises(RuntimeError, match='is_sfa'):
+        deep_gemm.transform_sf_into_required_layout(sf32, mn, k, (1, 1, 32))
+
+
+def _desc(m, n, k, d_dtype=L.BF16, **kw):
+    d = L.GemmDesc()
+    d.a = d.b = d.d = d.sfa = d.sfb = 0x1000
+    d.a_dtype, d.b_dtype, d.d_dtype = L.E4M3, L.E4M3, d_dtype
+    d.m, d.n, d.k = m, n, k
+    d.outer_stride_a = d.outer_stride_b = k
+    d.outer_stride_d = n
+    d.sfa_stride, d.sfb_stride = (m + 7) // 8 * 8, (n + 7) // 8 * 8
+    for key, value in kw.items():
+        setattr(d, key, value)
+    return d
+
+
+def test_heuristic_respects_hardware_limits():
+    lib = L.lib()
+    for m in (1, 64, 128, 4096):
+        for n, k in ((2112, 7168), (24576, 1536), (32768, 512), (7168, 16384), (4096, 7168), (7168, 2048)):
+            desc, cfg = _desc(m, n, k), L.GemmConfig()
+            assert lib.dg_select_config(ctypes.byref(desc), ctypes.byref(cfg)) == 0, L.last_error()
+            c = cfg.as_dict()
+            assert c['block_m'] == 128 * c['cta_group'] and c['block_k'] == 128
+            assert 32 <= c['block_n'] <= 256 and c['block_n'] % 32 == 0
+            assert c['smem_bytes'] <= 227 * 1024 and 1 <= c['num_stages'] <= 12
+            assert c['tmem_cols'] in (32, 64, 128, 256, 512)
+            assert c['accum_stages'] * c['block_n'] + 12 <= 512
+            assert 1 <= c['num_ctas'] <= 148
+            assert c['split_k'] >= 1 and (c['split_k'] == 1 or m <= 1024)
+            if c['split_k'] > 1:
+                assert lib.dg_gemm_workspace_bytes(ctypes.byref(desc), ctypes.byref(cfg)) >= m * n * 4
+
+
+def test_c_abi_validation_messages():
+    lib = L.lib()
+    cfg = L.GemmConfig()
+    bad = _desc(128, 128, 128, a_dtype=L.E2M1X2, b_dtype=L.E4M3)
+    assert lib.dg_select_config(ctypes.byref(bad), ctypes.byref(cfg)) == L.DG_ERR_INVALID
+    assert 'Unsupported operand dtypes' in L.last_error()
+    bad = _desc(128, 128, 128, epilogue=L.EPILOGUE_BIAS)
+    assert lib.dg_gemm_dry_run(ctypes.byref(bad), None) == L.DG_ERR_INVALID
+    bad = _desc(128, 128, 100)
+    bad.outer_stride_a = 100
+    assert lib.dg_gemm_dry_run(ctypes.byref(bad), None) == L.DG_ERR_UNSUPPORTED
+    assert '16 bytes' in L.last_error()
+    grouped = _desc(1000, 128, 128, gemm_type=L.GEMM_M_GROUPED_PSUM, num_groups=2, grouped_layout=0x1000)
+    assert lib.dg_gemm_dry_run(ctypes.byref(grouped), None) == L.DG_ERR_INVALID
+    assert '256' in L.last_error()
+    forced = L.GemmConfig()
+    forced.block_n, forced.cta_group, forced.split_k = 96, 1, 1
+    assert lib.dg_gemm_dry_run(ctypes.byref(_desc(128, 256, 256)), ctypes.byref(forced)) == L.DG_ERR_INVALID
+    assert 'block_n' in L.last_error()
