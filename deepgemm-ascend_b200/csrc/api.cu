@@ -207,9 +207,9 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
         if (split > 1 && (d.gemm_type != DG_GEMM_NORMAL || nkb / split < 4)) break;
         const bool out_fp32 = d_fp32 || split > 1;
         const uint32_t gran = ((tma_ok || split > 1) && !out_fp32) ? 64u : 32u;
-        for (uint32_t bn = gran; bn <= 256; bn += gran) {
-            if (d.major_b == DG_MAJOR_MN && bn % 128 != 0) continue;
-            if (bn > 64 && bn - gran >= d.n) continue;           // wider than the problem: no gain
+        const uint32_t step = d.major_b == DG_MAJOR_MN ? 128u : gran;   // MN-major B is fetched in 128-column atoms
+        for (uint32_t bn = step; bn <= 256; bn += step) {
+            if (bn > step && bn - step >= d.n) continue;         // a narrower legal tile already covers N
             const uint32_t n_blocks = ceil_div_u32(d.n, bn);
             const uint64_t tiles = (uint64_t)m_blocks * n_blocks * split;
             const uint64_t waves = (tiles + num_sms - 1) / num_sms;
