@@ -31,6 +31,9 @@ void set_last_error(const char* fmt, ...) {
     va_end(ap);
 }
 
+static std::atomic<unsigned long long> g_launches{0};
+void count_kernel_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
 // ------------------------------------------------------------------------------------------------
 // Runtime knobs
 // ------------------------------------------------------------------------------------------------
@@ -135,15 +138,13 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     const uint32_t num_sms = effective_num_sms(d);
     c.block_m = kBlockM * c.cta_group;
     c.block_k = kBlockK;
-    const bool d_fp32 = d.d_dtype == DG_F32;
     const bool split = c.split_k > 1;
     const bool tma_ok = split || tma_store_ok(d);
     if (split) c.epilogue_mode = kEpiTmaReduce;
     else if (d.accumulate) c.epilogue_mode = tma_ok ? kEpiTmaReduce : kEpiPlainAtomic;
     else c.epilogue_mode = tma_ok ? kEpiTmaStore : kEpiPlainStore;
 
-    const bool out_fp32 = split || d_fp32;
-    const uint32_t gran = (c.epilogue_mode <= kEpiTmaReduce && !out_fp32) ? 64u : 32u;
+    const uint32_t gran = 32u;
     DG_CHECK_ARG(c.cta_group == 1 || c.cta_group == 2, "cta_group must be 1 or 2");
     DG_CHECK_ARG(c.block_n >= gran && c.block_n <= 256 && c.block_n % gran == 0,
                  "block_n must be a multiple of %u in [%u, 256]", gran, gran);
@@ -188,54 +189,73 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     return DG_OK;
 }
 
+// Modelled cycles one CTA (or CTA pair) spends on one 128-wide K block of a tile. The tensor pipe needs
+// 2 * block_n cycles for 128 x block_n x 128 (16384 FP8 flop per cycle per SM). Operand bytes enter an SM at about
+// 50 bytes per cycle (measured: 43-56 B/clk/SM across tilings, the L2-to-SM path), which is what bounds every tiling
+// that does not share operands across SMs; a CTA pair halves the B bytes per SM.
+static double k_block_cycles(uint32_t cta_group, uint32_t bn) {
+    const double mma = 2.0 * bn;
+    const double ingest = (128.0 + (double)bn / cta_group) * 128.0 / 50.0;
+    return mma > ingest ? mma : ingest;
+}
+
 static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     memset(&c, 0, sizeof(c));
     const uint32_t num_sms = effective_num_sms(d);
     const bool d_fp32 = d.d_dtype == DG_F32;
-    const bool tma_ok = tma_store_ok(d);
     const uint32_t nkb = ceil_div_u32(d.k, kBlockK);
-    c.cta_group = 1;
+    const bool grouped = is_grouped(d.gemm_type);
 
-    // Rows one CTA wave has to cover per tile column, used to cost a candidate block_n.
-    const uint32_t m_blocks = d.gemm_type == DG_GEMM_NORMAL ? ceil_div_u32(d.m, kBlockM)
-                            : d.gemm_type == DG_GEMM_M_GROUPED_PSUM ? d.m / kBlockM
-                            : d.num_groups * ceil_div_u32(d.expected_m ? (d.expected_m < d.m ? d.expected_m : d.m) : d.m, kBlockM);
+    // Rows the problem has (an estimate for the masked layout, whose row counts live on the device).
+    uint64_t rows;
+    if (d.gemm_type == DG_GEMM_M_GROUPED_MASKED) {
+        const uint32_t per_group = d.expected_m ? (d.expected_m < d.m ? d.expected_m : d.m) : d.m;
+        rows = (uint64_t)d.num_groups * per_group;
+    } else {
+        rows = d.m;
+    }
+    const double hbm_bytes = (double)rows * d.k + (double)d.n * d.k * (grouped ? d.num_groups : 1) +
+                             (double)rows * d.n * elem_size(d.d_dtype);
+    const double t_hbm = hbm_bytes / 6.4;          // ns at 6.4 TB/s
 
     double best_cost = 1e30;
-    uint32_t best_bn = 0, best_split = 1;
-    for (uint32_t split = 1; split <= 16; ++split) {
-        if (split > 1 && (d.gemm_type != DG_GEMM_NORMAL || nkb / split < 4)) break;
-        const bool out_fp32 = d_fp32 || split > 1;
-        const uint32_t gran = ((tma_ok || split > 1) && !out_fp32) ? 64u : 32u;
-        const uint32_t step = d.major_b == DG_MAJOR_MN ? 128u : gran;   // MN-major B is fetched in 128-column atoms
-        for (uint32_t bn = step; bn <= 256; bn += step) {
-            if (bn > step && bn - step >= d.n) continue;         // a narrower legal tile already covers N
-            const uint32_t n_blocks = ceil_div_u32(d.n, bn);
-            const uint64_t tiles = (uint64_t)m_blocks * n_blocks * split;
-            const uint64_t waves = (tiles + num_sms - 1) / num_sms;
-            const uint32_t kb_per = ceil_div_u32(nkb, split);
-            const bool single_accum = 2 * bn + 4 + 4 * (sfb_rows(bn) / 128) > 512;
-            // Time per K block of one tile, ns: tensor pipe (128 x bn x 128 at ~30 TFLOP/s per SM) against
-            // the operand bytes over this SM's share of L2 bandwidth.
-            const double t_mma = bn * 1.1;
-            const double t_load = (128.0 + bn) * 128.0 / 90.0;
-            const double t_epi = bn * (out_fp32 ? 9.0 : 7.0);
-            const double t_tile = kb_per * (t_mma > t_load ? t_mma : t_load) + (single_accum || waves == 1 ? t_epi : 0.0) + 300.0;
-            double cost = (double)waves * t_tile;
-            if (split > 1) cost += 2500.0 + 0.002 * d.m * d.n;        // finalisation pass
-            // HBM floor: every operand byte is read once
-            const double bytes = (double)d.m * d.k + (double)d.n * d.k * (is_grouped(d.gemm_type) ? d.num_groups : 1) +
-                                 (double)d.m * d.n * elem_size(d.d_dtype);
-            const double t_hbm = bytes / 6400.0;
-            if (cost < t_hbm) cost = t_hbm + 1e-3 * waves;             // prefer fewer waves when HBM-bound
-            if (cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && bn > best_bn)) {
-                best_cost = cost; best_bn = bn; best_split = split;
+    uint32_t best_bn = 0, best_split = 1, best_cg = 1;
+    for (uint32_t cg = 1; cg <= 2; ++cg) {
+        if (cg == 2 && (d.gemm_type == DG_GEMM_M_GROUPED_MASKED || rows <= kBlockM || num_sms < 2)) continue;
+        const uint32_t units = num_sms / cg;
+        const uint32_t tile_m = kBlockM * cg;
+        uint64_t m_tiles;
+        if (d.gemm_type == DG_GEMM_M_GROUPED_MASKED)
+            m_tiles = (uint64_t)d.num_groups * ceil_div_u32((uint32_t)(rows / d.num_groups), tile_m);
+        else
+            m_tiles = (rows + tile_m - 1) / tile_m;
+        for (uint32_t split = 1; split <= 16; ++split) {
+            if (split > 1 && (d.gemm_type != DG_GEMM_NORMAL || nkb / split < 2 || cg == 2)) break;
+            const bool out_fp32 = d_fp32 || split > 1;
+            const uint32_t step = d.major_b == DG_MAJOR_MN ? 128u * cg : 32u;   // MN-major B comes in 128-column atoms
+            for (uint32_t bn = step; bn <= 256; bn += step) {
+                if (bn > step && bn - step >= d.n) continue;                 // a narrower legal tile already covers N
+                if (bn % (16 * cg) != 0) continue;
+                const uint32_t n_tiles = ceil_div_u32(d.n, bn);
+                const uint64_t tiles = m_tiles * n_tiles * split;
+                const uint64_t waves = (tiles + units - 1) / units;
+                const uint32_t kb_per = ceil_div_u32(nkb, split);
+                const bool single_accum = 2 * bn + 4 + 4 * (sfb_rows(bn) / 128) > 512;
+                const double t_epi = bn * (out_fp32 ? 8.0 : 6.0);
+                const double cycles = kb_per * k_block_cycles(cg, bn) + ((single_accum || waves == 1) ? t_epi : 0.0) + 700.0;
+                double cost = (double)waves * cycles / 1.8;                   // ns at ~1.8 GHz
+                if (split > 1) cost += 3000.0 + 0.004 * (double)d.m * d.n;    // reduce traffic + finalisation pass
+                if (cost < t_hbm) cost = t_hbm + 1e-3 * (double)waves * cycles;   // HBM-bound: then prefer the least work
+                if (cost < best_cost * (1.0 - 1e-9) || (cost <= best_cost * (1.0 + 1e-9) && bn > best_bn)) {
+                    best_cost = cost; best_bn = bn; best_split = split; best_cg = cg;
+                }
             }
         }
     }
     DG_CHECK_ARG(best_bn != 0, "no legal tiling for this problem");
     c.block_n = best_bn;
     c.split_k = best_split;
+    c.cta_group = best_cg;
     return complete_config(d, c);
 }
 
@@ -402,9 +422,18 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
             const uint32_t box[3] = {es == 4 ? 32u : 64u, kStoreBoxRows, 1};
             if (int rc = encode_map(&plan.tm_d, es == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                                     d.d, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "D")) return rc;
+            plan.tm_d_tail = plan.tm_d;
+            if (es == 2) {
+                // half-width box for the last 32 columns of a tile whose block_n is an odd multiple of 32
+                const uint32_t tail_box[3] = {32u, kStoreBoxRows, 1};
+                if (int rc = encode_map(&plan.tm_d_tail, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d.d, dims, str, tail_box,
+                                        CU_TENSOR_MAP_SWIZZLE_64B, "D tail")) return rc;
+            }
         }
+        if (split) plan.tm_d_tail = plan.tm_d;
     } else {
         plan.tm_d = plan.tm_a;    // unused by the plain-store epilogue, but must be a valid descriptor
+        plan.tm_d_tail = plan.tm_a;
     }
     return DG_OK;
 }
@@ -435,6 +464,7 @@ extern "C" {
 
 const char* dg_last_error(void) { return tls_error; }
 int dg_abi_version(void) { return DG_B200_ABI_VERSION; }
+uint64_t dg_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int dg_get_num_sms(void) { return g_num_sms.load() > 0 ? g_num_sms.load() : device_sm_count(); }
 int dg_set_num_sms(int num_sms) {

@@ -11,6 +11,7 @@
 namespace dg {
 
 void set_last_error(const char* fmt, ...);
+void count_kernel_launch(unsigned n = 1);
 
 }  // namespace dg
 

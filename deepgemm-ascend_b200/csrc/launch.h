@@ -10,7 +10,7 @@ namespace dg {
 
 struct LaunchPlan {
     GemmKernelArgs args;
-    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d;
+    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d, tm_d_tail;
     int cta_group, major_a, major_b;
     uint32_t num_ctas, smem_bytes;
     // split-K finalisation (workspace -> D)

@@ -1,6 +1,8 @@
 // Instantiation and launch of the block-scaled GEMM kernel, plus the split-K finalisation kernel.
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "host_common.h"
@@ -43,7 +45,7 @@ __global__ void splitk_finalize_kernel(float* __restrict__ ws, uint64_t ws_strid
 }
 
 using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
-                          const CUtensorMap, const GemmKernelArgs);
+                          const CUtensorMap, const CUtensorMap, const GemmKernelArgs);
 
 static KernelFn pick_kernel(int cta_group, int major_a, int major_b) {
     static const KernelFn table[2][2][2] = {
@@ -78,6 +80,15 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
     GemmKernelArgs args = plan.args;
     DG_CHECK_ARG(get_status_pointer(&args.status) == DG_OK, "%s", dg_last_error());
 
+    // DG_TRACE=1 (debugging only): the launch becomes synchronous and prints where each CTA spent its time.
+    static const bool trace_enabled = [] { const char* e = getenv("DG_TRACE"); return e && atoi(e) != 0; }();
+    static unsigned long long* trace_buf = nullptr;
+    if (trace_enabled) {
+        if (trace_buf == nullptr) DG_CHECK_CUDA(cudaMalloc(&trace_buf, 1024 * 8 * sizeof(unsigned long long)));
+        DG_CHECK_CUDA(cudaMemsetAsync(trace_buf, 0, 1024 * 8 * sizeof(unsigned long long), stream));
+        args.trace = trace_buf;
+    }
+
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(plan.num_ctas, 1, 1);
     cfg.blockDim = dim3(kNumThreads, 1, 1);
@@ -90,7 +101,55 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    DG_CHECK_CUDA(cudaLaunchKernelEx(&cfg, fn, plan.tm_a, plan.tm_b, plan.tm_sfa, plan.tm_sfb, plan.tm_d, args));
+    // A persistent grid must be fully co-resident: a CTA (pair) that only starts after another one has finished its
+    // whole tile sequence doubles the run time. Not every SM pair can host a 2-CTA cluster, so ask the runtime.
+    uint32_t grid = plan.num_ctas;
+    if (plan.cta_group > 1) {
+        struct Key { const void* fn; uint32_t smem; int dev; int clusters; };
+        static std::mutex mu;
+        static Key cache[32];
+        static int cached = 0;
+        int dev = 0;
+        DG_CHECK_CUDA(cudaGetDevice(&dev));
+        int clusters = -1;
+        {
+            std::lock_guard<std::mutex> lock(mu);
+            for (int i = 0; i < cached; ++i)
+                if (cache[i].fn == (const void*)fn && cache[i].smem == plan.smem_bytes && cache[i].dev == dev) clusters = cache[i].clusters;
+        }
+        if (clusters < 0) {
+            cudaLaunchConfig_t probe = cfg;
+            probe.gridDim = dim3(148 * 2, 1, 1);
+            DG_CHECK_CUDA(cudaOccupancyMaxActiveClusters(&clusters, fn, &probe));
+            std::lock_guard<std::mutex> lock(mu);
+            if (cached < 32) cache[cached++] = Key{(const void*)fn, plan.smem_bytes, dev, clusters};
+        }
+        DG_CHECK_ARG(clusters > 0, "no CTA pair of this kernel fits on the device");
+        if (grid > (uint32_t)clusters * plan.cta_group) grid = (uint32_t)clusters * plan.cta_group;
+        cfg.gridDim = dim3(grid, 1, 1);
+    }
+    DG_CHECK_CUDA(cudaLaunchKernelEx(&cfg, fn, plan.tm_a, plan.tm_b, plan.tm_sfa, plan.tm_sfb, plan.tm_d, plan.tm_d_tail, args));
+    count_kernel_launch();
+    if (trace_enabled) {
+        DG_CHECK_CUDA(cudaStreamSynchronize(stream));
+        static unsigned long long host[1024 * 8];
+        const uint32_t n = grid < 1024 ? grid : 1024;
+        DG_CHECK_CUDA(cudaMemcpy(host, trace_buf, n * 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+        unsigned long long t0 = ~0ull, t1 = 0;
+        double sum[8] = {0}, mx[8] = {0};
+        for (uint32_t i = 0; i < n; ++i) {
+            if (host[i * 8] < t0) t0 = host[i * 8];
+            if (host[i * 8] > t1) t1 = host[i * 8];
+            for (int j = 2; j < 8; ++j) {
+                const double d = host[i * 8 + j] ? (double)(host[i * 8 + j] - host[i * 8 + 1]) : 0.0;
+                sum[j] += d; if (d > mx[j]) mx[j] = d;
+            }
+        }
+        fprintf(stderr, "[dg_trace] m=%u n=%u k=%u bn=%u cg=%d split=%u ctas=%u start-skew=%.2f us | cycles since entry avg/max: "
+                "setup %.0f/%.0f  first-tma %.0f/%.0f  first-data %.0f/%.0f  last-mma %.0f/%.0f  first-acc %.0f/%.0f  epi-done %.0f/%.0f\n",
+                args.m, args.n, args.k, args.block_n, plan.cta_group, args.split_k, grid, (t1 - t0) / 1e3,
+                sum[2] / n, mx[2], sum[3] / n, mx[3], sum[4] / n, mx[4], sum[5] / n, mx[5], sum[6] / n, mx[6], sum[7] / n, mx[7]);
+    }
 
     if (plan.finalize) {
         const uint64_t total = (uint64_t)plan.args.m * ((plan.args.n + 3) / 4);
@@ -99,6 +158,7 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
                                                          plan.args.m, plan.args.n, plan.final_d_is_fp32,
                                                          plan.final_accumulate, plan.final_bias);
         DG_CHECK_CUDA(cudaGetLastError());
+        count_kernel_launch();
     }
     return DG_OK;
 }

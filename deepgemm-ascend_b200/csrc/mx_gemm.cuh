@@ -65,6 +65,7 @@ struct GemmKernelArgs {
     uint32_t idesc;                   // tcgen05 instruction descriptor without the scale ids
     uint32_t tmem_cols, accum_stages;
     int32_t* status;
+    unsigned long long* trace;        // debugging aid: per-CTA timestamps (8 slots each), or nullptr
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -104,6 +105,12 @@ __device__ __forceinline__ bool wait_barrier_cluster(uint32_t bar, uint32_t pari
         }
     }
     return true;
+}
+
+// Slot meanings: 0 kernel entry (globaltimer ns), 1..7 clock64 at: entry, set-up done, first TMA issued,
+// first operands landed (MMA side), last MMA committed, first accumulator ready (epilogue side), epilogue done.
+__device__ __forceinline__ void trace_mark(const GemmKernelArgs& p, uint32_t slot) {
+    if (p.trace != nullptr) p.trace[blockIdx.x * 8 + slot] = slot == 0 ? global_timer_ns() : (unsigned long long)clock64();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -254,7 +261,8 @@ template <int kCtaGroup, int kMajorA, int kMajorB>
 __global__ void __launch_bounds__(kNumThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
-               const __grid_constant__ CUtensorMap tm_d, const GemmKernelArgs p) {
+               const __grid_constant__ CUtensorMap tm_d, const __grid_constant__ CUtensorMap tm_d_tail,
+               const GemmKernelArgs p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -279,20 +287,21 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t sfb_slabs = sfb_rows(p.block_n) / 128;
 
     if (threadIdx.x == 0) {
+        trace_mark(p, 0); trace_mark(p, 1);
         tmem_ptr_smem[1] = 0;
         for (uint32_t s = 0; s < num_stages; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(sf_full_bar(s), 32 * kCtaGroup);
+            mbar_init(sf_full_bar(s), kCtaGroup);           // one arrival per packer warp
             mbar_init(empty_bar(s), 1);
         }
         for (uint32_t e = 0; e < 2; ++e) {
             mbar_init(tmem_full_bar(e), 1);
-            mbar_init(tmem_empty_bar(e), kNumEpilogueWarps * 32 * kCtaGroup);
+            mbar_init(tmem_empty_bar(e), kNumEpilogueWarps * kCtaGroup);   // one arrival per epilogue warp
         }
         fence_mbar_init();
         tma_prefetch_desc(&tm_a); tma_prefetch_desc(&tm_b);
         tma_prefetch_desc(&tm_sfa); tma_prefetch_desc(&tm_sfb);
-        tma_prefetch_desc(&tm_d);
+        tma_prefetch_desc(&tm_d); tma_prefetch_desc(&tm_d_tail);
     }
     if (warp == 2) {
         tmem_alloc<kCtaGroup>(smem_u32((const void*)tmem_ptr_smem), p.tmem_cols);
@@ -302,6 +311,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     if constexpr (kCtaGroup == 2) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_ptr_smem[0];
+    if (threadIdx.x == 0) trace_mark(p, 2);
     // TMEM columns: accumulators first, then the scale factors of A and of B.
     const uint32_t tmem_sfa = tmem_base + p.accum_stages * p.block_n;
     const uint32_t tmem_sfb = tmem_sfa + 4;
@@ -312,7 +322,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             Scheduler<kCtaGroup> sched(p);
             Tile t;
             uint32_t stage = 0, phase = 0;
-            bool ok = true;
+            bool ok = true, first_issue = true;
             while (ok && sched.next(t)) {
                 for (uint32_t kb = t.kb_begin; kb < t.kb_end; ++kb) {
                     if (!(ok = wait_barrier(empty_bar(stage), phase ^ 1, ab, kStatusTimeoutProducer))) break;
@@ -339,6 +349,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                 (int32_t)t.row0, (int32_t)(kb * 2), (int32_t)t.row_z);
                     tma_load_3d(smem_base + L.sf_raw_b + stage * L.sfb_stage, &tm_sfb, bar,
                                 (int32_t)t.n0, (int32_t)(kb * 2), (int32_t)t.b_z);
+                    if (first_issue) { trace_mark(p, 3); first_issue = false; }
                     if (++stage == num_stages) { stage = 0; phase ^= 1; }
                 }
             }
@@ -370,6 +381,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     if (kCtaGroup == 2) ok = wait_barrier_cluster(sf_full_bar(stage), phase, ab, kStatusTimeoutMma);
                     else ok = wait_barrier(sf_full_bar(stage), phase, ab, kStatusTimeoutMma);
                     if (!ok) break;
+                    if (tile_iter == 0 && kb == t.kb_begin) trace_mark(p, 4);
                     tc_fence_after_sync();
                     // scales: smem -> TMEM (A: 128 rows = one slab; B: one slab per 128 columns)
                     utccp_32x128b_warpx4<kCtaGroup>(tmem_sfa, make_sf_desc(smem_base + L.sf_pack_a + stage * L.sfa_stage));
@@ -397,6 +409,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 if (!ok) break;
                 if constexpr (kCtaGroup == 2) umma_commit_2cta(tmem_full_bar(e), 3);
                 else umma_commit_1cta(tmem_full_bar(e));
+                trace_mark(p, 5);
                 ++tile_iter;
             }
         }
@@ -435,8 +448,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     pack_b[i * 32 + lane] = make_uint4(v[0], v[1], v[2], v[3]);
                 }
                 fence_proxy_async_smem();
-                if constexpr (kCtaGroup == 2) mbar_arrive_cluster(leader_sf_full0 + stage * 8);
-                else mbar_arrive(sf_full_bar(stage));
+                __syncwarp();
+                // one (possibly remote) arrival per warp: remote arrivals are slow enough to matter per K block
+                if (lane == 0) {
+                    if constexpr (kCtaGroup == 2) mbar_arrive_cluster(leader_sf_full0 + stage * 8);
+                    else mbar_arrive(sf_full_bar(stage));
+                }
                 if (++stage == num_stages) { stage = 0; phase ^= 1; }
             }
         }
@@ -455,6 +472,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const uint32_t e = p.accum_stages == 2 ? (tile_iter & 1u) : 0u;
             const uint32_t e_phase = p.accum_stages == 2 ? ((tile_iter >> 1) & 1u) : (tile_iter & 1u);
             if (!(ok = wait_barrier(tmem_full_bar(e), e_phase, ab, kStatusTimeoutEpilogue))) break;
+            if (tile_iter == 0 && threadIdx.x == 128) trace_mark(p, 6);
             tc_fence_after_sync();
             const uint32_t row = t.row0 + q * 32 + lane;       // row of D held by this thread
             const uint32_t taddr = tmem_base + ((q * 32u) << 16) + e * p.block_n;
@@ -478,15 +496,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                 }
                 if (p.epilogue_mode <= kEpiTmaReduce) {
-                    // stage a [32 rows x 128 B] box, 16-byte chunk c of row r at chunk (c ^ (r & 7))
-                    const uint32_t half = p.d_is_fp32 ? 0u : ((c0 / 32) & 1u);   // bf16: two 32-col groups per box
+                    // Stage a [32 rows x 128 B] box, 16-byte chunk c of row r at chunk (c ^ (r & 7)). A BF16 box holds two
+                    // 32-column groups; when block_n is an odd multiple of 32 the last group goes out alone as a
+                    // [32 rows x 64 B] box (64B swizzle: chunk c of row r at c ^ ((r >> 1) & 3)) through tm_d_tail.
+                    const uint32_t half = p.d_is_fp32 ? 0u : ((c0 / 32) & 1u);
+                    const bool tail = !p.d_is_fp32 && half == 0 && c0 + 32 >= p.block_n;
                     if (half == 0) {
                         // the buffer may still be read by the store issued two boxes ago
                         tma_store_wait_read<kNumStoreBufs - 1>();
                         __syncwarp();
                     }
-                    uint8_t* rowp = store_gen + buf * kStoreBufBytes + lane * 128;
+                    uint8_t* bufp = store_gen + buf * kStoreBufBytes;
                     if (p.d_is_fp32) {
+                        uint8_t* rowp = bufp + lane * 128;
                         #pragma unroll
                         for (uint32_t c = 0; c < 8; ++c)
                             *reinterpret_cast<uint4*>(rowp + ((c ^ (lane & 7u)) * 16)) =
@@ -501,21 +523,23 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                                                          __uint_as_float(v[c * 8 + i * 2 + 1]));
                                 w[i] = *reinterpret_cast<uint32_t*>(&h);
                             }
-                            const uint32_t chunk = half * 4 + c;
-                            *reinterpret_cast<uint4*>(rowp + ((chunk ^ (lane & 7u)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                            uint8_t* dst = tail ? bufp + lane * 64 + ((c ^ ((lane >> 1) & 3u)) * 16)
+                                                : bufp + lane * 128 + (((half * 4 + c) ^ (lane & 7u)) * 16);
+                            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     }
-                    const bool box_done = p.d_is_fp32 || half == 1 || c0 + 32 >= p.block_n;
+                    const bool box_done = p.d_is_fp32 || half == 1 || tail;
                     if (box_done) {
                         fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            const int32_t x = (int32_t)(t.n0 + (c0 / cols_per_box) * cols_per_box);
+                            const int32_t x = (int32_t)(t.n0 + (tail ? c0 : (c0 / cols_per_box) * cols_per_box));
                             const int32_t y = (int32_t)(t.row0 + q * 32);
+                            const CUtensorMap* map = tail ? &tm_d_tail : &tm_d;
                             if (p.epilogue_mode == kEpiTmaStore)
-                                tma_store_3d(&tm_d, store_base + buf * kStoreBufBytes, x, y, (int32_t)t.row_z);
+                                tma_store_3d(map, store_base + buf * kStoreBufBytes, x, y, (int32_t)t.row_z);
                             else
-                                tma_reduce_add_3d(&tm_d, store_base + buf * kStoreBufBytes, x, y, (int32_t)t.row_z);
+                                tma_reduce_add_3d(map, store_base + buf * kStoreBufBytes, x, y, (int32_t)t.row_z);
                             tma_store_commit();
                         }
                         buf ^= 1;
@@ -542,12 +566,16 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
             // this accumulator may be overwritten by the next-but-one tile
             tc_fence_before_sync();
-            if constexpr (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty0 + e * 8);
-            else mbar_arrive(tmem_empty_bar(e));
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty0 + e * 8);
+                else mbar_arrive(tmem_empty_bar(e));
+            }
             ++tile_iter;
         }
-        // shared memory must outlive the bulk stores that read it
-        tma_store_wait_all<0>();
+        // shared memory must outlive the bulk stores that read it; their global writes complete with the grid
+        tma_store_wait_read<0>();
+        if (threadIdx.x == 128) trace_mark(p, 7);
     }
 
     // ============================================================================ teardown

@@ -182,6 +182,7 @@ extern "C" int dg_transform_sf_launch(const void* src, int src_is_fp32,
     const uint32_t grid_x = (uint32_t)(tiles < 148ull * 16 ? tiles : 148ull * 16);
     transform_sf_kernel<<<dim3(grid_x, num_batches), kTsfThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
     DG_CHECK_CUDA(cudaGetLastError());
+    count_kernel_launch();
     return DG_OK;
 }
 
@@ -195,6 +196,7 @@ extern "C" int dg_pad_rows_launch(const void* src, uint64_t src_pitch_bytes, voi
     pad_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint8_t*>(src), src_pitch_bytes, static_cast<uint8_t*>(dst), dst_pitch_bytes, rows, row_bytes);
     DG_CHECK_CUDA(cudaGetLastError());
+    count_kernel_launch();
     return DG_OK;
 }
 

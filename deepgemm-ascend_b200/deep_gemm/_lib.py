@@ -63,6 +63,7 @@ _PROTOTYPES = {
     'dg_pad_rows_launch': (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p]),
     'dg_l2_flush_launch': (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
     'dg_device_status': (C.c_int, [C.POINTER(C.c_int32)]),
+    'dg_kernel_launch_count': (C.c_uint64, []),
     'dg_get_num_sms': (C.c_int, []),
     'dg_set_num_sms': (C.c_int, [C.c_int]),
     'dg_get_mk_alignment_for_contiguous_layout': (C.c_int, []),

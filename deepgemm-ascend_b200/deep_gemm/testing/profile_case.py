@@ -1,0 +1,61 @@
+"""Run one GEMM shape a few times: the small, self-ending workload to put under `ncu`.
+
+    python -m deep_gemm.testing.profile_case --m 4096 --n 7168 --k 16384 --iters 3 [--block-n 192 --cta-group 1 ...]
+
+Operands are random E4M3 codes with random UE8M0 scales already in the required layout, so only the GEMM kernel
+(and the split-K finalisation, when the tiling uses it) is launched.
+"""
+
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+import deep_gemm
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--m', type=int, default=4096)
+    ap.add_argument('--n', type=int, default=7168)
+    ap.add_argument('--k', type=int, default=16384)
+    ap.add_argument('--groups', type=int, default=0, help='>0: m-grouped contiguous with this many groups of m rows')
+    ap.add_argument('--iters', type=int, default=3)
+    ap.add_argument('--block-n', type=int, default=0)
+    ap.add_argument('--cta-group', type=int, default=0)
+    ap.add_argument('--split-k', type=int, default=0)
+    ap.add_argument('--stages', type=int, default=0)
+    ap.add_argument('--out', default='bf16', choices=['bf16', 'f32'])
+    args = ap.parse_args()
+
+    torch.manual_seed(0)
+    dev = torch.device('cuda', 0)
+    m, n, k, g = args.m, args.n, args.k, args.groups
+    k64 = (k + 63) // 64
+    rows = m * g if g else m
+
+    def codes(*shape):
+        return torch.randint(0, 120, shape, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+
+    def scales(lead, mn):
+        t = torch.randint(120, 130, (*lead, k64, mn), dtype=torch.int16, device=dev)
+        return (t | (t << 8)).transpose(-2, -1)
+
+    a, sfa = codes(rows, k), scales((), rows)
+    b, sfb = (codes(g, n, k), scales((g,), n)) if g else (codes(n, k), scales((), n))
+    d = torch.empty(rows, n, dtype=torch.bfloat16 if args.out == 'bf16' else torch.float32, device=dev)
+    config = {key: val for key, val in (('block_n', args.block_n), ('cta_group', args.cta_group),
+                                        ('split_k', args.split_k), ('num_stages', args.stages)) if val}
+    layout = torch.arange(1, g + 1, dtype=torch.int32, device=dev) * m if g else None
+    for _ in range(args.iters):
+        if g:
+            deep_gemm.m_grouped_fp8_gemm_nt_contiguous((a, sfa), (b, sfb), d, layout, config=config or None)
+        else:
+            deep_gemm.fp8_gemm_nt((a, sfa), (b, sfb), d, config=config or None)
+    torch.cuda.synchronize()
+    print('status', deep_gemm.device_status(), 'launches', args.iters)
+
+
+if __name__ == '__main__':
+    main()

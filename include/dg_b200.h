@@ -161,6 +161,10 @@ int dg_l2_flush_launch(void* buffer, size_t bytes, void* stream);
  * bounded wait that gave up. Reading it synchronises the device. */
 int dg_device_status(int32_t* out_status);
 
+/* Number of kernels this library has enqueued in this process (all devices, all threads). Benchmarks
+ * read it before and after a timed region to report how many of the library's kernels ran. */
+uint64_t dg_kernel_launch_count(void);
+
 /* Runtime knobs, csrc/apis/runtime.hpp:12-62 / csrc/jit/jit.hpp:18-76. */
 int dg_get_num_sms(void);
 int dg_set_num_sms(int num_sms);

@@ -95,6 +95,22 @@ def test_dense_forced_tilings():
     _dense(128, 512, 4096, config={'block_n': 128, 'split_k': 4}, seed=1)
 
 
+@pytest.mark.parametrize('bn', [32, 64, 96, 128, 160, 224, 256])
+def test_dense_cta_pair(bn):
+    """Two CTAs of a cluster share one 256-row UMMA; each loads its own A rows and half of the B tile."""
+    _dense(512, 768, 1024, config={'cta_group': 2, 'block_n': bn})
+    _dense(300, 500, 640, config={'cta_group': 2, 'block_n': bn}, out=torch.float32, acc=True)
+
+
+def test_dense_cta_pair_variants():
+    _dense(1024, 2048, 2048, config={'cta_group': 2, 'block_n': 224}, bias=True)
+    _dense(130, 257, 2048, config={'cta_group': 2, 'block_n': 96}, out=torch.float32)
+    _dense(512, 512, 1024, trans='nn', config={'cta_group': 2, 'block_n': 256})
+    _dense(512, 512, 1024, trans='tn', config={'cta_group': 2, 'block_n': 256})
+    _dense(512, 512, 1024, trans='tt', config={'cta_group': 2, 'block_n': 128})
+    _dense(4096, 2112, 1024, dist='normal', recipe=(1, 128, 128))      # heuristic picks the CTA pair here
+
+
 def test_golden_fixtures_through_the_api(golden):
     for name in ('dense_fp8_nt_bf16', 'dense_fp8_nt_acc_f32', 'dense_fp8_unaligned_k', 'dense_fp8_recipe_32_32',
                  'dense_fp8_nn_bias', 'dense_fp8_tn_alpha'):
@@ -116,7 +132,7 @@ def test_golden_fixtures_through_the_api(golden):
         assert_close(d, c['d'], name)
 
 
-def _grouped_case(sizes, n, k, trans_b=False, out=torch.bfloat16, seed=0):
+def _grouped_case(sizes, n, k, trans_b=False, out=torch.bfloat16, seed=0, config=None):
     seed_all(seed)
     total, psum = oracle.make_psum_layout(sizes, 256)
     g = len(sizes)
@@ -132,9 +148,9 @@ def _grouped_case(sizes, n, k, trans_b=False, out=torch.bfloat16, seed=0):
     d = torch.full((total, n), float('nan'), dtype=out, device='cuda')
     layout = torch.tensor(psum, dtype=torch.int32, device='cuda')
     fn = deep_gemm.m_grouped_fp8_gemm_nn_contiguous if trans_b else deep_gemm.m_grouped_fp8_gemm_nt_contiguous
-    fn((a.cuda(), sfa.cuda()), b_arg, d, layout)
+    fn((a.cuda(), sfa.cuda()), b_arg, d, layout, config=config)
     assert deep_gemm.device_status() == 0
-    assert_close(d, ref, f'm-grouped sizes={sizes} n={n} k={k} trans_b={trans_b}')
+    assert_close(d, ref, f'm-grouped sizes={sizes} n={n} k={k} trans_b={trans_b} config={config}')
     # padding rows are computed from zero rows of A and must be exactly zero
     for span in oracle.psum_padding_spans(psum, 256):
         assert (d[span] == 0).all(), 'padding rows of D must be exactly zero'
@@ -144,6 +160,8 @@ def _grouped_case(sizes, n, k, trans_b=False, out=torch.bfloat16, seed=0):
 def test_m_grouped_contiguous(sizes):
     _grouped_case(sizes, 384, 512)
     _grouped_case(sizes, 256, 768, trans_b=True, out=torch.float32)
+    _grouped_case(sizes, 384, 512, config={'cta_group': 1, 'block_n': 128})
+    _grouped_case(sizes, 384, 512, config={'cta_group': 2, 'block_n': 224})
 
 
 def test_m_grouped_golden(golden):
