@@ -171,6 +171,6 @@ def test_c_abi_validation_messages():
     assert lib.dg_gemm_dry_run(ctypes.byref(grouped), None) == L.DG_ERR_INVALID
     assert '256' in L.last_error()
     forced = L.GemmConfig()
-    forced.block_n, forced.cta_group, forced.split_k = 96, 1, 1
+    forced.block_n, forced.cta_group, forced.split_k = 100, 1, 1
     assert lib.dg_gemm_dry_run(ctypes.byref(_desc(128, 256, 256)), ctypes.byref(forced)) == L.DG_ERR_INVALID
     assert 'block_n' in L.last_error()
