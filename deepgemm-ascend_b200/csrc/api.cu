@@ -456,11 +456,61 @@ static int resolve_config(const dg_gemm_desc_t& d, const dg_gemm_config_t* in, d
     return complete_config(d, out);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Fixed split-K scratch for callers that cannot allocate (dg_gemm_launch_static_scratch)
+// ------------------------------------------------------------------------------------------------
+// Lives in every GPU's memory from module load to process exit. In host code the name below is only a handle for
+// cudaGetSymbolAddress: it is not a device address and must never be handed to a kernel or a memset directly.
+static __device__ __align__(256) float g_static_scratch[DG_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+// Device address of the array on the current device, looked up once per device.
+static int static_scratch_address(float** out) {
+    static std::mutex mu;
+    static float* addresses[64] = {};
+    int dev = 0;
+    DG_CHECK_CUDA(cudaGetDevice(&dev));
+    DG_CHECK_ARG(dev >= 0 && dev < 64, "device index out of range");
+    std::lock_guard<std::mutex> lock(mu);
+    if (addresses[dev] == nullptr) {
+        float* ptr = nullptr;
+        DG_CHECK_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_scratch));
+        DG_CHECK_ARG(ptr != nullptr, "cudaGetSymbolAddress returned a null scratch address");
+        addresses[dev] = ptr;
+    }
+    *out = addresses[dev];
+    return DG_OK;
+}
+
 }  // namespace dg
 
 using namespace dg;
 
 extern "C" {
+
+int dg_gemm_launch_static_scratch(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config, void* stream) {
+    DG_CHECK_ARG(desc != nullptr, "dg_gemm_launch_static_scratch: null descriptor");
+    if (int rc = validate(*desc)) return rc;
+    dg_gemm_config_t c;
+    if (int rc = resolve_config(*desc, config, c)) return rc;
+    float* scratch = nullptr;
+    size_t need = 0;
+    if (c.split_k > 1) {
+        need = (size_t)desc->m * align_u64(desc->n, 4) * sizeof(float);
+        if (need > DG_STATIC_SCRATCH_BYTES) {
+            set_last_error("split-K scratch of %zu bytes (m=%u, n=%u) exceeds the built-in %u bytes: pass a config with "
+                           "split_k = 1 or call dg_gemm_launch with a workspace", need, desc->m, desc->n,
+                           (unsigned)DG_STATIC_SCRATCH_BYTES);
+            return DG_ERR_WORKSPACE;
+        }
+        if (int rc = static_scratch_address(&scratch)) return rc;
+        // The array keeps the previous call's contents; the reduction must start from zero.
+        DG_CHECK_CUDA(cudaMemsetAsync(scratch, 0, need, static_cast<cudaStream_t>(stream)));
+    }
+    LaunchPlan plan;
+    if (int rc = build_plan(*desc, c, scratch, need, /*encode=*/true, plan)) return rc;
+    maybe_print_config(*desc, c);
+    return launch_gemm_kernel(plan, static_cast<cudaStream_t>(stream));
+}
 
 const char* dg_last_error(void) { return tls_error; }
 int dg_abi_version(void) { return DG_B200_ABI_VERSION; }

@@ -56,6 +56,7 @@ _PROTOTYPES = {
     'dg_gemm_workspace_bytes': (C.c_size_t, [C.POINTER(GemmDesc), C.POINTER(GemmConfig)]),
     'dg_gemm_launch': (C.c_int, [C.POINTER(GemmDesc), C.POINTER(GemmConfig), C.c_void_p, C.c_size_t, C.c_void_p]),
     'dg_gemm_dry_run': (C.c_int, [C.POINTER(GemmDesc), C.POINTER(GemmConfig)]),
+    'dg_gemm_launch_static_scratch': (C.c_int, [C.POINTER(GemmDesc), C.POINTER(GemmConfig), C.c_void_p]),
     'dg_transform_sf_launch': (C.c_int, [
         C.c_void_p, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32,
         C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
@@ -71,6 +72,7 @@ _PROTOTYPES = {
     'dg_abi_version': (C.c_int, []),
 }
 
+STATIC_SCRATCH_BYTES = 4 << 20
 EXPORTED_SYMBOLS = tuple(_PROTOTYPES)
 _lib = None
 

@@ -121,6 +121,29 @@ size_t dg_gemm_workspace_bytes(const dg_gemm_desc_t* desc, const dg_gemm_config_
 int dg_gemm_launch(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config,
                    void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * Split-K GEMM for callers that cannot allocate device memory. No counterpart in the reference.
+ *
+ * Some hosts of this library may not call cudaMalloc (or torch's allocator) around a GEMM: a runtime that has
+ * handed all device memory to its own pool, code running inside a region where allocation is forbidden, a plugin
+ * that only receives pointers. dg_gemm_launch asks exactly those callers for a zeroed workspace whenever the tiling
+ * splits K. This entry point is the same GEMM with the FP32 partial-sum scratch taken from a fixed array inside the
+ * library instead: DG_STATIC_SCRATCH_BYTES of device memory that every GPU which loads the library holds until the
+ * process exits. The caller passes only inputs and outputs.
+ *
+ *   - it allocates nothing and calls no allocating routine;
+ *   - problems whose scratch (m * round_up(n, 4) * 4 bytes, needed only when the tiling uses split_k > 1) exceeds
+ *     DG_STATIC_SCRATCH_BYTES are rejected with DG_ERR_WORKSPACE and a message that states both sizes; pass a
+ *     config with split_k = 1 or use dg_gemm_launch for those;
+ *   - the first call on each device looks up the array's device address (with that device current); make that first
+ *     call before any stream capture begins;
+ *   - all calls share the one array, which keeps whatever the previous call left: the part a call needs is cleared
+ *     on `stream` before the GEMM, and two calls whose GPU work overlaps (different streams, different threads) race
+ *     on it — order them on one stream.
+ */
+#define DG_STATIC_SCRATCH_BYTES (4u << 20)
+int dg_gemm_launch_static_scratch(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config, void* stream);
+
 /* Validate (desc, config) and build the launch plan without touching the device: the counterpart
  * of the reference's dry-run compile, csrc/jit_kernels/fp8_gemm.hpp:67-70. */
 int dg_gemm_dry_run(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config);
