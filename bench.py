@@ -248,7 +248,7 @@ def run_dense(args, rank, world, device):
     for s in range(args.steps):
         timed_step(events[s])
     barrier()
-    launches = lib.dg_kernel_launch_count() - launches0 - args.steps * len(cases)   # minus the untimed flush kernels
+    launches = lib.dg_kernel_launch_count() - launches0     # the untimed flush kernels are not counted by the library
     clocks = sampler.stop() if sampler else None
     status = deep_gemm.device_status()
 
@@ -336,6 +336,8 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--workload', default='dense', choices=['dense', 'grouped', 'masked'])
+    ap.add_argument('--experts-per-gpu', type=int, default=0, help='grouped / masked workloads (default 8 / 32)')
+    ap.add_argument('--gather', action='store_true', help='grouped workload, N > 1: also time an NCCL all-gather of D')
     args = ap.parse_args()
 
     rank = int(os.environ.get('RANK', '0'))

@@ -84,7 +84,10 @@ static int validate(const dg_gemm_desc_t& d) {
     DG_CHECK_ARG(d.b_dtype == DG_E4M3 || d.b_dtype == DG_E2M1X2, "Unsupported operand dtypes");
     DG_CHECK_ARG(!(d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E4M3), "Unsupported operand dtypes");
     DG_UNSUPPORTED(d.a_dtype == DG_E2M1X2, "FP4 x FP4 GEMM is not built in this library");
-    DG_UNSUPPORTED(d.b_dtype == DG_E2M1X2, "FP8 x FP4 GEMM is not built yet");
+    if (d.b_dtype == DG_E2M1X2) {
+        DG_CHECK_ARG(d.k % 2 == 0, "packed FP4 needs an even K");
+        DG_CHECK_ARG(d.major_b == DG_MAJOR_K || d.n % 2 == 0, "MN-major packed FP4 needs an even N");
+    }
     DG_CHECK_ARG(d.d_dtype == DG_BF16 || d.d_dtype == DG_F32, "D must be bf16 or fp32");
     DG_CHECK_ARG(d.major_a == DG_MAJOR_K || d.major_a == DG_MAJOR_MN, "bad major_a");
     DG_CHECK_ARG(d.major_b == DG_MAJOR_K || d.major_b == DG_MAJOR_MN, "bad major_b");
@@ -125,11 +128,11 @@ static uint32_t tmem_cols_for(uint32_t block_n, uint32_t accum_stages) {
     return cols;
 }
 
-static uint32_t max_stages_for(uint32_t block_n, uint32_t cta_group) {
+static uint32_t max_stages_for(uint32_t block_n, uint32_t cta_group, bool decode_b) {
     constexpr uint32_t kSmemCap = 227 * 1024;
     uint32_t best = 0;
     for (uint32_t s = 1; s <= kMaxStages; ++s)
-        if (make_smem_layout(block_n, s, cta_group).total <= kSmemCap) best = s;
+        if (make_smem_layout(block_n, s, cta_group, decode_b).total <= kSmemCap) best = s;
     return best;
 }
 
@@ -157,7 +160,8 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     const uint32_t accum_stages = (2 * c.block_n + 4 + 4 * (sfb_rows(c.block_n) / 128) <= 512) ? 2u : 1u;
     c.tmem_cols = tmem_cols_for(c.block_n, accum_stages);
     c.reserved[0] = accum_stages;
-    const uint32_t max_stages = max_stages_for(c.block_n, c.cta_group);
+    const bool decode_b = d.b_dtype == DG_E2M1X2;
+    const uint32_t max_stages = max_stages_for(c.block_n, c.cta_group, decode_b);
     if (c.num_stages == 0 || c.num_stages > max_stages) c.num_stages = max_stages;
     DG_CHECK_ARG(c.num_stages >= 1, "tile does not fit in shared memory");
     const uint32_t nkb = ceil_div_u32(d.k, kBlockK);
@@ -170,7 +174,7 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
         c.split_k = ceil_div_u32(nkb, per);
     }
     // one CTA per SM: keep the dynamic shared memory above half of the SM's capacity
-    const uint32_t need = make_smem_layout(c.block_n, c.num_stages, c.cta_group).total;
+    const uint32_t need = make_smem_layout(c.block_n, c.num_stages, c.cta_group, decode_b).total;
     c.smem_bytes = need < 120u * 1024 ? 120u * 1024 : need;
 
     uint32_t grid_units;
@@ -193,10 +197,12 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
 // 2 * block_n cycles for 128 x block_n x 128 (16384 FP8 flop per cycle per SM). Operand bytes enter an SM at about
 // 50 bytes per cycle (measured: 43-56 B/clk/SM across tilings, the L2-to-SM path), which is what bounds every tiling
 // that does not share operands across SMs; a CTA pair halves the B bytes per SM.
-static double k_block_cycles(uint32_t cta_group, uint32_t bn) {
+static double k_block_cycles(uint32_t cta_group, uint32_t bn, bool packed_b = false) {
     const double mma = 2.0 * bn;
-    const double ingest = (128.0 + (double)bn / cta_group) * 128.0 / 50.0;
-    return mma > ingest ? mma : ingest;
+    const double ingest = (128.0 + (double)bn / cta_group / (packed_b ? 2 : 1)) * 128.0 / 50.0;
+    const double decode = packed_b ? 2.5 * bn / cta_group : 0.0;       // four decoder warps, ~40 instructions per 16 codes
+    double t = mma > ingest ? mma : ingest;
+    return t > decode ? t : decode;
 }
 
 static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
@@ -216,7 +222,7 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     }
     const double hbm_bytes = (double)rows * d.k + (double)d.n * d.k * (grouped ? d.num_groups : 1) +
                              (double)rows * d.n * elem_size(d.d_dtype);
-    const double t_hbm = hbm_bytes / 6.4;          // ns at 6.4 TB/s
+    const double t_hbm = hbm_bytes / 6400.0;       // ns at 6.4 TB/s
 
     double best_cost = 1e30;
     uint32_t best_bn = 0, best_split = 1, best_cg = 1;
@@ -242,10 +248,11 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
                 const uint32_t kb_per = ceil_div_u32(nkb, split);
                 const bool single_accum = 2 * bn + 4 + 4 * (sfb_rows(bn) / 128) > 512;
                 const double t_epi = bn * (out_fp32 ? 8.0 : 6.0);
-                const double cycles = kb_per * k_block_cycles(cg, bn) + ((single_accum || waves == 1) ? t_epi : 0.0) + 700.0;
+                const double cycles = kb_per * k_block_cycles(cg, bn, d.b_dtype == DG_E2M1X2) + ((single_accum || waves == 1) ? t_epi : 0.0) + 700.0;
                 double cost = (double)waves * cycles / 1.8;                   // ns at ~1.8 GHz
-                if (split > 1) cost += 3000.0 + 0.004 * (double)d.m * d.n;    // reduce traffic + finalisation pass
-                if (cost < t_hbm) cost = t_hbm + 1e-3 * (double)waves * cycles;   // HBM-bound: then prefer the least work
+                if (cost < t_hbm) cost = t_hbm + 1e-3 * cost;     // HBM-bound: the cheaper schedule still wins ties
+                // second kernel (launch gap, FP32 read + zero + write) and the FP32 reduce traffic of the partials
+                if (split > 1) cost += 6000.0 + 0.004 * (double)d.m * d.n * split;
                 if (cost < best_cost * (1.0 - 1e-9) || (cost <= best_cost * (1.0 + 1e-9) && bn > best_bn)) {
                     best_cost = cost; best_bn = bn; best_split = split; best_cg = cg;
                 }
@@ -337,6 +344,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     plan.cta_group = (int)c.cta_group;
     plan.major_a = d.major_a;
     plan.major_b = d.major_b;
+    plan.decode_b = d.b_dtype == DG_E2M1X2;
     plan.num_ctas = c.num_ctas;
     plan.smem_bytes = c.smem_bytes;
 
@@ -377,7 +385,22 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
         }
     }
     // ---- B
-    {
+    if (plan.decode_b) {
+        // packed E2M1, fetched as plain bytes (no swizzle) and decoded in shared memory
+        if (d.major_b == DG_MAJOR_K) {
+            const uint64_t gs = nonzero_stride(d.group_stride_b, (uint64_t)d.n * d.outer_stride_b);
+            const uint64_t dims[3] = {d.k / 2, d.n, groups};
+            const uint64_t str[2] = {d.outer_stride_b, gs};
+            const uint32_t box[3] = {kBlockK / 2, load_n, 1};
+            if (int rc = encode_map(&plan.tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE, "B (packed FP4)")) return rc;
+        } else {
+            const uint64_t gs = nonzero_stride(d.group_stride_b, (uint64_t)d.k * d.outer_stride_b);
+            const uint64_t dims[3] = {d.n / 2, d.k, groups};
+            const uint64_t str[2] = {d.outer_stride_b, gs};
+            const uint32_t box[3] = {load_n / 2, kBlockK, 1};
+            if (int rc = encode_map(&plan.tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE, "B (packed FP4)")) return rc;
+        }
+    } else {
         if (d.major_b == DG_MAJOR_K) {
             const uint64_t gs = nonzero_stride(d.group_stride_b, (uint64_t)d.n * d.outer_stride_b);
             const uint64_t dims[3] = {d.k, d.n, groups};

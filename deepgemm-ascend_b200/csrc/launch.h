@@ -12,6 +12,7 @@ struct LaunchPlan {
     GemmKernelArgs args;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d, tm_d_tail;
     int cta_group, major_a, major_b;
+    bool decode_b;               // B is packed E2M1 and is decoded to E4M3 in shared memory
     uint32_t num_ctas, smem_bytes;
     // split-K finalisation (workspace -> D)
     bool finalize;

@@ -47,12 +47,14 @@ __global__ void splitk_finalize_kernel(float* __restrict__ ws, uint64_t ws_strid
 using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
                           const CUtensorMap, const CUtensorMap, const GemmKernelArgs);
 
-static KernelFn pick_kernel(int cta_group, int major_a, int major_b) {
-    static const KernelFn table[2][2][2] = {
-        {{mx_gemm_kernel<1, 0, 0>, mx_gemm_kernel<1, 0, 1>}, {mx_gemm_kernel<1, 1, 0>, mx_gemm_kernel<1, 1, 1>}},
-        {{mx_gemm_kernel<2, 0, 0>, mx_gemm_kernel<2, 0, 1>}, {mx_gemm_kernel<2, 1, 0>, mx_gemm_kernel<2, 1, 1>}},
+static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode_b) {
+    static const KernelFn table[2][2][2][2] = {
+        {{{mx_gemm_kernel<1, 0, 0, false>, mx_gemm_kernel<1, 0, 0, true>}, {mx_gemm_kernel<1, 0, 1, false>, mx_gemm_kernel<1, 0, 1, true>}},
+         {{mx_gemm_kernel<1, 1, 0, false>, mx_gemm_kernel<1, 1, 0, true>}, {mx_gemm_kernel<1, 1, 1, false>, mx_gemm_kernel<1, 1, 1, true>}}},
+        {{{mx_gemm_kernel<2, 0, 0, false>, mx_gemm_kernel<2, 0, 0, true>}, {mx_gemm_kernel<2, 0, 1, false>, mx_gemm_kernel<2, 0, 1, true>}},
+         {{mx_gemm_kernel<2, 1, 0, false>, mx_gemm_kernel<2, 1, 0, true>}, {mx_gemm_kernel<2, 1, 1, false>, mx_gemm_kernel<2, 1, 1, true>}}},
     };
-    return table[cta_group - 1][major_a][major_b];
+    return table[cta_group - 1][major_a][major_b][decode_b ? 1 : 0];
 }
 
 int get_status_pointer(int32_t** out) {
@@ -73,7 +75,7 @@ int get_status_pointer(int32_t** out) {
 }
 
 int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
-    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b);
+    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b);
     // The attribute is per device and per function; setting it is cheap, so do it on every launch.
     DG_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem_bytes));
 
@@ -91,7 +93,7 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
 
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(plan.num_ctas, 1, 1);
-    cfg.blockDim = dim3(kNumThreads, 1, 1);
+    cfg.blockDim = dim3(plan.decode_b ? kNumThreadsDecode : kNumThreads, 1, 1);
     cfg.dynamicSmemBytes = plan.smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];

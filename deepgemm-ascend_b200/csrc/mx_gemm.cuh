@@ -29,6 +29,8 @@ constexpr uint32_t kBlockM = 128;        // rows of A per CTA
 constexpr uint32_t kBlockK = 128;        // K elements (bytes of FP8) per pipeline stage
 constexpr uint32_t kUmmaK = 32;          // K per tcgen05.mma for 8-bit operands
 constexpr uint32_t kNumThreads = 256;
+constexpr uint32_t kNumDecodeWarps = 4;                    // extra warps 8..11 when B is packed FP4
+constexpr uint32_t kNumThreadsDecode = kNumThreads + kNumDecodeWarps * 32;
 constexpr uint32_t kNumEpilogueWarps = 4;
 constexpr uint32_t kStoreBoxRows = 32;   // each epilogue warp stores its own 32 rows
 constexpr uint32_t kStoreBufBytes = kStoreBoxRows * 128;  // one 128B-swizzled box
@@ -230,19 +232,23 @@ __host__ __device__ __forceinline__ uint32_t sfb_rows(uint32_t block_n) { return
 
 // Shared-memory carve-up, computed identically on host and device.
 struct SmemLayout {
-    uint32_t store_bufs, a, b, sf_raw_a, sf_raw_b, sf_pack_a, sf_pack_b, barriers, total;
-    uint32_t a_stage, b_stage, sfa_stage, sfb_stage;
+    uint32_t store_bufs, a, b, b_raw, sf_raw_a, sf_raw_b, sf_pack_a, sf_pack_b, barriers, total;
+    uint32_t a_stage, b_stage, b_raw_stage, sfa_stage, sfb_stage;
 };
-__host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_t num_stages, uint32_t cta_group) {
+__host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_t num_stages, uint32_t cta_group,
+                                                       bool decode_b = false) {
     SmemLayout L;
     L.a_stage = kBlockM * kBlockK;
     L.b_stage = (block_n / cta_group) * kBlockK;
+    L.b_raw_stage = decode_b ? (block_n / cta_group) * (kBlockK / 2) : 0;    // packed FP4: two codes per byte
     L.sfa_stage = 128 * 4;
     L.sfb_stage = sfb_rows(block_n) * 4;
     uint32_t off = 0;
     L.store_bufs = off; off += kNumEpilogueWarps * kNumStoreBufs * kStoreBufBytes;
     L.a = off; off += num_stages * L.a_stage;
     L.b = off; off += num_stages * L.b_stage;
+    off = (off + 1023u) & ~1023u;
+    L.b_raw = off; off += num_stages * L.b_raw_stage;
     off = (off + 1023u) & ~1023u;
     L.sf_raw_a = off; off += num_stages * L.sfa_stage;
     L.sf_raw_b = off; off += num_stages * L.sfb_stage;
@@ -254,11 +260,36 @@ __host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_
 }
 
 // ------------------------------------------------------------------------------------------------
+// Packed E2M1 -> E4M3 (exact: every E2M1 value is an E4M3 value). Same byte map as the reference's vector-core
+// decoder, deep_gemm/include/deep_gemm/fp8_dequant_gemm.hpp:24-38: magnitude 0 -> 0x00, 1 -> 0x30,
+// m >= 2 -> 0x30 + 4m, sign bit 3 -> bit 7. Four codes (the low 16 bits of `codes`) become four bytes.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t selector) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
+    return d;
+}
+__device__ __forceinline__ uint32_t e2m1x4_to_e4m3x4(uint32_t codes) {
+    // byte permute as an 8-entry table look-up: selector nibble i picks the byte for code i
+    const uint32_t mag = prmt_b32(0x3C383000u, 0x4C484440u, codes & 0x7777u);
+    // prmt.b32 with bit 3 of a selector nibble set replicates the MSB of the selected byte over the result byte:
+    // 0x80 becomes 0xFF for a negative code and stays 0x80 otherwise, so bit 0 of each byte is the sign
+    const uint32_t sgn = prmt_b32(0x80808080u, 0x80808080u, codes & 0xFFFFu);
+    return mag | ((sgn << 7) & 0x80808080u);
+}
+// Eight bytes (16 codes, low nibble first) -> 16 E4M3 bytes.
+__device__ __forceinline__ uint4 e2m1x16_to_e4m3x16(uint2 packed) {
+    return make_uint4(e2m1x4_to_e4m3x4(packed.x), e2m1x4_to_e4m3x4(packed.x >> 16),
+                      e2m1x4_to_e4m3x4(packed.y), e2m1x4_to_e4m3x4(packed.y >> 16));
+}
+
+// ------------------------------------------------------------------------------------------------
 // The kernel
 // ------------------------------------------------------------------------------------------------
 // kMajorA / kMajorB: 0 = K-major, 1 = MN-major operand in global memory.
-template <int kCtaGroup, int kMajorA, int kMajorB>
-__global__ void __launch_bounds__(kNumThreads, 1)
+// kDecodeB: B is packed E2M1 in global memory; warps 8..11 decode each stage into the E4M3 tile the MMA reads.
+template <int kCtaGroup, int kMajorA, int kMajorB, bool kDecodeB>
+__global__ void __launch_bounds__(kDecodeB ? kNumThreadsDecode : kNumThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
                const __grid_constant__ CUtensorMap tm_d, const __grid_constant__ CUtensorMap tm_d_tail,
@@ -266,7 +297,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const SmemLayout L = make_smem_layout(p.block_n, p.num_stages, kCtaGroup);
+    const SmemLayout L = make_smem_layout(p.block_n, p.num_stages, kCtaGroup, kDecodeB);
 
     const uint32_t warp = threadIdx.x / 32, lane = lane_id();
     const uint32_t cta_rank = kCtaGroup == 2 ? cluster_ctarank() : 0u;
@@ -291,7 +322,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         tmem_ptr_smem[1] = 0;
         for (uint32_t s = 0; s < num_stages; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(sf_full_bar(s), kCtaGroup);           // one arrival per packer warp
+            // one arrival per warp that prepares the stage for the MMA: the packer, and the decoders if any
+            mbar_init(sf_full_bar(s), kCtaGroup * (1 + (kDecodeB ? kNumDecodeWarps : 0)));
             mbar_init(empty_bar(s), 1);
         }
         for (uint32_t e = 0; e < 2; ++e) {
@@ -327,7 +359,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 for (uint32_t kb = t.kb_begin; kb < t.kb_end; ++kb) {
                     if (!(ok = wait_barrier(empty_bar(stage), phase ^ 1, ab, kStatusTimeoutProducer))) break;
                     const uint32_t bar = full_bar(stage);
-                    const uint32_t bytes = L.a_stage + load_n * kBlockK + L.sfa_stage + L.sfb_stage;
+                    const uint32_t bytes = L.a_stage + (kDecodeB ? L.b_raw_stage : load_n * kBlockK) + L.sfa_stage + L.sfb_stage;
                     mbar_arrive_expect_tx(bar, bytes);
                     const uint32_t sa = smem_base + L.a + stage * L.a_stage;
                     const uint32_t sb = smem_base + L.b + stage * L.b_stage;
@@ -338,7 +370,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         tma_load_3d(sa, &tm_a, bar, (int32_t)t.row0, k0, (int32_t)t.row_z);
                     }
                     const uint32_t bn0 = t.n0 + cta_rank * load_n;
-                    if constexpr (kMajorB == 0) {
+                    if constexpr (kDecodeB) {
+                        // packed bytes, unswizzled: [load_n rows][64 B of K] or [128 K rows][load_n / 2 B of N]
+                        const uint32_t sraw = smem_base + L.b_raw + stage * L.b_raw_stage;
+                        if constexpr (kMajorB == 0) tma_load_3d(sraw, &tm_b, bar, k0 / 2, (int32_t)bn0, (int32_t)t.b_z);
+                        else tma_load_3d(sraw, &tm_b, bar, (int32_t)(bn0 / 2), k0, (int32_t)t.b_z);
+                    } else if constexpr (kMajorB == 0) {
                         tma_load_3d(sb, &tm_b, bar, k0, (int32_t)bn0, (int32_t)t.b_z);
                     } else {
                         // one box per 128-column atom: [atom][block_k rows][128 B]
@@ -457,7 +494,48 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 if (++stage == num_stages) { stage = 0; phase ^= 1; }
             }
         }
-    } else if (warp >= 4) {
+    } else if (kDecodeB && warp >= 8) {
+        // ======================================================================== FP4 decoders
+        // One work item = 8 packed bytes (16 codes) -> one 16-byte chunk of the swizzled E4M3 tile.
+        Scheduler<kCtaGroup> sched(p);
+        Tile t;
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        const uint32_t tid = threadIdx.x - 256;                         // 0..127
+        const uint32_t leader_sf_full0 = kCtaGroup == 2 ? mapa_shared(sf_full_bar(0), 0) : sf_full_bar(0);
+        while (ok && sched.next(t)) {
+            for (uint32_t kb = t.kb_begin; kb < t.kb_end; ++kb) {
+                if (!(ok = wait_barrier(full_bar(stage), phase, ab, kStatusTimeoutDecoder))) break;
+                const uint8_t* raw = smem_gen + L.b_raw + stage * L.b_raw_stage;
+                uint8_t* tile = smem_gen + L.b + stage * L.b_stage;
+                const uint32_t items = load_n * (kBlockK / 16);
+                if constexpr (kMajorB == 0) {
+                    // raw [n][64 B]; tile row n = 128 B, chunk c at position c ^ (n & 7)
+                    for (uint32_t i = tid; i < items; i += kNumDecodeWarps * 32) {
+                        const uint32_t n = i >> 3, c = i & 7u;
+                        const uint2 v = *reinterpret_cast<const uint2*>(raw + n * 64 + c * 8);
+                        *reinterpret_cast<uint4*>(tile + n * 128 + ((c ^ (n & 7u)) * 16)) = e2m1x16_to_e4m3x16(v);
+                    }
+                } else {
+                    // raw [k][load_n / 2 B]; tile [atom of 128 n][k][128 B], chunk c at position c ^ (k & 7)
+                    const uint32_t raw_pitch = load_n / 2;
+                    for (uint32_t i = tid; i < items; i += kNumDecodeWarps * 32) {
+                        const uint32_t c = i & 7u, k = (i >> 3) & (kBlockK - 1), atom = i >> 10;
+                        const uint2 v = *reinterpret_cast<const uint2*>(raw + k * raw_pitch + atom * 64 + c * 8);
+                        *reinterpret_cast<uint4*>(tile + atom * (kBlockK * 128) + k * 128 + ((c ^ (k & 7u)) * 16)) =
+                            e2m1x16_to_e4m3x16(v);
+                    }
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (kCtaGroup == 2) mbar_arrive_cluster(leader_sf_full0 + stage * 8);
+                    else mbar_arrive(sf_full_bar(stage));
+                }
+                if (++stage == num_stages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp >= 4 && warp < 8) {
         // ======================================================================== epilogue
         const uint32_t q = warp - 4;                         // TMEM lane quadrant == warp index % 4
         Scheduler<kCtaGroup> sched(p);

@@ -1,0 +1,159 @@
+"""MoE workloads of the benchmark: m-grouped contiguous (psum layout) and m-grouped masked FP8 GEMM.
+
+Experts are sharded across ranks (`sharding.py`); each rank runs the single-GPU kernel on its own experts, no
+data-path collective. `--gather` times an NCCL all-gather of the outputs separately.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import json
+import random
+
+import torch
+
+from .. import _api
+from .. import _lib as L
+from .bench import l2_flush_buffer
+from .sharding import shard_psum_layout
+
+NK_LIST = [(4096, 7168), (7168, 2048)]
+
+
+def _codes(shape, device, gen):
+    raw = torch.randint(0, 254, shape, dtype=torch.uint8, device=device, generator=gen)
+    raw += (raw >= 0x7F).to(torch.uint8)
+    return raw.view(torch.float8_e4m3fn)
+
+
+def _scales(lead, mn, k, device, gen):
+    k64 = (k + 63) // 64
+    e = torch.randint(118, 121, (*lead, k64, mn), dtype=torch.int16, device=device, generator=gen)
+    return (e | (e << 8)).transpose(-2, -1)
+
+
+class GroupedCase:
+    def __init__(self, sizes, n, k, device, seed, masked_max_m=0):
+        gen = torch.Generator(device=device).manual_seed(seed)
+        self.n, self.k, g = n, k, len(sizes)
+        self.valid_rows = sum(sizes)
+        if masked_max_m:
+            rows_shape, self.rows = (g, masked_max_m), g * masked_max_m
+            layout = sizes
+            gemm_type = L.GEMM_M_GROUPED_MASKED
+        else:
+            local = shard_psum_layout(sizes, 1, 0)
+            rows_shape, self.rows = (local['rows'],), local['rows']
+            layout = local['psum']
+            gemm_type = L.GEMM_M_GROUPED_PSUM
+        self.a = _codes((*rows_shape, k), device, gen)
+        self.b = _codes((g, n, k), device, gen)
+        self.sfa = _scales(rows_shape[:-1], rows_shape[-1], k, device, gen)
+        self.sfb = _scales((g,), n, k, device, gen)
+        self.d = torch.empty((*rows_shape, n), dtype=torch.bfloat16, device=device)
+        self.layout = torch.tensor(layout, dtype=torch.int32, device=device)
+        self.desc = _api._run_gemm(gemm_type, self.a, self.b, self.d, None, _api.Identity(), self.sfa, self.sfb,
+                                   (1, 1, 32), None, None, self.layout, 'nk', False,
+                                   expected_m=max(1, self.valid_rows // g))
+        self.flops = 2.0 * self.valid_rows * n * k
+        k64 = (k + 63) // 64
+        self.bytes = self.valid_rows * (k + k64 * 2 + n * 2) + g * n * (k + k64 * 2)
+        cfg = L.GemmConfig()
+        L.check(L.lib().dg_select_config(ctypes.byref(self.desc), ctypes.byref(cfg)))
+        self.config = cfg.as_dict()
+
+    def launch(self, lib, sptr):
+        rc = lib.dg_gemm_launch(ctypes.byref(self.desc), None, None, 0, sptr)
+        if rc:
+            raise RuntimeError(L.last_error())
+
+
+def run(args, rank, world, device):
+    lib = L.lib()
+    stream = torch.cuda.current_stream(device)
+    sptr = stream.cuda_stream
+    flush = l2_flush_buffer(device)
+    masked = args.workload == 'masked'
+    per_rank = getattr(args, 'experts_per_gpu', 0) or (32 if masked else 8)
+    random.seed(1234)                       # the global problem is the same on every rank
+    g_total = per_rank * world
+    if masked:
+        sizes = [random.randint(0, 256) for _ in range(g_total)]
+    else:
+        sizes = [int(random.uniform(0.7, 1.3) * 8192) for _ in range(g_total)]
+    mine = sizes[rank * per_rank:(rank + 1) * per_rank]
+    cases = [GroupedCase(mine, n, k, device, seed=100 * rank + i, masked_max_m=256 if masked else 0)
+             for i, (n, k) in enumerate(NK_LIST)]
+    torch.cuda.synchronize(device)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(device)
+
+    def step(events):
+        for ci, c in enumerate(cases):
+            L.check(lib.dg_l2_flush_launch(flush.data_ptr(), flush.numel(), sptr))
+            if events is not None:
+                events[ci][0].record(stream)
+            c.launch(lib, sptr)
+            if events is not None:
+                events[ci][1].record(stream)
+
+    for _ in range(max(args.warmup, 3)):
+        step(None)
+    barrier()
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in cases]
+          for _ in range(args.steps)]
+    launches0 = lib.dg_kernel_launch_count()
+    for s in range(args.steps):
+        step(ev[s])
+    barrier()
+    launches = lib.dg_kernel_launch_count() - launches0
+    per_case_us = [sum(ev[s][ci][0].elapsed_time(ev[s][ci][1]) for s in range(args.steps)) / args.steps * 1e3
+                   for ci in range(len(cases))]
+    step_ms = torch.tensor([sum(per_case_us) / 1e3], dtype=torch.float64, device=device)
+    flops = torch.tensor([sum(c.flops for c in cases)], dtype=torch.float64, device=device)
+    gather_ms = None
+    if world > 1:
+        torch.distributed.all_reduce(step_ms, op=torch.distributed.ReduceOp.MAX)
+        torch.distributed.all_reduce(flops, op=torch.distributed.ReduceOp.SUM)
+        if getattr(args, 'gather', False):
+            # outputs have rank-dependent row counts: gather equal-sized padded chunks
+            rows = torch.tensor([cases[0].rows], dtype=torch.int64, device=device)
+            torch.distributed.all_reduce(rows, op=torch.distributed.ReduceOp.MAX)
+            chunk = torch.zeros(int(rows.item()), cases[0].n, dtype=torch.bfloat16, device=device)
+            chunk[:cases[0].rows].copy_(cases[0].d.reshape(-1, cases[0].n))
+            out = torch.empty(world * chunk.size(0), chunk.size(1), dtype=torch.bfloat16, device=device)
+            torch.distributed.all_gather_into_tensor(out, chunk)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            torch.distributed.all_gather_into_tensor(out, chunk)
+            e1.record(stream)
+            barrier()
+            g_ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+            torch.distributed.all_reduce(g_ms, op=torch.distributed.ReduceOp.MAX)
+            gather_ms = float(g_ms.item())
+    status = _api.device_status()
+    if rank != 0:
+        return
+    value = float(flops.item()) / (float(step_ms.item()) * 1e-3) / 1e12
+    line = {
+        'metric': 'fp8_block_scaled_gemm_tflops', 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world,
+        'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': float(step_ms.item()),
+        'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+        'dtype': 'fp8_e4m3 x ue8m0, fp32 accumulate', 'data': 'synthetic',
+        'config': {'workload': ('m-grouped masked FP8 GEMM, %d experts x max_m 256 per GPU' if masked else
+                                'm-grouped contiguous FP8 GEMM (psum layout), %d experts per GPU, m ~ U(0.7,1.3) x 8192')
+                               % per_rank + ', (N,K) in ' + str(NK_LIST) + ', BF16 out',
+                   'sharding': 'experts, contiguous blocks per rank, no data-path collective',
+                   'l2': 'flushed before every GEMM, untimed', 'flops': 'valid rows only'},
+        'gpu_launches': int(launches), 'device_status': status,
+        'shapes': [{'rows': c.rows, 'valid_rows': c.valid_rows, 'n': c.n, 'k': c.k, 'us': round(per_case_us[i], 1),
+                    'tflops': round(c.flops / per_case_us[i] / 1e6, 1), 'gbs': round(c.bytes / per_case_us[i] / 1e3, 1),
+                    'block_n': c.config['block_n'], 'cta_group': c.config['cta_group']} for i, c in enumerate(cases)],
+    }
+    if gather_ms is not None:
+        line['gather_ms'] = gather_ms
+    print(json.dumps(line), flush=True)

@@ -36,6 +36,22 @@ def uniform_fp8(shape, gran, sf_choices=(2.0 ** -9, 2.0 ** -8, 2.0 ** -7)):
     return data, sf, oracle.dequantize(data.float(), sf, gran[0], gran[1])
 
 
+def uniform_fp4(mn, k, gran, mn_major: bool, sf_choices=(0.25, 0.5, 1.0)):
+    """Uniform random packed E2M1 (tests/generators.py:155-164): returns (packed int8 whose logical shape is
+    [MN, K] with two codes per byte along the contiguous axis, sf fp32, dequantised fp32 [MN, K]).
+    K-major: tensor [MN, K/2]; MN-major: tensor of shape [MN/2, K] with strides (1, MN/2)."""
+    if mn_major:
+        storage = torch.randint(-128, 128, (k, mn // 2), dtype=torch.int8)
+        data = storage.transpose(0, 1)
+        vals = oracle.decode_e2m1_packed(storage, axis=-1).transpose(0, 1)
+    else:
+        data = torch.randint(-128, 128, (mn, k // 2), dtype=torch.int8)
+        vals = oracle.decode_e2m1_packed(data, axis=-1)
+    table = torch.tensor(sf_choices, dtype=torch.float32)
+    sf = table[torch.randint(0, len(sf_choices), (oracle.ceil_div(mn, gran[0]), oracle.ceil_div(k, gran[1])))].contiguous()
+    return data, sf, oracle.dequantize(vals, sf, gran[0], gran[1])
+
+
 def normal_fp8(shape, gran):
     x = torch.randn(shape, dtype=torch.float32)
     if x.dim() == 2:

@@ -9,7 +9,7 @@ import torch
 
 import deep_gemm
 import oracle
-from helpers import assert_close, normal_fp8, seed_all, uniform_fp8, with_major
+from helpers import assert_close, normal_fp8, seed_all, uniform_fp4, uniform_fp8, with_major
 
 pytestmark = pytest.mark.gpu
 
@@ -109,6 +109,60 @@ def test_dense_cta_pair_variants():
     _dense(512, 512, 1024, trans='tn', config={'cta_group': 2, 'block_n': 256})
     _dense(512, 512, 1024, trans='tt', config={'cta_group': 2, 'block_n': 128})
     _dense(4096, 2112, 1024, dist='normal', recipe=(1, 128, 128))      # heuristic picks the CTA pair here
+
+
+def _mixed(m, n, k, *, trans='nn', recipe_a=(1, 32), out=torch.bfloat16, config=None, bias=False, seed=0):
+    """FP8 A times packed-FP4 B. 'nn': B is given as [K, N/2] (MN-major codes); 'nt': B is [N, K/2]."""
+    seed_all(seed)
+    a, sfa, a_ref = uniform_fp8((m, k), recipe_a)
+    b, sfb, b_ref = uniform_fp4(n, k, (1, 32), mn_major=trans[1] == 'n')
+    c = torch.randn(1, n).to(out) if bias else None
+    ref = oracle.gemm_ref(a_ref, b_ref, out, bias=c)
+    b_dev, sfb_dev = b.cuda(), sfb.cuda()
+    b_arg = (b_dev.transpose(0, 1), sfb_dev.transpose(0, 1)) if trans[1] == 'n' else (b_dev, sfb_dev)
+    d = torch.full((m, n), float('nan'), dtype=out, device='cuda')
+    getattr(deep_gemm, f'fp8_fp4_gemm_{trans}')((a.cuda(), sfa.cuda()), b_arg, d, c=c.cuda() if bias else None,
+                                                recipe_a=recipe_a, recipe_b=(1, 32), config=config)
+    assert deep_gemm.device_status() == 0
+    return assert_close(d, ref, f'fp8xfp4 {trans} {m}x{n}x{k} recipe_a={recipe_a} config={config}')
+
+
+@pytest.mark.parametrize('trans', ['nn', 'nt'])
+def test_mixed_fp8_fp4(trans):
+    _mixed(128, 256, 512, trans=trans)
+    _mixed(384, 768, 1024, trans=trans, out=torch.float32)
+    _mixed(300, 520, 640, trans=trans, bias=True)
+    _mixed(512, 512, 2048, trans=trans, recipe_a=(1, 128))       # per-128 scales on A, per-32 on B (BASELINE config 3)
+    _mixed(512, 512, 1024, trans=trans, config={'cta_group': 2, 'block_n': 256})
+    _mixed(512, 1024, 1024, trans=trans, config={'cta_group': 1, 'block_n': 128})
+
+
+def test_mixed_fp8_fp4_nt_narrow_tiles():
+    for bn in (32, 96, 224):
+        _mixed(256, 672, 768, trans='nt', config={'cta_group': 1, 'block_n': bn})
+    _mixed(512, 448, 768, trans='nt', config={'cta_group': 2, 'block_n': 224})
+
+
+def test_mixed_golden(golden):
+    for name, trans in (('dense_fp8fp4_nn', 'nn'), ('dense_fp8fp4_nt', 'nt')):
+        c = golden[name]
+        a = c['a'].view(torch.float8_e4m3fn).cuda()
+        if trans == 'nn':      # fixture holds the logical [N/2, K] view made contiguous; storage is [K, N/2]
+            b_arg = (c['b'].transpose(0, 1).contiguous().cuda(), c['sfb'].cuda().transpose(0, 1))
+        else:
+            b_arg = (c['b'].cuda(), c['sfb'].cuda())
+        d = torch.zeros_like(c['d']).cuda()
+        getattr(deep_gemm, f'fp8_fp4_gemm_{trans}')((a, c['sfa'].cuda()), b_arg, d)
+        assert_close(d, c['d'], name)
+
+
+def test_fp4_operand_rules():
+    a = torch.zeros(128, 64, dtype=torch.int8, device='cuda')
+    b = torch.zeros(128, 128, dtype=torch.float8_e4m3fn, device='cuda')
+    sf = torch.ones(128, 4, dtype=torch.float32, device='cuda')
+    d = torch.zeros(128, 128, dtype=torch.bfloat16, device='cuda')
+    with pytest.raises(RuntimeError, match='Unsupported operand dtypes'):
+        deep_gemm.fp8_fp4_gemm_nt((a, sf), (b, sf), d)
 
 
 def test_golden_fixtures_through_the_api(golden):
