@@ -204,7 +204,7 @@ def run_reference(args, rank, world):
         'e2e': {'value': value, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ----------------------------------------------------------------------------------------------------------------
@@ -267,15 +267,36 @@ def run_dense(args, rank, world, device):
         c.pin_host_copies()
     e2e_steps = max(1, min(args.steps, 5))
 
+    # Three streams so that the PCIe link runs in both directions while the GPU computes: inputs of shape i+1 go up
+    # while shape i is multiplied and the result of shape i-1 comes down. Every byte still crosses inside the timed
+    # region, and each GEMM is the public API call on host-provided data.
+    s_in, s_mm, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device), torch.cuda.Stream(device)
+    done_mm = [None] * len(cases)      # last GEMM that read case i's device inputs / wrote its D
+    done_out = [None] * len(cases)     # last D2H copy of case i's D
+
     def e2e_step():
-        for c in cases:
-            a = c.h_a.to(device, non_blocking=True).view(torch.float8_e4m3fn)
-            b = c.h_b.to(device, non_blocking=True).view(torch.float8_e4m3fn)
-            sfa = c.h_sfa.to(device, non_blocking=True)
-            sfb = c.h_sfb.to(device, non_blocking=True)
-            d = torch.empty(c.m, c.n, dtype=torch.bfloat16, device=device)
-            deep_gemm.fp8_gemm_nt((a, sfa), (b, sfb), d, recipe=(1, 128, 128))
-            c.h_d.copy_(d, non_blocking=True)
+        for i, c in enumerate(cases):
+            with torch.cuda.stream(s_in):
+                if done_mm[i] is not None:
+                    s_in.wait_event(done_mm[i])          # do not overwrite inputs a previous GEMM still reads
+                c.a.view(torch.uint8).copy_(c.h_a, non_blocking=True)
+                c.b.view(torch.uint8).copy_(c.h_b, non_blocking=True)
+                c.sfa32.copy_(c.h_sfa, non_blocking=True)
+                c.sfb32.copy_(c.h_sfb, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            with torch.cuda.stream(s_mm):
+                s_mm.wait_event(ready)
+                if done_out[i] is not None:
+                    s_mm.wait_event(done_out[i])         # D is still being copied out from the previous step
+                deep_gemm.fp8_gemm_nt((c.a, c.sfa32), (c.b, c.sfb32), c.d, recipe=(1, 128, 128))
+                done_mm[i] = torch.cuda.Event()
+                done_mm[i].record(s_mm)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done_mm[i])
+                c.h_d.copy_(c.d, non_blocking=True)
+                done_out[i] = torch.cuda.Event()
+                done_out[i].record(s_out)
 
     e2e_step()
     barrier()
@@ -326,16 +347,29 @@ def run_dense(args, rank, world, device):
     if cpu_tf is not None:
         line['cpu_baseline'] = {'value': cpu_tf, 'unit': 'TFLOP/s', 'cores': torch.get_num_threads(), 'kind': 'port',
                                 'sample': CPU_SAMPLE_TEXT + ' (%.1f s)' % cpu_s}
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+def emit(line: dict) -> None:
+    """Write the result line to the process's original stdout (everything else is routed to stderr)."""
+    os.write(_RESULT_FD, (json.dumps(line) + '\n').encode())
+
+
+_RESULT_FD = 1
 
 
 def main():
+    global _RESULT_FD
+    # Libraries (NCCL's version banner, for one) print to stdout; keep stdout for the one JSON line.
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='dense', choices=['dense', 'grouped', 'masked'])
+    ap.add_argument('--workload', default='dense', choices=['dense', 'grouped', 'masked', 'mixed'])
     ap.add_argument('--experts-per-gpu', type=int, default=0, help='grouped / masked workloads (default 8 / 32)')
     ap.add_argument('--gather', action='store_true', help='grouped workload, N > 1: also time an NCCL all-gather of D')
     args = ap.parse_args()
@@ -358,7 +392,7 @@ def main():
             run_dense(args, rank, world, device)
         else:
             from deep_gemm.testing import moe_bench
-            moe_bench.run(args, rank, world, device)
+            moe_bench.run(args, rank, world, device, emit)
     finally:
         if world > 1:
             torch.distributed.destroy_process_group()

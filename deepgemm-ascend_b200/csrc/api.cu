@@ -128,11 +128,11 @@ static uint32_t tmem_cols_for(uint32_t block_n, uint32_t accum_stages) {
     return cols;
 }
 
-static uint32_t max_stages_for(uint32_t block_n, uint32_t cta_group, bool decode_b) {
+static uint32_t max_stages_for(uint32_t block_n, uint32_t cta_group, bool decode_b, uint32_t store_bufs) {
     constexpr uint32_t kSmemCap = 227 * 1024;
     uint32_t best = 0;
     for (uint32_t s = 1; s <= kMaxStages; ++s)
-        if (make_smem_layout(block_n, s, cta_group, decode_b).total <= kSmemCap) best = s;
+        if (make_smem_layout(block_n, s, cta_group, decode_b, store_bufs).total <= kSmemCap) best = s;
     return best;
 }
 
@@ -161,10 +161,15 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     c.tmem_cols = tmem_cols_for(c.block_n, accum_stages);
     c.reserved[0] = accum_stages;
     const bool decode_b = d.b_dtype == DG_E2M1X2;
-    const uint32_t max_stages = max_stages_for(c.block_n, c.cta_group, decode_b);
+    const uint32_t nkb = ceil_div_u32(d.k, kBlockK);
+    // Staging boxes per epilogue warp. Measured: more than two never helped (the stores then compete with the operand
+    // loads), and the shared memory is worth more as pipeline stages.
+    if (c.reserved[1] == 0) c.reserved[1] = 2u;
+    DG_CHECK_ARG(c.reserved[1] >= 2 && c.reserved[1] <= kMaxStoreBufs, "store buffers per warp must be 2..4");
+    const uint32_t store_bufs = c.reserved[1];
+    const uint32_t max_stages = max_stages_for(c.block_n, c.cta_group, decode_b, store_bufs);
     if (c.num_stages == 0 || c.num_stages > max_stages) c.num_stages = max_stages;
     DG_CHECK_ARG(c.num_stages >= 1, "tile does not fit in shared memory");
-    const uint32_t nkb = ceil_div_u32(d.k, kBlockK);
     if (c.num_stages > nkb * 4 && c.num_stages > 2) c.num_stages = nkb * 4 > 2 ? nkb * 4 : 2;
     if (c.num_stages > max_stages) c.num_stages = max_stages;
     if (split) {
@@ -174,7 +179,7 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
         c.split_k = ceil_div_u32(nkb, per);
     }
     // one CTA per SM: keep the dynamic shared memory above half of the SM's capacity
-    const uint32_t need = make_smem_layout(c.block_n, c.num_stages, c.cta_group, decode_b).total;
+    const uint32_t need = make_smem_layout(c.block_n, c.num_stages, c.cta_group, decode_b, store_bufs).total;
     c.smem_bytes = need < 120u * 1024 ? 120u * 1024 : need;
 
     uint32_t grid_units;
@@ -337,6 +342,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.d_group_stride = d.group_stride_d;
     a.tmem_cols = c.tmem_cols;
     a.accum_stages = accum_stages;
+    a.store_bufs = c.reserved[1];
     // Instruction descriptor (block-scaled, kind::mxf8f6f4): E4M3 x E4M3, UE8M0 scales, FP32 accumulate.
     a.idesc = ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) | ((c.block_n >> 3) << 17) | (1u << 23) |
               (((kBlockM * c.cta_group) >> 4) << 24);

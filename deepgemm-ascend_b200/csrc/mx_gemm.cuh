@@ -34,7 +34,7 @@ constexpr uint32_t kNumThreadsDecode = kNumThreads + kNumDecodeWarps * 32;
 constexpr uint32_t kNumEpilogueWarps = 4;
 constexpr uint32_t kStoreBoxRows = 32;   // each epilogue warp stores its own 32 rows
 constexpr uint32_t kStoreBufBytes = kStoreBoxRows * 128;  // one 128B-swizzled box
-constexpr uint32_t kNumStoreBufs = 2;    // per epilogue warp
+constexpr uint32_t kMaxStoreBufs = 4;    // staging boxes per epilogue warp (2..4, chosen per problem)
 constexpr uint32_t kMaxStages = 12;
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;  // 2 s
 
@@ -66,6 +66,7 @@ struct GemmKernelArgs {
     uint64_t d_stride, d_group_stride;  // elements
     uint32_t idesc;                   // tcgen05 instruction descriptor without the scale ids
     uint32_t tmem_cols, accum_stages;
+    uint32_t store_bufs;              // staging boxes per epilogue warp
     int32_t* status;
     unsigned long long* trace;        // debugging aid: per-CTA timestamps (8 slots each), or nullptr
 };
@@ -236,7 +237,7 @@ struct SmemLayout {
     uint32_t a_stage, b_stage, b_raw_stage, sfa_stage, sfb_stage;
 };
 __host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_t num_stages, uint32_t cta_group,
-                                                       bool decode_b = false) {
+                                                       bool decode_b, uint32_t store_bufs) {
     SmemLayout L;
     L.a_stage = kBlockM * kBlockK;
     L.b_stage = (block_n / cta_group) * kBlockK;
@@ -244,7 +245,7 @@ __host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_
     L.sfa_stage = 128 * 4;
     L.sfb_stage = sfb_rows(block_n) * 4;
     uint32_t off = 0;
-    L.store_bufs = off; off += kNumEpilogueWarps * kNumStoreBufs * kStoreBufBytes;
+    L.store_bufs = off; off += kNumEpilogueWarps * store_bufs * kStoreBufBytes;
     L.a = off; off += num_stages * L.a_stage;
     L.b = off; off += num_stages * L.b_stage;
     off = (off + 1023u) & ~1023u;
@@ -297,7 +298,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const SmemLayout L = make_smem_layout(p.block_n, p.num_stages, kCtaGroup, kDecodeB);
+    const SmemLayout L = make_smem_layout(p.block_n, p.num_stages, kCtaGroup, kDecodeB, p.store_bufs);
 
     const uint32_t warp = threadIdx.x / 32, lane = lane_id();
     const uint32_t cta_rank = kCtaGroup == 2 ? cluster_ctarank() : 0u;
@@ -542,8 +543,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         Tile t;
         uint32_t tile_iter = 0, buf = 0;
         bool ok = true;
-        const uint32_t store_base = smem_base + L.store_bufs + q * kNumStoreBufs * kStoreBufBytes;
-        uint8_t* store_gen = smem_gen + L.store_bufs + q * kNumStoreBufs * kStoreBufBytes;
+        const uint32_t store_base = smem_base + L.store_bufs + q * p.store_bufs * kStoreBufBytes;
+        uint8_t* store_gen = smem_gen + L.store_bufs + q * p.store_bufs * kStoreBufBytes;
         const uint32_t cols_per_box = p.d_is_fp32 ? 32u : 64u;
         const uint32_t leader_tmem_empty0 = kCtaGroup == 2 ? mapa_shared(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
         while (ok && sched.next(t)) {
@@ -554,10 +555,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             tc_fence_after_sync();
             const uint32_t row = t.row0 + q * 32 + lane;       // row of D held by this thread
             const uint32_t taddr = tmem_base + ((q * 32u) << 16) + e * p.block_n;
-            for (uint32_t c0 = 0; c0 < p.block_n; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(taddr + c0, v);
-                tmem_ld_wait();
+
+            // One 32-column chunk of this thread's row: alpha / bias, cast, stage, store.
+            auto process_chunk = [&](uint32_t (&v)[32], uint32_t c0) {
                 const uint32_t col0 = t.n0 + c0;
                 if (p.has_alpha) {
                     #pragma unroll
@@ -580,8 +580,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     const uint32_t half = p.d_is_fp32 ? 0u : ((c0 / 32) & 1u);
                     const bool tail = !p.d_is_fp32 && half == 0 && c0 + 32 >= p.block_n;
                     if (half == 0) {
-                        // the buffer may still be read by the store issued two boxes ago
-                        tma_store_wait_read<kNumStoreBufs - 1>();
+                        // the buffer may still be read by the store issued `store_bufs` boxes ago
+                        if (p.store_bufs == 2) tma_store_wait_read<1>();
+                        else if (p.store_bufs == 3) tma_store_wait_read<2>();
+                        else tma_store_wait_read<3>();
                         __syncwarp();
                     }
                     uint8_t* bufp = store_gen + buf * kStoreBufBytes;
@@ -620,7 +622,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                 tma_reduce_add_3d(map, store_base + buf * kStoreBufBytes, x, y, (int32_t)t.row_z);
                             tma_store_commit();
                         }
-                        buf ^= 1;
+                        if (++buf == p.store_bufs) buf = 0;
                     }
                 } else {
                     // plain path: bounds-checked element stores / atomics, any N and any stride
@@ -640,6 +642,20 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             }
                         }
                     }
+                }
+            };
+
+            // Two register sets: the TMEM load of the next chunk is in flight while this one is converted and staged.
+            uint32_t va[32], vb[32];
+            tmem_ld_32x32b_x32(taddr, va);
+            for (uint32_t c0 = 0; c0 < p.block_n; c0 += 64) {
+                tmem_ld_wait();
+                if (c0 + 32 < p.block_n) tmem_ld_32x32b_x32(taddr + c0 + 32, vb);
+                process_chunk(va, c0);
+                if (c0 + 32 < p.block_n) {
+                    tmem_ld_wait();
+                    if (c0 + 64 < p.block_n) tmem_ld_32x32b_x32(taddr + c0 + 64, va);
+                    process_chunk(vb, c0 + 32);
                 }
             }
             // this accumulator may be overwritten by the next-but-one tile

@@ -450,7 +450,10 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
     if config is not None:
         cfg = L.GemmConfig()
         for key, value in config.items():
-            setattr(cfg, key, int(value))
+            if key == 'store_bufs':
+                cfg.reserved[1] = int(value)
+            else:
+                setattr(cfg, key, int(value))
     cfg_ptr = C.byref(cfg) if cfg is not None else None
     lib = L.lib()
     if get_dry_run() or d.is_meta:

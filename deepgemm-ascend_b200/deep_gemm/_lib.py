@@ -48,7 +48,7 @@ class GemmConfig(C.Structure):
 
     def as_dict(self) -> dict:
         return {name: getattr(self, name) for name, _ in self._fields_ if name != 'reserved'} | {
-            'accum_stages': self.reserved[0]}
+            'accum_stages': self.reserved[0], 'store_bufs': self.reserved[1]}
 
 
 _PROTOTYPES = {

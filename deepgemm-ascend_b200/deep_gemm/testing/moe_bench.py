@@ -68,7 +68,9 @@ class GroupedCase:
             raise RuntimeError(L.last_error())
 
 
-def run(args, rank, world, device):
+def run(args, rank, world, device, emit=None):
+    if args.workload == 'mixed':
+        return run_mixed(args, rank, world, device, emit)
     lib = L.lib()
     stream = torch.cuda.current_stream(device)
     sptr = stream.cuda_stream
@@ -156,4 +158,52 @@ def run(args, rank, world, device):
     }
     if gather_ms is not None:
         line['gather_ms'] = gather_ms
-    print(json.dumps(line), flush=True)
+    (emit or (lambda l: print(json.dumps(l), flush=True)))(line)
+
+
+def run_mixed(args, rank, world, device, emit=None):
+    """FP8 x packed-FP4 GEMM "NN": A [M,K] E4M3 with per-128 scales, B [K, N/2] packed E2M1 (uniform codes) with
+    per-32 scales, BF16 out; M=4096, N=7168, K=2048. Normalised by the FP8 peak (the MMA runs on E4M3 operands)."""
+    lib = L.lib()
+    stream = torch.cuda.current_stream(device)
+    sptr = stream.cuda_stream
+    flush = l2_flush_buffer(device)
+    gen = torch.Generator(device=device).manual_seed(7 + rank)
+    m, n, k = 4096, 7168, 2048
+    a = _codes((m, k), device, gen)
+    b = torch.randint(-128, 128, (k, n // 2), dtype=torch.int8, device=device, generator=gen)
+    sfa = _scales((), m, k, device, gen)
+    sfb = _scales((), n, k, device, gen)
+    d = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+    desc = _api._run_gemm(L.GEMM_NORMAL, a, b.transpose(0, 1), d, None, _api.Identity(), sfa, sfb,
+                          (1, 1, 32), None, None, None, 'nk', False)
+    cfg = L.GemmConfig()
+    L.check(lib.dg_select_config(ctypes.byref(desc), ctypes.byref(cfg)))
+
+    def once(events=None):
+        L.check(lib.dg_l2_flush_launch(flush.data_ptr(), flush.numel(), sptr))
+        if events:
+            events[0].record(stream)
+        L.check(lib.dg_gemm_launch(ctypes.byref(desc), None, None, 0, sptr))
+        if events:
+            events[1].record(stream)
+
+    for _ in range(max(args.warmup, 3)):
+        once()
+    torch.cuda.synchronize(device)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for e in ev:
+        once(e)
+    torch.cuda.synchronize(device)
+    us = sum(a_.elapsed_time(b_) for a_, b_ in ev) / args.steps * 1e3
+    if rank != 0:
+        return
+    flops = 2.0 * m * n * k
+    nbytes = m * k + n * k // 2 + (m + n) * ((k + 63) // 64) * 2 + m * n * 2
+    line = {'metric': 'fp8_block_scaled_gemm_tflops', 'value': world * flops / us / 1e6, 'unit': 'TFLOP/s', 'n_gpus': world,
+            'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': us / 1e3, 'higher_is_better': True,
+            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp8_e4m3 x fp4_e2m1 (decoded to e4m3), ue8m0 scales',
+            'data': 'synthetic',
+            'config': {'workload': 'mixed FP8xFP4 GEMM NN, M=4096 N=7168 K=2048, BF16 out', 'l2': 'flushed, untimed'},
+            'gbs': nbytes / us / 1e3, 'tiling': cfg.as_dict(), 'device_status': _api.device_status()}
+    (emit or (lambda l: print(json.dumps(l), flush=True)))(line)

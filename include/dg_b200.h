@@ -105,7 +105,7 @@ typedef struct {
     uint32_t tmem_cols;
     uint32_t smem_bytes;
     uint32_t epilogue_mode;   /* 0 TMA store, 1 TMA reduce-add, 2 plain stores, 3 plain atomics */
-    uint32_t reserved[6];
+    uint32_t reserved[6];     /* [0] TMEM accumulators (1 or 2, derived); [1] epilogue staging boxes per warp (0 = auto, 2..4) */
 } dg_gemm_config_t;
 
 /* The B200 tiling heuristic. Replaces select_gemm_config, csrc/jit_kernels/heuristics.hpp:592-755. */
