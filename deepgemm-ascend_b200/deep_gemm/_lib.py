@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, 'libdg_b200.so')
+# DG_B200_LIB overrides the location of the library (a differently built libdg_b200.so, for example).
+LIB_PATH = os.environ.get('DG_B200_LIB') or os.path.join(_HERE, 'libdg_b200.so')
 
 DG_OK, DG_ERR_INVALID, DG_ERR_UNSUPPORTED, DG_ERR_CUDA, DG_ERR_WORKSPACE = 0, -1, -2, -3, -4
 MAJOR_K, MAJOR_MN = 0, 1
