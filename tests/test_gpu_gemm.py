@@ -165,6 +165,22 @@ def test_fp4_operand_rules():
         deep_gemm.fp8_fp4_gemm_nt((a, sf), (b, sf), d)
 
 
+@pytest.mark.parametrize('m,n,k', [(4, 4, 4), (4, 4, 16384), (4, 16384, 4), (16384, 4, 4), (16384, 4, 16384),
+                                   (4, 16384, 16384), (128, 128, 128), (256, 512, 1024), (1024, 256, 512)])
+def test_reference_extra_shape_list_all_majors(m, n, k):
+    """The shape list of tests/generators.py:466-488 with every major combination, FP32 accumulate."""
+    for trans in ('nt', 'nn', 'tn', 'tt'):
+        _dense(m, n, k, trans=trans, out=torch.float32, acc=True)
+
+
+def test_m_grouped_minimal_case():
+    """tests/generators.py:594: 128 groups of about one row, N = K = 4."""
+    import random
+    random.seed(0)
+    sizes = [max(int(random.uniform(0.7, 1.3) * 1), 0) for _ in range(128)]
+    _grouped_case(sizes, 4, 4)
+
+
 def test_golden_fixtures_through_the_api(golden):
     for name in ('dense_fp8_nt_bf16', 'dense_fp8_nt_acc_f32', 'dense_fp8_unaligned_k', 'dense_fp8_recipe_32_32',
                  'dense_fp8_nn_bias', 'dense_fp8_tn_alpha'):
