@@ -93,8 +93,10 @@ static int validate(const dg_gemm_desc_t& d) {
     DG_CHECK_ARG(d.major_b == DG_MAJOR_K || d.major_b == DG_MAJOR_MN, "bad major_b");
     DG_CHECK_ARG(d.m > 0 && d.n > 0 && d.k > 0, "empty problems are handled by the caller (m, n, k must be > 0)");
     DG_CHECK_ARG(d.a && d.b && d.d && d.sfa && d.sfb, "null operand pointer");
-    DG_CHECK_ARG(d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_ALPHA || d.epilogue == DG_EPILOGUE_BIAS,
-                 "unknown epilogue");
+    DG_CHECK_ARG(d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_ALPHA || d.epilogue == DG_EPILOGUE_BIAS ||
+                 d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16, "unknown epilogue");
+    DG_CHECK_ARG(d.epilogue != DG_EPILOGUE_STOCHASTIC_BF16 || (d.d_dtype == DG_BF16 && !d.accumulate),
+                 "Stochastic rounding requires a direct BF16 output");
     DG_CHECK_ARG(!(d.epilogue == DG_EPILOGUE_BIAS && d.bias == nullptr), "bias epilogue without a bias pointer");
     DG_CHECK_ARG(!(d.epilogue == DG_EPILOGUE_BIAS && d.accumulate), "bias and accumulation cannot be used together");
     if (is_grouped(d.gemm_type)) {
@@ -156,6 +158,7 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
         DG_CHECK_ARG((c.block_n / c.cta_group) % 128 == 0, "MN-major B needs block_n / cta_group to be a multiple of 128");
     DG_CHECK_ARG(c.cta_group == 1 || d.gemm_type != DG_GEMM_M_GROUPED_MASKED, "masked grouped GEMM uses cta_group 1");
     DG_CHECK_ARG(!split || d.gemm_type == DG_GEMM_NORMAL, "split-K is only available for the dense GEMM");
+    DG_CHECK_ARG(!split || d.epilogue != DG_EPILOGUE_STOCHASTIC_BF16, "stochastic rounding cannot be combined with split-K");
 
     const uint32_t accum_stages = (2 * c.block_n + 4 + 4 * (sfb_rows(c.block_n) / 128) <= 512) ? 2u : 1u;
     c.tmem_cols = tmem_cols_for(c.block_n, accum_stages);
@@ -241,7 +244,8 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
         else
             m_tiles = (rows + tile_m - 1) / tile_m;
         for (uint32_t split = 1; split <= 16; ++split) {
-            if (split > 1 && (d.gemm_type != DG_GEMM_NORMAL || nkb / split < 2 || cg == 2)) break;
+            if (split > 1 && (d.gemm_type != DG_GEMM_NORMAL || nkb / split < 2 || cg == 2 ||
+                              d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16)) break;
             const bool out_fp32 = d_fp32 || split > 1;
             const uint32_t step = d.major_b == DG_MAJOR_MN ? 128u * cg : 32u;   // MN-major B comes in 128-column atoms
             for (uint32_t bn = step; bn <= 256; bn += step) {
@@ -334,6 +338,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.epilogue_mode = c.epilogue_mode;
     a.d_is_fp32 = (split || d.d_dtype == DG_F32) ? 1u : 0u;
     a.has_alpha = d.epilogue == DG_EPILOGUE_ALPHA ? 1u : 0u;
+    a.stochastic = d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16 ? 1u : 0u;
     a.alpha = d.alpha;
     a.has_bias = (d.epilogue == DG_EPILOGUE_BIAS && !split) ? 1u : 0u;
     a.bias = d.bias;

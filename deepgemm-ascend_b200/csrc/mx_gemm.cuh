@@ -60,6 +60,7 @@ struct GemmKernelArgs {
     uint32_t epilogue_mode;
     uint32_t d_is_fp32;
     uint32_t has_bias, has_alpha;
+    uint32_t stochastic;              // BF16 output is rounded stochastically instead of to nearest
     float alpha;
     const void* bias;
     void* d;                          // plain-store modes only
@@ -282,6 +283,28 @@ __device__ __forceinline__ uint32_t e2m1x4_to_e4m3x4(uint32_t codes) {
 __device__ __forceinline__ uint4 e2m1x16_to_e4m3x16(uint2 packed) {
     return make_uint4(e2m1x4_to_e4m3x4(packed.x), e2m1x4_to_e4m3x4(packed.x >> 16),
                       e2m1x4_to_e4m3x4(packed.y), e2m1x4_to_e4m3x4(packed.y >> 16));
+}
+
+// ------------------------------------------------------------------------------------------------
+// FP32 -> BF16 with stochastic rounding, bit-compatible with the reference's StochasticRoundToBF16
+// (deep_gemm/include/deep_gemm/epilogue/operators.hpp:224-343; model in tests/utils.py:70-92): the four FP32 bit
+// patterns of an aligned column quartet and the quartet's index within the row seed a hash; each value's discarded
+// 16 bits are compared against its 16 random bits. NaN becomes 0x7fc0. `v` are raw bits, columns past N count as 0.
+// Returns the four BF16 patterns packed as two 32-bit words.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint2 stochastic_round_quartet(uint32_t v0, uint32_t v1, uint32_t v2, uint32_t v3, uint32_t quartet) {
+    uint32_t h = v0 * 0x5671d42bu + v1 * 0x9995e499u + v2 * 0xace1b8a5u + v3 * 0xe153538du + quartet;
+    h = (h ^ (h >> 23)) * 0x7feb352du;
+    h ^= h >> 16;
+    uint32_t h1 = h * 0x846ca68bu, h2 = h * 0xd35a2d97u;
+    h1 ^= h1 >> 11;
+    h2 ^= h2 >> 11;
+    auto round_one = [](uint32_t v, uint32_t random16) -> uint32_t {
+        if ((v & 0x7fffffffu) > 0x7f800000u) return 0x7fc0u;
+        return ((v >> 16) + ((v & 0xffffu) > (0xffffu - random16) ? 1u : 0u)) & 0xffffu;
+    };
+    return make_uint2(round_one(v0, h1 & 0xffffu) | (round_one(v1, h1 >> 16) << 16),
+                      round_one(v2, h2 & 0xffffu) | (round_one(v3, h2 >> 16) << 16));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -573,6 +596,27 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         v[i] = __float_as_uint(__uint_as_float(v[i]) + bv);
                     }
                 }
+                // BF16 output: sixteen packed pairs, rounded to nearest or stochastically
+                uint32_t w16[16];
+                if (!p.d_is_fp32) {
+                    if (p.stochastic) {
+                        #pragma unroll
+                        for (uint32_t g = 0; g < 8; ++g) {
+                            uint32_t x[4];
+                            #pragma unroll
+                            for (uint32_t i = 0; i < 4; ++i) x[i] = (col0 + g * 4 + i < p.n) ? v[g * 4 + i] : 0u;
+                            const uint2 r = stochastic_round_quartet(x[0], x[1], x[2], x[3], (col0 >> 2) + g);
+                            w16[g * 2] = r.x;
+                            w16[g * 2 + 1] = r.y;
+                        }
+                    } else {
+                        #pragma unroll
+                        for (uint32_t i = 0; i < 16; ++i) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[i * 2]), __uint_as_float(v[i * 2 + 1]));
+                            w16[i] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                    }
+                }
                 if (p.epilogue_mode <= kEpiTmaReduce) {
                     // Stage a [32 rows x 128 B] box, 16-byte chunk c of row r at chunk (c ^ (r & 7)). A BF16 box holds two
                     // 32-column groups; when block_n is an odd multiple of 32 the last group goes out alone as a
@@ -596,16 +640,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     } else {
                         #pragma unroll
                         for (uint32_t c = 0; c < 4; ++c) {
-                            uint32_t w[4];
-                            #pragma unroll
-                            for (uint32_t i = 0; i < 4; ++i) {
-                                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[c * 8 + i * 2]),
-                                                                         __uint_as_float(v[c * 8 + i * 2 + 1]));
-                                w[i] = *reinterpret_cast<uint32_t*>(&h);
-                            }
                             uint8_t* dst = tail ? bufp + lane * 64 + ((c ^ ((lane >> 1) & 3u)) * 16)
                                                 : bufp + lane * 128 + (((half * 4 + c) ^ (lane & 7u)) * 16);
-                            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                            *reinterpret_cast<uint4*>(dst) = make_uint4(w16[c * 4], w16[c * 4 + 1], w16[c * 4 + 2], w16[c * 4 + 3]);
                         }
                     }
                     const bool box_done = p.d_is_fp32 || half == 1 || tail;
@@ -638,7 +675,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             } else {
                                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + base + col0 + i;
                                 if (p.epilogue_mode == kEpiPlainAtomic) atomicAdd(dst, __float2bfloat16_rn(f));
-                                else *dst = __float2bfloat16_rn(f);
+                                else *reinterpret_cast<uint16_t*>(dst) = (uint16_t)(w16[i >> 1] >> ((i & 1) * 16));
                             }
                         }
                     }

@@ -69,9 +69,10 @@ class _Bias(Epilogue):
 
 
 class BF16StochasticRounding(Epilogue):
+    """FP32 accumulator -> BF16 by stochastic rounding with the reference's hash (operators.hpp:224-343)."""
+
     def check(self, c, d) -> None:
         _host_assert(c is None and d.dtype == torch.bfloat16, 'Stochastic rounding requires a direct BF16 output')
-        raise NotImplementedError('BF16StochasticRounding is not built in this library yet')
 
 
 class FP8Quantization(Epilogue):
@@ -442,6 +443,8 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
         desc.epilogue, desc.alpha = L.EPILOGUE_ALPHA, epilogue_obj.alpha
     elif isinstance(epilogue_obj, _Bias):
         desc.epilogue, desc.bias = L.EPILOGUE_BIAS, _ptr(epilogue_obj.bias)
+    elif isinstance(epilogue_obj, BF16StochasticRounding):
+        desc.epilogue = L.EPILOGUE_STOCHASTIC_BF16
     else:
         desc.epilogue = L.EPILOGUE_IDENTITY
     desc.num_sms = 0

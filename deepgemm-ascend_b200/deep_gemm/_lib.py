@@ -16,7 +16,7 @@ DG_OK, DG_ERR_INVALID, DG_ERR_UNSUPPORTED, DG_ERR_CUDA, DG_ERR_WORKSPACE = 0, -1
 MAJOR_K, MAJOR_MN = 0, 1
 GEMM_NORMAL, GEMM_M_GROUPED_PSUM, GEMM_K_GROUPED_PSUM, GEMM_BATCHED, GEMM_M_GROUPED_MASKED = 0, 1, 2, 3, 4
 E4M3, E2M1X2, BF16, F32 = 0, 1, 2, 3
-EPILOGUE_IDENTITY, EPILOGUE_ALPHA, EPILOGUE_BIAS = 0, 1, 2
+EPILOGUE_IDENTITY, EPILOGUE_ALPHA, EPILOGUE_BIAS, EPILOGUE_STOCHASTIC_BF16 = 0, 1, 2, 3
 
 
 class GemmDesc(C.Structure):

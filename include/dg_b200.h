@@ -54,7 +54,13 @@ typedef enum {
 typedef enum { DG_E4M3 = 0, DG_E2M1X2 = 1, DG_BF16 = 2, DG_F32 = 3 } dg_dtype_t;
 
 /* csrc/jit_kernels/epilogue_class.hpp:29-66 (Identity / ScaleByAlpha / AddBias) */
-typedef enum { DG_EPILOGUE_IDENTITY = 0, DG_EPILOGUE_ALPHA = 1, DG_EPILOGUE_BIAS = 2 } dg_epilogue_t;
+/* STOCHASTIC_BF16: csrc/jit_kernels/epilogue_class.hpp:68-78, operators.hpp:224-343 (BF16 output, no C) */
+typedef enum {
+    DG_EPILOGUE_IDENTITY = 0,
+    DG_EPILOGUE_ALPHA = 1,
+    DG_EPILOGUE_BIAS = 2,
+    DG_EPILOGUE_STOCHASTIC_BF16 = 3
+} dg_epilogue_t;
 
 /*
  * Problem descriptor. Mirrors GemmDesc, csrc/jit_kernels/gemm_config.hpp:39-95, plus the

@@ -30,6 +30,7 @@ from .mxgemm import (  # noqa: F401
     max_rel_err,
     quantize_e2m1,
     quantize_e4m3,
+    stochastic_round_bf16,
 )
 from .sf_layout import (  # noqa: F401
     align,

@@ -171,3 +171,28 @@ def max_rel_err(x: torch.Tensor, y: torch.Tensor, floor_frac: float = 1.0 / 64) 
         return float((x - y).abs().max())
     den = torch.maximum(y.abs(), scale * floor_frac)
     return float(((x - y).abs() / den).max())
+
+
+def stochastic_round_bf16(fp32: torch.Tensor) -> torch.Tensor:
+    """BF16 stochastic rounding model of the reference (tests/utils.py:70-92): per row, each aligned quartet of
+    FP32 bit patterns (columns past N count as zero) and its index seed a hash; a value rounds up when its discarded
+    16 bits exceed 0xffff minus its 16 random bits; NaN becomes 0x7fc0. Returns a bfloat16 tensor."""
+    import numpy as np
+    values = fp32.detach().cpu().contiguous().numpy().view(np.uint32)
+    n = values.shape[-1]
+    values = np.pad(values, [(0, 0)] * (values.ndim - 1) + [(0, -n % 4)])
+    values = values.reshape(*values.shape[:-1], -1, 4)
+    with np.errstate(over='ignore'):
+        h = (values[..., 0] * np.uint32(0x5671d42b) + values[..., 1] * np.uint32(0x9995e499) +
+             values[..., 2] * np.uint32(0xace1b8a5) + values[..., 3] * np.uint32(0xe153538d) +
+             np.arange(values.shape[-2], dtype=np.uint32))
+        h = (h ^ (h >> np.uint32(23))) * np.uint32(0x7feb352d)
+        h ^= h >> np.uint32(16)
+        h1, h2 = h * np.uint32(0x846ca68b), h * np.uint32(0xd35a2d97)
+    h1 ^= h1 >> np.uint32(11)
+    h2 ^= h2 >> np.uint32(11)
+    random_bits = np.stack((h1 & 0xffff, h1 >> np.uint32(16), h2 & 0xffff, h2 >> np.uint32(16)), axis=-1)
+    rounded = (values >> np.uint32(16)) + ((values & 0xffff) > (0xffff - random_bits))
+    rounded = np.where((values & 0x7fffffff) > 0x7f800000, 0x7fc0, rounded).astype(np.uint16)
+    out = rounded.reshape(*fp32.shape[:-1], -1)[..., :n].copy()
+    return torch.from_numpy(out.view(np.int16)).view(torch.bfloat16)

@@ -42,6 +42,24 @@ def load_reference_layout_model(ref_root: str):
     return ns['reference']
 
 
+def load_reference_stochastic_model(ref_root: str):
+    """tests/utils.py::assert_stochastic_bf16_matches_fp32 with its final assert turned into `return expected`."""
+    import numpy as np
+    text = open(os.path.join(ref_root, 'tests', 'utils.py')).read()
+    tree = ast.parse(text)
+    fn = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == 'assert_stochastic_bf16_matches_fp32')
+    assert isinstance(fn.body[-1], ast.Assert)
+    fn.body[-1] = ast.Return(value=ast.Name(id='expected', ctx=ast.Load()))
+    ast.fix_missing_locations(fn)
+    ns = {'torch': torch, 'np': np}
+    exec(compile(ast.Module(body=[fn], type_ignores=[]), 'ref_utils', 'exec'), ns)
+    model = ns['assert_stochastic_bf16_matches_fp32']
+
+    def run(x: torch.Tensor) -> torch.Tensor:
+        return model(torch.empty(x.shape, dtype=torch.bfloat16), lambda buf: buf.copy_(x), 'golden')
+    return run
+
+
 def raw(t: torch.Tensor) -> torch.Tensor:
     """Store fp8 as bytes so that the files load on any torch build."""
     return t.contiguous().view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t.contiguous()
@@ -117,6 +135,13 @@ def main(ref_root: str) -> None:
                 sf=sf, mn=mn, k=k, gran=gran, expected=exp.contiguous(),
                 expected_stride=tuple(exp.stride()))
     out['sf_layout'] = sf_cases
+
+    # ---- stochastic BF16 rounding model ----------------------------------------------------
+    stochastic = load_reference_stochastic_model(ref_root)
+    torch.manual_seed(2)
+    x = torch.randn(9, 37) * 5
+    x[0, 0], x[1, 1], x[2, 2] = float('nan'), float('inf'), 0.0
+    out['stochastic_bf16'] = dict(x=x, expected=stochastic(x).view(torch.int16))
 
     torch.save(out, os.path.join(HERE, 'reference_vectors.pt'))
     size = os.path.getsize(os.path.join(HERE, 'reference_vectors.pt'))

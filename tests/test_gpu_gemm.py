@@ -181,6 +181,30 @@ def test_m_grouped_minimal_case():
     _grouped_case(sizes, 4, 4)
 
 
+@pytest.mark.parametrize('m,n,k,trans', [(256, 384, 512, 'nt'), (130, 257, 1024, 'nt'), (384, 224, 768, 'nn'),
+                                         (1024, 2112, 2048, 'nt'), (64, 100, 256, 'tn')])
+def test_stochastic_rounding_is_bit_exact(m, n, k, trans):
+    """BF16 output with the BF16StochasticRounding epilogue equals the reference's hash model applied to the FP32
+    output of the same GEMM, bit for bit (tests/utils.py:70-92, tests/common.py:215-221)."""
+    seed_all(m + n)
+    a, sfa, _ = uniform_fp8((m, k), (1, 32))
+    b, sfb, _ = uniform_fp8((n, k), (1, 32))
+    a_dev = with_major(a, trans[0] == 't').cuda()
+    b_dev = with_major(b, trans[1] == 'n').cuda()
+    a_arg = (a_dev.transpose(0, 1), sfa.cuda().transpose(0, 1)) if trans[0] == 't' else (a_dev, sfa.cuda())
+    b_arg = (b_dev.transpose(0, 1), sfb.cuda().transpose(0, 1)) if trans[1] == 'n' else (b_dev, sfb.cuda())
+    fn = getattr(deep_gemm, f'fp8_gemm_{trans}')
+    d32 = torch.empty(m, n, dtype=torch.float32, device='cuda')
+    fn(a_arg, b_arg, d32)
+    d16 = torch.empty(m, n, dtype=torch.bfloat16, device='cuda')
+    fn(a_arg, b_arg, d16, epilogue=deep_gemm.epilogue.BF16StochasticRounding())
+    assert deep_gemm.device_status() == 0
+    expected = oracle.stochastic_round_bf16(d32)
+    assert torch.equal(d16.cpu().view(torch.int16), expected.view(torch.int16))
+    with pytest.raises(RuntimeError, match='Stochastic rounding requires a direct BF16 output'):
+        fn(a_arg, b_arg, d32, epilogue=deep_gemm.epilogue.BF16StochasticRounding())
+
+
 def test_golden_fixtures_through_the_api(golden):
     for name in ('dense_fp8_nt_bf16', 'dense_fp8_nt_acc_f32', 'dense_fp8_unaligned_k', 'dense_fp8_recipe_32_32',
                  'dense_fp8_nn_bias', 'dense_fp8_tn_alpha'):

@@ -104,3 +104,27 @@ def test_metrics():
     assert oracle.calc_diff(x, x) == 0.0
     assert oracle.max_rel_err(x, x) == 0.0
     assert oracle.calc_diff(x, -x) > 1.9
+
+
+def test_stochastic_rounding_model_properties():
+    """The rounding model keeps exactly representable values, only ever picks one of the two neighbours, and is a
+    pure function of the row contents (tests/utils.py:70-92)."""
+    torch.manual_seed(0)
+    x = torch.randn(7, 37) * 3
+    r = oracle.stochastic_round_bf16(x)
+    assert torch.equal(r, oracle.stochastic_round_bf16(x))
+    lo = (x.view(torch.int32) & ~0xFFFF).view(torch.float32)                 # truncation towards zero
+    hi = ((x.view(torch.int32) & ~0xFFFF) + 0x10000).view(torch.float32)     # next BF16 away from zero
+    assert ((r.float() == lo) | (r.float() == hi)).all()
+    exact = torch.randn(5, 8).bfloat16().float()
+    assert torch.equal(oracle.stochastic_round_bf16(exact).float(), exact)
+    assert oracle.stochastic_round_bf16(torch.tensor([[float('nan'), 1.0]])).view(torch.int16)[0, 0].item() == 0x7fc0
+    # rounding is unbiased enough: the mean error over many values is far below one BF16 ulp
+    big = torch.rand(64, 4096) + 1.0
+    err = (oracle.stochastic_round_bf16(big).float() - big).mean().abs().item()
+    assert err < 2.0 ** -7 / 50
+
+
+def test_stochastic_rounding_model_matches_reference_fixture(golden):
+    c = golden['stochastic_bf16']
+    assert torch.equal(oracle.stochastic_round_bf16(c['x']).view(torch.int16), c['expected'])
