@@ -66,20 +66,21 @@ static inline uint64_t align_u64(uint64_t a, uint64_t b) { return (a + b - 1) / 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 static inline uint32_t elem_size(int dtype) { return dtype == DG_F32 ? 4u : dtype == DG_BF16 ? 2u : 1u; }
 
-static bool is_grouped(int t) { return t == DG_GEMM_M_GROUPED_PSUM || t == DG_GEMM_M_GROUPED_MASKED; }
+static bool is_grouped(int t) { return t == DG_GEMM_M_GROUPED_PSUM || t == DG_GEMM_M_GROUPED_MASKED || t == DG_GEMM_BATCHED; }
+// A, SFA and D carry a group / batch dimension of their own (the psum layout keeps them flat)
+static bool has_row_groups(int t) { return t == DG_GEMM_M_GROUPED_MASKED || t == DG_GEMM_BATCHED; }
 
 // Can D (or the split-K workspace) be written through TMA?
 static bool tma_store_ok(const dg_gemm_desc_t& d) {
     const uint32_t es = elem_size(d.d_dtype);
     return aligned16(d.d) && (d.outer_stride_d * es) % 16 == 0 &&
-           (d.gemm_type != DG_GEMM_M_GROUPED_MASKED || (d.group_stride_d * es) % 16 == 0);
+           (!has_row_groups(d.gemm_type) || (d.group_stride_d * es) % 16 == 0);
 }
 
 static int validate(const dg_gemm_desc_t& d) {
     DG_CHECK_ARG(d.gemm_type == DG_GEMM_NORMAL || is_grouped(d.gemm_type) ||
                  d.gemm_type == DG_GEMM_K_GROUPED_PSUM || d.gemm_type == DG_GEMM_BATCHED, "Unknown gemm type %d", d.gemm_type);
-    DG_UNSUPPORTED(d.gemm_type == DG_GEMM_K_GROUPED_PSUM || d.gemm_type == DG_GEMM_BATCHED,
-                   "K-grouped and batched GEMM are not built in this library");
+    DG_UNSUPPORTED(d.gemm_type == DG_GEMM_K_GROUPED_PSUM, "K-grouped GEMM is not built in this library");
     DG_CHECK_ARG(d.a_dtype == DG_E4M3 || d.a_dtype == DG_E2M1X2, "Unsupported operand dtypes");
     DG_CHECK_ARG(d.b_dtype == DG_E4M3 || d.b_dtype == DG_E2M1X2, "Unsupported operand dtypes");
     DG_CHECK_ARG(!(d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E4M3), "Unsupported operand dtypes");
@@ -88,18 +89,29 @@ static int validate(const dg_gemm_desc_t& d) {
         DG_CHECK_ARG(d.k % 2 == 0, "packed FP4 needs an even K");
         DG_CHECK_ARG(d.major_b == DG_MAJOR_K || d.n % 2 == 0, "MN-major packed FP4 needs an even N");
     }
-    DG_CHECK_ARG(d.d_dtype == DG_BF16 || d.d_dtype == DG_F32, "D must be bf16 or fp32");
+    if (d.epilogue == DG_EPILOGUE_FP8_QUANT) {
+        DG_CHECK_ARG(d.d_dtype == DG_E4M3 && !d.accumulate, "FP8 quantization requires a direct E4M3 output");
+        DG_CHECK_ARG(d.n % 128 == 0, "FP8 output requires N to be a multiple of 128");
+        DG_CHECK_ARG(d.sfd != nullptr && d.sfd_stride >= d.m, "FP8 quantization needs the scale output tensor");
+        DG_CHECK_ARG(aligned16(d.d) && d.outer_stride_d % 16 == 0 && d.group_stride_d % 16 == 0,
+                     "FP8 output: base and strides must be multiples of 16 bytes");
+    } else {
+        DG_CHECK_ARG(d.d_dtype == DG_BF16 || d.d_dtype == DG_F32, "D must be bf16 or fp32");
+    }
     DG_CHECK_ARG(d.major_a == DG_MAJOR_K || d.major_a == DG_MAJOR_MN, "bad major_a");
     DG_CHECK_ARG(d.major_b == DG_MAJOR_K || d.major_b == DG_MAJOR_MN, "bad major_b");
     DG_CHECK_ARG(d.m > 0 && d.n > 0 && d.k > 0, "empty problems are handled by the caller (m, n, k must be > 0)");
     DG_CHECK_ARG(d.a && d.b && d.d && d.sfa && d.sfb, "null operand pointer");
     DG_CHECK_ARG(d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_ALPHA || d.epilogue == DG_EPILOGUE_BIAS ||
-                 d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16, "unknown epilogue");
+                 d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16 || d.epilogue == DG_EPILOGUE_FP8_QUANT, "unknown epilogue");
     DG_CHECK_ARG(d.epilogue != DG_EPILOGUE_STOCHASTIC_BF16 || (d.d_dtype == DG_BF16 && !d.accumulate),
                  "Stochastic rounding requires a direct BF16 output");
     DG_CHECK_ARG(!(d.epilogue == DG_EPILOGUE_BIAS && d.bias == nullptr), "bias epilogue without a bias pointer");
     DG_CHECK_ARG(!(d.epilogue == DG_EPILOGUE_BIAS && d.accumulate), "bias and accumulation cannot be used together");
-    if (is_grouped(d.gemm_type)) {
+    if (d.gemm_type == DG_GEMM_BATCHED) {
+        DG_CHECK_ARG(d.num_groups > 0, "batched GEMM needs num_groups (the batch count)");
+        DG_CHECK_ARG(d.epilogue != DG_EPILOGUE_BIAS, "batched matmul doesn't support bias");
+    } else if (is_grouped(d.gemm_type)) {
         DG_CHECK_ARG(d.grouped_layout != nullptr && d.num_groups > 0, "grouped GEMM needs grouped_layout and num_groups");
         DG_CHECK_ARG(d.major_a == DG_MAJOR_K, "A must be K-major for m-grouped GEMM");
         DG_CHECK_ARG(!d.accumulate, "grouped matmul doesn't support accumulation");
@@ -145,7 +157,8 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     c.block_k = kBlockK;
     const bool split = c.split_k > 1;
     const bool tma_ok = split || tma_store_ok(d);
-    if (split) c.epilogue_mode = kEpiTmaReduce;
+    if (d.epilogue == DG_EPILOGUE_FP8_QUANT) c.epilogue_mode = kEpiFp8Quant;
+    else if (split) c.epilogue_mode = kEpiTmaReduce;
     else if (d.accumulate) c.epilogue_mode = tma_ok ? kEpiTmaReduce : kEpiPlainAtomic;
     else c.epilogue_mode = tma_ok ? kEpiTmaStore : kEpiPlainStore;
 
@@ -157,6 +170,7 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     if (d.major_b == DG_MAJOR_MN)
         DG_CHECK_ARG((c.block_n / c.cta_group) % 128 == 0, "MN-major B needs block_n / cta_group to be a multiple of 128");
     DG_CHECK_ARG(c.cta_group == 1 || d.gemm_type != DG_GEMM_M_GROUPED_MASKED, "masked grouped GEMM uses cta_group 1");
+    DG_CHECK_ARG(!split || d.epilogue != DG_EPILOGUE_FP8_QUANT, "FP8 quantization cannot be combined with split-K");
     DG_CHECK_ARG(!split || d.gemm_type == DG_GEMM_NORMAL, "split-K is only available for the dense GEMM");
     DG_CHECK_ARG(!split || d.epilogue != DG_EPILOGUE_STOCHASTIC_BF16, "stochastic rounding cannot be combined with split-K");
 
@@ -192,7 +206,7 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
         grid_units = (uint32_t)(tiles < max_units ? tiles : max_units);
     } else {
         uint64_t bound;   // an upper bound on the tile count; the real count is only known on device
-        if (d.gemm_type == DG_GEMM_M_GROUPED_PSUM) bound = (uint64_t)(d.m / c.block_m) * ceil_div_u32(d.n, c.block_n);
+        if (d.gemm_type == DG_GEMM_M_GROUPED_PSUM) bound = (uint64_t)ceil_div_u32(d.m, c.block_m) * ceil_div_u32(d.n, c.block_n);
         else bound = (uint64_t)d.num_groups * ceil_div_u32(d.m, c.block_m) * ceil_div_u32(d.n, c.block_n);
         grid_units = (uint32_t)(bound < max_units ? bound : max_units);
     }
@@ -225,6 +239,8 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     if (d.gemm_type == DG_GEMM_M_GROUPED_MASKED) {
         const uint32_t per_group = d.expected_m ? (d.expected_m < d.m ? d.expected_m : d.m) : d.m;
         rows = (uint64_t)d.num_groups * per_group;
+    } else if (d.gemm_type == DG_GEMM_BATCHED) {
+        rows = (uint64_t)d.num_groups * d.m;
     } else {
         rows = d.m;
     }
@@ -235,17 +251,18 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     double best_cost = 1e30;
     uint32_t best_bn = 0, best_split = 1, best_cg = 1;
     for (uint32_t cg = 1; cg <= 2; ++cg) {
-        if (cg == 2 && (d.gemm_type == DG_GEMM_M_GROUPED_MASKED || rows <= kBlockM || num_sms < 2)) continue;
+        if (cg == 2 && (d.gemm_type == DG_GEMM_M_GROUPED_MASKED || rows <= kBlockM || num_sms < 2 ||
+                        (d.gemm_type == DG_GEMM_BATCHED && d.m <= kBlockM))) continue;
         const uint32_t units = num_sms / cg;
         const uint32_t tile_m = kBlockM * cg;
         uint64_t m_tiles;
-        if (d.gemm_type == DG_GEMM_M_GROUPED_MASKED)
+        if (has_row_groups(d.gemm_type))
             m_tiles = (uint64_t)d.num_groups * ceil_div_u32((uint32_t)(rows / d.num_groups), tile_m);
         else
             m_tiles = (rows + tile_m - 1) / tile_m;
         for (uint32_t split = 1; split <= 16; ++split) {
             if (split > 1 && (d.gemm_type != DG_GEMM_NORMAL || nkb / split < 2 || cg == 2 ||
-                              d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16)) break;
+                              d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16 || d.epilogue == DG_EPILOGUE_FP8_QUANT)) break;
             const bool out_fp32 = d_fp32 || split > 1;
             const uint32_t step = d.major_b == DG_MAJOR_MN ? 128u * cg : 32u;   // MN-major B comes in 128-column atoms
             for (uint32_t bn = step; bn <= 256; bn += step) {
@@ -317,7 +334,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
                       bool encode, LaunchPlan& plan) {
     memset(&plan, 0, sizeof(plan));
     GemmKernelArgs& a = plan.args;
-    const bool masked = d.gemm_type == DG_GEMM_M_GROUPED_MASKED;
+    const bool masked = has_row_groups(d.gemm_type);       // A, SFA and D have a group / batch dimension
     const bool grouped = is_grouped(d.gemm_type);
     const bool split = c.split_k > 1;
     const uint32_t accum_stages = c.reserved[0];
@@ -339,6 +356,8 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.d_is_fp32 = (split || d.d_dtype == DG_F32) ? 1u : 0u;
     a.has_alpha = d.epilogue == DG_EPILOGUE_ALPHA ? 1u : 0u;
     a.stochastic = d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16 ? 1u : 0u;
+    a.sfd = reinterpret_cast<uint8_t*>(d.sfd);
+    a.sfd_stride = d.sfd_stride;
     a.alpha = d.alpha;
     a.has_bias = (d.epilogue == DG_EPILOGUE_BIAS && !split) ? 1u : 0u;
     a.bias = d.bias;
@@ -389,8 +408,9 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
             const uint32_t box[3] = {kBlockK, kBlockM, 1};
             if (int rc = encode_map(&plan.tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "A")) return rc;
         } else {
-            const uint64_t dims[3] = {rows_a, d.k, 1};
-            const uint64_t str[2] = {d.outer_stride_a, align_u64((uint64_t)d.k * d.outer_stride_a, 16)};
+            const uint64_t dims[3] = {rows_a, d.k, masked ? groups : 1};
+            const uint64_t str[2] = {d.outer_stride_a, masked ? nonzero_stride(d.group_stride_a, (uint64_t)d.k * d.outer_stride_a)
+                                                               : align_u64((uint64_t)d.k * d.outer_stride_a, 16)};
             const uint32_t box[3] = {kBlockM, kBlockK, 1};
             if (int rc = encode_map(&plan.tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "A")) return rc;
         }

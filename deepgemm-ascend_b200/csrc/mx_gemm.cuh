@@ -19,6 +19,7 @@
 
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cstdint>
 
 #include "ptx.cuh"
@@ -38,8 +39,8 @@ constexpr uint32_t kMaxStoreBufs = 4;    // staging boxes per epilogue warp (2..
 constexpr uint32_t kMaxStages = 12;
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;  // 2 s
 
-enum GemmTypeDev : uint32_t { kNormal = 0, kMGroupedPsum = 1, kMGroupedMasked = 4 };
-enum EpilogueMode : uint32_t { kEpiTmaStore = 0, kEpiTmaReduce = 1, kEpiPlainStore = 2, kEpiPlainAtomic = 3 };
+enum GemmTypeDev : uint32_t { kNormal = 0, kMGroupedPsum = 1, kBatched = 3, kMGroupedMasked = 4 };
+enum EpilogueMode : uint32_t { kEpiTmaStore = 0, kEpiTmaReduce = 1, kEpiPlainStore = 2, kEpiPlainAtomic = 3, kEpiFp8Quant = 4 };
 enum StatusCode : int32_t {
     kStatusOk = 0,
     kStatusTimeoutProducer = 101, kStatusTimeoutPacker = 102, kStatusTimeoutMma = 103,
@@ -61,6 +62,8 @@ struct GemmKernelArgs {
     uint32_t d_is_fp32;
     uint32_t has_bias, has_alpha;
     uint32_t stochastic;              // BF16 output is rounded stochastically instead of to nearest
+    uint8_t* sfd;                     // FP8-quantised output: UE8M0 scale bytes, two per int16 element
+    uint64_t sfd_stride;              // int16 elements between consecutive 64-column groups
     float alpha;
     const void* bias;
     void* d;                          // plain-store modes only
@@ -151,7 +154,8 @@ struct Scheduler {
             cur_row0 = start;
             cur_blocks = (rows + 255u) / 256u * (256u / (kBlockM * kCtaGroup));
         } else {
-            const uint32_t rows = min((uint32_t)max(__ldg(p.grouped_layout + cur_group), 0), p.m);
+            // masked: the group's valid row count comes from the device array; batched: every row is valid
+            const uint32_t rows = p.gemm_type == kBatched ? p.m : min((uint32_t)max(__ldg(p.grouped_layout + cur_group), 0), p.m);
             cur_row0 = 0;
             cur_blocks = (rows + kBlockM * kCtaGroup - 1) / (kBlockM * kCtaGroup);
         }
@@ -187,7 +191,7 @@ struct Scheduler {
             }
             const uint32_t mb = mb_lin - cur_first;
             t.row0 = cur_row0 + (mb * kCtaGroup + rank) * kBlockM;
-            t.row_z = p.gemm_type == kMGroupedMasked ? cur_group : 0u;
+            t.row_z = p.gemm_type == kMGroupedPsum ? 0u : cur_group;
             t.n0 = nb * p.block_n;
             t.b_z = cur_group;
             t.kb_begin = 0;
@@ -595,6 +599,38 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                              : __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0 + i));
                         v[i] = __float_as_uint(__uint_as_float(v[i]) + bv);
                     }
+                }
+                if (p.epilogue_mode == kEpiFp8Quant) {
+                    // E4M3 output with one UE8M0 scale per row per 32 columns (exactly this thread's chunk). As the
+                    // reference does (operators.hpp:368-411, tests/test_einsum.py:74-84): round to BF16 first, scale =
+                    // 2^ceil(log2(max(amax, 1e-4) / 448)), divide, round to nearest E4M3.
+                    float y[32], amax = 0.f;
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        y[i] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
+                        amax = fmaxf(amax, fabsf(y[i]));
+                    }
+                    const uint32_t xbits = __float_as_uint(__fdiv_rn(fmaxf(amax, 1e-4f), 448.0f));
+                    uint32_t e = ((xbits >> 23) & 0xffu) + ((xbits & 0x7fffffu) != 0u ? 1u : 0u);
+                    e = min(max(e, 1u), 254u);
+                    const float inv = __uint_as_float((254u - e) << 23);           // 2^(127 - e), exact for e <= 253
+                    uint32_t q[8];
+                    #pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        uint32_t word = 0;
+                        #pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            word |= (uint32_t)__nv_cvt_float_to_fp8(y[i * 4 + j] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+                        q[i] = word;
+                    }
+                    if (row < p.m && col0 + 32 <= p.n) {
+                        uint8_t* dst = reinterpret_cast<uint8_t*>(p.d) + (uint64_t)t.row_z * p.d_group_stride + (uint64_t)row * p.d_stride + col0;
+                        reinterpret_cast<uint4*>(dst)[0] = make_uint4(q[0], q[1], q[2], q[3]);
+                        reinterpret_cast<uint4*>(dst)[1] = make_uint4(q[4], q[5], q[6], q[7]);
+                        const uint64_t sf_col = ((uint64_t)t.row_z * p.n + col0) >> 6;
+                        p.sfd[(sf_col * p.sfd_stride + row) * 2 + ((col0 >> 5) & 1u)] = (uint8_t)e;
+                    }
+                    return;
                 }
                 // BF16 output: sixteen packed pairs, rounded to nearest or stochastically
                 uint32_t w16[16];

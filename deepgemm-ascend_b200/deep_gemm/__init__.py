@@ -10,6 +10,8 @@ __version__ = '0.1.1'
 from . import epilogue, locality_domain, testing  # noqa: F401
 from ._api import (  # noqa: F401
     device_status,
+    fp8_bmm,
+    fp8_einsum,
     fp8_fp4_gemm_nn,
     fp8_fp4_gemm_nt,
     fp8_fp4_gemm_tn,

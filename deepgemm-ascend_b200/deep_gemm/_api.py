@@ -76,6 +76,9 @@ class BF16StochasticRounding(Epilogue):
 
 
 class FP8Quantization(Epilogue):
+    """E4M3 output with one UE8M0 scale per row per 32 columns, written to `sfd` (int16 [M, batches * N / 64],
+    MN-major, two scale bytes per element); csrc/jit_kernels/epilogue_class.hpp:80-108."""
+
     def __init__(self, sfd: torch.Tensor):
         self.sfd = sfd
 
@@ -84,13 +87,28 @@ class FP8Quantization(Epilogue):
 
     def check(self, c, d) -> None:
         _host_assert(c is None and d.dtype == torch.float8_e4m3fn, 'FP8 quantization requires a direct E4M3 output')
-        raise NotImplementedError('FP8Quantization is not built in this library yet')
+        _host_assert(d.dim() in (2, 3))
+        m, n = d.size(-2), d.size(-1)
+        batches = d.size(0) if d.dim() == 3 else 1
+        _host_assert(n % 128 == 0, 'FP8 output requires N to be a multiple of 128')
+        _host_assert(d.stride(-1) == 1 and (d.dim() == 2 or d.stride(0) == n),
+                     'FP8 output must be contiguous in N and, when batched, hold the batches side by side in a row')
+        sfd = self.sfd
+        _host_assert(sfd.dtype == torch.int16 and sfd.dim() == 2 and sfd.device == d.device,
+                     'sfd must be a 2-D int16 tensor on the output device')
+        _host_assert(sfd.size(0) == m and sfd.size(1) == batches * n // 64, 'sfd must have shape [M, batches * N / 64]')
+        _host_assert((sfd.stride(0) == 1 or m == 1) and sfd.stride(1) == m, 'sfd must be MN-major')
 
 
-def _resolve_epilogue(epilogue, c, d, alpha=None) -> Epilogue:
-    _host_assert((epilogue is not None) + (alpha is not None) <= 1,
+def _resolve_epilogue(epilogue, c, d, alpha=None, sfd=None) -> Epilogue:
+    _host_assert((epilogue is not None) + (alpha is not None) + (sfd is not None) <= 1,
                  'The epilogue class, alpha and the FP8 output pair are exclusive')
-    resolved = Alpha(alpha) if alpha is not None else (epilogue if epilogue is not None else Identity())
+    if alpha is not None:
+        resolved = Alpha(alpha)
+    elif sfd is not None:
+        resolved = FP8Quantization(sfd)
+    else:
+        resolved = epilogue if epilogue is not None else Identity()
     _host_assert(isinstance(resolved, Epilogue), 'epilogue must be a deep_gemm.epilogue object')
     resolved.check(c, d)
     return resolved
@@ -216,7 +234,7 @@ def _gemm_early_return(m, n, k, d, c, with_bias) -> bool:
     is_cd_same = c is not None and _same_buffer(c, d)
     if is_cd_same:
         _host_assert(c.shape == d.shape and c.stride() == d.stride())
-    _host_assert(d.dtype in (torch.bfloat16, torch.float32))
+    _host_assert(d.dtype in (torch.bfloat16, torch.float32, torch.float8_e4m3fn))
     if c is not None:
         _host_assert(c.dim() >= 2 and c.stride(-1) == 1)
         _host_assert(d.dtype == c.dtype)
@@ -327,6 +345,11 @@ def _transform_sf(sf, mn, k, gran_mn, gran_k, num_groups, disable_ue8m0_cast, ps
 # GEMM (csrc/apis/gemm.hpp)
 # ------------------------------------------------------------------------------------------------
 _DTYPES = {torch.float8_e4m3fn: L.E4M3, PACKED_FP4: L.E2M1X2, torch.bfloat16: L.BF16, torch.float32: L.F32}
+_BATCH_SPECS = {   # csrc/apis/einsum.hpp:187-215: expression -> permutations of (A, B, D / C) and compiled_dims
+    'bhr,hdr->bhd': ((1, 0, 2), None, (1, 0, 2), 'nk'),
+    'bhd,hdr->bhr': ((1, 0, 2), (0, 2, 1), (1, 0, 2), 'nk'),
+    'bhd,bhr->hdr': ((1, 2, 0), (1, 2, 0), None, 'mn'),
+}
 
 
 def _ptr(t: torch.Tensor) -> int:
@@ -388,6 +411,8 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
     elif gemm_type == L.GEMM_M_GROUPED_MASKED:
         g, m, n, k = _shape_by_spec('gmnk', [('gmk', a), ('gnk', b), ('gmn', d), ('g', grouped_layout)])
         _host_assert(major_a == L.MAJOR_K, 'A must be K-major for the m-grouped masked layout')
+    elif gemm_type == L.GEMM_BATCHED:
+        g, m, n, k = _shape_by_spec('bmnk', [('bmk', a), ('bnk', b), ('bmn', d)])
     else:
         raise RuntimeError('Unsupported gemm type')
     _host_assert(d.dim() >= 2 and d.stride(-1) == 1, 'D must be contiguous in its last dimension')
@@ -410,7 +435,7 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
         epilogue_obj = _Bias(c)
 
     gran_m, gran_n, gran_k_a, gran_k_b = get_recipe(recipe, recipe_a, recipe_b)
-    masked = gemm_type == L.GEMM_M_GROUPED_MASKED
+    masked = gemm_type in (L.GEMM_M_GROUPED_MASKED, L.GEMM_BATCHED)    # A, SFA and D carry the group dimension
     sfa = _transform_sf(sfa_in, m, k, gran_m, gran_k_a, g if masked else None, disable_ue8m0_cast,
                         grouped_layout if gemm_type == L.GEMM_M_GROUPED_PSUM else None, True)
     sfb = _transform_sf(sfb_in, n, k, gran_n, gran_k_b, g if gemm_type != L.GEMM_NORMAL else None,
@@ -445,6 +470,9 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
         desc.epilogue, desc.bias = L.EPILOGUE_BIAS, _ptr(epilogue_obj.bias)
     elif isinstance(epilogue_obj, BF16StochasticRounding):
         desc.epilogue = L.EPILOGUE_STOCHASTIC_BF16
+    elif isinstance(epilogue_obj, FP8Quantization):
+        desc.epilogue = L.EPILOGUE_FP8_QUANT
+        desc.sfd, desc.sfd_stride = _ptr(epilogue_obj.sfd), epilogue_obj.sfd.stride(1)
     else:
         desc.epilogue = L.EPILOGUE_IDENTITY
     desc.num_sms = 0
@@ -533,6 +561,41 @@ def m_grouped_fp8_fp4_gemm_nt_masked(a, b, d, masked_m, expected_m, recipe=None,
 
 
 m_grouped_fp8_gemm_nt_masked = m_grouped_fp8_fp4_gemm_nt_masked
+
+
+def fp8_bmm(a, b, d, c=None, recipe=(1, 1, 32), compiled_dims='nk', epilogue=None, *, config=None):
+    """Batched D[i] = A[i] @ B[i]^T (+ C[i]); csrc/apis/einsum.hpp:37-71. A [B,M,K], B [B,N,K] (E4M3, either major, any
+    batch stride), D [B,M,N] bf16 / fp32, or a (D, sfd) pair for E4M3 output with UE8M0 scales per 1x32."""
+    a_t, sfa = a
+    b_t, sfb = b
+    d_t, sfd = d if isinstance(d, (tuple, list)) else (d, None)
+    _host_assert(a_t.dtype == torch.float8_e4m3fn and b_t.dtype == torch.float8_e4m3fn, 'fp8_bmm operands must be E4M3')
+    _host_assert(d_t.dim() == 3 and d_t.stride(-1) == 1, 'D must be [B, M, N] and contiguous in N')
+    if a_t.size(0) == 0:
+        return
+    resolved = _resolve_epilogue(epilogue, c, d_t, None, sfd)
+    if isinstance(resolved, FP8Quantization) and 0 in (a_t.size(-2), b_t.size(-2), a_t.size(-1)):
+        if not d_t.is_meta:
+            d_t.zero_()
+            resolved.sfd.zero_()
+        return
+    _run_gemm(L.GEMM_BATCHED, a_t, b_t, d_t, c, resolved, sfa, sfb, recipe, None, None, None, compiled_dims, False,
+              config=config)
+
+
+def fp8_einsum(expr, a, b, d, c=None, recipe=(1, 1, 32), epilogue=None, *, config=None):
+    """FP8 einsum over the reference's three contraction strings (csrc/apis/einsum.hpp:161-216): operands and their
+    scale factors are permuted (views only) into a batched GEMM."""
+    _host_assert(expr in _BATCH_SPECS, 'Unsupported einsum expression')
+    pa, pb, pd, dims = _BATCH_SPECS[expr]
+
+    def perm(t, p):
+        return t if p is None or t is None else t.permute(p)
+    is_pair = isinstance(d, (tuple, list))
+    _host_assert(not is_pair or expr == 'bhr,hdr->bhd', 'only the forward expression accepts a (D, SFD) pair')
+    d_arg = (perm(d[0], pd), d[1]) if is_pair else perm(d, pd)
+    fp8_bmm((perm(a[0], pa), perm(a[1], pa)), (perm(b[0], pb), perm(b[1], pb)), d_arg, perm(c, pd), recipe, dims,
+            epilogue, config=config)
 
 
 def device_status() -> int:

@@ -16,7 +16,7 @@ DG_OK, DG_ERR_INVALID, DG_ERR_UNSUPPORTED, DG_ERR_CUDA, DG_ERR_WORKSPACE = 0, -1
 MAJOR_K, MAJOR_MN = 0, 1
 GEMM_NORMAL, GEMM_M_GROUPED_PSUM, GEMM_K_GROUPED_PSUM, GEMM_BATCHED, GEMM_M_GROUPED_MASKED = 0, 1, 2, 3, 4
 E4M3, E2M1X2, BF16, F32 = 0, 1, 2, 3
-EPILOGUE_IDENTITY, EPILOGUE_ALPHA, EPILOGUE_BIAS, EPILOGUE_STOCHASTIC_BF16 = 0, 1, 2, 3
+EPILOGUE_IDENTITY, EPILOGUE_ALPHA, EPILOGUE_BIAS, EPILOGUE_STOCHASTIC_BF16, EPILOGUE_FP8_QUANT = 0, 1, 2, 3, 4
 
 
 class GemmDesc(C.Structure):
@@ -36,6 +36,7 @@ class GemmDesc(C.Structure):
         ('epilogue', C.c_int32), ('alpha', C.c_float),
         ('bias', C.c_void_p),
         ('num_sms', C.c_uint32),
+        ('sfd', C.c_void_p), ('sfd_stride', C.c_uint64),
     ]
 
 
@@ -74,6 +75,7 @@ _PROTOTYPES = {
 }
 
 STATIC_SCRATCH_BYTES = 4 << 20
+ABI_VERSION = 2
 EXPORTED_SYMBOLS = tuple(_PROTOTYPES)
 _lib = None
 
@@ -90,7 +92,7 @@ def lib() -> C.CDLL:
         for name, (restype, argtypes) in _PROTOTYPES.items():
             fn = getattr(handle, name)
             fn.restype, fn.argtypes = restype, argtypes
-        if handle.dg_abi_version() != 1:
+        if handle.dg_abi_version() != ABI_VERSION:
             raise RuntimeError('libdg_b200.so has an unexpected ABI version')
         _lib = handle
     return _lib

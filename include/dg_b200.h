@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define DG_B200_ABI_VERSION 1
+#define DG_B200_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #pragma GCC visibility push(default)
@@ -46,7 +46,7 @@ typedef enum {
     DG_GEMM_NORMAL = 0,
     DG_GEMM_M_GROUPED_PSUM = 1,
     DG_GEMM_K_GROUPED_PSUM = 2, /* not built */
-    DG_GEMM_BATCHED = 3,        /* not built */
+    DG_GEMM_BATCHED = 3,        /* A [B,M,K], B [B,N,K], D [B,M,N]; csrc/apis/einsum.hpp:37-71 */
     DG_GEMM_M_GROUPED_MASKED = 4
 } dg_gemm_type_t;
 
@@ -59,7 +59,8 @@ typedef enum {
     DG_EPILOGUE_IDENTITY = 0,
     DG_EPILOGUE_ALPHA = 1,
     DG_EPILOGUE_BIAS = 2,
-    DG_EPILOGUE_STOCHASTIC_BF16 = 3
+    DG_EPILOGUE_STOCHASTIC_BF16 = 3,
+    DG_EPILOGUE_FP8_QUANT = 4   /* E4M3 output + UE8M0 scales per 1x32, epilogue_class.hpp:80-108, operators.hpp:345-447 */
 } dg_epilogue_t;
 
 /*
@@ -69,6 +70,7 @@ typedef enum {
  *   Normal            A [M,K]          B [N,K]        D [M,N]
  *   M-grouped psum    A [M_total,K]    B [G,N,K]      D [M_total,N]     grouped_layout = psum int32[G]
  *   M-grouped masked  A [G,max_m,K]    B [G,N,K]      D [G,max_m,N]     grouped_layout = masked_m int32[G], m = max_m
+ *   Batched           A [G,M,K]        B [G,N,K]      D [G,M,N]         num_groups = G, no layout array
  *
  * "[MN,K]" is the logical shape; `major_*` says which axis is contiguous in memory and
  * `outer_stride_*` is the stride of the other axis in ELEMENTS (bytes for packed FP4 operands:
@@ -99,6 +101,10 @@ typedef struct {
     float alpha;
     const void* bias;                         /* [1,N], D's dtype */
     uint32_t num_sms;                         /* cap of the persistent grid; 0 = all SMs */
+    /* DG_EPILOGUE_FP8_QUANT only (d_dtype = DG_E4M3): int16 scale output [M, groups * N / 64], two UE8M0 bytes per
+     * element, element (row, col) at sfd[col * sfd_stride + row]; batch g owns columns [g*N/64, (g+1)*N/64) */
+    int16_t* sfd;
+    uint64_t sfd_stride;
 } dg_gemm_desc_t;
 
 /* Tiling chosen for a problem. Replaces GemmConfig, csrc/jit_kernels/gemm_config.hpp:98-121. */

@@ -37,12 +37,12 @@ def test_library_exports_every_declared_symbol():
     for name in sorted(declared):
         assert hasattr(handle, name), f'{name} is declared but not exported'
     assert declared == set(L.EXPORTED_SYMBOLS)
-    assert L.lib().dg_abi_version() == 1
+    assert L.lib().dg_abi_version() == L.ABI_VERSION == 2
 
 
 def test_struct_sizes_match_the_header():
-    # 5 pointers, 8 x 4-byte, 10 x 8-byte, 2 x 4, pointer, 2 x 4, 2 x 4, pointer, 4 (+4 padding)
-    assert ctypes.sizeof(L.GemmDesc) == 200
+    # 5 pointers, 8 x 4-byte, 10 x 8-byte, 2 x 4, pointer, 2 x 4, 2 x 4, pointer, 4 (+4 padding), pointer, 8
+    assert ctypes.sizeof(L.GemmDesc) == 216
     assert ctypes.sizeof(L.GemmConfig) == 64
 
 
