@@ -66,7 +66,9 @@ static inline uint64_t align_u64(uint64_t a, uint64_t b) { return (a + b - 1) / 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 static inline uint32_t elem_size(int dtype) { return dtype == DG_F32 ? 4u : dtype == DG_BF16 ? 2u : 1u; }
 
-static bool is_grouped(int t) { return t == DG_GEMM_M_GROUPED_PSUM || t == DG_GEMM_M_GROUPED_MASKED || t == DG_GEMM_BATCHED; }
+static bool is_grouped(int t) {
+    return t == DG_GEMM_M_GROUPED_PSUM || t == DG_GEMM_M_GROUPED_MASKED || t == DG_GEMM_BATCHED || t == DG_GEMM_K_GROUPED_PSUM;
+}
 // A, SFA and D carry a group / batch dimension of their own (the psum layout keeps them flat)
 static bool has_row_groups(int t) { return t == DG_GEMM_M_GROUPED_MASKED || t == DG_GEMM_BATCHED; }
 
@@ -74,13 +76,12 @@ static bool has_row_groups(int t) { return t == DG_GEMM_M_GROUPED_MASKED || t ==
 static bool tma_store_ok(const dg_gemm_desc_t& d) {
     const uint32_t es = elem_size(d.d_dtype);
     return aligned16(d.d) && (d.outer_stride_d * es) % 16 == 0 &&
-           (!has_row_groups(d.gemm_type) || (d.group_stride_d * es) % 16 == 0);
+           ((!has_row_groups(d.gemm_type) && d.gemm_type != DG_GEMM_K_GROUPED_PSUM) || (d.group_stride_d * es) % 16 == 0);
 }
 
 static int validate(const dg_gemm_desc_t& d) {
     DG_CHECK_ARG(d.gemm_type == DG_GEMM_NORMAL || is_grouped(d.gemm_type) ||
                  d.gemm_type == DG_GEMM_K_GROUPED_PSUM || d.gemm_type == DG_GEMM_BATCHED, "Unknown gemm type %d", d.gemm_type);
-    DG_UNSUPPORTED(d.gemm_type == DG_GEMM_K_GROUPED_PSUM, "K-grouped GEMM is not built in this library");
     DG_CHECK_ARG(d.a_dtype == DG_E4M3 || d.a_dtype == DG_E2M1X2, "Unsupported operand dtypes");
     DG_CHECK_ARG(d.b_dtype == DG_E4M3 || d.b_dtype == DG_E2M1X2, "Unsupported operand dtypes");
     DG_CHECK_ARG(!(d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E4M3), "Unsupported operand dtypes");
@@ -108,7 +109,14 @@ static int validate(const dg_gemm_desc_t& d) {
                  "Stochastic rounding requires a direct BF16 output");
     DG_CHECK_ARG(!(d.epilogue == DG_EPILOGUE_BIAS && d.bias == nullptr), "bias epilogue without a bias pointer");
     DG_CHECK_ARG(!(d.epilogue == DG_EPILOGUE_BIAS && d.accumulate), "bias and accumulation cannot be used together");
-    if (d.gemm_type == DG_GEMM_BATCHED) {
+    if (d.gemm_type == DG_GEMM_K_GROUPED_PSUM) {
+        DG_CHECK_ARG(d.grouped_layout != nullptr && d.num_groups > 0, "grouped GEMM needs grouped_layout and num_groups");
+        DG_CHECK_ARG(d.major_a == DG_MAJOR_MN && d.major_b == DG_MAJOR_MN, "A and B must be MN-major for the k-grouped layout");
+        DG_CHECK_ARG(d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16,
+                     "k-grouped matmul takes no epilogue besides accumulation and stochastic BF16 rounding");
+        DG_CHECK_ARG(d.k % 256 == 0, "k-grouped psum layout: total K must be a multiple of the 256 alignment");
+        DG_CHECK_ARG(d.b_dtype == DG_E4M3, "k-grouped matmul is built for FP8 operands only");
+    } else if (d.gemm_type == DG_GEMM_BATCHED) {
         DG_CHECK_ARG(d.num_groups > 0, "batched GEMM needs num_groups (the batch count)");
         DG_CHECK_ARG(d.epilogue != DG_EPILOGUE_BIAS, "batched matmul doesn't support bias");
     } else if (is_grouped(d.gemm_type)) {
@@ -207,7 +215,7 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     } else {
         uint64_t bound;   // an upper bound on the tile count; the real count is only known on device
         if (d.gemm_type == DG_GEMM_M_GROUPED_PSUM) bound = (uint64_t)ceil_div_u32(d.m, c.block_m) * ceil_div_u32(d.n, c.block_n);
-        else bound = (uint64_t)d.num_groups * ceil_div_u32(d.m, c.block_m) * ceil_div_u32(d.n, c.block_n);
+        else bound = (uint64_t)d.num_groups * ceil_div_u32(d.m, c.block_m) * ceil_div_u32(d.n, c.block_n);   // masked, batched, k-grouped
         grid_units = (uint32_t)(bound < max_units ? bound : max_units);
     }
     if (grid_units == 0) grid_units = 1;
@@ -231,20 +239,23 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     memset(&c, 0, sizeof(c));
     const uint32_t num_sms = effective_num_sms(d);
     const bool d_fp32 = d.d_dtype == DG_F32;
-    const uint32_t nkb = ceil_div_u32(d.k, kBlockK);
-    const bool grouped = is_grouped(d.gemm_type);
+    // K blocks one tile runs through (the k-grouped layout splits K over the groups)
+    const uint32_t nkb = d.gemm_type == DG_GEMM_K_GROUPED_PSUM ? ceil_div_u32(ceil_div_u32(d.k, d.num_groups), kBlockK)
+                                                               : ceil_div_u32(d.k, kBlockK);
+    const bool grouped = is_grouped(d.gemm_type) && d.gemm_type != DG_GEMM_K_GROUPED_PSUM;
 
     // Rows the problem has (an estimate for the masked layout, whose row counts live on the device).
     uint64_t rows;
     if (d.gemm_type == DG_GEMM_M_GROUPED_MASKED) {
         const uint32_t per_group = d.expected_m ? (d.expected_m < d.m ? d.expected_m : d.m) : d.m;
         rows = (uint64_t)d.num_groups * per_group;
-    } else if (d.gemm_type == DG_GEMM_BATCHED) {
+    } else if (d.gemm_type == DG_GEMM_BATCHED || d.gemm_type == DG_GEMM_K_GROUPED_PSUM) {
         rows = (uint64_t)d.num_groups * d.m;
     } else {
         rows = d.m;
     }
-    const double hbm_bytes = (double)rows * d.k + (double)d.n * d.k * (grouped ? d.num_groups : 1) +
+    const double hbm_bytes = (double)(d.gemm_type == DG_GEMM_K_GROUPED_PSUM ? d.m : rows) * d.k +
+                             (double)d.n * d.k * (grouped ? d.num_groups : 1) +
                              (double)rows * d.n * elem_size(d.d_dtype);
     const double t_hbm = hbm_bytes / 6400.0;       // ns at 6.4 TB/s
 
@@ -252,11 +263,11 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     uint32_t best_bn = 0, best_split = 1, best_cg = 1;
     for (uint32_t cg = 1; cg <= 2; ++cg) {
         if (cg == 2 && (d.gemm_type == DG_GEMM_M_GROUPED_MASKED || rows <= kBlockM || num_sms < 2 ||
-                        (d.gemm_type == DG_GEMM_BATCHED && d.m <= kBlockM))) continue;
+                        ((d.gemm_type == DG_GEMM_BATCHED || d.gemm_type == DG_GEMM_K_GROUPED_PSUM) && d.m <= kBlockM))) continue;
         const uint32_t units = num_sms / cg;
         const uint32_t tile_m = kBlockM * cg;
         uint64_t m_tiles;
-        if (has_row_groups(d.gemm_type))
+        if (has_row_groups(d.gemm_type) || d.gemm_type == DG_GEMM_K_GROUPED_PSUM)
             m_tiles = (uint64_t)d.num_groups * ceil_div_u32((uint32_t)(rows / d.num_groups), tile_m);
         else
             m_tiles = (rows + tile_m - 1) / tile_m;
@@ -338,7 +349,9 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     const bool grouped = is_grouped(d.gemm_type);
     const bool split = c.split_k > 1;
     const uint32_t accum_stages = c.reserved[0];
-    const uint32_t groups = grouped ? d.num_groups : 1;
+    const bool k_grouped = d.gemm_type == DG_GEMM_K_GROUPED_PSUM;
+    const uint32_t groups = (grouped && !k_grouped) ? d.num_groups : 1;     // group dimension of B / SFB (and A / SFA when `masked`)
+    const uint32_t d_groups = (masked || k_grouped) ? d.num_groups : 1;     // group dimension of D
 
     a.m = d.m; a.n = d.n; a.k = d.k;
     a.block_n = c.block_n;
@@ -347,7 +360,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.num_m_blocks = ceil_div_u32(d.m, c.block_m);
     a.num_n_blocks = ceil_div_u32(d.n, c.block_n);
     a.gemm_type = (uint32_t)d.gemm_type;
-    a.num_groups = groups;
+    a.num_groups = grouped ? d.num_groups : 1;
     a.grouped_layout = d.grouped_layout;
     a.split_k = c.split_k;
     a.k_blocks_per_split = ceil_div_u32(a.num_k_blocks, c.split_k);
@@ -375,6 +388,12 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     plan.major_a = d.major_a;
     plan.major_b = d.major_b;
     plan.decode_b = d.b_dtype == DG_E2M1X2;
+    // k-grouped, no accumulation: D of groups whose K range is empty must read as zero
+    plan.zero_empty_groups = k_grouped && !d.accumulate;
+    plan.zero_d = d.d;
+    plan.zero_row_bytes = (uint64_t)d.n * elem_size(d.d_dtype);
+    plan.zero_row_pitch = d.outer_stride_d * elem_size(d.d_dtype);
+    plan.zero_group_pitch = nonzero_stride(d.group_stride_d, (uint64_t)d.m * d.outer_stride_d) * elem_size(d.d_dtype);
     plan.num_ctas = c.num_ctas;
     plan.smem_bytes = c.smem_bytes;
 
@@ -471,7 +490,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
         } else {
             const uint32_t es = elem_size(d.d_dtype);
             const uint64_t gs = nonzero_stride(d.group_stride_d, (uint64_t)d.m * d.outer_stride_d);
-            const uint64_t dims[3] = {d.n, d.m, masked ? groups : 1};
+            const uint64_t dims[3] = {d.n, d.m, d_groups};
             const uint64_t str[2] = {d.outer_stride_d * es, align_u64(gs * es, 16)};
             const uint32_t box[3] = {es == 4 ? 32u : 64u, kStoreBoxRows, 1};
             if (int rc = encode_map(&plan.tm_d, es == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,

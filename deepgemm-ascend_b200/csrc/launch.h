@@ -14,6 +14,10 @@ struct LaunchPlan {
     int cta_group, major_a, major_b;
     bool decode_b;               // B is packed E2M1 and is decoded to E4M3 in shared memory
     uint32_t num_ctas, smem_bytes;
+    // k-grouped layout without accumulation: zero D[g] of the groups that own no K
+    bool zero_empty_groups;
+    void* zero_d;
+    uint64_t zero_row_bytes, zero_row_pitch, zero_group_pitch;
     // split-K finalisation (workspace -> D)
     bool finalize;
     float* ws;

@@ -44,6 +44,19 @@ __global__ void splitk_finalize_kernel(float* __restrict__ ws, uint64_t ws_strid
     }
 }
 
+// K-grouped layout: a group whose K range is empty contributes no tile, so its D[g] is cleared here
+// (the reference does this on its vector cores, deep_gemm/include/deep_gemm/epilogue.hpp:108-141).
+__global__ void zero_empty_k_groups_kernel(uint8_t* __restrict__ d, const int32_t* __restrict__ psum, uint32_t num_groups,
+                                           uint32_t rows, uint64_t row_bytes, uint64_t row_pitch, uint64_t group_pitch) {
+    for (uint32_t g = 0; g < num_groups; ++g) {
+        const uint32_t begin = g == 0 ? 0u : ((uint32_t)psum[g - 1] + 255u) / 256u * 256u;
+        if ((uint32_t)psum[g] > begin) continue;
+        const uint64_t total = (uint64_t)rows * row_bytes;
+        for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x)
+            d[g * group_pitch + (i / row_bytes) * row_pitch + i % row_bytes] = 0;
+    }
+}
+
 using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
                           const CUtensorMap, const CUtensorMap, const GemmKernelArgs);
 
@@ -89,6 +102,14 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
         if (trace_buf == nullptr) DG_CHECK_CUDA(cudaMalloc(&trace_buf, 1024 * 8 * sizeof(unsigned long long)));
         DG_CHECK_CUDA(cudaMemsetAsync(trace_buf, 0, 1024 * 8 * sizeof(unsigned long long), stream));
         args.trace = trace_buf;
+    }
+
+    if (plan.zero_empty_groups) {
+        zero_empty_k_groups_kernel<<<148, 256, 0, stream>>>(static_cast<uint8_t*>(plan.zero_d), plan.args.grouped_layout,
+                                                            plan.args.num_groups, plan.args.m, plan.zero_row_bytes,
+                                                            plan.zero_row_pitch, plan.zero_group_pitch);
+        DG_CHECK_CUDA(cudaGetLastError());
+        count_kernel_launch();
     }
 
     cudaLaunchConfig_t cfg{};

@@ -39,7 +39,7 @@ constexpr uint32_t kMaxStoreBufs = 4;    // staging boxes per epilogue warp (2..
 constexpr uint32_t kMaxStages = 12;
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;  // 2 s
 
-enum GemmTypeDev : uint32_t { kNormal = 0, kMGroupedPsum = 1, kBatched = 3, kMGroupedMasked = 4 };
+enum GemmTypeDev : uint32_t { kNormal = 0, kMGroupedPsum = 1, kKGroupedPsum = 2, kBatched = 3, kMGroupedMasked = 4 };
 enum EpilogueMode : uint32_t { kEpiTmaStore = 0, kEpiTmaReduce = 1, kEpiPlainStore = 2, kEpiPlainAtomic = 3, kEpiFp8Quant = 4 };
 enum StatusCode : int32_t {
     kStatusOk = 0,
@@ -125,7 +125,8 @@ __device__ __forceinline__ void trace_mark(const GemmKernelArgs& p, uint32_t slo
 // ------------------------------------------------------------------------------------------------
 struct Tile {
     uint32_t row0;        // first row of this CTA in A / SFA / D (within the group for masked)
-    uint32_t row_z;       // third TMA coordinate of A / SFA / D (group for masked, else 0)
+    uint32_t row_z;       // third TMA coordinate of A / SFA (group for masked / batched, else 0)
+    uint32_t d_z;         // third TMA coordinate of D (as row_z, but the group for the K-grouped layout)
     uint32_t n0;          // first column of D == first row of B
     uint32_t b_z;         // third TMA coordinate of B / SFB (group)
     uint32_t kb_begin, kb_end;
@@ -144,8 +145,19 @@ struct Scheduler {
     }
 
     // m-blocks are counted in units of (128 * kCtaGroup) rows.
+    uint32_t cur_kb_begin = 0, cur_kb_end = 0;
+
     __device__ __forceinline__ void load_group() {
-        if (p.gemm_type == kMGroupedPsum) {
+        if (p.gemm_type == kKGroupedPsum) {
+            // scheduler.hpp:163-180: group g owns the K range [align(psum[g-1],256), psum[g]); every group spans the
+            // whole M x N grid, an empty group has no tiles (its D is zeroed by a separate kernel).
+            const uint32_t start = cur_group == 0 ? 0u : ((uint32_t)__ldg(p.grouped_layout + cur_group - 1) + 255u) / 256u * 256u;
+            const uint32_t end = (uint32_t)__ldg(p.grouped_layout + cur_group);
+            cur_row0 = 0;
+            cur_kb_begin = start / kBlockK;
+            cur_kb_end = end > start ? (end + kBlockK - 1) / kBlockK : cur_kb_begin;
+            cur_blocks = end > start ? p.num_m_blocks : 0u;
+        } else if (p.gemm_type == kMGroupedPsum) {
             // scheduler.hpp:147-162: group g owns rows [align(psum[g-1],256), psum[g]) and the
             // kernel computes whole 256-row blocks of it.
             const uint32_t start = cur_group == 0 ? 0u : ((uint32_t)__ldg(p.grouped_layout + cur_group - 1) + 255u) / 256u * 256u;
@@ -175,6 +187,7 @@ struct Scheduler {
             const uint32_t mb = first_m + in_group % rows, nb = in_group / rows;
             t.row0 = (mb * kCtaGroup + rank) * kBlockM;
             t.row_z = 0;
+            t.d_z = 0;
             t.n0 = nb * p.block_n;
             t.b_z = 0;
             t.kb_begin = ks * p.k_blocks_per_split;
@@ -191,11 +204,13 @@ struct Scheduler {
             }
             const uint32_t mb = mb_lin - cur_first;
             t.row0 = cur_row0 + (mb * kCtaGroup + rank) * kBlockM;
-            t.row_z = p.gemm_type == kMGroupedPsum ? 0u : cur_group;
+            const bool flat_rows = p.gemm_type == kMGroupedPsum || p.gemm_type == kKGroupedPsum;
+            t.row_z = flat_rows ? 0u : cur_group;
+            t.d_z = p.gemm_type == kMGroupedPsum ? 0u : cur_group;
             t.n0 = nb * p.block_n;
-            t.b_z = cur_group;
-            t.kb_begin = 0;
-            t.kb_end = p.num_k_blocks;
+            t.b_z = p.gemm_type == kKGroupedPsum ? 0u : cur_group;
+            t.kb_begin = p.gemm_type == kKGroupedPsum ? cur_kb_begin : 0u;
+            t.kb_end = p.gemm_type == kKGroupedPsum ? cur_kb_end : p.num_k_blocks;
         }
         tile += stride;
         return true;
@@ -624,10 +639,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         q[i] = word;
                     }
                     if (row < p.m && col0 + 32 <= p.n) {
-                        uint8_t* dst = reinterpret_cast<uint8_t*>(p.d) + (uint64_t)t.row_z * p.d_group_stride + (uint64_t)row * p.d_stride + col0;
+                        uint8_t* dst = reinterpret_cast<uint8_t*>(p.d) + (uint64_t)t.d_z * p.d_group_stride + (uint64_t)row * p.d_stride + col0;
                         reinterpret_cast<uint4*>(dst)[0] = make_uint4(q[0], q[1], q[2], q[3]);
                         reinterpret_cast<uint4*>(dst)[1] = make_uint4(q[4], q[5], q[6], q[7]);
-                        const uint64_t sf_col = ((uint64_t)t.row_z * p.n + col0) >> 6;
+                        const uint64_t sf_col = ((uint64_t)t.d_z * p.n + col0) >> 6;
                         p.sfd[(sf_col * p.sfd_stride + row) * 2 + ((col0 >> 5) & 1u)] = (uint8_t)e;
                     }
                     return;
@@ -690,9 +705,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             const int32_t y = (int32_t)(t.row0 + q * 32);
                             const CUtensorMap* map = tail ? &tm_d_tail : &tm_d;
                             if (p.epilogue_mode == kEpiTmaStore)
-                                tma_store_3d(map, store_base + buf * kStoreBufBytes, x, y, (int32_t)t.row_z);
+                                tma_store_3d(map, store_base + buf * kStoreBufBytes, x, y, (int32_t)t.d_z);
                             else
-                                tma_reduce_add_3d(map, store_base + buf * kStoreBufBytes, x, y, (int32_t)t.row_z);
+                                tma_reduce_add_3d(map, store_base + buf * kStoreBufBytes, x, y, (int32_t)t.d_z);
                             tma_store_commit();
                         }
                         if (++buf == p.store_bufs) buf = 0;
@@ -700,7 +715,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 } else {
                     // plain path: bounds-checked element stores / atomics, any N and any stride
                     const bool row_ok = row < p.m;
-                    const uint64_t base = (uint64_t)t.row_z * p.d_group_stride + (uint64_t)row * p.d_stride;
+                    const uint64_t base = (uint64_t)t.d_z * p.d_group_stride + (uint64_t)row * p.d_stride;
                     #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         if (row_ok && col0 + i < p.n) {

@@ -33,7 +33,24 @@ struct TransformSfArgs {
     uint32_t num_groups, alignment;
     int32_t* invalid_flag;
     uint32_t tiles_m, tiles_c;
+    const int32_t* k_psum;            // K-grouped operands: psum layout along K, scales inside a group's padding become 0
+    uint32_t num_k_groups;
 };
+
+// Is K unit `idx` (a 32-wide block when div = 32, an int16 column when div = 64) inside the padding of a K group?
+// Group g pads the units [ceil(psum[g]/div), align(psum[g], alignment)/div)  (tests/test_layout.py:95-97).
+__device__ __forceinline__ bool k_unit_in_group_padding(const TransformSfArgs& a, uint32_t idx, uint32_t div) {
+    uint32_t lo = 0, hi = a.num_k_groups;
+    while (lo < hi) {
+        const uint32_t mid = (lo + hi) / 2;
+        const uint32_t p = (uint32_t)__ldg(a.k_psum + mid);
+        const uint32_t end = (p + a.alignment - 1) / a.alignment * a.alignment / div;
+        if (end > idx) hi = mid; else lo = mid + 1;
+    }
+    if (lo >= a.num_k_groups) return true;
+    const uint32_t p = (uint32_t)__ldg(a.k_psum + lo);
+    return idx >= (p + div - 1) / div;
+}
 
 // Is source row r (in units of gran_mn rows) inside the padding of some group?  Group g pads the
 // source rows [ceil(psum[g]/gran), align(psum[g], alignment)/gran).
@@ -83,7 +100,8 @@ __global__ void __launch_bounds__(kTsfThreads) transform_sf_kernel(const Transfo
                     const uint64_t off = batch * a.src_batch_stride + (uint64_t)(r0 + r) * a.src_row_stride + (uint64_t)(s0 + s) * a.src_col_stride;
                     const uint32_t bits = __ldg(reinterpret_cast<const uint32_t*>(src_base) + off);
                     e = (uint8_t)((bits >> 23) & 0xff);
-                    bad |= (bits & 0x807fffffu) != 0;      // negative, or not a power of two
+                    // negative, or not a power of two (scales inside a K group's padding are garbage by contract)
+                    if ((bits & 0x807fffffu) != 0 && !(a.k_psum != nullptr && k_unit_in_group_padding(a, s0 + s, 32))) bad = true;
                 }
                 bytes[r][s] = e;
             }
@@ -124,6 +142,14 @@ __global__ void __launch_bounds__(kTsfThreads) transform_sf_kernel(const Transfo
                 const uint32_t rel0 = kb / a.k_repeat - s0, rel1 = (kb + 1) / a.k_repeat - s0;
                 if (passthrough || kb < a.k32_blocks) lo = bytes[r][rel0];
                 if (passthrough || kb + 1 < a.k32_blocks) hi = bytes[r][rel1];
+                if (a.k_psum != nullptr) {
+                    if (passthrough) {
+                        if (k_unit_in_group_padding(a, col, 64)) lo = hi = 0;
+                    } else {
+                        if (k_unit_in_group_padding(a, kb, 32)) lo = 0;
+                        if (k_unit_in_group_padding(a, kb + 1, 32)) hi = 0;
+                    }
+                }
             }
             a.dst[batch * a.dst_batch_stride + (uint64_t)col * a.dst_col_stride + mn] = (int16_t)(lo | (hi << 8));
         }
@@ -154,7 +180,8 @@ extern "C" int dg_transform_sf_launch(const void* src, int src_is_fp32,
                                       int16_t* dst, uint64_t dst_col_stride, uint64_t dst_batch_stride,
                                       uint32_t dst_mn, uint32_t k32_blocks, uint32_t gran_mn, uint32_t k_repeat,
                                       uint32_t num_batches, const int32_t* psum, uint32_t num_groups,
-                                      uint32_t alignment, int32_t* invalid_flag, void* stream) {
+                                      uint32_t alignment, int32_t* invalid_flag,
+                                      const int32_t* k_psum, uint32_t num_k_groups, void* stream) {
     DG_CHECK_ARG(src != nullptr && dst != nullptr, "transform_sf: null pointer");
     DG_CHECK_ARG(gran_mn >= 1 && gran_mn <= 128 && (gran_mn & (gran_mn - 1)) == 0,
                  "gran_mn only support a power of two in [1, 128]");
@@ -163,6 +190,8 @@ extern "C" int dg_transform_sf_launch(const void* src, int src_is_fp32,
                  "Grouped transform SF requires one logical batch and grouped_layout");
     DG_CHECK_ARG(alignment > 0 && alignment % gran_mn == 0, "transform_sf: alignment must be a multiple of gran_mn");
     DG_CHECK_ARG(num_batches >= 1 && num_batches <= 65535, "transform_sf: num_batches out of range");
+    DG_CHECK_ARG(k_psum == nullptr || (num_k_groups > 0 && num_batches == 1 && k_repeat == 1 && psum == nullptr),
+                 "K-grouped transform SF requires one logical batch, gran_k = 32 and a non-empty psum layout");
     if (dst_mn == 0 || k32_blocks == 0) return DG_OK;
 
     TransformSfArgs a{};
@@ -176,6 +205,7 @@ extern "C" int dg_transform_sf_launch(const void* src, int src_is_fp32,
     a.gran_mn = gran_mn; a.k_repeat = k_repeat; a.src_is_fp32 = src_is_fp32 ? 1 : 0;
     a.psum = psum; a.num_groups = num_groups; a.alignment = alignment;
     a.invalid_flag = invalid_flag;
+    a.k_psum = k_psum; a.num_k_groups = num_k_groups;
     a.tiles_m = (dst_mn + kTileRows - 1) / kTileRows;
     a.tiles_c = (a.dst_cols + kTileCols - 1) / kTileCols;
     const uint64_t tiles = (uint64_t)a.tiles_m * a.tiles_c;

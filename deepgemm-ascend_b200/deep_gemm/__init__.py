@@ -1,7 +1,7 @@
 """deep_gemm for NVIDIA B200: block-scaled FP8 / FP8xFP4 GEMM behind the DeepGEMM-Ascend Python API.
 
 The names, arguments and error text of the hot path follow the reference's `deep_gemm/__init__.py:25-81`;
-everything else of the reference (attention, MegaMoE, einsum, BF16 GEMM, ACLNN wrappers) is out of scope
+everything else of the reference (attention, MegaMoE, BF16 GEMM, ACLNN wrappers) is out of scope
 and not exported. Importing this package never initialises a CUDA context.
 """
 
@@ -28,6 +28,8 @@ from ._api import (  # noqa: F401
     get_recipe,
     get_theoretical_mk_alignment_for_contiguous_layout,
     init,
+    k_grouped_fp8_gemm_nt_contiguous,
+    k_grouped_fp8_gemm_tn_contiguous,
     m_grouped_fp8_fp4_gemm_nn_contiguous,
     m_grouped_fp8_fp4_gemm_nt_contiguous,
     m_grouped_fp8_fp4_gemm_nt_masked,
@@ -38,6 +40,7 @@ from ._api import (  # noqa: F401
     set_mk_alignment_for_contiguous_layout,
     set_npu_arch,
     set_num_sms,
+    transform_k_grouped_sf_into_required_layout,
     transform_sf_into_required_layout,
     use_deterministic_algorithms,
 )

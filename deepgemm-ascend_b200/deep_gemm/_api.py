@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes as C
 import threading
+import warnings
 from typing import Optional
 
 import torch
@@ -281,9 +282,18 @@ def _check_sf_layout(sf, mn, k, gran_mn, gran_k, num_groups) -> bool:
     return False
 
 
-def _launch_transform_sf(sf, mn, k, gran_mn, gran_k, psum_layout, tma_aligned: bool):
+def _check_psum_layout(psum_layout, sf) -> int:
+    _host_assert(psum_layout.device == sf.device, 'grouped_layout must be on the same device as the SF input')
+    _host_assert(psum_layout.dtype == torch.int32 and psum_layout.dim() == 1 and psum_layout.is_contiguous(),
+                 'grouped_layout must be a contiguous 1D int32 tensor')
+    _host_assert(psum_layout.numel() > 0, 'grouped_layout must contain at least one group')
+    return psum_layout.numel()
+
+
+def _launch_transform_sf(sf, mn, k, gran_mn, gran_k, psum_layout, tma_aligned: bool, k_psum_layout=None):
     """csrc/jit_kernels/transform_sf.hpp:15-105. With `tma_aligned` the column stride of the result is
-    rounded up to 8 elements (what the GEMM's TMA descriptor needs); the public entry point never does that."""
+    rounded up to 8 elements (what the GEMM's TMA descriptor needs); the public entry point never does that.
+    `psum_layout` pads along MN (m-grouped operands), `k_psum_layout` along K (k-grouped operands)."""
     squeeze = sf.dim() == 2
     if squeeze:
         sf = sf.unsqueeze(0)
@@ -293,11 +303,13 @@ def _launch_transform_sf(sf, mn, k, gran_mn, gran_k, psum_layout, tma_aligned: b
     num_groups = 0
     if psum_layout is not None:
         _host_assert(batches == 1, 'Grouped transform SF requires one logical batch and grouped_layout')
-        _host_assert(psum_layout.device == sf.device, 'grouped_layout must be on the same device as the SF input')
-        _host_assert(psum_layout.dtype == torch.int32 and psum_layout.dim() == 1 and psum_layout.is_contiguous(),
-                     'grouped_layout must be a contiguous 1D int32 tensor')
-        num_groups = psum_layout.numel()
-        _host_assert(num_groups > 0, 'grouped_layout must contain at least one group')
+        num_groups = _check_psum_layout(psum_layout, sf)
+    num_k_groups = 0
+    if k_psum_layout is not None:
+        _host_assert(batches == 1 and psum_layout is None,
+                     'Grouped transform SF requires one logical batch and grouped_layout')
+        _host_assert(gran_k == 32, 'K-grouped transform SF requires gran_k = 32')
+        num_k_groups = _check_psum_layout(k_psum_layout, sf)
     is_fp32 = sf.dtype == torch.float32
     k32 = _ceil_div(k, 32)
     dst_cols = sf.size(-1) if (not is_fp32 and gran_k == 32) else _ceil_div(k32, 2)
@@ -309,7 +321,8 @@ def _launch_transform_sf(sf, mn, k, gran_mn, gran_k, psum_layout, tma_aligned: b
             sf.data_ptr(), int(is_fp32), sf.stride(-2), sf.stride(-1), sf.stride(0), sf.size(-2), sf.size(-1),
             storage.data_ptr(), col_stride, dst_cols * col_stride, mn, k32, gran_mn, gran_k // 32, batches,
             psum_layout.data_ptr() if psum_layout is not None else None, num_groups, MK_ALIGNMENT,
-            None, _stream_ptr(sf.device))
+            None, k_psum_layout.data_ptr() if k_psum_layout is not None else None, num_k_groups,
+            _stream_ptr(sf.device))
         L.check(rc)
     return out.squeeze(0) if squeeze else out
 
@@ -330,7 +343,21 @@ def transform_sf_into_required_layout(sf: torch.Tensor, mn: int, k: int, recipe,
     return _transform_sf(sf, mn, k, int(gran_mn), int(gran_k), num_groups, disable_ue8m0_cast, psum_layout, False)
 
 
-def _transform_sf(sf, mn, k, gran_mn, gran_k, num_groups, disable_ue8m0_cast, psum_layout, tma_aligned):
+def transform_k_grouped_sf_into_required_layout(sf: torch.Tensor, mn: int, k: int, recipe, is_sfa: Optional[bool],
+                                                psum_layout: torch.Tensor) -> torch.Tensor:
+    """csrc/apis/layout.hpp:94-111. Scale factors of a k-grouped operand ([MN, K] with K holding the groups in
+    psum layout): same result layout as above, with every K unit inside a group's padding set to 0 (a 32-block
+    of an fp32 source, a whole packed column of an int16 source; tests/test_layout.py:95-97). An input that
+    already has the required layout is returned as it is."""
+    _host_assert(is_sfa is not None, 'is_sfa must be set')
+    recipe = tuple(recipe)
+    _host_assert(len(recipe) == 3, 'recipe must have 3 elements')
+    gran_mn, gran_k = int(recipe[0] if is_sfa else recipe[1]), int(recipe[2])
+    return _transform_sf(sf, mn, k, gran_mn, gran_k, None, False, None, False, k_psum_layout=psum_layout)
+
+
+def _transform_sf(sf, mn, k, gran_mn, gran_k, num_groups, disable_ue8m0_cast, psum_layout, tma_aligned,
+                  k_psum_layout=None):
     if _check_sf_layout(sf, mn, k, gran_mn, gran_k, num_groups):
         if not tma_aligned or mn % 8 == 0 or sf.is_meta:
             return sf
@@ -338,7 +365,7 @@ def _transform_sf(sf, mn, k, gran_mn, gran_k, num_groups, disable_ue8m0_cast, ps
         _host_assert(not disable_ue8m0_cast,
                      'Float32 SF must be converted into ue8m0, but disable_ue8m0_cast is set true')
     return _launch_transform_sf(sf, mn, gran_mn=gran_mn, gran_k=gran_k, k=k, psum_layout=psum_layout,
-                                tma_aligned=tma_aligned)
+                                tma_aligned=tma_aligned, k_psum_layout=k_psum_layout)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -411,6 +438,10 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
     elif gemm_type == L.GEMM_M_GROUPED_MASKED:
         g, m, n, k = _shape_by_spec('gmnk', [('gmk', a), ('gnk', b), ('gmn', d), ('g', grouped_layout)])
         _host_assert(major_a == L.MAJOR_K, 'A must be K-major for the m-grouped masked layout')
+    elif gemm_type == L.GEMM_K_GROUPED_PSUM:
+        g, m, n, k = _shape_by_spec('gmnk', [('mk', a), ('nk', b), ('gmn', d), ('g', grouped_layout)])
+        _host_assert(major_a == L.MAJOR_MN, 'A must be MN-major for the k-grouped layout')
+        _host_assert(major_b == L.MAJOR_MN, 'B must be MN-major for the k-grouped layout')
     elif gemm_type == L.GEMM_BATCHED:
         g, m, n, k = _shape_by_spec('bmnk', [('bmk', a), ('bnk', b), ('bmn', d)])
     else:
@@ -436,10 +467,14 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
 
     gran_m, gran_n, gran_k_a, gran_k_b = get_recipe(recipe, recipe_a, recipe_b)
     masked = gemm_type in (L.GEMM_M_GROUPED_MASKED, L.GEMM_BATCHED)    # A, SFA and D carry the group dimension
-    sfa = _transform_sf(sfa_in, m, k, gran_m, gran_k_a, g if masked else None, disable_ue8m0_cast,
-                        grouped_layout if gemm_type == L.GEMM_M_GROUPED_PSUM else None, True)
-    sfb = _transform_sf(sfb_in, n, k, gran_n, gran_k_b, g if gemm_type != L.GEMM_NORMAL else None,
-                        disable_ue8m0_cast, None, True)
+    if gemm_type == L.GEMM_K_GROUPED_PSUM:
+        sfa = _transform_sf(sfa_in, m, k, gran_m, gran_k_a, None, False, None, True, k_psum_layout=grouped_layout)
+        sfb = _transform_sf(sfb_in, n, k, gran_n, gran_k_b, None, False, None, True, k_psum_layout=grouped_layout)
+    else:
+        sfa = _transform_sf(sfa_in, m, k, gran_m, gran_k_a, g if masked else None, disable_ue8m0_cast,
+                            grouped_layout if gemm_type == L.GEMM_M_GROUPED_PSUM else None, True)
+        sfb = _transform_sf(sfb_in, n, k, gran_n, gran_k_b, g if gemm_type != L.GEMM_NORMAL else None,
+                            disable_ue8m0_cast, None, True)
 
     _host_assert(a.dtype in _DTYPES and b.dtype in _DTYPES, 'Unsupported operand dtypes')
     a_use, b_use = _tma_ready_operand(a, major_a), _tma_ready_operand(b, major_b)
@@ -455,7 +490,7 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
     desc.outer_stride_d = d.stride(-2)
     desc.group_stride_a = a_use.stride(0) if masked else 0
     desc.group_stride_b = b_use.stride(0) if b_use.dim() == 3 else 0
-    desc.group_stride_d = d.stride(0) if masked else 0
+    desc.group_stride_d = d.stride(0) if masked or gemm_type == L.GEMM_K_GROUPED_PSUM else 0
     desc.sfa_stride, desc.sfb_stride = sfa.stride(-1), sfb.stride(-1)
     desc.sfa_group_stride = sfa.stride(0) if sfa.dim() == 3 else 0
     desc.sfb_group_stride = sfb.stride(0) if sfb.dim() == 3 else 0
@@ -463,6 +498,7 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
     desc.gemm_type = gemm_type
     desc.grouped_layout = _ptr(grouped_layout) if grouped_layout is not None else None
     desc.num_groups = g
+    # (for the k-grouped layout `expected_m` carries the expected K of one group, csrc/apis/gemm.hpp:35-43)
     desc.expected_m = int(expected_m) if expected_m else (m // g if gemm_type == L.GEMM_M_GROUPED_PSUM and g else m)
     if isinstance(epilogue_obj, Alpha):
         desc.epilogue, desc.alpha = L.EPILOGUE_ALPHA, epilogue_obj.alpha
@@ -561,6 +597,32 @@ def m_grouped_fp8_fp4_gemm_nt_masked(a, b, d, masked_m, expected_m, recipe=None,
 
 
 m_grouped_fp8_gemm_nt_masked = m_grouped_fp8_fp4_gemm_nt_masked
+
+
+def k_grouped_fp8_gemm_tn_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, recipe=(1, 1, 32), compiled_dims='mn',
+                                     use_psum_layout=True, epilogue=None, *, config=None):
+    """csrc/apis/gemm.hpp:325-384. Weight-gradient GEMM of an MoE layer: a = (A [K, M], sfA [ceil(K/32), M]),
+    b = (B [K, N], sfB), K holding G groups in psum layout (`grouped_layout[g]` = end of group g, each group
+    starting at the previous end rounded up to the 256 alignment, operand data zero in the padding);
+    D[g] = A[group g]^T @ B[group g] (+ C[g] when `c` is D itself), D[g] = 0 (or kept) for an empty group."""
+    (a_data, sfa), (b_data, sfb) = _transposed(a, True, 0, 1), _transposed(b, True, 0, 1)
+    _host_assert(a_data.dtype == torch.float8_e4m3fn and b_data.dtype == torch.float8_e4m3fn,
+                 'k-grouped matmul is built for FP8 operands')
+    _host_assert(d.dtype in (torch.bfloat16, torch.float32))
+    _host_assert(use_psum_layout is True)
+    k, g = a_data.size(-1), grouped_layout.numel()
+    expected_k = max(1, sum(ks_cpu) // len(ks_cpu)) if ks_cpu else (k // g if g else k)
+    _run_gemm(L.GEMM_K_GROUPED_PSUM, a_data, b_data, d, c, _resolve_epilogue(epilogue, c, d), sfa, sfb,
+              tuple(recipe), None, None, grouped_layout, compiled_dims, False, expected_m=expected_k, config=config)
+
+
+def k_grouped_fp8_gemm_nt_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, recipe=(1, 1, 32), compiled_dims='mn',
+                                     use_psum_layout=True, epilogue=None, *, config=None):
+    """csrc/apis/gemm.hpp:386-410. Deprecated: takes A [M, K] and B [N, K] and forwards their transposes."""
+    warnings.warn('Calling k_grouped_fp8_gemm_nt_contiguous is deprecated, please transpose a, b into [k, m] and [k, n] '
+                  'shape and call `k_grouped_fp8_gemm_tn_contiguous` instead', DeprecationWarning, stacklevel=2)
+    k_grouped_fp8_gemm_tn_contiguous(_transposed(a, True, 0, 1), _transposed(b, True, 0, 1), d, ks_cpu, grouped_layout,
+                                     c, recipe, compiled_dims, use_psum_layout, epilogue, config=config)
 
 
 def fp8_bmm(a, b, d, c=None, recipe=(1, 1, 32), compiled_dims='nk', epilogue=None, *, config=None):

@@ -62,7 +62,7 @@ _PROTOTYPES = {
     'dg_transform_sf_launch': (C.c_int, [
         C.c_void_p, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32,
         C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
-        C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
+        C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     'dg_pad_rows_launch': (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p]),
     'dg_l2_flush_launch': (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
     'dg_device_status': (C.c_int, [C.POINTER(C.c_int32)]),

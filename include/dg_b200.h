@@ -45,7 +45,7 @@ typedef enum { DG_MAJOR_K = 0, DG_MAJOR_MN = 1 } dg_major_t;
 typedef enum {
     DG_GEMM_NORMAL = 0,
     DG_GEMM_M_GROUPED_PSUM = 1,
-    DG_GEMM_K_GROUPED_PSUM = 2, /* not built */
+    DG_GEMM_K_GROUPED_PSUM = 2, /* A [M,K_total], B [N,K_total] (both MN-major), D [G,M,N]; csrc/apis/gemm.hpp:351-384 */
     DG_GEMM_BATCHED = 3,        /* A [B,M,K], B [B,N,K], D [B,M,N]; csrc/apis/einsum.hpp:37-71 */
     DG_GEMM_M_GROUPED_MASKED = 4
 } dg_gemm_type_t;
@@ -71,6 +71,8 @@ typedef enum {
  *   M-grouped psum    A [M_total,K]    B [G,N,K]      D [M_total,N]     grouped_layout = psum int32[G]
  *   M-grouped masked  A [G,max_m,K]    B [G,N,K]      D [G,max_m,N]     grouped_layout = masked_m int32[G], m = max_m
  *   Batched           A [G,M,K]        B [G,N,K]      D [G,M,N]         num_groups = G, no layout array
+ *   K-grouped psum    A [M,K_total]    B [N,K_total]  D [G,M,N]         grouped_layout = psum int32[G] along K; empty
+ *                                                                       groups give D[g] = 0 (or leave it when accumulating)
  *
  * "[MN,K]" is the logical shape; `major_*` says which axis is contiguous in memory and
  * `outer_stride_*` is the stride of the other axis in ELEMENTS (bytes for packed FP4 operands:
@@ -172,6 +174,8 @@ int dg_gemm_dry_run(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config);
  *   k32_blocks     number of 32-wide K blocks of the operand, ceil(K/32)
  *   k_repeat       1 (gran_k = 32) or 4 (gran_k = 128: each source scale covers four blocks)
  *   psum           NULL, or int32[num_groups] psum layout: rows in a group's padding get scale byte 0
+ *   k_psum         NULL, or int32[num_k_groups] psum layout along K (K-grouped operands,
+ *                  csrc/apis/layout.hpp:94-111): scales of the K units inside a group's padding become 0
  *   invalid_flag   NULL, or a device int32 set to 1 when an fp32 scale is negative or has mantissa bits
  *                  (the reference asserts on device, transform_sf.hpp:13-21; this library never traps)
  */
@@ -181,7 +185,8 @@ int dg_transform_sf_launch(const void* src, int src_is_fp32,
                            int16_t* dst, uint64_t dst_col_stride, uint64_t dst_batch_stride,
                            uint32_t dst_mn, uint32_t k32_blocks, uint32_t gran_mn, uint32_t k_repeat,
                            uint32_t num_batches, const int32_t* psum, uint32_t num_groups,
-                           uint32_t alignment, int32_t* invalid_flag, void* stream);
+                           uint32_t alignment, int32_t* invalid_flag,
+                           const int32_t* k_psum, uint32_t num_k_groups, void* stream);
 
 /* Copy a 2-D byte matrix into a buffer whose row pitch satisfies the 16-byte rule of TMA, zero
  * filling the tail of each row. Used for operands whose contiguous extent is not a multiple of 16

@@ -25,6 +25,7 @@ from .mxgemm import (  # noqa: F401
     dequantize,
     e2m1_to_e4m3_byte,
     gemm_ref,
+    k_grouped_psum_ref,
     m_grouped_masked_ref,
     m_grouped_psum_ref,
     max_rel_err,

@@ -7,7 +7,7 @@ Restates the ground truth used by the reference's tests:
   * N(0,1) block quantisation: tests/generators.py:34-58 (FP4 rounding
     boundaries, nibble packing), :61-95 (``quantize_with_major``);
   * expected outputs: tests/generators.py:300-322 (dense, alpha/bias/acc),
-    :324-359 (m-grouped psum layout);
+    :324-359 (m-grouped psum layout), :361-398 (k-grouped psum layout);
   * metric: tests/utils.py:36-43 (``calc_diff``);
   * FP4 -> E4M3 byte map: deep_gemm/include/deep_gemm/fp8_dequant_gemm.hpp:24-38.
 
@@ -136,6 +136,20 @@ def m_grouped_psum_ref(a_deq: torch.Tensor, b_deq: torch.Tensor, psum: list[int]
     for g, span in enumerate(psum_valid_spans(psum, alignment)):
         d[span] = (a_deq[span].float() @ b_deq[g].float().T).to(out_dtype)
     return d
+
+
+def k_grouped_psum_ref(a_deq: torch.Tensor, b_deq: torch.Tensor, psum: list[int], out_dtype: torch.dtype,
+                       c: torch.Tensor | None = None, alignment: int = 256) -> torch.Tensor:
+    """D[g] = A[span g]^T @ B[span g] (+ C[g]) with ``a_deq`` [K, M] and ``b_deq`` [K, N]; span g is
+    [align(psum[g-1]), psum[g]) along K; an empty span gives 0 (+ C[g]) (tests/generators.py:392-396).
+    With ``c`` the sum is formed in FP32 before the one cast, as the accumulating kernel does."""
+    from .sf_layout import psum_valid_spans
+    d = torch.zeros(len(psum), a_deq.shape[1], b_deq.shape[1], dtype=torch.float32)
+    for g, span in enumerate(psum_valid_spans(psum, alignment)):
+        d[g] = a_deq[span].float().T @ b_deq[span].float()
+        if c is not None:
+            d[g] += c[g].float()
+    return d.to(out_dtype)
 
 
 def m_grouped_masked_ref(a_deq: torch.Tensor, b_deq: torch.Tensor, masked_m: list[int],

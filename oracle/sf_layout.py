@@ -57,12 +57,21 @@ def _ue8m0_bytes(sf: torch.Tensor) -> torch.Tensor:
 
 
 def required_sf_layout(sf: torch.Tensor, mn: int, k: int, gran_mn: int, gran_k: int = 32,
-                       psum: list[int] | None = None, alignment: int = 256) -> torch.Tensor:
+                       psum: list[int] | None = None, alignment: int = 256,
+                       k_psum: list[int] | None = None) -> torch.Tensor:
     """Any accepted SF input -> the required int16 MN-major layout.
 
     ``sf`` is fp32 [..., ceil(MN/gran_mn), ceil(K/gran_k)] or int16
-    [..., ceil(MN/gran_mn), ceil(K/(2*gran_k))] in any major."""
+    [..., ceil(MN/gran_mn), ceil(K/(2*gran_k))] in any major. ``psum`` zeroes the
+    padding rows of an m-grouped operand; ``k_psum`` zeroes the padding K units of
+    a k-grouped operand (32-blocks of an fp32 source, whole packed columns of an
+    int16 source: tests/test_layout.py:95-97)."""
     assert gran_k in (32, 128)
+    if k_psum is not None:
+        assert gran_k == 32 and psum is None
+        sf = sf.clone()
+        for span in psum_padding_spans(k_psum, alignment, 32 if sf.dtype == torch.float32 else 64):
+            sf[..., span] = 0
     k32 = ceil_div(k, 32)
     if sf.dtype == torch.float32:
         b = _ue8m0_bytes(sf)

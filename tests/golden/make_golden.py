@@ -100,6 +100,15 @@ def main(ref_root: str) -> None:
         out[name] = dict(m=m, n=n, k=k, a=raw(a[0]), sfa=a[1], b=raw(b[0]), sfb=b[1],
                          b_major=mb.name, d=d_ref, psum=g_layout.tolist(), recipe=d.recipe)
 
+    # ---- k-grouped psum cases (operands [K, M] / [K, N], scale padding poisoned by the generator) ----
+    for name, ks, acc, cdt in (('kgrouped_fp8_bf16', [300, 0, 170], False, torch.bfloat16),
+                               ('kgrouped_fp8_acc_f32', [96, 512, 33], True, torch.float32)):
+        d = Desc(GemmType.KGroupedContiguousWithPsumLayout, fp8, fp8, cdt, (40, 48, 256), Major.MN, Major.MN,
+                 accumulate=acc, num_groups=3, ks_cpu=ks)
+        (m, n, k), a, b, c, d_ref, (g_layout, _) = d.generate()
+        out[name] = dict(m=m, n=n, k=k, a=raw(a[0]), sfa=a[1], b=raw(b[0]), sfb=b[1], c=c, d=d_ref,
+                         psum=g_layout.tolist(), ks=ks, recipe=d.recipe)
+
     # ---- psum layout and N(0,1) quantiser ------------------------------------------------
     g.reset_seed()
     total, psum_list, _ = g.generate_psum_layout(300, 5, 256, device='cpu')
@@ -135,6 +144,27 @@ def main(ref_root: str) -> None:
                 sf=sf, mn=mn, k=k, gran=gran, expected=exp.contiguous(),
                 expected_stride=tuple(exp.stride()))
     out['sf_layout'] = sf_cases
+
+    # ---- scale-factor layout of k-grouped operands (tests/test_layout.py:77-104 with its own helpers) ----
+    kg_cases = {}
+    for dtype in (torch.float32, torch.int16):
+        for mn, sizes, gran, mn_major in ((72, (240, 0, 512, 100), 1, False), (130, (256, 33), 32, True),
+                                          (257, (16, 496, 1), 128, False)):
+            div = 32 if dtype == torch.float32 else 64
+            k, psum = g.generate_psum_layout_with_sizes(sizes, 256)
+            shape = ((mn + gran - 1) // gran, (k + div - 1) // div)
+            if dtype == torch.float32:
+                sf = (torch.randint(1, 255, shape, dtype=torch.int32) * (1 << 23)).view(torch.float32)
+            else:
+                sf = torch.randint(-32768, 32768, shape, dtype=torch.int16)
+            expected = sf.clone()
+            for span in g.iter_psum_sep(psum, 256, div):
+                expected[..., span] = 0
+                sf[..., span] = 0 if dtype == torch.int16 else -1
+            exp = layout_reference(expected, mn, gran)
+            kg_cases[f'{str(dtype)[6:]}_mn{mn}_k{k}_g{gran}_{"mn" if mn_major else "k"}major'] = dict(
+                sf=sf, mn=mn, k=k, gran=gran, psum=list(psum), mn_major=mn_major, expected=exp.contiguous())
+    out['sf_layout_k_grouped'] = kg_cases
 
     # ---- stochastic BF16 rounding model ----------------------------------------------------
     stochastic = load_reference_stochastic_model(ref_root)

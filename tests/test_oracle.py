@@ -46,6 +46,32 @@ def test_m_grouped_matches_reference_oracle(golden):
         assert torch.equal(d, c['d']), name
 
 
+def _k_grouped_operands(c):
+    """Dequantised [K, M] and [K, N]; the generator poisons the scales inside each group's padding,
+    where the data is zero."""
+    a = oracle.dequantize(oracle.decode_e4m3(c['a']), c['sfa'], 32, 1)
+    b = oracle.dequantize(oracle.decode_e4m3(c['b']), c['sfb'], 32, 1)
+    return a, b
+
+
+def test_k_grouped_matches_reference_oracle(golden):
+    for name in ('kgrouped_fp8_bf16', 'kgrouped_fp8_acc_f32'):
+        c = golden[name]
+        a, b = _k_grouped_operands(c)
+        d = oracle.k_grouped_psum_ref(a, b, c['psum'], c['d'].dtype, c=c['c'])
+        assert d.shape == c['d'].shape == (3, c['m'], c['n'])
+        assert torch.equal(d, c['d']), name
+    assert golden['kgrouped_fp8_bf16']['d'][1].abs().max() == 0        # the empty group
+
+
+def test_k_grouped_sf_layout_model(golden):
+    cases = golden['sf_layout_k_grouped']
+    assert len(cases) == 6
+    for name, c in cases.items():
+        out = oracle.required_sf_layout(c['sf'], c['mn'], c['k'], c['gran'], k_psum=c['psum'])
+        assert out.stride(-2) == 1 and torch.equal(out, c['expected']), name
+
+
 def test_psum_layout(golden):
     c = golden['psum_layout']
     sizes, last = [], 0
