@@ -150,20 +150,28 @@ static uint32_t tmem_cols_for(uint32_t block_n, uint32_t accum_stages) {
     return cols;
 }
 
-static uint32_t max_stages_for(uint32_t block_n, uint32_t cta_group, bool decode_b, uint32_t store_bufs) {
+static uint32_t max_stages_for(uint32_t block_n, uint32_t cta_group, bool decode_b, uint32_t store_bufs, uint32_t cluster_split) {
     constexpr uint32_t kSmemCap = 227 * 1024;
     uint32_t best = 0;
     for (uint32_t s = 1; s <= kMaxStages; ++s)
-        if (make_smem_layout(block_n, s, cta_group, decode_b, store_bufs).total <= kSmemCap) best = s;
+        if (make_smem_layout(block_n, s, cta_group, decode_b, store_bufs, cluster_split).total <= kSmemCap) best = s;
     return best;
 }
+
+// Two ways to split K: partial sums reduced into an FP32 workspace that a second kernel casts (reserved[3] == 0), or
+// the splits of one tile form a thread-block cluster and reduce through shared memory (reserved[3] == 1).
+static bool splits_in_cluster(const dg_gemm_config_t& c) { return c.split_k > 1 && c.reserved[3] != 0; }
+static bool splits_in_workspace(const dg_gemm_config_t& c) { return c.split_k > 1 && c.reserved[3] == 0; }
+constexpr uint32_t kMaxClusterSplit = 8;        // portable cluster size
 
 // Fill the derived fields of a configuration whose block_n / cta_group / split_k are set.
 static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     const uint32_t num_sms = effective_num_sms(d);
     c.block_m = kBlockM * c.cta_group;
     c.block_k = kBlockK;
-    const bool split = c.split_k > 1;
+    if (c.split_k <= 1) c.reserved[3] = 0;
+    const bool split = splits_in_workspace(c);
+    const bool in_cluster = splits_in_cluster(c);
     const bool tma_ok = split || tma_store_ok(d);
     if (d.epilogue == DG_EPILOGUE_FP8_QUANT) c.epilogue_mode = kEpiFp8Quant;
     else if (split) c.epilogue_mode = kEpiTmaReduce;
@@ -179,8 +187,11 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
         DG_CHECK_ARG((c.block_n / c.cta_group) % 128 == 0, "MN-major B needs block_n / cta_group to be a multiple of 128");
     DG_CHECK_ARG(c.cta_group == 1 || d.gemm_type != DG_GEMM_M_GROUPED_MASKED, "masked grouped GEMM uses cta_group 1");
     DG_CHECK_ARG(!split || d.epilogue != DG_EPILOGUE_FP8_QUANT, "FP8 quantization cannot be combined with split-K");
-    DG_CHECK_ARG(!split || d.gemm_type == DG_GEMM_NORMAL, "split-K is only available for the dense GEMM");
+    DG_CHECK_ARG(c.split_k <= 1 || d.gemm_type == DG_GEMM_NORMAL, "split-K is only available for the dense GEMM");
     DG_CHECK_ARG(!split || d.epilogue != DG_EPILOGUE_STOCHASTIC_BF16, "stochastic rounding cannot be combined with split-K");
+    DG_CHECK_ARG(!in_cluster || (c.cta_group == 1 && c.split_k <= kMaxClusterSplit && d.b_dtype != DG_E2M1X2),
+                 "cluster split-K needs cta_group 1, unpacked B and at most %u splits", kMaxClusterSplit);
+    const uint32_t cluster_split = in_cluster ? c.split_k : 1u;
 
     const uint32_t accum_stages = (2 * c.block_n + 4 + 4 * (sfb_rows(c.block_n) / 128) <= 512) ? 2u : 1u;
     c.tmem_cols = tmem_cols_for(c.block_n, accum_stages);
@@ -192,19 +203,23 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     if (c.reserved[1] == 0) c.reserved[1] = 2u;
     DG_CHECK_ARG(c.reserved[1] >= 2 && c.reserved[1] <= kMaxStoreBufs, "store buffers per warp must be 2..4");
     const uint32_t store_bufs = c.reserved[1];
-    const uint32_t max_stages = max_stages_for(c.block_n, c.cta_group, decode_b, store_bufs);
+    uint32_t max_stages = max_stages_for(c.block_n, c.cta_group, decode_b, store_bufs, cluster_split);
     if (c.num_stages == 0 || c.num_stages > max_stages) c.num_stages = max_stages;
     DG_CHECK_ARG(c.num_stages >= 1, "tile does not fit in shared memory");
     if (c.num_stages > nkb * 4 && c.num_stages > 2) c.num_stages = nkb * 4 > 2 ? nkb * 4 : 2;
     if (c.num_stages > max_stages) c.num_stages = max_stages;
-    if (split) {
+    // cluster split-K stages its outgoing partial sums (16 KB per 32 columns) in the operand ring
+    DG_CHECK_ARG(!in_cluster || c.num_stages >= 3, "cluster split-K needs at least three pipeline stages");
+    if (c.split_k > 1) {
         DG_CHECK_ARG(c.split_k <= nkb, "split_k larger than the number of K blocks");
         // every split must own at least one K block
         const uint32_t per = ceil_div_u32(nkb, c.split_k);
         c.split_k = ceil_div_u32(nkb, per);
+        if (c.split_k <= 1) c.reserved[3] = 0;
     }
     // one CTA per SM: keep the dynamic shared memory above half of the SM's capacity
-    const uint32_t need = make_smem_layout(c.block_n, c.num_stages, c.cta_group, decode_b, store_bufs).total;
+    const uint32_t need = make_smem_layout(c.block_n, c.num_stages, c.cta_group, decode_b, store_bufs,
+                                           splits_in_cluster(c) ? c.split_k : 1u).total;
     c.smem_bytes = need < 120u * 1024 ? 120u * 1024 : need;
 
     uint32_t grid_units;
@@ -212,6 +227,11 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     if (d.gemm_type == DG_GEMM_NORMAL) {
         const uint64_t tiles = (uint64_t)ceil_div_u32(d.m, c.block_m) * ceil_div_u32(d.n, c.block_n) * c.split_k;
         grid_units = (uint32_t)(tiles < max_units ? tiles : max_units);
+        // cluster split-K is not persistent: one tile per CTA, the splits of a tile adjacent in the grid
+        if (splits_in_cluster(c)) {
+            DG_CHECK_ARG(tiles <= 0x7fffffffull, "too many tiles");
+            grid_units = (uint32_t)tiles;
+        }
     } else {
         uint64_t bound;   // an upper bound on the tile count; the real count is only known on device
         if (d.gemm_type == DG_GEMM_M_GROUPED_PSUM) bound = (uint64_t)ceil_div_u32(d.m, c.block_m) * ceil_div_u32(d.n, c.block_n);
@@ -296,10 +316,34 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
             }
         }
     }
+    // Cluster split-K (dense GEMM, single CTAs, unpacked B): the K splits of one tile run as one thread-block cluster
+    // and reduce through shared memory, so no second kernel and no FP32 round trip through L2. Modelled cost: the
+    // main loop of one split, the exchange (staging, bulk copies, waiting for the slowest rank, summation: measured
+    // ~6000 cycles), and a cluster launch that starts ~2.5 us later than a plain one.
+    bool best_in_cluster = false;
+    if (d.gemm_type == DG_GEMM_NORMAL && d.b_dtype != DG_E2M1X2 && d.major_b == DG_MAJOR_K) {
+        const uint64_t m_tiles = (rows + kBlockM - 1) / kBlockM;
+        for (uint32_t split = 2; split <= kMaxClusterSplit && nkb / split >= 2; ++split) {
+            for (uint32_t bn = 32; bn <= 256; bn += 32) {
+                if (bn > 32 && bn - 32 >= d.n) continue;
+                if (max_stages_for(bn, 1, false, 2, split) < 4) continue;
+                const uint64_t tiles = m_tiles * ceil_div_u32(d.n, bn) * split;
+                const uint64_t waves = (tiles + num_sms - 1) / num_sms;
+                const uint32_t kb_per = ceil_div_u32(nkb, split);
+                const double cycles = kb_per * k_block_cycles(1, bn) + bn * (d_fp32 ? 8.0 : 6.0) + 700.0 + 6000.0;
+                double cost = (double)waves * cycles / 1.8 + 2500.0;
+                if (cost < t_hbm) cost = t_hbm + 1e-3 * cost;
+                if (cost < best_cost * (1.0 - 1e-9)) {
+                    best_cost = cost; best_bn = bn; best_split = split; best_cg = 1; best_in_cluster = true;
+                }
+            }
+        }
+    }
     DG_CHECK_ARG(best_bn != 0, "no legal tiling for this problem");
     c.block_n = best_bn;
     c.split_k = best_split;
     c.cta_group = best_cg;
+    c.reserved[3] = best_in_cluster ? 1u : 0u;
     return complete_config(d, c);
 }
 
@@ -347,7 +391,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     GemmKernelArgs& a = plan.args;
     const bool masked = has_row_groups(d.gemm_type);       // A, SFA and D have a group / batch dimension
     const bool grouped = is_grouped(d.gemm_type);
-    const bool split = c.split_k > 1;
+    const bool split = splits_in_workspace(c);
     const uint32_t accum_stages = c.reserved[0];
     const bool k_grouped = d.gemm_type == DG_GEMM_K_GROUPED_PSUM;
     const uint32_t groups = (grouped && !k_grouped) ? d.num_groups : 1;     // group dimension of B / SFB (and A / SFA when `masked`)
@@ -380,6 +424,9 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.tmem_cols = c.tmem_cols;
     a.accum_stages = accum_stages;
     a.store_bufs = c.reserved[1];
+    a.k_stagger = c.reserved[2];
+    a.cluster_split = splits_in_cluster(c) ? c.split_k : 1u;
+    plan.cluster_x = c.cta_group > 1 ? c.cta_group : a.cluster_split;
     // Instruction descriptor (block-scaled, kind::mxf8f6f4): E4M3 x E4M3, UE8M0 scales, FP32 accumulate.
     a.idesc = ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) | ((c.block_n >> 3) << 17) | (1u << 23) |
               (((kBlockM * c.cta_group) >> 4) << 24);
@@ -516,9 +563,9 @@ static void maybe_print_config(const dg_gemm_desc_t& d, const dg_gemm_config_t& 
     static const bool enabled = [] { const char* e = getenv("DG_PRINT_CONFIGS"); return e && atoi(e) != 0; }();
     if (!enabled) return;
     fprintf(stderr, "[dg_b200] type=%d m=%u n=%u k=%u majors=%d%d d=%s acc=%d groups=%u -> block=%ux%ux%u stages=%u cta_group=%u "
-            "split_k=%u ctas=%u tmem=%u smem=%u epilogue=%u\n",
+            "split_k=%u%s ctas=%u tmem=%u smem=%u epilogue=%u\n",
             d.gemm_type, d.m, d.n, d.k, d.major_a, d.major_b, d.d_dtype == DG_F32 ? "f32" : "bf16", d.accumulate, d.num_groups,
-            c.block_m, c.block_n, c.block_k, c.num_stages, c.cta_group, c.split_k, c.num_ctas, c.tmem_cols, c.smem_bytes, c.epilogue_mode);
+            c.block_m, c.block_n, c.block_k, c.num_stages, c.cta_group, c.split_k, splits_in_cluster(c) ? " (cluster)" : "", c.num_ctas, c.tmem_cols, c.smem_bytes, c.epilogue_mode);
 }
 
 static int resolve_config(const dg_gemm_desc_t& d, const dg_gemm_config_t* in, dg_gemm_config_t& out) {
@@ -567,7 +614,7 @@ int dg_gemm_launch_static_scratch(const dg_gemm_desc_t* desc, const dg_gemm_conf
     if (int rc = resolve_config(*desc, config, c)) return rc;
     float* scratch = nullptr;
     size_t need = 0;
-    if (c.split_k > 1) {
+    if (splits_in_workspace(c)) {
         need = (size_t)desc->m * align_u64(desc->n, 4) * sizeof(float);
         if (need > DG_STATIC_SCRATCH_BYTES) {
             set_last_error("split-K scratch of %zu bytes (m=%u, n=%u) exceeds the built-in %u bytes: pass a config with "
@@ -607,7 +654,7 @@ size_t dg_gemm_workspace_bytes(const dg_gemm_desc_t* desc, const dg_gemm_config_
     if (desc == nullptr) return 0;
     dg_gemm_config_t c;
     if (validate(*desc) != DG_OK || resolve_config(*desc, config, c) != DG_OK) return 0;
-    if (c.split_k <= 1) return 0;
+    if (!splits_in_workspace(c)) return 0;
     return (size_t)desc->m * align_u64(desc->n, 4) * sizeof(float);
 }
 

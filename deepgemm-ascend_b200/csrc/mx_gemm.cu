@@ -119,7 +119,7 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = plan.cta_group;
+    attr[0].val.clusterDim.x = plan.cluster_x;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;

@@ -44,7 +44,7 @@ enum EpilogueMode : uint32_t { kEpiTmaStore = 0, kEpiTmaReduce = 1, kEpiPlainSto
 enum StatusCode : int32_t {
     kStatusOk = 0,
     kStatusTimeoutProducer = 101, kStatusTimeoutPacker = 102, kStatusTimeoutMma = 103,
-    kStatusTimeoutEpilogue = 104, kStatusTimeoutDrain = 105, kStatusTimeoutDecoder = 106,
+    kStatusTimeoutEpilogue = 104, kStatusTimeoutDrain = 105, kStatusTimeoutDecoder = 106, kStatusTimeoutReduce = 107,
 };
 
 struct GemmKernelArgs {
@@ -71,6 +71,8 @@ struct GemmKernelArgs {
     uint32_t idesc;                   // tcgen05 instruction descriptor without the scale ids
     uint32_t tmem_cols, accum_stages;
     uint32_t store_bufs;              // staging boxes per epilogue warp
+    uint32_t cluster_split;           // 1, or the K splits of one tile run as one cluster and reduce through shared memory
+    uint32_t k_stagger;               // dense GEMM: tile with column index nb starts its K loop at block (nb * k_stagger) % len
     int32_t* status;
     unsigned long long* trace;        // debugging aid: per-CTA timestamps (8 slots each), or nullptr
 };
@@ -130,6 +132,7 @@ struct Tile {
     uint32_t n0;          // first column of D == first row of B
     uint32_t b_z;         // third TMA coordinate of B / SFB (group)
     uint32_t kb_begin, kb_end;
+    uint32_t kb_rot;      // the loads walk the K blocks rotated by this much (CTAs that share A then read different lines)
 };
 
 template <int kCtaGroup>
@@ -192,6 +195,7 @@ struct Scheduler {
             t.b_z = 0;
             t.kb_begin = ks * p.k_blocks_per_split;
             t.kb_end = min(t.kb_begin + p.k_blocks_per_split, p.num_k_blocks);
+            t.kb_rot = (nb * p.k_stagger) % (t.kb_end - t.kb_begin);
         } else {
             const uint32_t mb_lin = tile / p.num_n_blocks, nb = tile - mb_lin * p.num_n_blocks;
             while (true) {
@@ -211,6 +215,7 @@ struct Scheduler {
             t.b_z = p.gemm_type == kKGroupedPsum ? 0u : cur_group;
             t.kb_begin = p.gemm_type == kKGroupedPsum ? cur_kb_begin : 0u;
             t.kb_end = p.gemm_type == kKGroupedPsum ? cur_kb_end : p.num_k_blocks;
+            t.kb_rot = 0;
         }
         tile += stride;
         return true;
@@ -253,11 +258,19 @@ __host__ __device__ __forceinline__ uint32_t sfb_rows(uint32_t block_n) { return
 
 // Shared-memory carve-up, computed identically on host and device.
 struct SmemLayout {
-    uint32_t store_bufs, a, b, b_raw, sf_raw_a, sf_raw_b, sf_pack_a, sf_pack_b, barriers, total;
+    uint32_t store_bufs, a, b, b_raw, sf_raw_a, sf_raw_b, sf_pack_a, sf_pack_b, reduce, barriers, total;
     uint32_t a_stage, b_stage, b_raw_stage, sfa_stage, sfb_stage;
 };
+// Cluster split-K: 32-column chunk c of the tile is finalised by cluster rank c % S, which receives the other ranks'
+// partial sums of that chunk as [128 rows][32 floats] slabs: slab index (c / S) * (S - 1) + sender.
+constexpr uint32_t kReduceSlabBytes = kBlockM * 32 * 4;
+__host__ __device__ __forceinline__ uint32_t cluster_reduce_bytes(uint32_t block_n, uint32_t cluster_split) {
+    if (cluster_split <= 1) return 0;
+    const uint32_t chunks = block_n / 32;
+    return (chunks + cluster_split - 1) / cluster_split * (cluster_split - 1) * kReduceSlabBytes;
+}
 __host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_t num_stages, uint32_t cta_group,
-                                                       bool decode_b, uint32_t store_bufs) {
+                                                       bool decode_b, uint32_t store_bufs, uint32_t cluster_split = 1) {
     SmemLayout L;
     L.a_stage = kBlockM * kBlockK;
     L.b_stage = (block_n / cta_group) * kBlockK;
@@ -275,6 +288,8 @@ __host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_
     L.sf_raw_b = off; off += num_stages * L.sfb_stage;
     L.sf_pack_a = off; off += num_stages * L.sfa_stage;
     L.sf_pack_b = off; off += num_stages * L.sfb_stage;
+    off = (off + 127u) & ~127u;
+    L.reduce = off; off += cluster_reduce_bytes(block_n, cluster_split);
     L.barriers = off; off += (3 * kMaxStages + 4) * 8 + 16;
     L.total = off + 1024;    // slack for the manual 1024-B alignment of the dynamic base
     return L;
@@ -340,7 +355,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const SmemLayout L = make_smem_layout(p.block_n, p.num_stages, kCtaGroup, kDecodeB, p.store_bufs);
+    const uint32_t cluster_split = (kCtaGroup == 1 && !kDecodeB) ? p.cluster_split : 1u;
+    const SmemLayout L = make_smem_layout(p.block_n, p.num_stages, kCtaGroup, kDecodeB, p.store_bufs, cluster_split);
 
     const uint32_t warp = threadIdx.x / 32, lane = lane_id();
     const uint32_t cta_rank = kCtaGroup == 2 ? cluster_ctarank() : 0u;
@@ -355,6 +371,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     auto tmem_empty_bar = [&](uint32_t e) { return bar_base + (3 * kMaxStages + 2 + e) * 8; };
     volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + L.barriers + (3 * kMaxStages + 4) * 8);
     const AbortFlag ab{tmem_ptr_smem + 1, p.status};
+    const uint32_t reduce_bar = bar_base + (3 * kMaxStages + 5) * 8;     // cluster split-K: partial sums have arrived
 
     const uint32_t num_stages = p.num_stages;
     const uint32_t load_n = p.block_n / kCtaGroup;            // rows of B this CTA fetches
@@ -373,6 +390,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             mbar_init(tmem_full_bar(e), 1);
             mbar_init(tmem_empty_bar(e), kNumEpilogueWarps * kCtaGroup);   // one arrival per epilogue warp
         }
+        if (cluster_split > 1) {
+            // the chunks this rank finalises arrive as bulk copies from the other ranks, counted in bytes
+            const uint32_t chunks = p.block_n / 32, r = cluster_ctarank();
+            const uint32_t owned = r < chunks ? (chunks - r + cluster_split - 1) / cluster_split : 0u;
+            mbar_init(reduce_bar, 1);
+            if (owned) mbar_arrive_expect_tx(reduce_bar, owned * (cluster_split - 1) * kReduceSlabBytes);
+        }
         fence_mbar_init();
         tma_prefetch_desc(&tm_a); tma_prefetch_desc(&tm_b);
         tma_prefetch_desc(&tm_sfa); tma_prefetch_desc(&tm_sfb);
@@ -383,7 +407,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         tmem_relinquish<kCtaGroup>();
     }
     tc_fence_before_sync();
-    if constexpr (kCtaGroup == 2) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
+    if (kCtaGroup == 2 || cluster_split > 1) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_ptr_smem[0];
     if (threadIdx.x == 0) trace_mark(p, 2);
@@ -399,7 +423,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             uint32_t stage = 0, phase = 0;
             bool ok = true, first_issue = true;
             while (ok && sched.next(t)) {
-                for (uint32_t kb = t.kb_begin; kb < t.kb_end; ++kb) {
+                const uint32_t kb_len = t.kb_end - t.kb_begin;
+                for (uint32_t i = 0; i < kb_len; ++i) {
+                    const uint32_t kb = t.kb_begin + (i + t.kb_rot >= kb_len ? i + t.kb_rot - kb_len : i + t.kb_rot);
                     if (!(ok = wait_barrier(empty_bar(stage), phase ^ 1, ab, kStatusTimeoutProducer))) break;
                     const uint32_t bar = full_bar(stage);
                     const uint32_t bytes = L.a_stage + (kDecodeB ? L.b_raw_stage : load_n * kBlockK) + L.sfa_stage + L.sfb_stage;
@@ -599,7 +625,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const uint32_t taddr = tmem_base + ((q * 32u) << 16) + e * p.block_n;
 
             // One 32-column chunk of this thread's row: alpha / bias, cast, stage, store.
-            auto process_chunk = [&](uint32_t (&v)[32], uint32_t c0) {
+            // `single`: the chunk goes out on its own (BF16 boxes normally pair two chunks).
+            auto process_chunk = [&](uint32_t (&v)[32], uint32_t c0, bool single) {
                 const uint32_t col0 = t.n0 + c0;
                 if (p.has_alpha) {
                     #pragma unroll
@@ -672,8 +699,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     // Stage a [32 rows x 128 B] box, 16-byte chunk c of row r at chunk (c ^ (r & 7)). A BF16 box holds two
                     // 32-column groups; when block_n is an odd multiple of 32 the last group goes out alone as a
                     // [32 rows x 64 B] box (64B swizzle: chunk c of row r at c ^ ((r >> 1) & 3)) through tm_d_tail.
-                    const uint32_t half = p.d_is_fp32 ? 0u : ((c0 / 32) & 1u);
-                    const bool tail = !p.d_is_fp32 && half == 0 && c0 + 32 >= p.block_n;
+                    const uint32_t half = (p.d_is_fp32 || single) ? 0u : ((c0 / 32) & 1u);
+                    const bool tail = !p.d_is_fp32 && half == 0 && (single || c0 + 32 >= p.block_n);
                     if (half == 0) {
                         // the buffer may still be read by the store issued `store_bufs` boxes ago
                         if (p.store_bufs == 2) tma_store_wait_read<1>();
@@ -733,18 +760,76 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
             };
 
-            // Two register sets: the TMEM load of the next chunk is in flight while this one is converted and staged.
             uint32_t va[32], vb[32];
+            if (cluster_split > 1) {
+                // Cluster split-K: this CTA holds the partial sums of its K range. Chunk c is finalised by rank
+                // c % S: everybody else pushes its partial chunk into that rank's shared memory, the owner adds
+                // the partials in rank order (so the result does not depend on timing) and runs the usual epilogue.
+                const uint32_t S = cluster_split, r = cluster_ctarank();
+                const uint32_t chunks = p.block_n / 32;
+                const uint32_t row_off = (q * 32 + lane) * 128, sw = lane & 7u;
+                // Outgoing chunks are staged in the operand ring (this CTA's only tile has been multiplied, so the
+                // ring is free) and leave as one 4 KB bulk copy per warp; the staging must stay untouched until the
+                // copy has been read, which the cluster barrier at the end of the kernel guarantees.
+                uint32_t sent = 0;
+                for (uint32_t c = 0; c < chunks; ++c) {
+                    const uint32_t owner = c % S;
+                    if (owner == r) continue;
+                    tmem_ld_32x32b_x32(taddr + c * 32, va);
+                    tmem_ld_wait();
+                    uint8_t* out = smem_gen + L.a + sent * kReduceSlabBytes + row_off;
+                    #pragma unroll
+                    for (uint32_t u = 0; u < 8; ++u)
+                        *reinterpret_cast<uint4*>(out + ((u ^ sw) * 16)) = make_uint4(va[u * 4], va[u * 4 + 1], va[u * 4 + 2], va[u * 4 + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const uint32_t slab = (c / S) * (S - 1) + (r < owner ? r : r - 1);
+                        bulk_copy_to_cluster(mapa_shared(smem_base + L.reduce + slab * kReduceSlabBytes + q * 4096, owner),
+                                             smem_base + L.a + sent * kReduceSlabBytes + q * 4096, 4096,
+                                             mapa_shared(reduce_bar, owner));
+                    }
+                    ++sent;
+                }
+                if (r < chunks) {
+                    if (!(ok = wait_barrier(reduce_bar, tile_iter & 1u, ab, kStatusTimeoutReduce))) break;
+                    for (uint32_t slot = 0, c = r; c < chunks; ++slot, c += S) {
+                        tmem_ld_32x32b_x32(taddr + c * 32, va);
+                        tmem_ld_wait();
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i) vb[i] = 0u;        // +0.0f
+                        for (uint32_t s = 0; s < S; ++s) {
+                            if (s == r) {
+                                #pragma unroll
+                                for (int i = 0; i < 32; ++i) vb[i] = __float_as_uint(__uint_as_float(vb[i]) + __uint_as_float(va[i]));
+                            } else {
+                                const uint8_t* slab = smem_gen + L.reduce + (slot * (S - 1) + (s < r ? s : s - 1)) * kReduceSlabBytes + row_off;
+                                #pragma unroll
+                                for (uint32_t u = 0; u < 8; ++u) {
+                                    const uint4 x = *reinterpret_cast<const uint4*>(slab + ((u ^ sw) * 16));
+                                    vb[u * 4] = __float_as_uint(__uint_as_float(vb[u * 4]) + __uint_as_float(x.x));
+                                    vb[u * 4 + 1] = __float_as_uint(__uint_as_float(vb[u * 4 + 1]) + __uint_as_float(x.y));
+                                    vb[u * 4 + 2] = __float_as_uint(__uint_as_float(vb[u * 4 + 2]) + __uint_as_float(x.z));
+                                    vb[u * 4 + 3] = __float_as_uint(__uint_as_float(vb[u * 4 + 3]) + __uint_as_float(x.w));
+                                }
+                            }
+                        }
+                        process_chunk(vb, c * 32, true);
+                    }
+                }
+            } else {
+            // Two register sets: the TMEM load of the next chunk is in flight while this one is converted and staged.
             tmem_ld_32x32b_x32(taddr, va);
             for (uint32_t c0 = 0; c0 < p.block_n; c0 += 64) {
                 tmem_ld_wait();
                 if (c0 + 32 < p.block_n) tmem_ld_32x32b_x32(taddr + c0 + 32, vb);
-                process_chunk(va, c0);
+                process_chunk(va, c0, false);
                 if (c0 + 32 < p.block_n) {
                     tmem_ld_wait();
                     if (c0 + 64 < p.block_n) tmem_ld_32x32b_x32(taddr + c0 + 64, va);
-                    process_chunk(vb, c0 + 32);
+                    process_chunk(vb, c0 + 32, false);
                 }
+            }
             }
             // this accumulator may be overwritten by the next-but-one tile
             tc_fence_before_sync();
@@ -762,7 +847,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
     // ============================================================================ teardown
     tc_fence_before_sync();
-    if constexpr (kCtaGroup == 2) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
+    if (kCtaGroup == 2 || cluster_split > 1) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
     if (warp == 2) {
         tc_fence_after_sync();
         tmem_dealloc<kCtaGroup>(tmem_base, p.tmem_cols);

@@ -66,6 +66,12 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+// Bulk copy from this CTA's shared memory into the shared memory of a CTA of this cluster; the bytes are counted
+// on a barrier of the destination CTA (both destination addresses come from mapa_shared). 16-byte granularity.
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t cluster_dst, uint32_t src, uint32_t bytes, uint32_t cluster_bar) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(cluster_dst), "r"(src), "r"(bytes), "r"(cluster_bar) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }

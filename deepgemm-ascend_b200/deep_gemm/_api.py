@@ -519,6 +519,10 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
         for key, value in config.items():
             if key == 'store_bufs':
                 cfg.reserved[1] = int(value)
+            elif key == 'k_stagger':
+                cfg.reserved[2] = int(value)
+            elif key == 'cluster_split':
+                cfg.reserved[3] = int(value)
             else:
                 setattr(cfg, key, int(value))
     cfg_ptr = C.byref(cfg) if cfg is not None else None

@@ -50,7 +50,8 @@ class GemmConfig(C.Structure):
 
     def as_dict(self) -> dict:
         return {name: getattr(self, name) for name, _ in self._fields_ if name != 'reserved'} | {
-            'accum_stages': self.reserved[0], 'store_bufs': self.reserved[1]}
+            'accum_stages': self.reserved[0], 'store_bufs': self.reserved[1], 'k_stagger': self.reserved[2],
+            'cluster_split': self.reserved[3]}
 
 
 _PROTOTYPES = {

@@ -95,6 +95,43 @@ def test_dense_forced_tilings():
     _dense(128, 512, 4096, config={'block_n': 128, 'split_k': 4}, seed=1)
 
 
+@pytest.mark.parametrize('bn,split', [(32, 2), (64, 3), (64, 8), (96, 3), (96, 5), (128, 2), (128, 4), (128, 5),
+                                      (160, 2), (192, 2), (192, 3)])
+def test_dense_cluster_split_k(bn, split):
+    """The K splits of one tile run as one thread-block cluster: every rank pushes its partial sums of the
+    32-column chunks it does not own into the owner's shared memory; the owner adds them in rank order."""
+    cfg = {'block_n': bn, 'split_k': split, 'cluster_split': 1}
+    _dense(128, 512, 4096, config=cfg)
+    _dense(128, 512, 4096, config=cfg, bias=True)
+    _dense(100, 500, 4096, config=cfg, out=torch.float32, acc=True)
+    _dense(64, 2112, 7168, config=cfg, out=torch.float32)
+
+
+def test_dense_cluster_split_k_variants():
+    cfg = {'block_n': 128, 'split_k': 4, 'cluster_split': 1}
+    _dense(300, 640, 2048, config=cfg)                                  # three row blocks, each its own clusters
+    _dense(128, 4096, 7168, config=cfg, dist='normal', recipe=(1, 128, 128), alpha=0.5)
+    _dense(128, 516, 2000, config=cfg, out=torch.bfloat16, acc=True)    # K tail, odd N: plain stores / atomics
+    _dense(128, 1000, 4096, config={'block_n': 96, 'split_k': 3, 'cluster_split': 1}, trans='tt')    # MN-major A
+    # the result is the sum of the partials in rank order: two runs agree bit for bit
+    seed_all(7)
+    a, sfa, _ = uniform_fp8((128, 4096), (1, 32))
+    b, sfb, _ = uniform_fp8((1024, 4096), (1, 32))
+    outs = []
+    for _ in range(2):
+        d = torch.empty(128, 1024, dtype=torch.float32, device='cuda')
+        deep_gemm.fp8_gemm_nt((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d, config=cfg)
+        outs.append(d)
+    assert torch.equal(outs[0], outs[1])
+    # heuristic choice for a decode shape (prints nothing; must simply be right)
+    _dense(128, 2112, 7168, dist='normal', recipe=(1, 128, 128))
+    _dense(64, 4096, 7168, dist='normal', recipe=(1, 128, 128), bias=True)
+    with pytest.raises(RuntimeError):
+        _dense(512, 512, 1024, config={'cta_group': 2, 'block_n': 128, 'split_k': 2, 'cluster_split': 1})
+    with pytest.raises(RuntimeError):
+        _dense(128, 512, 4096, config={'block_n': 128, 'split_k': 9, 'cluster_split': 1})
+
+
 @pytest.mark.parametrize('bn', [32, 64, 96, 128, 160, 224, 256])
 def test_dense_cta_pair(bn):
     """Two CTAs of a cluster share one 256-row UMMA; each loads its own A rows and half of the B tile."""

@@ -149,10 +149,15 @@ def test_heuristic_respects_hardware_limits():
             assert c['smem_bytes'] <= 227 * 1024 and 1 <= c['num_stages'] <= 12
             assert c['tmem_cols'] in (32, 64, 128, 256, 512)
             assert c['accum_stages'] * c['block_n'] + 12 <= 512
-            assert 1 <= c['num_ctas'] <= 148
             assert c['split_k'] >= 1 and (c['split_k'] == 1 or m <= 1024)
-            if c['split_k'] > 1:
-                assert lib.dg_gemm_workspace_bytes(ctypes.byref(desc), ctypes.byref(cfg)) >= m * n * 4
+            ws = lib.dg_gemm_workspace_bytes(ctypes.byref(desc), ctypes.byref(cfg))
+            if c['split_k'] > 1 and c['cluster_split']:
+                # the splits of a tile form a cluster (at most 8 CTAs) and need no workspace; the grid is not persistent
+                assert c['split_k'] <= 8 and c['cta_group'] == 1 and c['num_ctas'] % c['split_k'] == 0 and ws == 0
+                assert c['num_stages'] >= 3
+            else:
+                assert 1 <= c['num_ctas'] <= 148
+                assert (ws >= m * n * 4) if c['split_k'] > 1 else ws == 0
 
 
 def test_c_abi_validation_messages():
