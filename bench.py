@@ -1,8 +1,10 @@
 """Benchmark of the block-scaled FP8 GEMM hot path on B200.
 
 One "step" is one pass over the dense FP8 NT sweep named by the baseline: M in {64, 128, 4096} times six (N, K)
-pairs, BF16 output, A quantised per 1x128 and B per 128x128 from N(0,1) data (synthetic, seeded). Every GEMM of a
-step is timed on the device with its own CUDA-event pair after an untimed L2 flush; a step's time is the sum.
+pairs, BF16 output, A quantised per 1x128 and B per 128x128 from N(0,1) data (synthetic, seeded). Every GEMM has its
+own operands, so a step touches about 1.5 GB and no launch finds its inputs in L2. The steps are timed on the device
+with one CUDA-event pair around all of them, each step being one replay of a CUDA graph of the 18 launches; a second
+pass with one event pair per launch gives the per-shape table and the roofline figures.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload dense|grouped|masked]
 
@@ -213,23 +215,26 @@ def run_reference(args, rank, world):
 def run_dense(args, rank, world, device):
     import deep_gemm
     from deep_gemm import _lib as L
-    from deep_gemm.testing import l2_flush_buffer
     lib = L.lib()
     pk = peaks()
     stream = torch.cuda.current_stream(device)
     sptr = stream.cuda_stream
-    flush = l2_flush_buffer(device)
-
     cases = [DenseCase(m, n, k, device, seed=1000 * rank + i)
              for i, (m, (n, k)) in enumerate((m, nk) for m in M_LIST for nk in NK_LIST)]
     torch.cuda.synchronize(device)
 
-    def timed_step(record):
+    # One step = the 18 GEMMs back to back. Every GEMM has its own operands and the sweep touches far more than the
+    # L2 holds between two uses of the same buffer (`footprint` below), so every launch finds its inputs in HBM
+    # without a flush kernel in between.
+    footprint = sum(c.bytes for c in cases)
+    l2_bytes = torch.cuda.get_device_properties(device).L2_cache_size
+    assert footprint > 4 * l2_bytes, 'the sweep must not fit in L2'
+
+    def sweep(stream_ptr, record=None):
         for ci, c in enumerate(cases):
-            L.check(lib.dg_l2_flush_launch(flush.data_ptr(), flush.numel(), sptr))
             if record is not None:
                 record[ci][0].record(stream)
-            c.launch(lib, sptr)
+            c.launch(lib, stream_ptr)
             if record is not None:
                 record[ci][1].record(stream)
 
@@ -238,23 +243,56 @@ def run_dense(args, rank, world, device):
             torch.distributed.barrier()
         torch.cuda.synchronize(device)
 
-    for _ in range(max(args.warmup, 3)):
-        timed_step(None)
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        sweep(sptr)
     barrier()
+    # The step as a CUDA graph (launch-bound for the small shapes otherwise); plain stream launches if capture fails.
+    graph, launches_per_step = None, 0
+    try:
+        side = torch.cuda.Stream(device)
+        graph = torch.cuda.CUDAGraph()
+        launches0 = lib.dg_kernel_launch_count()
+        with torch.cuda.graph(graph, stream=side):
+            sweep(torch.cuda.current_stream(device).cuda_stream)
+        launches_per_step = lib.dg_kernel_launch_count() - launches0
+    except Exception as exc:      # noqa: BLE001 - any capture problem falls back to plain launches
+        print(f'bench: graph capture failed ({exc}); timing plain stream launches', file=sys.stderr)
+        graph = None
+        torch.cuda.synchronize(device)
+
+    def step():
+        if graph is not None:
+            graph.replay()
+        else:
+            sweep(sptr)
+
+    for _ in range(warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(device.index) if rank == 0 else None
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = lib.dg_kernel_launch_count()
+    t_begin.record(stream)
+    for _ in range(args.steps):
+        step()
+    t_end.record(stream)
+    barrier()
+    launches = launches_per_step * args.steps if graph is not None else lib.dg_kernel_launch_count() - launches0
+    step_ms = t_begin.elapsed_time(t_end) / args.steps
+
+    # Second pass, same sweep with one CUDA-event pair around every launch: the per-shape table and the roofline
+    # figures (a launch timed this way includes the gap to its neighbours, so these are upper bounds on kernel time).
     events = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in cases]
               for _ in range(args.steps)]
-    sampler = ClockSampler(device.index) if rank == 0 else None
-    launches0 = lib.dg_kernel_launch_count()
     for s in range(args.steps):
-        timed_step(events[s])
+        sweep(sptr, events[s])
     barrier()
-    launches = lib.dg_kernel_launch_count() - launches0     # the untimed flush kernels are not counted by the library
     clocks = sampler.stop() if sampler else None
     status = deep_gemm.device_status()
 
     per_case_us = [sum(events[s][ci][0].elapsed_time(events[s][ci][1]) for s in range(args.steps)) / args.steps * 1e3
                    for ci in range(len(cases))]
-    step_ms = sum(per_case_us) / 1e3
     step_ms_t = torch.tensor([step_ms], dtype=torch.float64, device=device)
     if world > 1:
         torch.distributed.all_reduce(step_ms_t, op=torch.distributed.ReduceOp.MAX)
@@ -321,6 +359,7 @@ def run_dense(args, rank, world, device):
     shapes = [{'m': c.m, 'n': c.n, 'k': c.k, 'us': round(per_case_us[i], 2),
                'tflops': round(c.flops / per_case_us[i] / 1e6, 1), 'gbs': round(c.bytes / per_case_us[i] / 1e3, 1),
                'block_n': c.config['block_n'], 'cta_group': c.config['cta_group'], 'split_k': c.config['split_k'],
+               'split_in_cluster': bool(c.config['cluster_split']),
                'stages': c.config['num_stages']} for i, c in enumerate(cases)]
     cpu_tf, cpu_s = cpu_oracle_sample(CPU_SAMPLE) if world == 1 else (None, None)
     line = {
@@ -329,9 +368,12 @@ def run_dense(args, rank, world, device):
         'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp8_e4m3 x ue8m0, fp32 accumulate', 'data': 'synthetic',
         'config': {'workload': 'dense FP8 NT sweep: M in {64,128,4096} x (N,K) in ' + str(NK_LIST) +
                                ', BF16 out, A scaled per 1x128, B per 128x128 (UE8M0)',
-                   'l2': 'flushed before every GEMM by a %d MiB write, untimed' % (flush.numel() >> 20),
+                   'l2': 'inputs larger than L2: every GEMM has its own operands, %d MB per step against %d MB of L2'
+                         % (footprint // 10**6, l2_bytes // 10**6),
                    'sharding': 'none' if world == 1 else 'N-slabs, one per rank, no collective',
-                   'timing': 'one CUDA-event pair per GEMM; ms_per_step is their sum'},
+                   'timing': ('one CUDA-event pair around the %d steps, each step one replay of a CUDA graph of the 18 launches'
+                              % args.steps if graph is not None else 'one CUDA-event pair around the steps, plain stream launches')
+                             + '; per-shape and roofline figures from a second pass with one event pair per launch'},
         'roofline': {'bound': 'tensor', 'achieved': tf_big, 'peak': fp8_peak, 'unit': 'TFLOP/s', 'frac': tf_big / fp8_peak,
                      'traffic': None, 'kernel': 'mx_gemm_kernel on the six M=4096 launches',
                      'peak_source': '2 x bf16 burst of MEASURED_PEAKS.json (%s)' % pk['source']},

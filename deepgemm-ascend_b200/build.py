@@ -45,7 +45,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     procs = []
     for src in SOURCES:
         obj = os.path.join(build_dir, src.replace('.cu', '.o'))
-        cmd = [nvcc, *NVCC_FLAGS, '-c', os.path.join(CSRC, src), '-o', obj]
+        cmd = [nvcc, *NVCC_FLAGS, *os.environ.get('DG_EXTRA_NVCC_FLAGS', '').split(), '-c', os.path.join(CSRC, src), '-o', obj]
         if verbose:
             cmd += ['-Xptxas', '-v']
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

@@ -3,6 +3,7 @@
 // Host-side counterpart of the reference's launchers (csrc/jit_kernels/fp8_gemm.hpp:11-151,
 // fp8_dequant_gemm.hpp:24-95), of its tiling search (csrc/jit_kernels/heuristics.hpp:592-755) and of the
 // runtime knobs (csrc/jit/jit.hpp:18-76). Nothing here allocates device memory or synchronises.
+#include <string>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cudaTypedefs.h>
@@ -160,6 +161,12 @@ static uint32_t max_stages_for(uint32_t block_n, uint32_t cta_group, bool decode
 
 // Two ways to split K: partial sums reduced into an FP32 workspace that a second kernel casts (reserved[3] == 0), or
 // the splits of one tile form a thread-block cluster and reduce through shared memory (reserved[3] == 1).
+// DG_DISABLE=lean,cluster (debugging aid for A/B timing): keeps the heuristic away from cluster split-K and / or the
+// launch away from the lean kernel instantiations.
+static bool feature_disabled(const char* name) {
+    static const std::string list = [] { const char* e = getenv("DG_DISABLE"); return std::string(e ? e : ""); }();
+    return list.find(name) != std::string::npos;
+}
 static bool splits_in_cluster(const dg_gemm_config_t& c) { return c.split_k > 1 && c.reserved[3] != 0; }
 static bool splits_in_workspace(const dg_gemm_config_t& c) { return c.split_k > 1 && c.reserved[3] == 0; }
 constexpr uint32_t kMaxClusterSplit = 8;        // portable cluster size
@@ -208,8 +215,12 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     DG_CHECK_ARG(c.num_stages >= 1, "tile does not fit in shared memory");
     if (c.num_stages > nkb * 4 && c.num_stages > 2) c.num_stages = nkb * 4 > 2 ? nkb * 4 : 2;
     if (c.num_stages > max_stages) c.num_stages = max_stages;
-    // cluster split-K stages its outgoing partial sums (16 KB per 32 columns) in the operand ring
-    DG_CHECK_ARG(!in_cluster || c.num_stages >= 3, "cluster split-K needs at least three pipeline stages");
+    // cluster split-K stages its outgoing partial sums (16 KB per 32 columns) and its output boxes in the operand ring
+    if (in_cluster) {
+        const uint32_t ring = c.num_stages * (kBlockM * kBlockK + c.block_n * kBlockK);
+        const uint32_t need = (c.block_n / 32) * kReduceSlabBytes + kNumEpilogueWarps * store_bufs * kStoreBufBytes;
+        DG_CHECK_ARG(ring >= need, "cluster split-K needs a pipeline of at least %u bytes, %u stages give %u", need, c.num_stages, ring);
+    }
     if (c.split_k > 1) {
         DG_CHECK_ARG(c.split_k <= nkb, "split_k larger than the number of K blocks");
         // every split must own at least one K block
@@ -240,6 +251,11 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     }
     if (grid_units == 0) grid_units = 1;
     c.num_ctas = grid_units * c.cta_group;
+    // A CTA with a single tile cannot hide its epilogue behind a next tile, and there the TMA store (staging, proxy
+    // fence, descriptor fetch) costs more latency than plain 16-byte stores straight from the registers.
+    if (c.epilogue_mode == kEpiTmaStore && d.gemm_type == DG_GEMM_NORMAL && c.cta_group == 1 &&
+        (uint64_t)ceil_div_u32(d.m, c.block_m) * ceil_div_u32(d.n, c.block_n) * c.split_k <= grid_units)
+        c.epilogue_mode = kEpiPlainStore;
     return DG_OK;
 }
 
@@ -321,7 +337,7 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     // main loop of one split, the exchange (staging, bulk copies, waiting for the slowest rank, summation: measured
     // ~6000 cycles), and a cluster launch that starts ~2.5 us later than a plain one.
     bool best_in_cluster = false;
-    if (d.gemm_type == DG_GEMM_NORMAL && d.b_dtype != DG_E2M1X2 && d.major_b == DG_MAJOR_K) {
+    if (d.gemm_type == DG_GEMM_NORMAL && d.b_dtype != DG_E2M1X2 && d.major_b == DG_MAJOR_K && !feature_disabled("cluster")) {
         const uint64_t m_tiles = (rows + kBlockM - 1) / kBlockM;
         for (uint32_t split = 2; split <= kMaxClusterSplit && nkb / split >= 2; ++split) {
             for (uint32_t bn = 32; bn <= 256; bn += 32) {
@@ -435,6 +451,8 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     plan.major_a = d.major_a;
     plan.major_b = d.major_b;
     plan.decode_b = d.b_dtype == DG_E2M1X2;
+    plan.lean = d.gemm_type == DG_GEMM_NORMAL && c.cta_group == 1 && !plan.decode_b && c.epilogue_mode == kEpiPlainStore &&
+                (d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_BIAS) && !feature_disabled("lean");
     // k-grouped, no accumulation: D of groups whose K range is empty must read as zero
     plan.zero_empty_groups = k_grouped && !d.accumulate;
     plan.zero_d = d.d;

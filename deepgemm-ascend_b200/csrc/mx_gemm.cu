@@ -60,7 +60,14 @@ __global__ void zero_empty_k_groups_kernel(uint8_t* __restrict__ d, const int32_
 using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
                           const CUtensorMap, const CUtensorMap, const GemmKernelArgs);
 
-static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode_b) {
+static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode_b, bool lean) {
+    if (lean) {
+        static const KernelFn lean_table[2][2] = {
+            {mx_gemm_kernel<1, 0, 0, false, true>, mx_gemm_kernel<1, 0, 1, false, true>},
+            {mx_gemm_kernel<1, 1, 0, false, true>, mx_gemm_kernel<1, 1, 1, false, true>},
+        };
+        return lean_table[major_a][major_b];
+    }
     static const KernelFn table[2][2][2][2] = {
         {{{mx_gemm_kernel<1, 0, 0, false>, mx_gemm_kernel<1, 0, 0, true>}, {mx_gemm_kernel<1, 0, 1, false>, mx_gemm_kernel<1, 0, 1, true>}},
          {{mx_gemm_kernel<1, 1, 0, false>, mx_gemm_kernel<1, 1, 0, true>}, {mx_gemm_kernel<1, 1, 1, false>, mx_gemm_kernel<1, 1, 1, true>}}},
@@ -88,7 +95,7 @@ int get_status_pointer(int32_t** out) {
 }
 
 int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
-    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b);
+    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b, plan.lean);
     // The attribute is per device and per function; setting it is cheap, so do it on every launch.
     DG_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem_bytes));
 
@@ -99,8 +106,8 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
     static const bool trace_enabled = [] { const char* e = getenv("DG_TRACE"); return e && atoi(e) != 0; }();
     static unsigned long long* trace_buf = nullptr;
     if (trace_enabled) {
-        if (trace_buf == nullptr) DG_CHECK_CUDA(cudaMalloc(&trace_buf, 1024 * 8 * sizeof(unsigned long long)));
-        DG_CHECK_CUDA(cudaMemsetAsync(trace_buf, 0, 1024 * 8 * sizeof(unsigned long long), stream));
+        if (trace_buf == nullptr) DG_CHECK_CUDA(cudaMalloc(&trace_buf, 1024 * 16 * sizeof(unsigned long long)));
+        DG_CHECK_CUDA(cudaMemsetAsync(trace_buf, 0, 1024 * 16 * sizeof(unsigned long long), stream));
         args.trace = trace_buf;
     }
 
@@ -155,19 +162,21 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
     count_kernel_launch();
     if (trace_enabled) {
         DG_CHECK_CUDA(cudaStreamSynchronize(stream));
-        static unsigned long long host[1024 * 8];
+        static unsigned long long host[1024 * 16];
         const uint32_t n = grid < 1024 ? grid : 1024;
-        DG_CHECK_CUDA(cudaMemcpy(host, trace_buf, n * 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+        DG_CHECK_CUDA(cudaMemcpy(host, trace_buf, n * 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
         unsigned long long t0 = ~0ull, t1 = 0;
-        double sum[8] = {0}, mx[8] = {0};
+        double sum[16] = {0}, mx[16] = {0};
         for (uint32_t i = 0; i < n; ++i) {
-            if (host[i * 8] < t0) t0 = host[i * 8];
-            if (host[i * 8] > t1) t1 = host[i * 8];
-            for (int j = 2; j < 8; ++j) {
-                const double d = host[i * 8 + j] ? (double)(host[i * 8 + j] - host[i * 8 + 1]) : 0.0;
+            if (host[i * 16] < t0) t0 = host[i * 16];
+            if (host[i * 16] > t1) t1 = host[i * 16];
+            for (int j = 2; j < 16; ++j) {
+                const double d = host[i * 16 + j] ? (double)(host[i * 16 + j] - host[i * 16 + 1]) : 0.0;
                 sum[j] += d; if (d > mx[j]) mx[j] = d;
             }
         }
+        fprintf(stderr, "[dg_trace] producer: role-start %.0f sched %.0f wait %.0f ab-issued %.0f stage0-issued %.0f | epilogue: sent %.0f reduce-ready %.0f chunks-done %.0f\n",
+                sum[8] / n, sum[9] / n, sum[10] / n, sum[11] / n, sum[12] / n, sum[13] / n, sum[14] / n, sum[15] / n);
         fprintf(stderr, "[dg_trace] m=%u n=%u k=%u bn=%u cg=%d split=%u ctas=%u start-skew=%.2f us | cycles since entry avg/max: "
                 "setup %.0f/%.0f  first-tma %.0f/%.0f  first-data %.0f/%.0f  last-mma %.0f/%.0f  first-acc %.0f/%.0f  epi-done %.0f/%.0f\n",
                 args.m, args.n, args.k, args.block_n, plan.cta_group, args.split_k, grid, (t1 - t0) / 1e3,

@@ -116,10 +116,12 @@ __device__ __forceinline__ bool wait_barrier_cluster(uint32_t bar, uint32_t pari
     return true;
 }
 
-// Slot meanings: 0 kernel entry (globaltimer ns), 1..7 clock64 at: entry, set-up done, first TMA issued,
-// first operands landed (MMA side), last MMA committed, first accumulator ready (epilogue side), epilogue done.
+// Slot meanings: 0 kernel entry (globaltimer ns), 1..7 clock64 at: entry, set-up done, first stage about to be
+// requested, first operands landed (MMA side), last MMA committed, first accumulator ready (epilogue side), epilogue
+// done; 8..12 producer: role entered, first tile known, first stage free, A and B requested, first stage requested;
+// 13..15 epilogue: partial sums sent (cluster split-K), partial sums received, all chunks of the first tile written.
 __device__ __forceinline__ void trace_mark(const GemmKernelArgs& p, uint32_t slot) {
-    if (p.trace != nullptr) p.trace[blockIdx.x * 8 + slot] = slot == 0 ? global_timer_ns() : (unsigned long long)clock64();
+    if (p.trace != nullptr) p.trace[blockIdx.x * 16 + slot] = slot == 0 ? global_timer_ns() : (unsigned long long)clock64();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -135,7 +137,8 @@ struct Tile {
     uint32_t kb_rot;      // the loads walk the K blocks rotated by this much (CTAs that share A then read different lines)
 };
 
-template <int kCtaGroup>
+// kLean: dense GEMM only (the other layouts are compiled out).
+template <int kCtaGroup, bool kLean = false>
 struct Scheduler {
     const GemmKernelArgs& p;
     uint32_t tile, stride;
@@ -179,7 +182,7 @@ struct Scheduler {
 
     __device__ bool next(Tile& t) {
         const uint32_t rank = kCtaGroup == 2 ? (blockIdx.x & 1u) : 0u;
-        if (p.gemm_type == kNormal) {
+        if (kLean || p.gemm_type == kNormal) {
             const uint32_t total = p.num_m_blocks * p.num_n_blocks * p.split_k;
             if (tile >= total) return false;
             const uint32_t ks = tile % p.split_k, mn = tile / p.split_k;
@@ -195,8 +198,8 @@ struct Scheduler {
             t.b_z = 0;
             t.kb_begin = ks * p.k_blocks_per_split;
             t.kb_end = min(t.kb_begin + p.k_blocks_per_split, p.num_k_blocks);
-            t.kb_rot = (nb * p.k_stagger) % (t.kb_end - t.kb_begin);
-        } else {
+            t.kb_rot = p.k_stagger ? (nb * p.k_stagger) % (t.kb_end - t.kb_begin) : 0u;
+        } else if constexpr (!kLean) {
             const uint32_t mb_lin = tile / p.num_n_blocks, nb = tile - mb_lin * p.num_n_blocks;
             while (true) {
                 if (cur_group >= p.num_groups) return false;
@@ -278,7 +281,13 @@ __host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_
     L.sfa_stage = 128 * 4;
     L.sfb_stage = sfb_rows(block_n) * 4;
     uint32_t off = 0;
-    L.store_bufs = off; off += kNumEpilogueWarps * store_bufs * kStoreBufBytes;
+    if (cluster_split > 1) {
+        // One tile per CTA: when the epilogue runs the operand ring is free, so the outgoing partial sums (one 16 KB
+        // slab per 32 columns) and the store staging behind them live there and the ring keeps the memory.
+        L.store_bufs = (block_n / 32) * kReduceSlabBytes;
+    } else {
+        L.store_bufs = off; off += kNumEpilogueWarps * store_bufs * kStoreBufBytes;
+    }
     L.a = off; off += num_stages * L.a_stage;
     L.b = off; off += num_stages * L.b_stage;
     off = (off + 1023u) & ~1023u;
@@ -346,7 +355,11 @@ __device__ __forceinline__ uint2 stochastic_round_quartet(uint32_t v0, uint32_t 
 // ------------------------------------------------------------------------------------------------
 // kMajorA / kMajorB: 0 = K-major, 1 = MN-major operand in global memory.
 // kDecodeB: B is packed E2M1 in global memory; warps 8..11 decode each stage into the E4M3 tile the MMA reads.
-template <int kCtaGroup, int kMajorA, int kMajorB, bool kDecodeB>
+// kLean: dense GEMM whose CTAs have one tile each and write BF16 / FP32 with plain stores (optional bias). Such a
+// kernel runs its set-up and its epilogue exactly once, straight from a cold instruction cache, and the generic
+// epilogue (staged TMA stores, alpha, stochastic rounding, FP8 quantisation) costs it several microseconds of
+// instruction fetch for code it never needs; the lean instantiation leaves all of that out.
+template <int kCtaGroup, int kMajorA, int kMajorB, bool kDecodeB, bool kLean = false>
 __global__ void __launch_bounds__(kDecodeB ? kNumThreadsDecode : kNumThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
@@ -398,18 +411,29 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             if (owned) mbar_arrive_expect_tx(reduce_bar, owned * (cluster_split - 1) * kReduceSlabBytes);
         }
         fence_mbar_init();
+        fence_proxy_async_smem();
         tma_prefetch_desc(&tm_a); tma_prefetch_desc(&tm_b);
         tma_prefetch_desc(&tm_sfa); tma_prefetch_desc(&tm_sfb);
-        tma_prefetch_desc(&tm_d); tma_prefetch_desc(&tm_d_tail);
+        if (!kLean) { tma_prefetch_desc(&tm_d); tma_prefetch_desc(&tm_d_tail); }
     }
+    __syncwarp();
     if (warp == 2) {
         tmem_alloc<kCtaGroup>(smem_u32((const void*)tmem_ptr_smem), p.tmem_cols);
         tmem_relinquish<kCtaGroup>();
     }
     tc_fence_before_sync();
-    if (kCtaGroup == 2 || cluster_split > 1) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
+    // Warp 0 (whose first lane initialised the barriers and is the TMA producer) only checks in: its loads fill this
+    // CTA's own ring and need nothing from the other warps or CTAs, so they start while TMEM is still being allocated.
+    const bool in_cluster = kCtaGroup == 2 || cluster_split > 1;
+    const uint32_t num_threads = kDecodeB ? kNumThreadsDecode : kNumThreads;
+    if (in_cluster) {
+        cluster_arrive();
+        if (warp != 0) cluster_wait();
+    } else {
+        if (warp == 0) named_bar_arrive(1, num_threads); else named_bar_sync(1, num_threads);
+    }
     tc_fence_after_sync();
-    const uint32_t tmem_base = tmem_ptr_smem[0];
+    const uint32_t tmem_base = tmem_ptr_smem[0];      // (not yet written when warp 0 gets here; warp 0 never uses it)
     if (threadIdx.x == 0) trace_mark(p, 2);
     // TMEM columns: accumulators first, then the scale factors of A and of B.
     const uint32_t tmem_sfa = tmem_base + p.accum_stages * p.block_n;
@@ -417,19 +441,24 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
     if (warp == 0) {
         // ======================================================================== TMA producer
-        if (elect_one()) {
-            Scheduler<kCtaGroup> sched(p);
+        if (lane == 0) {        // the thread that initialised the barriers
+            trace_mark(p, 8);
+            Scheduler<kCtaGroup, kLean> sched(p);
             Tile t;
             uint32_t stage = 0, phase = 0;
-            bool ok = true, first_issue = true;
+            bool ok = true, first_issue = true, ring_used = false;
             while (ok && sched.next(t)) {
+                if (first_issue) trace_mark(p, 9);
                 const uint32_t kb_len = t.kb_end - t.kb_begin;
                 for (uint32_t i = 0; i < kb_len; ++i) {
                     const uint32_t kb = t.kb_begin + (i + t.kb_rot >= kb_len ? i + t.kb_rot - kb_len : i + t.kb_rot);
-                    if (!(ok = wait_barrier(empty_bar(stage), phase ^ 1, ab, kStatusTimeoutProducer))) break;
+                    // (on the first pass over the ring every stage is free by construction)
+                    if (ring_used && !(ok = wait_barrier(empty_bar(stage), phase ^ 1, ab, kStatusTimeoutProducer))) break;
+                    if (first_issue) trace_mark(p, 10);
                     const uint32_t bar = full_bar(stage);
                     const uint32_t bytes = L.a_stage + (kDecodeB ? L.b_raw_stage : load_n * kBlockK) + L.sfa_stage + L.sfb_stage;
                     mbar_arrive_expect_tx(bar, bytes);
+                    if (first_issue) { trace_mark(p, 3); first_issue = false; }
                     const uint32_t sa = smem_base + L.a + stage * L.a_stage;
                     const uint32_t sb = smem_base + L.b + stage * L.b_stage;
                     const int32_t k0 = (int32_t)(kb * kBlockK);
@@ -451,12 +480,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         for (uint32_t a0 = 0; a0 < load_n; a0 += 128)
                             tma_load_3d(sb + a0 * kBlockK, &tm_b, bar, (int32_t)(bn0 + a0), k0, (int32_t)t.b_z);
                     }
+                    if (i == 0) trace_mark(p, 11);
                     tma_load_3d(smem_base + L.sf_raw_a + stage * L.sfa_stage, &tm_sfa, bar,
                                 (int32_t)t.row0, (int32_t)(kb * 2), (int32_t)t.row_z);
                     tma_load_3d(smem_base + L.sf_raw_b + stage * L.sfb_stage, &tm_sfb, bar,
                                 (int32_t)t.n0, (int32_t)(kb * 2), (int32_t)t.b_z);
-                    if (first_issue) { trace_mark(p, 3); first_issue = false; }
-                    if (++stage == num_stages) { stage = 0; phase ^= 1; }
+                    if (i == 0) trace_mark(p, 12);
+                    if (++stage == num_stages) { stage = 0; phase ^= 1; ring_used = true; }
                 }
             }
             // Before leaving, make sure nothing this thread issued is still writing into shared memory:
@@ -467,10 +497,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
         }
         __syncwarp();
+        if (in_cluster) cluster_wait();       // second half of the set-up barrier
     } else if (warp == 1) {
         // ======================================================================== MMA issuer
         if (is_leader && elect_one()) {
-            Scheduler<kCtaGroup> sched(p);
+            Scheduler<kCtaGroup, kLean> sched(p);
             Tile t;
             uint32_t stage = 0, phase = 0, tile_iter = 0;
             bool ok = true;
@@ -524,7 +555,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         // ======================================================================== scale-factor packer
         // raw slab (TMA): [2 K64 columns][rows] int16  ->  packed: [32][4] uint32, entry [l][j] = the four
         // UE8M0 bytes (K blocks 0..3 of this stage) of row j*32+l.
-        Scheduler<kCtaGroup> sched(p);
+        Scheduler<kCtaGroup, kLean> sched(p);
         Tile t;
         uint32_t stage = 0, phase = 0;
         bool ok = true;
@@ -566,7 +597,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     } else if (kDecodeB && warp >= 8) {
         // ======================================================================== FP4 decoders
         // One work item = 8 packed bytes (16 codes) -> one 16-byte chunk of the swizzled E4M3 tile.
-        Scheduler<kCtaGroup> sched(p);
+        Scheduler<kCtaGroup, kLean> sched(p);
         Tile t;
         uint32_t stage = 0, phase = 0;
         bool ok = true;
@@ -607,7 +638,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     } else if (warp >= 4 && warp < 8) {
         // ======================================================================== epilogue
         const uint32_t q = warp - 4;                         // TMEM lane quadrant == warp index % 4
-        Scheduler<kCtaGroup> sched(p);
+        Scheduler<kCtaGroup, kLean> sched(p);
         Tile t;
         uint32_t tile_iter = 0, buf = 0;
         bool ok = true;
@@ -628,7 +659,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             // `single`: the chunk goes out on its own (BF16 boxes normally pair two chunks).
             auto process_chunk = [&](uint32_t (&v)[32], uint32_t c0, bool single) {
                 const uint32_t col0 = t.n0 + c0;
-                if (p.has_alpha) {
+                if (!kLean && p.has_alpha) {
                     #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * p.alpha);
                 }
@@ -642,7 +673,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         v[i] = __float_as_uint(__uint_as_float(v[i]) + bv);
                     }
                 }
-                if (p.epilogue_mode == kEpiFp8Quant) {
+                if (!kLean && p.epilogue_mode == kEpiFp8Quant) {
                     // E4M3 output with one UE8M0 scale per row per 32 columns (exactly this thread's chunk). As the
                     // reference does (operators.hpp:368-411, tests/test_einsum.py:74-84): round to BF16 first, scale =
                     // 2^ceil(log2(max(amax, 1e-4) / 448)), divide, round to nearest E4M3.
@@ -677,7 +708,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 // BF16 output: sixteen packed pairs, rounded to nearest or stochastically
                 uint32_t w16[16];
                 if (!p.d_is_fp32) {
-                    if (p.stochastic) {
+                    if (!kLean && p.stochastic) {
                         #pragma unroll
                         for (uint32_t g = 0; g < 8; ++g) {
                             uint32_t x[4];
@@ -695,7 +726,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         }
                     }
                 }
-                if (p.epilogue_mode <= kEpiTmaReduce) {
+                if (!kLean && p.epilogue_mode <= kEpiTmaReduce) {
                     // Stage a [32 rows x 128 B] box, 16-byte chunk c of row r at chunk (c ^ (r & 7)). A BF16 box holds two
                     // 32-column groups; when block_n is an odd multiple of 32 the last group goes out alone as a
                     // [32 rows x 64 B] box (64B swizzle: chunk c of row r at c ^ ((r >> 1) & 3)) through tm_d_tail.
@@ -740,19 +771,37 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         if (++buf == p.store_bufs) buf = 0;
                     }
                 } else {
-                    // plain path: bounds-checked element stores / atomics, any N and any stride
+                    // plain path: bounds-checked element stores / atomics, any N and any stride; a whole chunk that lies
+                    // inside D on a 16-byte boundary goes out as 16-byte stores
                     const bool row_ok = row < p.m;
                     const uint64_t base = (uint64_t)t.d_z * p.d_group_stride + (uint64_t)row * p.d_stride;
+                    if ((kLean || p.epilogue_mode == kEpiPlainStore) && col0 + 32 <= p.n) {
+                        uint8_t* dst = reinterpret_cast<uint8_t*>(p.d) + (base + col0) * (p.d_is_fp32 ? 4u : 2u);
+                        if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                            if (row_ok) {
+                                if (p.d_is_fp32) {
+                                    #pragma unroll
+                                    for (uint32_t c = 0; c < 8; ++c)
+                                        reinterpret_cast<uint4*>(dst)[c] = make_uint4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+                                } else {
+                                    #pragma unroll
+                                    for (uint32_t c = 0; c < 4; ++c)
+                                        reinterpret_cast<uint4*>(dst)[c] = make_uint4(w16[c * 4], w16[c * 4 + 1], w16[c * 4 + 2], w16[c * 4 + 3]);
+                                }
+                            }
+                            return;
+                        }
+                    }
                     #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         if (row_ok && col0 + i < p.n) {
                             const float f = __uint_as_float(v[i]);
                             if (p.d_is_fp32) {
                                 float* dst = reinterpret_cast<float*>(p.d) + base + col0 + i;
-                                if (p.epilogue_mode == kEpiPlainAtomic) atomicAdd(dst, f); else *dst = f;
+                                if (!kLean && p.epilogue_mode == kEpiPlainAtomic) atomicAdd(dst, f); else *dst = f;
                             } else {
                                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + base + col0 + i;
-                                if (p.epilogue_mode == kEpiPlainAtomic) atomicAdd(dst, __float2bfloat16_rn(f));
+                                if (!kLean && p.epilogue_mode == kEpiPlainAtomic) atomicAdd(dst, __float2bfloat16_rn(f));
                                 else *reinterpret_cast<uint16_t*>(dst) = (uint16_t)(w16[i >> 1] >> ((i & 1) * 16));
                             }
                         }
@@ -781,19 +830,28 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     #pragma unroll
                     for (uint32_t u = 0; u < 8; ++u)
                         *reinterpret_cast<uint4*>(out + ((u ^ sw) * 16)) = make_uint4(va[u * 4], va[u * 4 + 1], va[u * 4 + 2], va[u * 4 + 3]);
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
+                    ++sent;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    sent = 0;
+                    for (uint32_t c = 0; c < chunks; ++c) {
+                        const uint32_t owner = c % S;
+                        if (owner == r) continue;
                         const uint32_t slab = (c / S) * (S - 1) + (r < owner ? r : r - 1);
                         bulk_copy_to_cluster(mapa_shared(smem_base + L.reduce + slab * kReduceSlabBytes + q * 4096, owner),
                                              smem_base + L.a + sent * kReduceSlabBytes + q * 4096, 4096,
                                              mapa_shared(reduce_bar, owner));
+                        ++sent;
                     }
-                    ++sent;
                 }
+                if (threadIdx.x == 128) trace_mark(p, 13);
                 if (r < chunks) {
                     if (!(ok = wait_barrier(reduce_bar, tile_iter & 1u, ab, kStatusTimeoutReduce))) break;
+                    if (threadIdx.x == 128) trace_mark(p, 14);
                     for (uint32_t slot = 0, c = r; c < chunks; ++slot, c += S) {
+                        if (t.n0 + c * 32 >= p.n && (kLean || p.epilogue_mode >= kEpiPlainStore)) break;   // beyond N
                         tmem_ld_32x32b_x32(taddr + c * 32, va);
                         tmem_ld_wait();
                         #pragma unroll
@@ -819,18 +877,23 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
             } else {
             // Two register sets: the TMEM load of the next chunk is in flight while this one is converted and staged.
+            // With plain stores the columns of the tile that lie beyond N are not even read (the staged TMA boxes are
+            // clipped by the hardware instead).
+            const bool plain = kLean || p.epilogue_mode == kEpiPlainStore || p.epilogue_mode == kEpiPlainAtomic;
+            const uint32_t cols = plain ? min(p.block_n, (p.n - t.n0 + 31u) & ~31u) : p.block_n;
             tmem_ld_32x32b_x32(taddr, va);
-            for (uint32_t c0 = 0; c0 < p.block_n; c0 += 64) {
+            for (uint32_t c0 = 0; c0 < cols; c0 += 64) {
                 tmem_ld_wait();
-                if (c0 + 32 < p.block_n) tmem_ld_32x32b_x32(taddr + c0 + 32, vb);
+                if (c0 + 32 < cols) tmem_ld_32x32b_x32(taddr + c0 + 32, vb);
                 process_chunk(va, c0, false);
-                if (c0 + 32 < p.block_n) {
+                if (c0 + 32 < cols) {
                     tmem_ld_wait();
-                    if (c0 + 64 < p.block_n) tmem_ld_32x32b_x32(taddr + c0 + 64, va);
+                    if (c0 + 64 < cols) tmem_ld_32x32b_x32(taddr + c0 + 64, va);
                     process_chunk(vb, c0 + 32, false);
                 }
             }
             }
+            if (tile_iter == 0 && threadIdx.x == 128) trace_mark(p, 15);
             // this accumulator may be overwritten by the next-but-one tile
             tc_fence_before_sync();
             __syncwarp();

@@ -235,9 +235,6 @@ extern "C" int dg_l2_flush_launch(void* buffer, size_t bytes, void* stream) {
     DG_CHECK_ARG(buffer != nullptr && (reinterpret_cast<uintptr_t>(buffer) & 15) == 0, "l2_flush: buffer must be 16-byte aligned");
     const size_t n16 = bytes / 16;
     if (n16 == 0) return DG_OK;
-    static const bool max_shared = [] { const char* e = getenv("DG_FLUSH_CARVEOUT"); return e && atoi(e) != 0; }();
-    if (max_shared)
-        DG_CHECK_CUDA(cudaFuncSetAttribute(l2_flush_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     l2_flush_kernel<<<148 * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(buffer), n16);
     DG_CHECK_CUDA(cudaGetLastError());
     return DG_OK;

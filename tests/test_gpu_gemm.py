@@ -96,7 +96,7 @@ def test_dense_forced_tilings():
 
 
 @pytest.mark.parametrize('bn,split', [(32, 2), (64, 3), (64, 8), (96, 3), (96, 5), (128, 2), (128, 4), (128, 5),
-                                      (160, 2), (192, 2), (192, 3)])
+                                      (160, 2), (160, 3), (192, 2)])
 def test_dense_cluster_split_k(bn, split):
     """The K splits of one tile run as one thread-block cluster: every rank pushes its partial sums of the
     32-column chunks it does not own into the owner's shared memory; the owner adds them in rank order."""
