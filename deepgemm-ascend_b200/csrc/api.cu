@@ -80,13 +80,24 @@ static bool tma_store_ok(const dg_gemm_desc_t& d) {
            ((!has_row_groups(d.gemm_type) && d.gemm_type != DG_GEMM_K_GROUPED_PSUM) || (d.group_stride_d * es) % 16 == 0);
 }
 
+// Both operands packed E2M1: the kind::mxf4 path. The kernel then counts K in bytes (two elements each).
+static bool is_fp4_pair(const dg_gemm_desc_t& d) { return d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E2M1X2; }
+static uint32_t k_bytes(const dg_gemm_desc_t& d) { return is_fp4_pair(d) ? d.k / 2 : d.k; }
+static uint32_t sf_atoms(const dg_gemm_desc_t& d) { return is_fp4_pair(d) ? 2u : 1u; }
+// packed E2M1 B next to an E4M3 A is decoded to E4M3 in shared memory
+static bool decodes_b(const dg_gemm_desc_t& d) { return d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3; }
+
 static int validate(const dg_gemm_desc_t& d) {
     DG_CHECK_ARG(d.gemm_type == DG_GEMM_NORMAL || is_grouped(d.gemm_type) ||
                  d.gemm_type == DG_GEMM_K_GROUPED_PSUM || d.gemm_type == DG_GEMM_BATCHED, "Unknown gemm type %d", d.gemm_type);
     DG_CHECK_ARG(d.a_dtype == DG_E4M3 || d.a_dtype == DG_E2M1X2, "Unsupported operand dtypes");
     DG_CHECK_ARG(d.b_dtype == DG_E4M3 || d.b_dtype == DG_E2M1X2, "Unsupported operand dtypes");
     DG_CHECK_ARG(!(d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E4M3), "Unsupported operand dtypes");
-    DG_UNSUPPORTED(d.a_dtype == DG_E2M1X2, "FP4 x FP4 GEMM is not built in this library");
+    if (is_fp4_pair(d)) {
+        // csrc/jit_kernels/fp8_gemm.hpp:81: "K-major A/B only"
+        DG_CHECK_ARG(d.major_a == DG_MAJOR_K && d.major_b == DG_MAJOR_K, "FP4 x FP4 GEMM takes K-major A and B only");
+        DG_UNSUPPORTED(d.gemm_type == DG_GEMM_K_GROUPED_PSUM, "k-grouped matmul is built for FP8 operands only");
+    }
     if (d.b_dtype == DG_E2M1X2) {
         DG_CHECK_ARG(d.k % 2 == 0, "packed FP4 needs an even K");
         DG_CHECK_ARG(d.major_b == DG_MAJOR_K || d.n % 2 == 0, "MN-major packed FP4 needs an even N");
@@ -144,18 +155,22 @@ static int validate(const dg_gemm_desc_t& d) {
 // ------------------------------------------------------------------------------------------------
 // Heuristic
 // ------------------------------------------------------------------------------------------------
-static uint32_t tmem_cols_for(uint32_t block_n, uint32_t accum_stages) {
-    const uint32_t need = accum_stages * block_n + 4 + 4 * (sfb_rows(block_n) / 128);
+// TMEM columns of the scale factors: four per 128 rows of A / of the B tile, per 32-bit word of scales
+static uint32_t sf_tmem_cols(uint32_t block_n, uint32_t atoms) { return atoms * (4 + 4 * (sfb_rows(block_n) / 128)); }
+
+static uint32_t tmem_cols_for(uint32_t block_n, uint32_t accum_stages, uint32_t atoms) {
+    const uint32_t need = accum_stages * block_n + sf_tmem_cols(block_n, atoms);
     uint32_t cols = 32;
     while (cols < need) cols *= 2;
     return cols;
 }
 
-static uint32_t max_stages_for(uint32_t block_n, uint32_t cta_group, bool decode_b, uint32_t store_bufs, uint32_t cluster_split) {
+static uint32_t max_stages_for(uint32_t block_n, uint32_t cta_group, bool decode_b, uint32_t store_bufs, uint32_t cluster_split,
+                               uint32_t atoms = 1) {
     constexpr uint32_t kSmemCap = 227 * 1024;
     uint32_t best = 0;
     for (uint32_t s = 1; s <= kMaxStages; ++s)
-        if (make_smem_layout(block_n, s, cta_group, decode_b, store_bufs, cluster_split).total <= kSmemCap) best = s;
+        if (make_smem_layout(block_n, s, cta_group, decode_b, store_bufs, cluster_split, atoms).total <= kSmemCap) best = s;
     return best;
 }
 
@@ -196,21 +211,22 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     DG_CHECK_ARG(!split || d.epilogue != DG_EPILOGUE_FP8_QUANT, "FP8 quantization cannot be combined with split-K");
     DG_CHECK_ARG(c.split_k <= 1 || d.gemm_type == DG_GEMM_NORMAL, "split-K is only available for the dense GEMM");
     DG_CHECK_ARG(!split || d.epilogue != DG_EPILOGUE_STOCHASTIC_BF16, "stochastic rounding cannot be combined with split-K");
-    DG_CHECK_ARG(!in_cluster || (c.cta_group == 1 && c.split_k <= kMaxClusterSplit && d.b_dtype != DG_E2M1X2),
+    DG_CHECK_ARG(!in_cluster || (c.cta_group == 1 && c.split_k <= kMaxClusterSplit && !decodes_b(d)),
                  "cluster split-K needs cta_group 1, unpacked B and at most %u splits", kMaxClusterSplit);
     const uint32_t cluster_split = in_cluster ? c.split_k : 1u;
 
-    const uint32_t accum_stages = (2 * c.block_n + 4 + 4 * (sfb_rows(c.block_n) / 128) <= 512) ? 2u : 1u;
-    c.tmem_cols = tmem_cols_for(c.block_n, accum_stages);
+    const uint32_t atoms = sf_atoms(d);
+    const uint32_t accum_stages = (2 * c.block_n + sf_tmem_cols(c.block_n, atoms) <= 512) ? 2u : 1u;
+    c.tmem_cols = tmem_cols_for(c.block_n, accum_stages, atoms);
     c.reserved[0] = accum_stages;
-    const bool decode_b = d.b_dtype == DG_E2M1X2;
-    const uint32_t nkb = ceil_div_u32(d.k, kBlockK);
+    const bool decode_b = decodes_b(d);
+    const uint32_t nkb = ceil_div_u32(k_bytes(d), kBlockK);
     // Staging boxes per epilogue warp. Measured: more than two never helped (the stores then compete with the operand
     // loads), and the shared memory is worth more as pipeline stages.
     if (c.reserved[1] == 0) c.reserved[1] = 2u;
     DG_CHECK_ARG(c.reserved[1] >= 2 && c.reserved[1] <= kMaxStoreBufs, "store buffers per warp must be 2..4");
     const uint32_t store_bufs = c.reserved[1];
-    uint32_t max_stages = max_stages_for(c.block_n, c.cta_group, decode_b, store_bufs, cluster_split);
+    uint32_t max_stages = max_stages_for(c.block_n, c.cta_group, decode_b, store_bufs, cluster_split, atoms);
     if (c.num_stages == 0 || c.num_stages > max_stages) c.num_stages = max_stages;
     DG_CHECK_ARG(c.num_stages >= 1, "tile does not fit in shared memory");
     if (c.num_stages > nkb * 4 && c.num_stages > 2) c.num_stages = nkb * 4 > 2 ? nkb * 4 : 2;
@@ -230,7 +246,7 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     }
     // one CTA per SM: keep the dynamic shared memory above half of the SM's capacity
     const uint32_t need = make_smem_layout(c.block_n, c.num_stages, c.cta_group, decode_b, store_bufs,
-                                           splits_in_cluster(c) ? c.split_k : 1u).total;
+                                           splits_in_cluster(c) ? c.split_k : 1u, atoms).total;
     c.smem_bytes = need < 120u * 1024 ? 120u * 1024 : need;
 
     uint32_t grid_units;
@@ -277,7 +293,8 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     const bool d_fp32 = d.d_dtype == DG_F32;
     // K blocks one tile runs through (the k-grouped layout splits K over the groups)
     const uint32_t nkb = d.gemm_type == DG_GEMM_K_GROUPED_PSUM ? ceil_div_u32(ceil_div_u32(d.k, d.num_groups), kBlockK)
-                                                               : ceil_div_u32(d.k, kBlockK);
+                                                               : ceil_div_u32(k_bytes(d), kBlockK);
+    const uint32_t atoms = sf_atoms(d);
     const bool grouped = is_grouped(d.gemm_type) && d.gemm_type != DG_GEMM_K_GROUPED_PSUM;
 
     // Rows the problem has (an estimate for the masked layout, whose row counts live on the device).
@@ -290,8 +307,8 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     } else {
         rows = d.m;
     }
-    const double hbm_bytes = (double)(d.gemm_type == DG_GEMM_K_GROUPED_PSUM ? d.m : rows) * d.k +
-                             (double)d.n * d.k * (grouped ? d.num_groups : 1) +
+    const double hbm_bytes = (double)(d.gemm_type == DG_GEMM_K_GROUPED_PSUM ? d.m : rows) * k_bytes(d) +
+                             (double)d.n * k_bytes(d) * (grouped ? d.num_groups : 1) +
                              (double)rows * d.n * elem_size(d.d_dtype);
     const double t_hbm = hbm_bytes / 6400.0;       // ns at 6.4 TB/s
 
@@ -319,9 +336,9 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
                 const uint64_t tiles = m_tiles * n_tiles * split;
                 const uint64_t waves = (tiles + units - 1) / units;
                 const uint32_t kb_per = ceil_div_u32(nkb, split);
-                const bool single_accum = 2 * bn + 4 + 4 * (sfb_rows(bn) / 128) > 512;
+                const bool single_accum = 2 * bn + sf_tmem_cols(bn, atoms) > 512;
                 const double t_epi = bn * (out_fp32 ? 8.0 : 6.0);
-                const double cycles = kb_per * k_block_cycles(cg, bn, d.b_dtype == DG_E2M1X2) + ((single_accum || waves == 1) ? t_epi : 0.0) + 700.0;
+                const double cycles = kb_per * k_block_cycles(cg, bn, decodes_b(d)) + ((single_accum || waves == 1) ? t_epi : 0.0) + 700.0;
                 double cost = (double)waves * cycles / 1.8;                   // ns at ~1.8 GHz
                 if (cost < t_hbm) cost = t_hbm + 1e-3 * cost;     // HBM-bound: the cheaper schedule still wins ties
                 // second kernel (launch gap, FP32 read + zero + write) and the FP32 reduce traffic of the partials
@@ -337,12 +354,12 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     // main loop of one split, the exchange (staging, bulk copies, waiting for the slowest rank, summation: measured
     // ~6000 cycles), and a cluster launch that starts ~2.5 us later than a plain one.
     bool best_in_cluster = false;
-    if (d.gemm_type == DG_GEMM_NORMAL && d.b_dtype != DG_E2M1X2 && d.major_b == DG_MAJOR_K && !feature_disabled("cluster")) {
+    if (d.gemm_type == DG_GEMM_NORMAL && !decodes_b(d) && d.major_b == DG_MAJOR_K && !feature_disabled("cluster")) {
         const uint64_t m_tiles = (rows + kBlockM - 1) / kBlockM;
         for (uint32_t split = 2; split <= kMaxClusterSplit && nkb / split >= 2; ++split) {
             for (uint32_t bn = 32; bn <= 256; bn += 32) {
                 if (bn > 32 && bn - 32 >= d.n) continue;
-                if (max_stages_for(bn, 1, false, 2, split) < 4) continue;
+                if (max_stages_for(bn, 1, false, 2, split, atoms) < 4) continue;
                 const uint64_t tiles = m_tiles * ceil_div_u32(d.n, bn) * split;
                 const uint64_t waves = (tiles + num_sms - 1) / num_sms;
                 const uint32_t kb_per = ceil_div_u32(nkb, split);
@@ -416,7 +433,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.m = d.m; a.n = d.n; a.k = d.k;
     a.block_n = c.block_n;
     a.num_stages = c.num_stages;
-    a.num_k_blocks = ceil_div_u32(d.k, kBlockK);
+    a.num_k_blocks = ceil_div_u32(k_bytes(d), kBlockK);
     a.num_m_blocks = ceil_div_u32(d.m, c.block_m);
     a.num_n_blocks = ceil_div_u32(d.n, c.block_n);
     a.gemm_type = (uint32_t)d.gemm_type;
@@ -446,13 +463,15 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     // Instruction descriptor (block-scaled, kind::mxf8f6f4): E4M3 x E4M3, UE8M0 scales, FP32 accumulate.
     a.idesc = ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) | ((c.block_n >> 3) << 17) | (1u << 23) |
               (((kBlockM * c.cta_group) >> 4) << 24);
+    if (is_fp4_pair(d)) a.idesc |= (1u << 7) | (1u << 10);       // kind::mxf4: both operand formats E2M1
 
     plan.cta_group = (int)c.cta_group;
     plan.major_a = d.major_a;
     plan.major_b = d.major_b;
-    plan.decode_b = d.b_dtype == DG_E2M1X2;
+    plan.decode_b = decodes_b(d);
+    plan.fp4_pair = is_fp4_pair(d);
     plan.lean = d.gemm_type == DG_GEMM_NORMAL && c.cta_group == 1 && !plan.decode_b && c.epilogue_mode == kEpiPlainStore &&
-                (d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_BIAS) && !feature_disabled("lean");
+                (d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_BIAS) && !plan.fp4_pair && !feature_disabled("lean");
     // k-grouped, no accumulation: D of groups whose K range is empty must read as zero
     plan.zero_empty_groups = k_grouped && !d.accumulate;
     plan.zero_d = d.d;
@@ -487,7 +506,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     {
         const uint64_t gs = nonzero_stride(d.group_stride_a, rows_a * d.outer_stride_a);
         if (d.major_a == DG_MAJOR_K) {
-            const uint64_t dims[3] = {d.k, rows_a, masked ? groups : 1};
+            const uint64_t dims[3] = {k_bytes(d), rows_a, masked ? groups : 1};
             const uint64_t str[2] = {d.outer_stride_a, gs};
             const uint32_t box[3] = {kBlockK, kBlockM, 1};
             if (int rc = encode_map(&plan.tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "A")) return rc;
@@ -518,7 +537,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     } else {
         if (d.major_b == DG_MAJOR_K) {
             const uint64_t gs = nonzero_stride(d.group_stride_b, (uint64_t)d.n * d.outer_stride_b);
-            const uint64_t dims[3] = {d.k, d.n, groups};
+            const uint64_t dims[3] = {k_bytes(d), d.n, groups};
             const uint64_t str[2] = {d.outer_stride_b, gs};
             const uint32_t box[3] = {kBlockK, load_n, 1};
             if (int rc = encode_map(&plan.tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "B")) return rc;
@@ -535,14 +554,14 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
         const uint64_t gs = nonzero_stride(d.sfa_group_stride, k64 * d.sfa_stride);
         const uint64_t dims[3] = {rows_a, k64, masked ? groups : 1};
         const uint64_t str[2] = {d.sfa_stride * 2, gs * 2};
-        const uint32_t box[3] = {128, 2, 1};
+        const uint32_t box[3] = {128, 2 * sf_atoms(d), 1};
         if (int rc = encode_map(&plan.tm_sfa, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.sfa, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE, "SFA")) return rc;
     }
     {
         const uint64_t gs = nonzero_stride(d.sfb_group_stride, k64 * d.sfb_stride);
         const uint64_t dims[3] = {d.n, k64, groups};
         const uint64_t str[2] = {d.sfb_stride * 2, gs * 2};
-        const uint32_t box[3] = {sfb_rows(c.block_n), 2, 1};
+        const uint32_t box[3] = {sfb_rows(c.block_n), 2 * sf_atoms(d), 1};
         if (int rc = encode_map(&plan.tm_sfb, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.sfb, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE, "SFB")) return rc;
     }
     // ---- D (or the split-K workspace)

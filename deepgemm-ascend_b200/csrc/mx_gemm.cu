@@ -60,7 +60,9 @@ __global__ void zero_empty_k_groups_kernel(uint8_t* __restrict__ d, const int32_
 using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
                           const CUtensorMap, const CUtensorMap, const GemmKernelArgs);
 
-static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode_b, bool lean) {
+static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode_b, bool lean, bool fp4_pair) {
+    if (fp4_pair)
+        return cta_group == 2 ? mx_gemm_kernel<2, 0, 0, false, false, true> : mx_gemm_kernel<1, 0, 0, false, false, true>;
     if (lean) {
         static const KernelFn lean_table[2][2] = {
             {mx_gemm_kernel<1, 0, 0, false, true>, mx_gemm_kernel<1, 0, 1, false, true>},
@@ -95,7 +97,7 @@ int get_status_pointer(int32_t** out) {
 }
 
 int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
-    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b, plan.lean);
+    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b, plan.lean, plan.fp4_pair);
     // The attribute is per device and per function; setting it is cheap, so do it on every launch.
     DG_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem_bytes));
 

@@ -272,14 +272,17 @@ __host__ __device__ __forceinline__ uint32_t cluster_reduce_bytes(uint32_t block
     const uint32_t chunks = block_n / 32;
     return (chunks + cluster_split - 1) / cluster_split * (cluster_split - 1) * kReduceSlabBytes;
 }
+// sf_atoms: 32-bit words of scales per row and stage: 1 for 8-bit operands (128 K-elements per stage, one scale per
+// 32), 2 when both operands are packed E2M1 (256 K-elements per stage).
 __host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_t num_stages, uint32_t cta_group,
-                                                       bool decode_b, uint32_t store_bufs, uint32_t cluster_split = 1) {
+                                                       bool decode_b, uint32_t store_bufs, uint32_t cluster_split = 1,
+                                                       uint32_t sf_atoms = 1) {
     SmemLayout L;
     L.a_stage = kBlockM * kBlockK;
     L.b_stage = (block_n / cta_group) * kBlockK;
     L.b_raw_stage = decode_b ? (block_n / cta_group) * (kBlockK / 2) : 0;    // packed FP4: two codes per byte
-    L.sfa_stage = 128 * 4;
-    L.sfb_stage = sfb_rows(block_n) * 4;
+    L.sfa_stage = 128 * 4 * sf_atoms;
+    L.sfb_stage = sfb_rows(block_n) * 4 * sf_atoms;
     uint32_t off = 0;
     if (cluster_split > 1) {
         // One tile per CTA: when the epilogue runs the operand ring is free, so the outgoing partial sums (one 16 KB
@@ -359,7 +362,9 @@ __device__ __forceinline__ uint2 stochastic_round_quartet(uint32_t v0, uint32_t 
 // kernel runs its set-up and its epilogue exactly once, straight from a cold instruction cache, and the generic
 // epilogue (staged TMA stores, alpha, stochastic rounding, FP8 quantisation) costs it several microseconds of
 // instruction fetch for code it never needs; the lean instantiation leaves all of that out.
-template <int kCtaGroup, int kMajorA, int kMajorB, bool kDecodeB, bool kLean = false>
+// kFp4: both operands are packed E2M1, K-major: a stage is still 128 bytes of K per row (256 elements), the MMA is
+// kind::mxf4 with two scales per row per instruction, and a stage carries eight scale bytes per row instead of four.
+template <int kCtaGroup, int kMajorA, int kMajorB, bool kDecodeB, bool kLean = false, bool kFp4 = false>
 __global__ void __launch_bounds__(kDecodeB ? kNumThreadsDecode : kNumThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
@@ -369,7 +374,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t cluster_split = (kCtaGroup == 1 && !kDecodeB) ? p.cluster_split : 1u;
-    const SmemLayout L = make_smem_layout(p.block_n, p.num_stages, kCtaGroup, kDecodeB, p.store_bufs, cluster_split);
+    constexpr uint32_t kSfAtoms = kFp4 ? 2u : 1u;
+    const SmemLayout L = make_smem_layout(p.block_n, p.num_stages, kCtaGroup, kDecodeB, p.store_bufs, cluster_split, kSfAtoms);
 
     const uint32_t warp = threadIdx.x / 32, lane = lane_id();
     const uint32_t cta_rank = kCtaGroup == 2 ? cluster_ctarank() : 0u;
@@ -437,7 +443,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     if (threadIdx.x == 0) trace_mark(p, 2);
     // TMEM columns: accumulators first, then the scale factors of A and of B.
     const uint32_t tmem_sfa = tmem_base + p.accum_stages * p.block_n;
-    const uint32_t tmem_sfb = tmem_sfa + 4;
+    const uint32_t tmem_sfb = tmem_sfa + 4 * kSfAtoms;
 
     if (warp == 0) {
         // ======================================================================== TMA producer
@@ -482,9 +488,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                     if (i == 0) trace_mark(p, 11);
                     tma_load_3d(smem_base + L.sf_raw_a + stage * L.sfa_stage, &tm_sfa, bar,
-                                (int32_t)t.row0, (int32_t)(kb * 2), (int32_t)t.row_z);
+                                (int32_t)t.row0, (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.row_z);
                     tma_load_3d(smem_base + L.sf_raw_b + stage * L.sfb_stage, &tm_sfb, bar,
-                                (int32_t)t.n0, (int32_t)(kb * 2), (int32_t)t.b_z);
+                                (int32_t)t.n0, (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.b_z);
                     if (i == 0) trace_mark(p, 12);
                     if (++stage == num_stages) { stage = 0; phase ^= 1; ring_used = true; }
                 }
@@ -521,10 +527,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     if (tile_iter == 0 && kb == t.kb_begin) trace_mark(p, 4);
                     tc_fence_after_sync();
                     // scales: smem -> TMEM (A: 128 rows = one slab; B: one slab per 128 columns)
-                    utccp_32x128b_warpx4<kCtaGroup>(tmem_sfa, make_sf_desc(smem_base + L.sf_pack_a + stage * L.sfa_stage));
-                    for (uint32_t i = 0; i < sfb_slabs; ++i)
-                        utccp_32x128b_warpx4<kCtaGroup>(tmem_sfb + i * 4,
-                                                        make_sf_desc(smem_base + L.sf_pack_b + stage * L.sfb_stage + i * 512));
+                    // (packed E2M1: word g of a row holds the scales of K-elements [128 g, 128 g + 128) of the stage)
+                    #pragma unroll
+                    for (uint32_t g = 0; g < kSfAtoms; ++g) {
+                        utccp_32x128b_warpx4<kCtaGroup>(tmem_sfa + g * 4,
+                                                        make_sf_desc(smem_base + L.sf_pack_a + stage * L.sfa_stage + g * 512));
+                        for (uint32_t i = 0; i < sfb_slabs; ++i)
+                            utccp_32x128b_warpx4<kCtaGroup>(tmem_sfb + (g * sfb_slabs + i) * 4,
+                                                            make_sf_desc(smem_base + L.sf_pack_b + stage * L.sfb_stage + (g * sfb_slabs + i) * 512));
+                    }
                     const uint32_t sa = smem_base + L.a + stage * L.a_stage;
                     const uint32_t sb = smem_base + L.b + stage * L.b_stage;
                     #pragma unroll
@@ -534,9 +545,16 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         else da = make_mnmajor_sw128_desc(sa + k * kUmmaK * 128, kBlockK * 128);
                         if constexpr (kMajorB == 0) db = make_kmajor_sw128_desc(sb + k * kUmmaK);
                         else db = make_mnmajor_sw128_desc(sb + k * kUmmaK * 128, kBlockK * 128);
-                        const uint32_t idesc = p.idesc | (k << 4) | (k << 29);   // scale ids of B and of A
-                        umma_mxf8f6f4<kCtaGroup>(tmem_d, da, db, idesc, tmem_sfa, tmem_sfb,
-                                                 (kb > t.kb_begin || k > 0) ? 1u : 0u);
+                        if constexpr (kFp4) {
+                            // instruction k reads 64 K-elements: scale bytes 2(k&1), 2(k&1)+1 of word k/2
+                            const uint32_t id = (k & 1u) * 2u, g = k >> 1;
+                            umma_mxf4<kCtaGroup>(tmem_d, da, db, p.idesc | (id << 4) | (id << 29), tmem_sfa + g * 4,
+                                                 tmem_sfb + g * sfb_slabs * 4, (kb > t.kb_begin || k > 0) ? 1u : 0u);
+                        } else {
+                            const uint32_t idesc = p.idesc | (k << 4) | (k << 29);   // scale ids of B and of A
+                            umma_mxf8f6f4<kCtaGroup>(tmem_d, da, db, idesc, tmem_sfa, tmem_sfb,
+                                                     (kb > t.kb_begin || k > 0) ? 1u : 0u);
+                        }
                     }
                     // release the stage once these MMAs have read it
                     if constexpr (kCtaGroup == 2) umma_commit_2cta(empty_bar(stage), 3);
@@ -565,24 +583,24 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 if (!(ok = wait_barrier(full_bar(stage), phase, ab, kStatusTimeoutPacker))) break;
                 const uint16_t* raw_a = reinterpret_cast<const uint16_t*>(smem_gen + L.sf_raw_a + stage * L.sfa_stage);
                 uint4* pack_a = reinterpret_cast<uint4*>(smem_gen + L.sf_pack_a + stage * L.sfa_stage);
-                {
-                    uint32_t v[4];
-                    #pragma unroll
-                    for (uint32_t j = 0; j < 4; ++j)
-                        v[j] = (uint32_t)raw_a[j * 32 + lane] | ((uint32_t)raw_a[128 + j * 32 + lane] << 16);
-                    pack_a[lane] = make_uint4(v[0], v[1], v[2], v[3]);
-                }
                 const uint32_t rows_b = sfb_slabs * 128;
                 const uint16_t* raw_b = reinterpret_cast<const uint16_t*>(smem_gen + L.sf_raw_b + stage * L.sfb_stage);
                 uint4* pack_b = reinterpret_cast<uint4*>(smem_gen + L.sf_pack_b + stage * L.sfb_stage);
-                for (uint32_t i = 0; i < sfb_slabs; ++i) {
+                #pragma unroll
+                for (uint32_t g = 0; g < kSfAtoms; ++g) {        // word g of a row = int16 columns 2g and 2g + 1
                     uint32_t v[4];
                     #pragma unroll
-                    for (uint32_t j = 0; j < 4; ++j) {
-                        const uint32_t r = i * 128 + j * 32 + lane;
-                        v[j] = (uint32_t)raw_b[r] | ((uint32_t)raw_b[rows_b + r] << 16);
+                    for (uint32_t j = 0; j < 4; ++j)
+                        v[j] = (uint32_t)raw_a[(2 * g) * 128 + j * 32 + lane] | ((uint32_t)raw_a[(2 * g + 1) * 128 + j * 32 + lane] << 16);
+                    pack_a[g * 32 + lane] = make_uint4(v[0], v[1], v[2], v[3]);
+                    for (uint32_t i = 0; i < sfb_slabs; ++i) {
+                        #pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            const uint32_t r = i * 128 + j * 32 + lane;
+                            v[j] = (uint32_t)raw_b[(2 * g) * rows_b + r] | ((uint32_t)raw_b[(2 * g + 1) * rows_b + r] << 16);
+                        }
+                        pack_b[(g * sfb_slabs + i) * 32 + lane] = make_uint4(v[0], v[1], v[2], v[3]);
                     }
-                    pack_b[i * 32 + lane] = make_uint4(v[0], v[1], v[2], v[3]);
                 }
                 fence_proxy_async_smem();
                 __syncwarp();

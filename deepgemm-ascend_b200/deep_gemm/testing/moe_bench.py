@@ -71,6 +71,8 @@ class GroupedCase:
 def run(args, rank, world, device, emit=None):
     if args.workload == 'mixed':
         return run_mixed(args, rank, world, device, emit)
+    if args.workload == 'fp4':
+        return run_fp4(args, rank, world, device, emit)
     lib = L.lib()
     stream = torch.cuda.current_stream(device)
     sptr = stream.cuda_stream
@@ -206,4 +208,60 @@ def run_mixed(args, rank, world, device, emit=None):
             'data': 'synthetic',
             'config': {'workload': 'mixed FP8xFP4 GEMM NN, M=4096 N=7168 K=2048, BF16 out', 'l2': 'flushed, untimed'},
             'gbs': nbytes / us / 1e3, 'tiling': cfg.as_dict(), 'device_status': _api.device_status()}
+    (emit or (lambda l: print(json.dumps(l), flush=True)))(line)
+
+
+def run_fp4(args, rank, world, device, emit=None):
+    """FP4 x FP4 GEMM "NT" (both operands packed E2M1, K-major, per-32 UE8M0 scales, BF16 out) on the shapes the
+    reference publishes for this kind (README.md:108-113: 4096 x 7168 x 16384) plus two more of the dense sweep.
+    Normalised by the dense FP4 peak (twice the FP8 figure)."""
+    lib = L.lib()
+    stream = torch.cuda.current_stream(device)
+    sptr = stream.cuda_stream
+    flush = l2_flush_buffer(device)
+    gen = torch.Generator(device=device).manual_seed(11 + rank)
+    shapes = [(4096, 7168, 16384), (4096, 4096, 7168), (4096, 7168, 2048), (128, 7168, 16384)]
+    rows = []
+    for (m, n, k) in shapes:
+        a = torch.randint(-128, 128, (m, k // 2), dtype=torch.int8, device=device, generator=gen)
+        b = torch.randint(-128, 128, (n, k // 2), dtype=torch.int8, device=device, generator=gen)
+        sfa = _scales((), m, k, device, gen)
+        sfb = _scales((), n, k, device, gen)
+        d = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+        desc = _api._run_gemm(L.GEMM_NORMAL, a, b, d, None, _api.Identity(), sfa, sfb, (1, 1, 32), None, None, None, 'nk', False)
+        cfg = L.GemmConfig()
+        L.check(lib.dg_select_config(ctypes.byref(desc), ctypes.byref(cfg)))
+        ws_bytes = lib.dg_gemm_workspace_bytes(ctypes.byref(desc), None)
+        ws = _api._workspace(device, ws_bytes) if ws_bytes else None
+
+        def once(events=None):
+            L.check(lib.dg_l2_flush_launch(flush.data_ptr(), flush.numel(), sptr))
+            if events:
+                events[0].record(stream)
+            L.check(lib.dg_gemm_launch(ctypes.byref(desc), None, ws.data_ptr() if ws is not None else None,
+                                       ws.numel() if ws is not None else 0, sptr))
+            if events:
+                events[1].record(stream)
+
+        for _ in range(max(args.warmup, 3)):
+            once()
+        torch.cuda.synchronize(device)
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for e in ev:
+            once(e)
+        torch.cuda.synchronize(device)
+        us = sum(a_.elapsed_time(b_) for a_, b_ in ev) / args.steps * 1e3
+        nbytes = (m + n) * k // 2 + (m + n) * ((k + 63) // 64) * 2 + m * n * 2
+        rows.append({'m': m, 'n': n, 'k': k, 'us': round(us, 2), 'tflops': round(2.0 * m * n * k / us / 1e6, 1),
+                     'gbs': round(nbytes / us / 1e3, 1), 'tiling': cfg.as_dict()})
+    if rank != 0:
+        return
+    flops = sum(2.0 * m * n * k for m, n, k in shapes)
+    total_us = sum(r['us'] for r in rows)
+    line = {'metric': 'fp4_block_scaled_gemm_tflops', 'value': world * flops / total_us / 1e6, 'unit': 'TFLOP/s', 'n_gpus': world,
+            'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': total_us / 1e3, 'higher_is_better': True,
+            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp4_e2m1 x fp4_e2m1, ue8m0 scales per 32 (kind::mxf4)',
+            'data': 'synthetic',
+            'config': {'workload': 'FP4xFP4 GEMM NT, BF16 out: ' + str(shapes), 'l2': 'flushed before every GEMM, untimed'},
+            'shapes': rows, 'device_status': _api.device_status()}
     (emit or (lambda l: print(json.dumps(l), flush=True)))(line)

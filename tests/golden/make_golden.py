@@ -83,6 +83,8 @@ def main(ref_root: str) -> None:
          dict(accumulate=True, recipe=(32, 32, 32))),
         ('dense_fp8fp4_nn', fp8, fp4, torch.bfloat16, (32, 64, 128), Major.K, Major.MN, {}),
         ('dense_fp8fp4_nt', fp8, fp4, torch.bfloat16, (32, 48, 192), Major.K, Major.K, {}),
+        ('dense_fp4fp4_nt', fp4, fp4, torch.bfloat16, (32, 48, 192), Major.K, Major.K, {}),
+        ('dense_fp4fp4_nt_acc_f32', fp4, fp4, torch.float32, (40, 72, 448), Major.K, Major.K, dict(accumulate=True)),
     ]
     for name, adt, bdt, cdt, shape, ma, mb, kw in dense:
         d = Desc(GemmType.Normal, adt, bdt, cdt, shape, ma, mb, **kw)

@@ -193,7 +193,88 @@ def test_mixed_golden(golden):
         assert_close(d, c['d'], name)
 
 
+def _fp4_pair(m, n, k, *, out=torch.bfloat16, acc=False, bias=False, config=None, seed=0):
+    """Both operands packed E2M1, K-major ([MN, K/2] int8), per-32 UE8M0 scales: the kind::mxf4 path."""
+    seed_all(seed)
+    a, sfa, a_ref = uniform_fp4(m, k, (1, 32), mn_major=False)
+    b, sfb, b_ref = uniform_fp4(n, k, (1, 32), mn_major=False)
+    c = torch.randn(1 if bias else m, n).to(out) if (acc or bias) else None
+    ref = oracle.gemm_ref(a_ref, b_ref, out, c=c if acc else None, bias=c if bias else None)
+    d = torch.full((m, n), float('nan'), dtype=out, device='cuda')
+    kwargs = {}
+    if acc:
+        d.copy_(c)
+        kwargs['c'] = d
+    elif bias:
+        kwargs['c'] = c.cuda()
+    deep_gemm.fp8_fp4_gemm_nt((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d, recipe_a=(1, 32), recipe_b=(1, 32),
+                              config=config, **kwargs)
+    assert deep_gemm.device_status() == 0
+    return assert_close(d, ref, f'fp4xfp4 {m}x{n}x{k} out={out} acc={acc} bias={bias} config={config}')
+
+
+@pytest.mark.parametrize('m,n,k', [(128, 128, 256), (128, 256, 1024), (256, 192, 2048), (64, 2112, 7168), (4096, 512, 4096),
+                                   (130, 257, 2048), (17, 512, 4096), (64, 64, 64), (256, 512, 96), (128, 128, 468)])
+def test_fp4_pair_dense(m, n, k):
+    _fp4_pair(m, n, k)
+    _fp4_pair(m, n, k, out=torch.float32, acc=True)
+
+
+def test_fp4_pair_tilings_and_epilogues():
+    for bn in (32, 64, 96, 128, 160, 192, 224, 256):
+        _fp4_pair(384, 768, 2048, config={'block_n': bn})
+        _fp4_pair(512, 768, 2048, config={'cta_group': 2, 'block_n': bn})
+    _fp4_pair(256, 384, 1024, bias=True)
+    _fp4_pair(128, 512, 8192, config={'block_n': 128, 'split_k': 4})
+    _fp4_pair(128, 512, 8192, config={'block_n': 128, 'split_k': 4, 'cluster_split': 1})
+    _fp4_pair(4096, 2112, 7168)                         # heuristic: CTA pairs
+
+
+def test_fp4_pair_golden(golden):
+    for name in ('dense_fp4fp4_nt', 'dense_fp4fp4_nt_acc_f32'):
+        c = golden[name]
+        d = torch.zeros_like(c['d']).cuda()
+        kwargs = {}
+        if c['accumulate']:
+            d.copy_(c['c'])
+            kwargs['c'] = d
+        deep_gemm.fp8_fp4_gemm_nt((c['a'].cuda(), c['sfa'].cuda()), (c['b'].cuda(), c['sfb'].cuda()), d, **kwargs)
+        assert deep_gemm.device_status() == 0
+        assert_close(d, c['d'], name)
+
+
+def test_fp4_pair_m_grouped():
+    """m-grouped contiguous (psum layout) with both operands packed E2M1."""
+    seed_all(11)
+    sizes = [300, 0, 513, 128]
+    total, psum = oracle.make_psum_layout(sizes, 256)
+    n, k = 384, 1024
+    a, sfa, a_ref = uniform_fp4(total, k, (1, 32), mn_major=False)
+    raw = a.clone()
+    for span in oracle.psum_padding_spans(psum, 256):
+        raw[span] = 0
+        a_ref[span] = 0
+    bs = [uniform_fp4(n, k, (1, 32), mn_major=False) for _ in sizes]
+    b = torch.stack([x[0] for x in bs]); sfb = torch.stack([x[1] for x in bs]); b_ref = torch.stack([x[2] for x in bs])
+    ref = oracle.m_grouped_psum_ref(a_ref, b_ref, psum, torch.bfloat16)
+    d = torch.full((total, n), float('nan'), dtype=torch.bfloat16, device='cuda')
+    layout = torch.tensor(psum, dtype=torch.int32, device='cuda')
+    deep_gemm.m_grouped_fp8_fp4_gemm_nt_contiguous((raw.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d, layout,
+                                                   recipe_a=(1, 32), recipe_b=(1, 32))
+    assert deep_gemm.device_status() == 0
+    out = d.cpu()
+    for span in oracle.psum_valid_spans(psum, 256):
+        assert_close(out[span], ref[span], 'fp4xfp4 m-grouped')
+
+
 def test_fp4_operand_rules():
+    # MN-major packed operands are not accepted for FP4 x FP4 (csrc/jit_kernels/fp8_gemm.hpp:81)
+    a4 = torch.zeros(128, 128, dtype=torch.int8, device='cuda')          # [M, K/2], K = 256
+    b4 = torch.zeros(256, 64, dtype=torch.int8, device='cuda')           # [K, N/2]: MN-major codes, N = 128
+    d4 = torch.zeros(128, 128, dtype=torch.bfloat16, device='cuda')
+    with pytest.raises(RuntimeError, match='K-major A and B only'):
+        deep_gemm.fp8_fp4_gemm_nn((a4, torch.ones(128, 8, device='cuda')), (b4, torch.ones(8, 128, device='cuda')), d4,
+                                  recipe_a=(1, 32), recipe_b=(1, 32))
     a = torch.zeros(128, 64, dtype=torch.int8, device='cuda')
     b = torch.zeros(128, 128, dtype=torch.float8_e4m3fn, device='cuda')
     sf = torch.ones(128, 4, dtype=torch.float32, device='cuda')
