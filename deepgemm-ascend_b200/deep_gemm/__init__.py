@@ -7,7 +7,7 @@ and not exported. Importing this package never initialises a CUDA context.
 
 __version__ = '0.1.1'
 
-from . import epilogue, locality_domain, testing  # noqa: F401
+from . import epilogue, locality_domain, quant_ops, testing  # noqa: F401
 from ._api import (  # noqa: F401
     device_status,
     fp8_bmm,
@@ -44,6 +44,7 @@ from ._api import (  # noqa: F401
     transform_sf_into_required_layout,
     use_deterministic_algorithms,
 )
+from .quant_ops import cast_to_fp8, swiglu_apply_weight_to_fp8  # noqa: F401
 from .locality_domain import (  # noqa: F401
     destroy_localizer,
     get_num_locality_domains,

@@ -60,6 +60,9 @@ _PROTOTYPES = {
     'dg_gemm_launch': (C.c_int, [C.POINTER(GemmDesc), C.POINTER(GemmConfig), C.c_void_p, C.c_size_t, C.c_void_p]),
     'dg_gemm_dry_run': (C.c_int, [C.POINTER(GemmDesc), C.POINTER(GemmConfig)]),
     'dg_gemm_launch_static_scratch': (C.c_int, [C.POINTER(GemmDesc), C.POINTER(GemmConfig), C.c_void_p]),
+    'dg_quant_fp8_launch': (C.c_int, [
+        C.c_void_p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_int, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
+        C.c_int, C.c_float, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p]),
     'dg_transform_sf_launch': (C.c_int, [
         C.c_void_p, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32,
         C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,

@@ -73,6 +73,8 @@ def run(args, rank, world, device, emit=None):
         return run_mixed(args, rank, world, device, emit)
     if args.workload == 'fp4':
         return run_fp4(args, rank, world, device, emit)
+    if args.workload == 'quant':
+        return run_quant(args, rank, world, device, emit)
     lib = L.lib()
     stream = torch.cuda.current_stream(device)
     sptr = stream.cuda_stream
@@ -264,4 +266,57 @@ def run_fp4(args, rank, world, device, emit=None):
             'data': 'synthetic',
             'config': {'workload': 'FP4xFP4 GEMM NT, BF16 out: ' + str(shapes), 'l2': 'flushed before every GEMM, untimed'},
             'shapes': rows, 'device_status': _api.device_status()}
+    (emit or (lambda l: print(json.dumps(l), flush=True)))(line)
+
+
+def run_quant(args, rank, world, device, emit=None):
+    """The SwiGLU -> FP8 producer between the two expert GEMMs of the grouped workload: x [rows, 4096] BF16 (the
+    output of the N = 4096 GEMM over 8 experts of about 8192 rows, psum layout) -> E4M3 [rows, 2048] + packed scales,
+    and the plain cast of [rows, 7168] activations. HBM-bound; reported in GB/s of algorithmic bytes."""
+    import deep_gemm
+    from deep_gemm.testing import bench_events
+    import json as _json
+    peak = 6453.4
+    try:
+        import os
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), '..', '..', '..', 'MEASURED_PEAKS.json')) as f:
+            peak = float(_json.load(f)['hbm_gbs'])
+    except (OSError, KeyError, ValueError):
+        pass
+    gen = torch.Generator(device=device).manual_seed(5 + rank)
+    random.seed(1234 + rank)
+    sizes = [int(random.uniform(0.7, 1.3) * 8192) for _ in range(8)]
+    psum_list, rows = [], 0
+    for s in sizes:
+        psum_list.append(rows + s)
+        rows = (rows + s + 255) // 256 * 256
+    layout = torch.tensor(psum_list, dtype=torch.int32, device=device)
+    valid = sum(sizes)
+    out_rows = []
+    x = torch.randn(rows, 4096, device=device, generator=gen).bfloat16()
+    w = torch.rand(rows, device=device, generator=gen)
+    p = bench_events(lambda: deep_gemm.swiglu_apply_weight_to_fp8(x, w, layout, None, 256), max(args.warmup, 3), args.steps)
+    nbytes = valid * (4096 * 2 + 2048 + 2048 // 32 + 4)
+    out_rows.append({'op': 'swiglu_apply_weight_to_fp8', 'rows': valid, 'hidden': 2048, 'us': round(p.dur_us, 2),
+                     'gbs': round(nbytes / p.dur_us / 1e3, 1)})
+    total_bytes, total_us = nbytes, p.dur_us
+    del x
+    x = torch.randn(rows, 7168, device=device, generator=gen).bfloat16()
+    p = bench_events(lambda: deep_gemm.cast_to_fp8(x, layout, 256), max(args.warmup, 3), args.steps)
+    nbytes = valid * (7168 * 2 + 7168 + 7168 // 32)
+    out_rows.append({'op': 'cast_to_fp8', 'rows': valid, 'hidden': 7168, 'us': round(p.dur_us, 2),
+                     'gbs': round(nbytes / p.dur_us / 1e3, 1)})
+    total_bytes += nbytes
+    total_us += p.dur_us
+    if rank != 0:
+        return
+    achieved = total_bytes / total_us / 1e3
+    line = {'metric': 'fp8_quantiser_gbs', 'value': world * achieved, 'unit': 'GB/s', 'n_gpus': world, 'steps': args.steps,
+            'warmup': max(args.warmup, 3), 'ms_per_step': total_us / 1e3, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': 'bf16 -> fp8_e4m3 + ue8m0 per 1x32', 'data': 'synthetic',
+            'config': {'workload': 'SwiGLU->FP8 of [%d, 4096] and cast of [%d, 7168], 8 experts in psum layout' % (valid, valid),
+                       'l2': 'flushed before every launch, untimed'},
+            'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
+                         'traffic': None, 'kernel': 'quant_fp8_kernel'},
+            'ops': out_rows, 'device_status': _api.device_status()}
     (emit or (lambda l: print(json.dumps(l), flush=True)))(line)

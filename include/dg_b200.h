@@ -80,6 +80,10 @@ typedef enum {
  * (int16 [MN, ceil(K/64)], MN-major, csrc/apis/layout.hpp:19-36); `sf*_stride` is the distance in
  * int16 elements between consecutive K64 columns (== MN for a dense tensor) and must be a multiple
  * of 8; sf*_group_stride is the distance between groups of scales in int16 elements.
+ *
+ * Operand dtype pairs (csrc/apis/gemm.hpp:22-33): E4M3 x E4M3; E4M3 x E2M1X2 (B decoded to E4M3 on the fly,
+ * either major); E2M1X2 x E2M1X2 (tcgen05 kind::mxf4, K-major A and B only as in csrc/jit_kernels/fp8_gemm.hpp:81,
+ * per-32 scales; every layout but the K-grouped one). E2M1X2 x E4M3 is rejected as in the reference.
  */
 typedef struct {
     const void* a;
@@ -191,6 +195,19 @@ int dg_transform_sf_launch(const void* src, int src_is_fp32,
                            uint32_t num_batches, const int32_t* psum, uint32_t num_groups,
                            uint32_t alignment, int32_t* invalid_flag,
                            const int32_t* k_psum, uint32_t num_k_groups, void* stream);
+
+/* BF16 activations -> E4M3 plus UE8M0 scales per 1x32, the scales written directly in the layout the GEMM reads
+ * (int16 [tokens, ceil(hidden/64)], consecutive tokens contiguous, `sf_col_stride` int16 elements between columns), so
+ * no dg_transform_sf_launch runs between this producer and the GEMM. With `swiglu` the input row is [2 * hidden] and
+ * the quantised value is silu(x[:hidden]) * x[hidden:] (* topk_weights[token]), optionally clamped: the reference's
+ * third-party/tilelang_ops/swiglu_apply_weight_to_fp8.py:411-449 (the operator between the two expert GEMMs of an MoE
+ * layer). Without `swiglu` it is the plain cast of x[tokens, hidden] (no reference counterpart: the reference has no
+ * stand-alone quantiser). `psum` / `num_experts` / `alignment`: tokens in the padding of a psum layout are skipped, the
+ * alignment must be a multiple of 32. hidden % 32 == 0; x rows 16-byte aligned, out rows 8-byte aligned. */
+int dg_quant_fp8_launch(const void* x, uint64_t x_stride, uint32_t tokens, uint32_t hidden, int swiglu,
+                        const float* topk_weights, const int32_t* psum, uint32_t num_experts, uint32_t alignment,
+                        int has_clamp, float clamp_value, void* out, uint64_t out_stride,
+                        int16_t* out_sf, uint64_t sf_col_stride, void* stream);
 
 /* Copy a 2-D byte matrix into a buffer whose row pitch satisfies the 16-byte rule of TMA, zero
  * filling the tail of each row. Used for operands whose contiguous extent is not a multiple of 16

@@ -33,6 +33,7 @@ from .mxgemm import (  # noqa: F401
     quantize_e4m3,
     stochastic_round_bf16,
 )
+from .quant import swiglu_quant_ref  # noqa: F401
 from .sf_layout import (  # noqa: F401
     align,
     ceil_div,
