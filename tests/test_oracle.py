@@ -154,3 +154,27 @@ def test_stochastic_rounding_model_properties():
 def test_stochastic_rounding_model_matches_reference_fixture(golden):
     c = golden['stochastic_bf16']
     assert torch.equal(oracle.stochastic_round_bf16(c['x']).view(torch.int16), c['expected'])
+
+
+def test_swiglu_quant_model_properties():
+    """Scale = max(amax, 1e-4) / 448 rounded up to a power of two (the same rule as tests/generators.py:27-31 states
+    for operands), codes times scale reproduce the value within E4M3 precision, rows outside the psum spans invalid."""
+    torch.manual_seed(4)
+    x = (torch.randn(70, 512) * 3).bfloat16()
+    codes, sf, valid, deq = oracle.swiglu_quant_ref(x, swiglu=False)
+    assert codes.shape == (70, 512) and sf.shape == (70, 8) and valid.all()
+    amax = x.float().reshape(70, 16, 32).abs().amax(-1)
+    expected_scale = oracle.ceil_to_ue8m0(amax.clamp(1e-4) * torch.tensor(1.0 / 448.0))
+    got_scale = (sf.contiguous().view(torch.uint8).int() << 23).view(torch.float32)
+    assert torch.equal(got_scale, expected_scale)
+    assert (deq - x.float()).abs().max() <= (x.float().abs().max() / 16)        # 3 mantissa bits
+    assert (codes.view(torch.float8_e4m3fn).float().abs() <= 448).all()
+    # SwiGLU with weight, clamp and a psum layout
+    y = (torch.randn(384, 512) * 2).bfloat16()
+    w = torch.rand(384)
+    codes, sf, valid, deq = oracle.swiglu_quant_ref(y, w, [100, 256, 300], 1.5, 128)
+    assert valid.sum().item() == 100 + 128 + 44
+    assert valid[:100].all() and not valid[100:128].any() and valid[128:300].all() and not valid[300:].any()
+    xl, xr = y.float()[:, :256].clamp(max=1.5), y.float()[:, 256:].clamp(-1.5, 1.5)
+    ref = torch.nn.functional.silu(xl) * xr * w[:, None]
+    assert oracle.calc_diff(deq[valid], ref[valid]) < 2e-3
