@@ -250,6 +250,8 @@ def run_dense(args, rank, world, device):
     # The step as a CUDA graph (launch-bound for the small shapes otherwise); plain stream launches if capture fails.
     graph, launches_per_step = None, 0
     try:
+        if args.no_graph:
+            raise RuntimeError('--no-graph')
         side = torch.cuda.Stream(device)
         graph = torch.cuda.CUDAGraph()
         launches0 = lib.dg_kernel_launch_count()
@@ -413,6 +415,8 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--workload', default='dense', choices=['dense', 'grouped', 'masked', 'mixed', 'fp4', 'quant'])
     ap.add_argument('--experts-per-gpu', type=int, default=0, help='grouped / masked workloads (default 8 / 32)')
+    ap.add_argument('--no-graph', action='store_true',
+                    help='dense workload: plain stream launches instead of a CUDA graph (for profilers that cannot follow a capture)')
     ap.add_argument('--gather', action='store_true', help='grouped workload, N > 1: also time an NCCL all-gather of D')
     args = ap.parse_args()
 

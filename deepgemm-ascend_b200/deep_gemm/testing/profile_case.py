@@ -27,6 +27,9 @@ def main() -> None:
     ap.add_argument('--split-k', type=int, default=0)
     ap.add_argument('--stages', type=int, default=0)
     ap.add_argument('--out', default='bf16', choices=['bf16', 'f32'])
+    ap.add_argument('--fp4', action='store_true', help='both operands packed E2M1 (dense only)')
+    ap.add_argument('--quant', default='', choices=['', 'swiglu', 'cast'],
+                    help='run the FP8 producer on [m, k] activations instead of a GEMM')
     args = ap.parse_args()
 
     torch.manual_seed(0)
@@ -34,6 +37,17 @@ def main() -> None:
     m, n, k, g = args.m, args.n, args.k, args.groups
     k64 = (k + 63) // 64
     rows = m * g if g else m
+
+    if args.quant:
+        x = torch.randn(m, k * (2 if args.quant == 'swiglu' else 1), device=dev).bfloat16()
+        for _ in range(args.iters):
+            if args.quant == 'swiglu':
+                deep_gemm.swiglu_apply_weight_to_fp8(x)
+            else:
+                deep_gemm.cast_to_fp8(x)
+        torch.cuda.synchronize()
+        print('status', deep_gemm.device_status(), 'launches', args.iters)
+        return
 
     def codes(*shape):
         return torch.randint(0, 120, shape, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
@@ -44,6 +58,9 @@ def main() -> None:
 
     a, sfa = codes(rows, k), scales((), rows)
     b, sfb = (codes(g, n, k), scales((g,), n)) if g else (codes(n, k), scales((), n))
+    if args.fp4:
+        a = torch.randint(-128, 128, (rows, k // 2), dtype=torch.int8, device=dev)
+        b = torch.randint(-128, 128, (n, k // 2), dtype=torch.int8, device=dev)
     d = torch.empty(rows, n, dtype=torch.bfloat16 if args.out == 'bf16' else torch.float32, device=dev)
     config = {key: val for key, val in (('block_n', args.block_n), ('cta_group', args.cta_group),
                                         ('split_k', args.split_k), ('num_stages', args.stages)) if val}
