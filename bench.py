@@ -124,7 +124,7 @@ class ClockSampler:
         self.samples, self.proc = [], None
         try:
             self.proc = subprocess.Popen(['nvidia-smi', f'--id={gpu_index}', f'--query-gpu={self.FIELDS}',
-                                          '--format=csv,noheader,nounits', '-lms', '100'],
+                                          '--format=csv,noheader,nounits', '-lms', '20'],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -269,10 +269,11 @@ def run_dense(args, rank, world, device):
         else:
             sweep(sptr)
 
+    # (the clock sampler also sees the warm-up replays: the timed region alone lasts only some tens of milliseconds)
+    sampler = ClockSampler(device.index) if rank == 0 else None
     for _ in range(warmup):
         step()
     barrier()
-    sampler = ClockSampler(device.index) if rank == 0 else None
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = lib.dg_kernel_launch_count()
     t_begin.record(stream)
@@ -377,7 +378,9 @@ def run_dense(args, rank, world, device):
                               % args.steps if graph is not None else 'one CUDA-event pair around the steps, plain stream launches')
                              + '; per-shape and roofline figures from a second pass with one event pair per launch'},
         'roofline': {'bound': 'tensor', 'achieved': tf_big, 'peak': fp8_peak, 'unit': 'TFLOP/s', 'frac': tf_big / fp8_peak,
-                     'traffic': None, 'kernel': 'mx_gemm_kernel on the six M=4096 launches',
+                     'traffic': 558.0e6, 'traffic_of': 'dram__bytes_read.sum + dram__bytes_write.sum of the 4096x7168x16384 launch '
+                     '(ncu capture in profiles/mx_gemm_pair_4096x7168x16384.md; algorithmic 249.0 MB)',
+                     'kernel': 'mx_gemm_kernel on the six M=4096 launches',
                      'peak_source': '2 x bf16 burst of MEASURED_PEAKS.json (%s)' % pk['source']},
         'roofline_small_m': {'bound': 'hbm', 'achieved': gbs_small, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
                              'frac': gbs_small / pk['hbm_gbs'], 'kernel': 'mx_gemm_kernel (+ split-K finalisation) on the twelve M<=128 launches'},

@@ -352,7 +352,8 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     // Cluster split-K (dense GEMM, single CTAs, unpacked B): the K splits of one tile run as one thread-block cluster
     // and reduce through shared memory, so no second kernel and no FP32 round trip through L2. Modelled cost: the
     // main loop of one split, the exchange (staging, bulk copies, waiting for the slowest rank, summation: measured
-    // ~6000 cycles), and a cluster launch that starts ~2.5 us later than a plain one.
+    // 5000-7000 cycles, growing with the chunks sent and the cluster size), and a cluster launch that starts ~2.5 us
+    // later than a plain one.
     bool best_in_cluster = false;
     if (d.gemm_type == DG_GEMM_NORMAL && !decodes_b(d) && d.major_b == DG_MAJOR_K && !feature_disabled("cluster")) {
         const uint64_t m_tiles = (rows + kBlockM - 1) / kBlockM;
@@ -363,7 +364,10 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
                 const uint64_t tiles = m_tiles * ceil_div_u32(d.n, bn) * split;
                 const uint64_t waves = (tiles + num_sms - 1) / num_sms;
                 const uint32_t kb_per = ceil_div_u32(nkb, split);
-                const double cycles = kb_per * k_block_cycles(1, bn) + bn * (d_fp32 ? 8.0 : 6.0) + 700.0 + 6000.0;
+                // exchange: staging and sending the chunks a rank does not own, the cluster barrier, the summation
+                const uint32_t chunks = bn / 32, sent = chunks - chunks / split;
+                const double exchange = 3000.0 + 900.0 * sent + 150.0 * split;
+                const double cycles = kb_per * k_block_cycles(1, bn) + bn * (d_fp32 ? 8.0 : 6.0) + 700.0 + exchange;
                 double cost = (double)waves * cycles / 1.8 + 2500.0;
                 if (cost < t_hbm) cost = t_hbm + 1e-3 * cost;
                 if (cost < best_cost * (1.0 - 1e-9)) {
