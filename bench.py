@@ -6,7 +6,7 @@ own operands, so a step touches about 1.5 GB and no launch finds its inputs in L
 with one CUDA-event pair around all of them, each step being one replay of a CUDA graph of the 18 launches; a second
 pass with one event pair per launch gives the per-shape table and the roofline figures.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload dense|grouped|masked|mixed|fp4|quant]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload dense|grouped|masked|mixed|fp4|bf16|quant]
 
 Prints one JSON line (rank 0). `value` is whole-job TFLOP/s with operands resident in HBM; `e2e` is the same metric
 through the public Python API with pinned host buffers, host<->device copies inside the timed region.
@@ -416,7 +416,7 @@ def main():
     ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='dense', choices=['dense', 'grouped', 'masked', 'mixed', 'fp4', 'quant'])
+    ap.add_argument('--workload', default='dense', choices=['dense', 'grouped', 'masked', 'mixed', 'fp4', 'bf16', 'quant'])
     ap.add_argument('--experts-per-gpu', type=int, default=0, help='grouped / masked workloads (default 8 / 32)')
     ap.add_argument('--no-graph', action='store_true',
                     help='dense workload: plain stream launches instead of a CUDA graph (for profilers that cannot follow a capture)')

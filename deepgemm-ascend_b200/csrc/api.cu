@@ -82,17 +82,26 @@ static bool tma_store_ok(const dg_gemm_desc_t& d) {
 
 // Both operands packed E2M1: the kind::mxf4 path. The kernel then counts K in bytes (two elements each).
 static bool is_fp4_pair(const dg_gemm_desc_t& d) { return d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E2M1X2; }
-static uint32_t k_bytes(const dg_gemm_desc_t& d) { return is_fp4_pair(d) ? d.k / 2 : d.k; }
-static uint32_t sf_atoms(const dg_gemm_desc_t& d) { return is_fp4_pair(d) ? 2u : 1u; }
+// Both operands BF16: kind::f16, no scale factors; strides are in BF16 elements.
+static bool is_bf16_pair(const dg_gemm_desc_t& d) { return d.a_dtype == DG_BF16 && d.b_dtype == DG_BF16; }
+static uint32_t ab_elem_bytes(const dg_gemm_desc_t& d) { return is_bf16_pair(d) ? 2u : 1u; }
+static uint32_t k_bytes(const dg_gemm_desc_t& d) { return is_fp4_pair(d) ? d.k / 2 : d.k * ab_elem_bytes(d); }
+static uint32_t sf_atoms(const dg_gemm_desc_t& d) { return is_bf16_pair(d) ? 0u : is_fp4_pair(d) ? 2u : 1u; }
+// K elements in one 128-byte stage row
+static uint32_t stage_k(const dg_gemm_desc_t& d) { return is_fp4_pair(d) ? 256u : kBlockK / ab_elem_bytes(d); }
 // packed E2M1 B next to an E4M3 A is decoded to E4M3 in shared memory
 static bool decodes_b(const dg_gemm_desc_t& d) { return d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3; }
 
 static int validate(const dg_gemm_desc_t& d) {
     DG_CHECK_ARG(d.gemm_type == DG_GEMM_NORMAL || is_grouped(d.gemm_type) ||
                  d.gemm_type == DG_GEMM_K_GROUPED_PSUM || d.gemm_type == DG_GEMM_BATCHED, "Unknown gemm type %d", d.gemm_type);
-    DG_CHECK_ARG(d.a_dtype == DG_E4M3 || d.a_dtype == DG_E2M1X2, "Unsupported operand dtypes");
-    DG_CHECK_ARG(d.b_dtype == DG_E4M3 || d.b_dtype == DG_E2M1X2, "Unsupported operand dtypes");
-    DG_CHECK_ARG(!(d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E4M3), "Unsupported operand dtypes");
+    if (!is_bf16_pair(d)) {
+        DG_CHECK_ARG(d.a_dtype == DG_E4M3 || d.a_dtype == DG_E2M1X2, "Unsupported operand dtypes");
+        DG_CHECK_ARG(d.b_dtype == DG_E4M3 || d.b_dtype == DG_E2M1X2, "Unsupported operand dtypes");
+        DG_CHECK_ARG(!(d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E4M3), "Unsupported operand dtypes");
+    } else {
+        DG_CHECK_ARG(d.epilogue != DG_EPILOGUE_FP8_QUANT, "BF16 matmul has no FP8 output");
+    }
     if (is_fp4_pair(d)) {
         // csrc/jit_kernels/fp8_gemm.hpp:81: "K-major A/B only"
         DG_CHECK_ARG(d.major_a == DG_MAJOR_K && d.major_b == DG_MAJOR_K, "FP4 x FP4 GEMM takes K-major A and B only");
@@ -114,7 +123,7 @@ static int validate(const dg_gemm_desc_t& d) {
     DG_CHECK_ARG(d.major_a == DG_MAJOR_K || d.major_a == DG_MAJOR_MN, "bad major_a");
     DG_CHECK_ARG(d.major_b == DG_MAJOR_K || d.major_b == DG_MAJOR_MN, "bad major_b");
     DG_CHECK_ARG(d.m > 0 && d.n > 0 && d.k > 0, "empty problems are handled by the caller (m, n, k must be > 0)");
-    DG_CHECK_ARG(d.a && d.b && d.d && d.sfa && d.sfb, "null operand pointer");
+    DG_CHECK_ARG(d.a && d.b && d.d && (is_bf16_pair(d) || (d.sfa && d.sfb)), "null operand pointer");
     DG_CHECK_ARG(d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_ALPHA || d.epilogue == DG_EPILOGUE_BIAS ||
                  d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16 || d.epilogue == DG_EPILOGUE_FP8_QUANT, "unknown epilogue");
     DG_CHECK_ARG(d.epilogue != DG_EPILOGUE_STOCHASTIC_BF16 || (d.d_dtype == DG_BF16 && !d.accumulate),
@@ -127,7 +136,7 @@ static int validate(const dg_gemm_desc_t& d) {
         DG_CHECK_ARG(d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16,
                      "k-grouped matmul takes no epilogue besides accumulation and stochastic BF16 rounding");
         DG_CHECK_ARG(d.k % 256 == 0, "k-grouped psum layout: total K must be a multiple of the 256 alignment");
-        DG_CHECK_ARG(d.b_dtype == DG_E4M3, "k-grouped matmul is built for FP8 operands only");
+        DG_CHECK_ARG(d.b_dtype == DG_E4M3 || is_bf16_pair(d), "k-grouped matmul is built for FP8 and BF16 operands only");
     } else if (d.gemm_type == DG_GEMM_BATCHED) {
         DG_CHECK_ARG(d.num_groups > 0, "batched GEMM needs num_groups (the batch count)");
         DG_CHECK_ARG(d.epilogue != DG_EPILOGUE_BIAS, "batched matmul doesn't support bias");
@@ -141,14 +150,17 @@ static int validate(const dg_gemm_desc_t& d) {
         DG_CHECK_ARG(d.m % 256 == 0, "m-grouped psum layout: total rows must be a multiple of the 256-row alignment");
 
     // What TMA needs from the operands. The caller repacks (dg_pad_rows_launch) when these fail.
-    DG_UNSUPPORTED(!aligned16(d.a) || d.outer_stride_a % 16 != 0 || d.group_stride_a % 16 != 0,
+    const uint32_t eb = ab_elem_bytes(d);
+    DG_UNSUPPORTED(!aligned16(d.a) || (d.outer_stride_a * eb) % 16 != 0 || (d.group_stride_a * eb) % 16 != 0,
                    "A: base and strides must be multiples of 16 bytes");
-    DG_UNSUPPORTED(!aligned16(d.b) || d.outer_stride_b % 16 != 0 || d.group_stride_b % 16 != 0,
+    DG_UNSUPPORTED(!aligned16(d.b) || (d.outer_stride_b * eb) % 16 != 0 || (d.group_stride_b * eb) % 16 != 0,
                    "B: base and strides must be multiples of 16 bytes");
-    DG_UNSUPPORTED(!aligned16(d.sfa) || d.sfa_stride % 8 != 0 || d.sfa_group_stride % 8 != 0,
-                   "SFA: base and strides must be multiples of 16 bytes");
-    DG_UNSUPPORTED(!aligned16(d.sfb) || d.sfb_stride % 8 != 0 || d.sfb_group_stride % 8 != 0,
-                   "SFB: base and strides must be multiples of 16 bytes");
+    if (!is_bf16_pair(d)) {
+        DG_UNSUPPORTED(!aligned16(d.sfa) || d.sfa_stride % 8 != 0 || d.sfa_group_stride % 8 != 0,
+                       "SFA: base and strides must be multiples of 16 bytes");
+        DG_UNSUPPORTED(!aligned16(d.sfb) || d.sfb_stride % 8 != 0 || d.sfb_group_stride % 8 != 0,
+                       "SFB: base and strides must be multiples of 16 bytes");
+    }
     return DG_OK;
 }
 
@@ -205,8 +217,9 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     DG_CHECK_ARG(c.block_n >= gran && c.block_n <= 256 && c.block_n % gran == 0,
                  "block_n must be a multiple of %u in [%u, 256]", gran, gran);
     DG_CHECK_ARG(c.block_n % (16 * c.cta_group) == 0, "block_n not valid for this cta_group");
-    if (d.major_b == DG_MAJOR_MN)
-        DG_CHECK_ARG((c.block_n / c.cta_group) % 128 == 0, "MN-major B needs block_n / cta_group to be a multiple of 128");
+    if (d.major_b == DG_MAJOR_MN)      // MN-major B comes in 128-byte atoms along N
+        DG_CHECK_ARG((c.block_n / c.cta_group) % (128 / ab_elem_bytes(d)) == 0,
+                     "MN-major B needs block_n / cta_group to be a multiple of %u", 128 / ab_elem_bytes(d));
     DG_CHECK_ARG(c.cta_group == 1 || d.gemm_type != DG_GEMM_M_GROUPED_MASKED, "masked grouped GEMM uses cta_group 1");
     DG_CHECK_ARG(!split || d.epilogue != DG_EPILOGUE_FP8_QUANT, "FP8 quantization cannot be combined with split-K");
     DG_CHECK_ARG(c.split_k <= 1 || d.gemm_type == DG_GEMM_NORMAL, "split-K is only available for the dense GEMM");
@@ -328,7 +341,7 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
             if (split > 1 && (d.gemm_type != DG_GEMM_NORMAL || nkb / split < 2 || cg == 2 ||
                               d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16 || d.epilogue == DG_EPILOGUE_FP8_QUANT)) break;
             const bool out_fp32 = d_fp32 || split > 1;
-            const uint32_t step = d.major_b == DG_MAJOR_MN ? 128u * cg : 32u;   // MN-major B comes in 128-column atoms
+            const uint32_t step = d.major_b == DG_MAJOR_MN ? (128u / ab_elem_bytes(d)) * cg : 32u;   // MN-major B comes in 128-byte atoms
             for (uint32_t bn = step; bn <= 256; bn += step) {
                 if (bn > step && bn - step >= d.n) continue;                 // a narrower legal tile already covers N
                 if (bn % (16 * cg) != 0) continue;
@@ -438,6 +451,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.block_n = c.block_n;
     a.num_stages = c.num_stages;
     a.num_k_blocks = ceil_div_u32(k_bytes(d), kBlockK);
+    a.stage_k = stage_k(d);
     a.num_m_blocks = ceil_div_u32(d.m, c.block_m);
     a.num_n_blocks = ceil_div_u32(d.n, c.block_n);
     a.gemm_type = (uint32_t)d.gemm_type;
@@ -468,14 +482,18 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.idesc = ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) | ((c.block_n >> 3) << 17) | (1u << 23) |
               (((kBlockM * c.cta_group) >> 4) << 24);
     if (is_fp4_pair(d)) a.idesc |= (1u << 7) | (1u << 10);       // kind::mxf4: both operand formats E2M1
+    if (is_bf16_pair(d))                                         // kind::f16: FP32 accumulator, BF16 operands, no scale fields
+        a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) |
+                  ((c.block_n >> 3) << 17) | (((kBlockM * c.cta_group) >> 4) << 24);
 
     plan.cta_group = (int)c.cta_group;
     plan.major_a = d.major_a;
     plan.major_b = d.major_b;
     plan.decode_b = decodes_b(d);
     plan.fp4_pair = is_fp4_pair(d);
+    plan.bf16_pair = is_bf16_pair(d);
     plan.lean = d.gemm_type == DG_GEMM_NORMAL && c.cta_group == 1 && !plan.decode_b && c.epilogue_mode == kEpiPlainStore &&
-                (d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_BIAS) && !plan.fp4_pair && !feature_disabled("lean");
+                (d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_BIAS) && !plan.fp4_pair && !plan.bf16_pair && !feature_disabled("lean");
     // k-grouped, no accumulation: D of groups whose K range is empty must read as zero
     plan.zero_empty_groups = k_grouped && !d.accumulate;
     plan.zero_d = d.d;
@@ -507,19 +525,25 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     const uint64_t k64 = (d.k + 63) / 64;
     const uint64_t rows_a = d.m;      // rows per group for masked, all rows otherwise
     // ---- A
+    // Operand maps count in TMA elements: bytes for the 8-bit and packed 4-bit kinds, BF16 elements for BF16. A stage is
+    // 128 bytes of K per row; an MN-major tile is fetched as one box per 128-byte atom along MN.
+    const uint32_t eb = ab_elem_bytes(d);
+    const CUtensorMapDataType ab_type = is_bf16_pair(d) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const uint64_t k_elems = k_bytes(d) / eb;
+    const uint32_t box_k = kBlockK / eb, atom_mn = 128 / eb;
     {
         const uint64_t gs = nonzero_stride(d.group_stride_a, rows_a * d.outer_stride_a);
         if (d.major_a == DG_MAJOR_K) {
-            const uint64_t dims[3] = {k_bytes(d), rows_a, masked ? groups : 1};
-            const uint64_t str[2] = {d.outer_stride_a, gs};
-            const uint32_t box[3] = {kBlockK, kBlockM, 1};
-            if (int rc = encode_map(&plan.tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "A")) return rc;
+            const uint64_t dims[3] = {k_elems, rows_a, masked ? groups : 1};
+            const uint64_t str[2] = {d.outer_stride_a * eb, gs * eb};
+            const uint32_t box[3] = {box_k, kBlockM, 1};
+            if (int rc = encode_map(&plan.tm_a, ab_type, 3, d.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "A")) return rc;
         } else {
-            const uint64_t dims[3] = {rows_a, d.k, masked ? groups : 1};
-            const uint64_t str[2] = {d.outer_stride_a, masked ? nonzero_stride(d.group_stride_a, (uint64_t)d.k * d.outer_stride_a)
-                                                               : align_u64((uint64_t)d.k * d.outer_stride_a, 16)};
-            const uint32_t box[3] = {kBlockM, kBlockK, 1};
-            if (int rc = encode_map(&plan.tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "A")) return rc;
+            const uint64_t dims[3] = {rows_a, k_elems, masked ? groups : 1};
+            const uint64_t str[2] = {d.outer_stride_a * eb, masked ? nonzero_stride(d.group_stride_a, (uint64_t)d.k * d.outer_stride_a) * eb
+                                                                    : align_u64((uint64_t)d.k * d.outer_stride_a * eb, 16)};
+            const uint32_t box[3] = {atom_mn, box_k, 1};
+            if (int rc = encode_map(&plan.tm_a, ab_type, 3, d.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "A")) return rc;
         }
     }
     // ---- B
@@ -541,27 +565,30 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     } else {
         if (d.major_b == DG_MAJOR_K) {
             const uint64_t gs = nonzero_stride(d.group_stride_b, (uint64_t)d.n * d.outer_stride_b);
-            const uint64_t dims[3] = {k_bytes(d), d.n, groups};
-            const uint64_t str[2] = {d.outer_stride_b, gs};
-            const uint32_t box[3] = {kBlockK, load_n, 1};
-            if (int rc = encode_map(&plan.tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "B")) return rc;
+            const uint64_t dims[3] = {k_elems, d.n, groups};
+            const uint64_t str[2] = {d.outer_stride_b * eb, gs * eb};
+            const uint32_t box[3] = {box_k, load_n, 1};
+            if (int rc = encode_map(&plan.tm_b, ab_type, 3, d.b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "B")) return rc;
         } else {
             const uint64_t gs = nonzero_stride(d.group_stride_b, (uint64_t)d.k * d.outer_stride_b);
-            const uint64_t dims[3] = {d.n, d.k, groups};
-            const uint64_t str[2] = {d.outer_stride_b, gs};
-            const uint32_t box[3] = {128, kBlockK, 1};
-            if (int rc = encode_map(&plan.tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "B")) return rc;
+            const uint64_t dims[3] = {d.n, k_elems, groups};
+            const uint64_t str[2] = {d.outer_stride_b * eb, gs * eb};
+            const uint32_t box[3] = {atom_mn, box_k, 1};
+            if (int rc = encode_map(&plan.tm_b, ab_type, 3, d.b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "B")) return rc;
         }
     }
     // ---- scale factors: int16 [rows (contiguous), K64, groups]
-    {
+    if (is_bf16_pair(d)) {
+        plan.tm_sfa = plan.tm_a;      // never used by the BF16 kernel, but the parameters must be valid descriptors
+        plan.tm_sfb = plan.tm_b;
+    } else {
         const uint64_t gs = nonzero_stride(d.sfa_group_stride, k64 * d.sfa_stride);
         const uint64_t dims[3] = {rows_a, k64, masked ? groups : 1};
         const uint64_t str[2] = {d.sfa_stride * 2, gs * 2};
         const uint32_t box[3] = {128, 2 * sf_atoms(d), 1};
         if (int rc = encode_map(&plan.tm_sfa, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.sfa, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE, "SFA")) return rc;
     }
-    {
+    if (!is_bf16_pair(d)) {
         const uint64_t gs = nonzero_stride(d.sfb_group_stride, k64 * d.sfb_stride);
         const uint64_t dims[3] = {d.n, k64, groups};
         const uint64_t str[2] = {d.sfb_stride * 2, gs * 2};

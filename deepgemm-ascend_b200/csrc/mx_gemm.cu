@@ -60,7 +60,16 @@ __global__ void zero_empty_k_groups_kernel(uint8_t* __restrict__ d, const int32_
 using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
                           const CUtensorMap, const CUtensorMap, const GemmKernelArgs);
 
-static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode_b, bool lean, bool fp4_pair) {
+static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode_b, bool lean, bool fp4_pair, bool bf16_pair) {
+    if (bf16_pair) {
+        static const KernelFn bf16_table[2][2][2] = {
+            {{mx_gemm_kernel<1, 0, 0, false, false, false, true>, mx_gemm_kernel<1, 0, 1, false, false, false, true>},
+             {mx_gemm_kernel<1, 1, 0, false, false, false, true>, mx_gemm_kernel<1, 1, 1, false, false, false, true>}},
+            {{mx_gemm_kernel<2, 0, 0, false, false, false, true>, mx_gemm_kernel<2, 0, 1, false, false, false, true>},
+             {mx_gemm_kernel<2, 1, 0, false, false, false, true>, mx_gemm_kernel<2, 1, 1, false, false, false, true>}},
+        };
+        return bf16_table[cta_group - 1][major_a][major_b];
+    }
     if (fp4_pair)
         return cta_group == 2 ? mx_gemm_kernel<2, 0, 0, false, false, true> : mx_gemm_kernel<1, 0, 0, false, false, true>;
     if (lean) {
@@ -97,7 +106,7 @@ int get_status_pointer(int32_t** out) {
 }
 
 int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
-    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b, plan.lean, plan.fp4_pair);
+    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b, plan.lean, plan.fp4_pair, plan.bf16_pair);
     // The attribute is per device and per function; setting it is cheap, so do it on every launch.
     DG_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem_bytes));
 

@@ -51,7 +51,8 @@ struct GemmKernelArgs {
     uint32_t m, n, k;                 // m: rows of D (normal), total rows (psum), max_m (masked)
     uint32_t block_n;                 // multiple of 32, <= 256
     uint32_t num_stages;
-    uint32_t num_k_blocks;            // ceil(k / 128)
+    uint32_t num_k_blocks;            // K blocks of 128 bytes per row
+    uint32_t stage_k;                 // K elements in one block: 128 (FP8), 256 (packed FP4 pair), 64 (BF16)
     uint32_t num_m_blocks, num_n_blocks;
     uint32_t gemm_type;
     uint32_t num_groups;
@@ -160,8 +161,8 @@ struct Scheduler {
             const uint32_t start = cur_group == 0 ? 0u : ((uint32_t)__ldg(p.grouped_layout + cur_group - 1) + 255u) / 256u * 256u;
             const uint32_t end = (uint32_t)__ldg(p.grouped_layout + cur_group);
             cur_row0 = 0;
-            cur_kb_begin = start / kBlockK;
-            cur_kb_end = end > start ? (end + kBlockK - 1) / kBlockK : cur_kb_begin;
+            cur_kb_begin = start / p.stage_k;
+            cur_kb_end = end > start ? (end + p.stage_k - 1) / p.stage_k : cur_kb_begin;
             cur_blocks = end > start ? p.num_m_blocks : 0u;
         } else if (p.gemm_type == kMGroupedPsum) {
             // scheduler.hpp:147-162: group g owns rows [align(psum[g-1],256), psum[g]) and the
@@ -364,7 +365,9 @@ __device__ __forceinline__ uint2 stochastic_round_quartet(uint32_t v0, uint32_t 
 // instruction fetch for code it never needs; the lean instantiation leaves all of that out.
 // kFp4: both operands are packed E2M1, K-major: a stage is still 128 bytes of K per row (256 elements), the MMA is
 // kind::mxf4 with two scales per row per instruction, and a stage carries eight scale bytes per row instead of four.
-template <int kCtaGroup, int kMajorA, int kMajorB, bool kDecodeB, bool kLean = false, bool kFp4 = false>
+// kBf16: BF16 operands, no scale factors (kind::f16): a stage is 128 bytes = 64 K-elements per row; the packer
+// warp idles and the MMA thread waits for the operands directly.
+template <int kCtaGroup, int kMajorA, int kMajorB, bool kDecodeB, bool kLean = false, bool kFp4 = false, bool kBf16 = false>
 __global__ void __launch_bounds__(kDecodeB ? kNumThreadsDecode : kNumThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
@@ -374,7 +377,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t cluster_split = (kCtaGroup == 1 && !kDecodeB) ? p.cluster_split : 1u;
-    constexpr uint32_t kSfAtoms = kFp4 ? 2u : 1u;
+    constexpr uint32_t kSfAtoms = kBf16 ? 0u : kFp4 ? 2u : 1u;
+    constexpr uint32_t kElemBytes = kBf16 ? 2u : 1u;              // bytes per operand element as TMA counts them
+    constexpr uint32_t kStageK = kBlockK / kElemBytes;            // TMA elements of K per stage (= K rows of an MN-major tile)
+    constexpr uint32_t kAtomMn = 128 / kElemBytes;                // MN elements in one 128-byte swizzle atom
     const SmemLayout L = make_smem_layout(p.block_n, p.num_stages, kCtaGroup, kDecodeB, p.store_bufs, cluster_split, kSfAtoms);
 
     const uint32_t warp = threadIdx.x / 32, lane = lane_id();
@@ -463,15 +469,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     if (first_issue) trace_mark(p, 10);
                     const uint32_t bar = full_bar(stage);
                     const uint32_t bytes = L.a_stage + (kDecodeB ? L.b_raw_stage : load_n * kBlockK) + L.sfa_stage + L.sfb_stage;
+                    static_assert(!kBf16 || !kDecodeB, "BF16 operands are never decoded");
                     mbar_arrive_expect_tx(bar, bytes);
                     if (first_issue) { trace_mark(p, 3); first_issue = false; }
                     const uint32_t sa = smem_base + L.a + stage * L.a_stage;
                     const uint32_t sb = smem_base + L.b + stage * L.b_stage;
-                    const int32_t k0 = (int32_t)(kb * kBlockK);
+                    const int32_t k0 = (int32_t)(kb * kStageK);
                     if constexpr (kMajorA == 0) {
                         tma_load_3d(sa, &tm_a, bar, k0, (int32_t)t.row0, (int32_t)t.row_z);
                     } else {
-                        tma_load_3d(sa, &tm_a, bar, (int32_t)t.row0, k0, (int32_t)t.row_z);
+                        // one box per 128-byte atom along M: [atom][K rows of the stage][128 B]
+                        #pragma unroll
+                        for (uint32_t a0 = 0; a0 < kBlockM; a0 += kAtomMn)
+                            tma_load_3d(sa + (a0 / kAtomMn) * kStageK * 128, &tm_a, bar, (int32_t)(t.row0 + a0), k0, (int32_t)t.row_z);
                     }
                     const uint32_t bn0 = t.n0 + cta_rank * load_n;
                     if constexpr (kDecodeB) {
@@ -482,15 +492,17 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     } else if constexpr (kMajorB == 0) {
                         tma_load_3d(sb, &tm_b, bar, k0, (int32_t)bn0, (int32_t)t.b_z);
                     } else {
-                        // one box per 128-column atom: [atom][block_k rows][128 B]
-                        for (uint32_t a0 = 0; a0 < load_n; a0 += 128)
-                            tma_load_3d(sb + a0 * kBlockK, &tm_b, bar, (int32_t)(bn0 + a0), k0, (int32_t)t.b_z);
+                        // one box per 128-byte atom along N: [atom][K rows of the stage][128 B]
+                        for (uint32_t a0 = 0; a0 < load_n; a0 += kAtomMn)
+                            tma_load_3d(sb + (a0 / kAtomMn) * kStageK * 128, &tm_b, bar, (int32_t)(bn0 + a0), k0, (int32_t)t.b_z);
                     }
                     if (i == 0) trace_mark(p, 11);
-                    tma_load_3d(smem_base + L.sf_raw_a + stage * L.sfa_stage, &tm_sfa, bar,
-                                (int32_t)t.row0, (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.row_z);
-                    tma_load_3d(smem_base + L.sf_raw_b + stage * L.sfb_stage, &tm_sfb, bar,
-                                (int32_t)t.n0, (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.b_z);
+                    if constexpr (!kBf16) {
+                        tma_load_3d(smem_base + L.sf_raw_a + stage * L.sfa_stage, &tm_sfa, bar,
+                                    (int32_t)t.row0, (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.row_z);
+                        tma_load_3d(smem_base + L.sf_raw_b + stage * L.sfb_stage, &tm_sfb, bar,
+                                    (int32_t)t.n0, (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.b_z);
+                    }
                     if (i == 0) trace_mark(p, 12);
                     if (++stage == num_stages) { stage = 0; phase ^= 1; ring_used = true; }
                 }
@@ -521,6 +533,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + e * p.block_n;
                 for (uint32_t kb = t.kb_begin; kb < t.kb_end; ++kb) {
+                    // (BF16: the packer only forwards the arrival of the operands, which in a CTA pair is how the
+                    // leader learns that the peer's half has landed too)
                     if (kCtaGroup == 2) ok = wait_barrier_cluster(sf_full_bar(stage), phase, ab, kStatusTimeoutMma);
                     else ok = wait_barrier(sf_full_bar(stage), phase, ab, kStatusTimeoutMma);
                     if (!ok) break;
@@ -529,7 +543,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     // scales: smem -> TMEM (A: 128 rows = one slab; B: one slab per 128 columns)
                     // (packed E2M1: word g of a row holds the scales of K-elements [128 g, 128 g + 128) of the stage)
                     #pragma unroll
-                    for (uint32_t g = 0; g < kSfAtoms; ++g) {
+                    for (uint32_t g = 0; g + 1 <= kSfAtoms; ++g) {
                         utccp_32x128b_warpx4<kCtaGroup>(tmem_sfa + g * 4,
                                                         make_sf_desc(smem_base + L.sf_pack_a + stage * L.sfa_stage + g * 512));
                         for (uint32_t i = 0; i < sfb_slabs; ++i)
@@ -540,12 +554,16 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     const uint32_t sb = smem_base + L.b + stage * L.b_stage;
                     #pragma unroll
                     for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k) {
+                        // every instruction consumes 32 bytes of K per row: 32 FP8, 64 FP4 or 16 BF16 elements
+                        constexpr uint32_t kMmaKRows = kUmmaK / kElemBytes;
                         uint64_t da, db;
                         if constexpr (kMajorA == 0) da = make_kmajor_sw128_desc(sa + k * kUmmaK);
-                        else da = make_mnmajor_sw128_desc(sa + k * kUmmaK * 128, kBlockK * 128);
+                        else da = make_mnmajor_sw128_desc(sa + k * kMmaKRows * 128, kStageK * 128);
                         if constexpr (kMajorB == 0) db = make_kmajor_sw128_desc(sb + k * kUmmaK);
-                        else db = make_mnmajor_sw128_desc(sb + k * kUmmaK * 128, kBlockK * 128);
-                        if constexpr (kFp4) {
+                        else db = make_mnmajor_sw128_desc(sb + k * kMmaKRows * 128, kStageK * 128);
+                        if constexpr (kBf16) {
+                            umma_f16<kCtaGroup>(tmem_d, da, db, p.idesc, (kb > t.kb_begin || k > 0) ? 1u : 0u);
+                        } else if constexpr (kFp4) {
                             // instruction k reads 64 K-elements: scale bytes 2(k&1), 2(k&1)+1 of word k/2
                             const uint32_t id = (k & 1u) * 2u, g = k >> 1;
                             umma_mxf4<kCtaGroup>(tmem_d, da, db, p.idesc | (id << 4) | (id << 29), tmem_sfa + g * 4,
@@ -587,7 +605,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 const uint16_t* raw_b = reinterpret_cast<const uint16_t*>(smem_gen + L.sf_raw_b + stage * L.sfb_stage);
                 uint4* pack_b = reinterpret_cast<uint4*>(smem_gen + L.sf_pack_b + stage * L.sfb_stage);
                 #pragma unroll
-                for (uint32_t g = 0; g < kSfAtoms; ++g) {        // word g of a row = int16 columns 2g and 2g + 1
+                for (uint32_t g = 0; g + 1 <= kSfAtoms; ++g) {   // word g of a row = int16 columns 2g and 2g + 1
                     uint32_t v[4];
                     #pragma unroll
                     for (uint32_t j = 0; j < 4; ++j)

@@ -1,7 +1,7 @@
 """deep_gemm for NVIDIA B200: block-scaled FP8 / FP8xFP4 GEMM behind the DeepGEMM-Ascend Python API.
 
 The names, arguments and error text of the hot path follow the reference's `deep_gemm/__init__.py:25-81`;
-everything else of the reference (attention, MegaMoE, BF16 GEMM, ACLNN wrappers) is out of scope
+everything else of the reference (attention, MegaMoE, BF16 einsum, ACLNN wrappers) is out of scope
 and not exported. Importing this package never initialises a CUDA context.
 """
 
@@ -9,6 +9,10 @@ __version__ = '0.1.1'
 
 from . import epilogue, locality_domain, quant_ops, testing  # noqa: F401
 from ._api import (  # noqa: F401
+    bf16_gemm_nn,
+    bf16_gemm_nt,
+    bf16_gemm_tn,
+    bf16_gemm_tt,
     device_status,
     fp8_bmm,
     fp8_einsum,
@@ -28,8 +32,11 @@ from ._api import (  # noqa: F401
     get_recipe,
     get_theoretical_mk_alignment_for_contiguous_layout,
     init,
+    k_grouped_bf16_gemm_tn_contiguous,
     k_grouped_fp8_gemm_nt_contiguous,
     k_grouped_fp8_gemm_tn_contiguous,
+    m_grouped_bf16_gemm_nn_contiguous,
+    m_grouped_bf16_gemm_nt_contiguous,
     m_grouped_fp8_fp4_gemm_nn_contiguous,
     m_grouped_fp8_fp4_gemm_nt_contiguous,
     m_grouped_fp8_fp4_gemm_nt_masked,

@@ -465,23 +465,29 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
     if with_bias:
         epilogue_obj = _Bias(c)
 
-    gran_m, gran_n, gran_k_a, gran_k_b = get_recipe(recipe, recipe_a, recipe_b)
     masked = gemm_type in (L.GEMM_M_GROUPED_MASKED, L.GEMM_BATCHED)    # A, SFA and D carry the group dimension
-    if gemm_type == L.GEMM_K_GROUPED_PSUM:
+    bf16 = a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16       # no scale factors (csrc/apis/gemm.hpp:412-433)
+    _host_assert(bf16 or (sfa_in is not None and sfb_in is not None), 'Unsupported operand dtypes')
+    if bf16:
+        sfa = sfb = None
+    elif gemm_type == L.GEMM_K_GROUPED_PSUM:
+        gran_m, gran_n, gran_k_a, gran_k_b = get_recipe(recipe, recipe_a, recipe_b)
         sfa = _transform_sf(sfa_in, m, k, gran_m, gran_k_a, None, False, None, True, k_psum_layout=grouped_layout)
         sfb = _transform_sf(sfb_in, n, k, gran_n, gran_k_b, None, False, None, True, k_psum_layout=grouped_layout)
     else:
+        gran_m, gran_n, gran_k_a, gran_k_b = get_recipe(recipe, recipe_a, recipe_b)
         sfa = _transform_sf(sfa_in, m, k, gran_m, gran_k_a, g if masked else None, disable_ue8m0_cast,
                             grouped_layout if gemm_type == L.GEMM_M_GROUPED_PSUM else None, True)
         sfb = _transform_sf(sfb_in, n, k, gran_n, gran_k_b, g if gemm_type != L.GEMM_NORMAL else None,
                             disable_ue8m0_cast, None, True)
 
     _host_assert(a.dtype in _DTYPES and b.dtype in _DTYPES, 'Unsupported operand dtypes')
-    a_use, b_use = _tma_ready_operand(a, major_a), _tma_ready_operand(b, major_b)
+    # (BF16 operands are not repacked: the library answers "strides must be multiples of 16 bytes" for odd views)
+    a_use, b_use = (a, b) if bf16 else (_tma_ready_operand(a, major_a), _tma_ready_operand(b, major_b))
 
     desc = L.GemmDesc()
     desc.a, desc.b, desc.d = _ptr(a_use), _ptr(b_use), _ptr(d)
-    desc.sfa, desc.sfb = _ptr(sfa), _ptr(sfb)
+    desc.sfa, desc.sfb = (None, None) if bf16 else (_ptr(sfa), _ptr(sfb))
     desc.a_dtype, desc.b_dtype, desc.d_dtype = _DTYPES[a.dtype], _DTYPES[b.dtype], _DTYPES[d.dtype]
     desc.m, desc.n, desc.k = m, n, k
     desc.major_a, desc.major_b = major_a, major_b
@@ -491,9 +497,10 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
     desc.group_stride_a = a_use.stride(0) if masked else 0
     desc.group_stride_b = b_use.stride(0) if b_use.dim() == 3 else 0
     desc.group_stride_d = d.stride(0) if masked or gemm_type == L.GEMM_K_GROUPED_PSUM else 0
-    desc.sfa_stride, desc.sfb_stride = sfa.stride(-1), sfb.stride(-1)
-    desc.sfa_group_stride = sfa.stride(0) if sfa.dim() == 3 else 0
-    desc.sfb_group_stride = sfb.stride(0) if sfb.dim() == 3 else 0
+    if not bf16:
+        desc.sfa_stride, desc.sfb_stride = sfa.stride(-1), sfb.stride(-1)
+        desc.sfa_group_stride = sfa.stride(0) if sfa.dim() == 3 else 0
+        desc.sfb_group_stride = sfb.stride(0) if sfb.dim() == 3 else 0
     desc.accumulate = int(c is not None and not with_bias)
     desc.gemm_type = gemm_type
     desc.grouped_layout = _ptr(grouped_layout) if grouped_layout is not None else None
@@ -627,6 +634,57 @@ def k_grouped_fp8_gemm_nt_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, re
                   'shape and call `k_grouped_fp8_gemm_tn_contiguous` instead', DeprecationWarning, stacklevel=2)
     k_grouped_fp8_gemm_tn_contiguous(_transposed(a, True, 0, 1), _transposed(b, True, 0, 1), d, ks_cpu, grouped_layout,
                                      c, recipe, compiled_dims, use_psum_layout, epilogue, config=config)
+
+
+# ------------------------------------------------------------------------------------------------
+# BF16 GEMM family (csrc/apis/gemm.hpp:412-560): same kernels with kind::f16 MMAs and no scale factors
+# ------------------------------------------------------------------------------------------------
+def _make_bf16_dense(trans_a: bool, trans_b: bool, default_dims: str):
+    def fn(a, b, d, c=None, compiled_dims=default_dims, alpha=None, epilogue=None, *, config=None):
+        a_t = a.transpose(0, 1) if trans_a else a
+        b_t = b.transpose(0, 1) if trans_b else b
+        _host_assert(a_t.dtype == torch.bfloat16 and b_t.dtype == torch.bfloat16, 'A and B must be bfloat16')
+        _host_assert(d.dtype in (torch.bfloat16, torch.float32), 'D must be bf16 or fp32')
+        _run_gemm(L.GEMM_NORMAL, a_t, b_t, d, c, _resolve_epilogue(epilogue, c, d, alpha), None, None,
+                  None, None, None, None, compiled_dims, False, config=config)
+    fn.__doc__ = 'D = A @ B^T (+ C) for BF16 operands; see csrc/apis/gemm.hpp:412-440.'
+    return fn
+
+
+bf16_gemm_nt = _make_bf16_dense(False, False, 'nk')
+bf16_gemm_nn = _make_bf16_dense(False, True, 'nk')
+bf16_gemm_tn = _make_bf16_dense(True, True, 'mn')
+bf16_gemm_tt = _make_bf16_dense(True, False, 'mn')
+
+
+def _make_m_grouped_bf16_contiguous(trans_b: bool):
+    def fn(a, b, d, grouped_layout, compiled_dims='nk', use_psum_layout=True, ensure_zero_padding=True,
+           expected_m_for_psum_layout=None, epilogue=None, *, config=None):
+        b_t = b.transpose(1, 2) if trans_b else b
+        _host_assert(a.dtype == torch.bfloat16 and b_t.dtype == torch.bfloat16, 'A and B must be bfloat16')
+        _host_assert(d.dtype in (torch.bfloat16, torch.float32), 'D must be bf16 or fp32')
+        _host_assert(use_psum_layout is True, 'use_psum_layout must be True')
+        _run_gemm(L.GEMM_M_GROUPED_PSUM, a, b_t, d, None, _resolve_epilogue(epilogue, None, d), None, None,
+                  None, None, None, grouped_layout, compiled_dims, True, expected_m=expected_m_for_psum_layout, config=config)
+    fn.__doc__ = 'Per-group D[rows_g] = A[rows_g] @ B[g]^T for BF16 operands; see csrc/apis/gemm.hpp:442-475.'
+    return fn
+
+
+m_grouped_bf16_gemm_nt_contiguous = _make_m_grouped_bf16_contiguous(False)
+m_grouped_bf16_gemm_nn_contiguous = _make_m_grouped_bf16_contiguous(True)
+
+
+def k_grouped_bf16_gemm_tn_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, compiled_dims='mn', use_psum_layout=True,
+                                      epilogue=None, *, config=None):
+    """csrc/apis/gemm.hpp:477-514. A [K, M], B [K, N] BF16 with K in psum layout; D[g] = A[group g]^T @ B[group g] (+ C[g])."""
+    a_t, b_t = a.transpose(0, 1), b.transpose(0, 1)
+    _host_assert(a_t.dtype == torch.bfloat16 and b_t.dtype == torch.bfloat16, 'A and B must be bfloat16')
+    _host_assert(d.dtype in (torch.bfloat16, torch.float32))
+    _host_assert(use_psum_layout is True)
+    k, g = a_t.size(-1), grouped_layout.numel()
+    expected_k = max(1, sum(ks_cpu) // len(ks_cpu)) if ks_cpu else (k // g if g else k)
+    _run_gemm(L.GEMM_K_GROUPED_PSUM, a_t, b_t, d, c, _resolve_epilogue(epilogue, c, d), None, None,
+              None, None, None, grouped_layout, compiled_dims, False, expected_m=expected_k, config=config)
 
 
 def fp8_bmm(a, b, d, c=None, recipe=(1, 1, 32), compiled_dims='nk', epilogue=None, *, config=None):

@@ -73,6 +73,8 @@ def run(args, rank, world, device, emit=None):
         return run_mixed(args, rank, world, device, emit)
     if args.workload == 'fp4':
         return run_fp4(args, rank, world, device, emit)
+    if args.workload == 'bf16':
+        return run_bf16(args, rank, world, device, emit)
     if args.workload == 'quant':
         return run_quant(args, rank, world, device, emit)
     lib = L.lib()
@@ -319,4 +321,58 @@ def run_quant(args, rank, world, device, emit=None):
             'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
                          'traffic': None, 'kernel': 'quant_fp8_kernel'},
             'ops': out_rows, 'device_status': _api.device_status()}
+    (emit or (lambda l: print(json.dumps(l), flush=True)))(line)
+
+
+def run_bf16(args, rank, world, device, emit=None):
+    """BF16 GEMM "NT" (kind::f16, no scale factors), BF16 out, on three M = 4096 shapes of the dense sweep and one
+    decode shape. Normalised by the measured BF16 burst figure."""
+    lib = L.lib()
+    stream = torch.cuda.current_stream(device)
+    sptr = stream.cuda_stream
+    flush = l2_flush_buffer(device)
+    gen = torch.Generator(device=device).manual_seed(13 + rank)
+    shapes = [(4096, 7168, 16384), (4096, 4096, 7168), (4096, 7168, 2048), (128, 7168, 16384)]
+    rows = []
+    for (m, n, k) in shapes:
+        a = torch.randn(m, k, device=device, generator=gen).bfloat16()
+        b = torch.randn(n, k, device=device, generator=gen).bfloat16()
+        d = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+        desc = _api._run_gemm(L.GEMM_NORMAL, a, b, d, None, _api.Identity(), None, None, None, None, None, None, 'nk', False)
+        cfg = L.GemmConfig()
+        L.check(lib.dg_select_config(ctypes.byref(desc), ctypes.byref(cfg)))
+        ws_bytes = lib.dg_gemm_workspace_bytes(ctypes.byref(desc), None)
+        ws = _api._workspace(device, ws_bytes) if ws_bytes else None
+
+        def once(events=None):
+            L.check(lib.dg_l2_flush_launch(flush.data_ptr(), flush.numel(), sptr))
+            if events:
+                events[0].record(stream)
+            L.check(lib.dg_gemm_launch(ctypes.byref(desc), None, ws.data_ptr() if ws is not None else None,
+                                       ws.numel() if ws is not None else 0, sptr))
+            if events:
+                events[1].record(stream)
+
+        for _ in range(max(args.warmup, 3)):
+            once()
+        torch.cuda.synchronize(device)
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for e in ev:
+            once(e)
+        torch.cuda.synchronize(device)
+        us = sum(a_.elapsed_time(b_) for a_, b_ in ev) / args.steps * 1e3
+        nbytes = (m + n) * k * 2 + m * n * 2
+        c = cfg.as_dict()
+        rows.append({'m': m, 'n': n, 'k': k, 'us': round(us, 2), 'tflops': round(2.0 * m * n * k / us / 1e6, 1),
+                     'gbs': round(nbytes / us / 1e3, 1), 'block_n': c['block_n'], 'cta_group': c['cta_group'],
+                     'split_k': c['split_k'], 'stages': c['num_stages']})
+    if rank != 0:
+        return
+    flops = sum(2.0 * m * n * k for m, n, k in shapes)
+    total_us = sum(r['us'] for r in rows)
+    line = {'metric': 'bf16_gemm_tflops', 'value': world * flops / total_us / 1e6, 'unit': 'TFLOP/s', 'n_gpus': world,
+            'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': total_us / 1e3, 'higher_is_better': True,
+            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16 x bf16, fp32 accumulate (kind::f16)', 'data': 'synthetic',
+            'config': {'workload': 'BF16 GEMM NT, BF16 out: ' + str(shapes), 'l2': 'flushed before every GEMM, untimed'},
+            'shapes': rows, 'device_status': _api.device_status()}
     (emit or (lambda l: print(json.dumps(l), flush=True)))(line)

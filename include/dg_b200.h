@@ -84,6 +84,8 @@ typedef enum {
  * Operand dtype pairs (csrc/apis/gemm.hpp:22-33): E4M3 x E4M3; E4M3 x E2M1X2 (B decoded to E4M3 on the fly,
  * either major); E2M1X2 x E2M1X2 (tcgen05 kind::mxf4, K-major A and B only as in csrc/jit_kernels/fp8_gemm.hpp:81,
  * per-32 scales; every layout but the K-grouped one). E2M1X2 x E4M3 is rejected as in the reference.
+ * BF16 x BF16 (csrc/apis/gemm.hpp:412-514, launch_bf16_gemm): a_dtype = b_dtype = DG_BF16, sfa = sfb = NULL, strides in
+ * BF16 elements, rows 16-byte aligned; every layout, both majors.
  */
 typedef struct {
     const void* a;

@@ -94,6 +94,24 @@ def main(ref_root: str) -> None:
                          recipe=d.recipe, alpha=d.alpha, accumulate=d.accumulate, with_bias=d.with_bias,
                          a_is_fp4=adt == fp4, b_is_fp4=bdt == fp4)
 
+    # ---- BF16 family: operands are plain tensors, no scale factors --------------------------
+    bf16 = torch.bfloat16
+    for name, cdt, shape, ma, mb, kw in (
+            ('bf16_dense_nt', bf16, (48, 72, 160), Major.K, Major.K, {}),
+            ('bf16_dense_tn_acc_f32', torch.float32, (64, 48, 96), Major.MN, Major.MN, dict(accumulate=True)),
+            ('bf16_dense_nn_bias', bf16, (40, 64, 128), Major.K, Major.MN, dict(with_bias=True))):
+        d = Desc(GemmType.Normal, bf16, bf16, cdt, shape, ma, mb, **kw)
+        (m, n, k), a, b, c, d_ref, _ = d.generate()
+        out[name] = dict(m=m, n=n, k=k, a=a.contiguous(), b=b.contiguous(), a_major=ma.name, b_major=mb.name, c=c, d=d_ref,
+                         accumulate=d.accumulate, with_bias=d.with_bias)
+    d = Desc(GemmType.MGroupedContiguousWithPsumLayout, bf16, bf16, bf16, (200, 64, 96), Major.K, Major.K, num_groups=3)
+    (m, n, k), a, b, c, d_ref, (g_layout, _) = d.generate()
+    out['bf16_mgrouped_nt'] = dict(m=m, n=n, k=k, a=a.contiguous(), b=b.contiguous(), d=d_ref, psum=g_layout.tolist())
+    d = Desc(GemmType.KGroupedContiguousWithPsumLayout, bf16, bf16, torch.float32, (40, 48, 256), Major.MN, Major.MN,
+             accumulate=True, num_groups=3, ks_cpu=[300, 0, 170])
+    (m, n, k), a, b, c, d_ref, (g_layout, _) = d.generate()
+    out['bf16_kgrouped_acc_f32'] = dict(m=m, n=n, k=k, a=a.contiguous(), b=b.contiguous(), c=c, d=d_ref, psum=g_layout.tolist())
+
     # ---- m-grouped psum case -------------------------------------------------------------
     for name, mb in (('mgrouped_fp8_nt', Major.K), ('mgrouped_fp8_nn', Major.MN)):
         d = Desc(GemmType.MGroupedContiguousWithPsumLayout, fp8, fp8, torch.bfloat16, (200, 64, 96),

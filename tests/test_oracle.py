@@ -178,3 +178,19 @@ def test_swiglu_quant_model_properties():
     xl, xr = y.float()[:, :256].clamp(max=1.5), y.float()[:, 256:].clamp(-1.5, 1.5)
     ref = torch.nn.functional.silu(xl) * xr * w[:, None]
     assert oracle.calc_diff(deq[valid], ref[valid]) < 2e-3
+
+
+def test_bf16_family_matches_reference_oracle(golden):
+    """BF16 operands carry no scale factors: the same dequantise-free FP32 matmul (tests/generators.py:316-322)."""
+    for name in ('bf16_dense_nt', 'bf16_dense_tn_acc_f32', 'bf16_dense_nn_bias'):
+        c = golden[name]
+        d = oracle.gemm_ref(c['a'].float(), c['b'].float(), c['d'].dtype, c=c['c'] if c['accumulate'] else None,
+                            bias=c['c'] if c['with_bias'] else None)
+        assert torch.equal(d, c['d']), name
+    c = golden['bf16_mgrouped_nt']
+    d = oracle.m_grouped_psum_ref(c['a'].float(), c['b'].float(), c['psum'], torch.bfloat16)
+    # the reference multiplies in BF16 here (tests/generators.py:351-353): equal up to the last BF16 bit
+    assert oracle.calc_diff(d, c['d']) < 1e-5 and oracle.max_rel_err(d, c['d']) < 1e-2
+    c = golden['bf16_kgrouped_acc_f32']
+    d = oracle.k_grouped_psum_ref(c['a'].float(), c['b'].float(), c['psum'], torch.float32, c=c['c'])
+    assert torch.allclose(d, c['d'], rtol=1e-5, atol=1e-4)
