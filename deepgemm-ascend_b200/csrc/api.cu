@@ -235,9 +235,14 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     const bool decode_b = decodes_b(d);
     const uint32_t nkb = ceil_div_u32(k_bytes(d), kBlockK);
     // Staging boxes per epilogue warp. Measured: more than two never helped (the stores then compete with the operand
-    // loads), and the shared memory is worth more as pipeline stages.
-    if (c.reserved[1] == 0) c.reserved[1] = 2u;
-    DG_CHECK_ARG(c.reserved[1] >= 2 && c.reserved[1] <= kMaxStoreBufs, "store buffers per warp must be 2..4");
+    // loads), and the shared memory is worth more as pipeline stages: the main loop is bound by the bytes in flight
+    // (4096x7168x16384: 5 -> 6 stages = +9 %), so one box per warp is taken when that buys a stage.
+    if (c.reserved[1] == 0) {
+        const uint32_t cs = in_cluster ? c.split_k : 1u;
+        c.reserved[1] = max_stages_for(c.block_n, c.cta_group, d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3, 1, cs, sf_atoms(d)) >
+                        max_stages_for(c.block_n, c.cta_group, d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3, 2, cs, sf_atoms(d)) ? 1u : 2u;
+    }
+    DG_CHECK_ARG(c.reserved[1] >= 1 && c.reserved[1] <= kMaxStoreBufs, "store buffers per warp must be 1..4");
     const uint32_t store_bufs = c.reserved[1];
     uint32_t max_stages = max_stages_for(c.block_n, c.cta_group, decode_b, store_bufs, cluster_split, atoms);
     if (c.num_stages == 0 || c.num_stages > max_stages) c.num_stages = max_stages;

@@ -297,10 +297,9 @@ __host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_
     off = (off + 1023u) & ~1023u;
     L.b_raw = off; off += num_stages * L.b_raw_stage;
     off = (off + 1023u) & ~1023u;
-    L.sf_raw_a = off; off += num_stages * L.sfa_stage;
-    L.sf_raw_b = off; off += num_stages * L.sfb_stage;
-    L.sf_pack_a = off; off += num_stages * L.sfa_stage;
-    L.sf_pack_b = off; off += num_stages * L.sfb_stage;
+    // the scale factors are packed in place: what TMA delivered is read into registers and the atoms written over it
+    L.sf_raw_a = off; L.sf_pack_a = off; off += num_stages * L.sfa_stage;
+    L.sf_raw_b = off; L.sf_pack_b = off; off += num_stages * L.sfb_stage;
     off = (off + 127u) & ~127u;
     L.reduce = off; off += cluster_reduce_bytes(block_n, cluster_split);
     L.barriers = off; off += (3 * kMaxStages + 4) * 8 + 16;
@@ -604,21 +603,35 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 const uint32_t rows_b = sfb_slabs * 128;
                 const uint16_t* raw_b = reinterpret_cast<const uint16_t*>(smem_gen + L.sf_raw_b + stage * L.sfb_stage);
                 uint4* pack_b = reinterpret_cast<uint4*>(smem_gen + L.sf_pack_b + stage * L.sfb_stage);
+                // In place: everything is read into registers first, then the atoms overwrite the raw columns.
+                constexpr uint32_t kMaxSlabs = 2;                // block_n <= 256
+                uint4 va[kSfAtoms ? kSfAtoms : 1], vb[kSfAtoms ? kSfAtoms : 1][kMaxSlabs];
                 #pragma unroll
                 for (uint32_t g = 0; g + 1 <= kSfAtoms; ++g) {   // word g of a row = int16 columns 2g and 2g + 1
                     uint32_t v[4];
                     #pragma unroll
                     for (uint32_t j = 0; j < 4; ++j)
                         v[j] = (uint32_t)raw_a[(2 * g) * 128 + j * 32 + lane] | ((uint32_t)raw_a[(2 * g + 1) * 128 + j * 32 + lane] << 16);
-                    pack_a[g * 32 + lane] = make_uint4(v[0], v[1], v[2], v[3]);
-                    for (uint32_t i = 0; i < sfb_slabs; ++i) {
-                        #pragma unroll
-                        for (uint32_t j = 0; j < 4; ++j) {
-                            const uint32_t r = i * 128 + j * 32 + lane;
-                            v[j] = (uint32_t)raw_b[(2 * g) * rows_b + r] | ((uint32_t)raw_b[(2 * g + 1) * rows_b + r] << 16);
+                    va[g] = make_uint4(v[0], v[1], v[2], v[3]);
+                    #pragma unroll
+                    for (uint32_t i = 0; i < kMaxSlabs; ++i) {
+                        if (i < sfb_slabs) {
+                            #pragma unroll
+                            for (uint32_t j = 0; j < 4; ++j) {
+                                const uint32_t r = i * 128 + j * 32 + lane;
+                                v[j] = (uint32_t)raw_b[(2 * g) * rows_b + r] | ((uint32_t)raw_b[(2 * g + 1) * rows_b + r] << 16);
+                            }
+                            vb[g][i] = make_uint4(v[0], v[1], v[2], v[3]);
                         }
-                        pack_b[(g * sfb_slabs + i) * 32 + lane] = make_uint4(v[0], v[1], v[2], v[3]);
                     }
+                }
+                __syncwarp();
+                #pragma unroll
+                for (uint32_t g = 0; g + 1 <= kSfAtoms; ++g) {
+                    pack_a[g * 32 + lane] = va[g];
+                    #pragma unroll
+                    for (uint32_t i = 0; i < kMaxSlabs; ++i)
+                        if (i < sfb_slabs) pack_b[(g * sfb_slabs + i) * 32 + lane] = vb[g][i];
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -770,7 +783,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     const bool tail = !p.d_is_fp32 && half == 0 && (single || c0 + 32 >= p.block_n);
                     if (half == 0) {
                         // the buffer may still be read by the store issued `store_bufs` boxes ago
-                        if (p.store_bufs == 2) tma_store_wait_read<1>();
+                        if (p.store_bufs == 1) tma_store_wait_read<0>();
+                        else if (p.store_bufs == 2) tma_store_wait_read<1>();
                         else if (p.store_bufs == 3) tma_store_wait_read<2>();
                         else tma_store_wait_read<3>();
                         __syncwarp();
