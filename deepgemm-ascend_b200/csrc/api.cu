@@ -178,13 +178,15 @@ static uint32_t tmem_cols_for(uint32_t block_n, uint32_t accum_stages, uint32_t 
 }
 
 static uint32_t max_stages_for(uint32_t block_n, uint32_t cta_group, bool decode_b, uint32_t store_bufs, uint32_t cluster_split,
-                               uint32_t atoms = 1) {
+                               uint32_t atoms = 1, uint32_t epi_warps = kNumEpilogueWarps) {
     constexpr uint32_t kSmemCap = 227 * 1024;
     uint32_t best = 0;
     for (uint32_t s = 1; s <= kMaxStages; ++s)
-        if (make_smem_layout(block_n, s, cta_group, decode_b, store_bufs, cluster_split, atoms).total <= kSmemCap) best = s;
+        if (make_smem_layout(block_n, s, cta_group, decode_b, store_bufs, cluster_split, atoms, epi_warps).total <= kSmemCap) best = s;
     return best;
 }
+// Eight epilogue warps (reserved[5] == 2) exist for the FP8 x FP8 kernels with K-major operands
+static bool wide_epilogue(const dg_gemm_config_t& c) { return c.reserved[5] == 2; }
 
 // Two ways to split K: partial sums reduced into an FP32 workspace that a second kernel casts (reserved[3] == 0), or
 // the splits of one tile form a thread-block cluster and reduce through shared memory (reserved[3] == 1).
@@ -229,6 +231,21 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     const uint32_t cluster_split = in_cluster ? c.split_k : 1u;
 
     const uint32_t atoms = sf_atoms(d);
+    // reserved[5]: epilogue warps, 0 = choose, 1 = four, 2 = eight
+    const bool wide_possible = d.a_dtype == DG_E4M3 && d.b_dtype == DG_E4M3 && d.major_a == DG_MAJOR_K && d.major_b == DG_MAJOR_K &&
+                               !in_cluster;
+    DG_CHECK_ARG(c.reserved[5] <= 2 && (c.reserved[5] != 2 || wide_possible),
+                 "eight epilogue warps need FP8 x FP8, K-major operands and no cluster split-K");
+    const uint32_t nkb_tile = ceil_div_u32(ceil_div_u32(k_bytes(d), kBlockK), c.split_k > 1 ? c.split_k : 1);
+    if (c.reserved[5] == 0) {
+        // Short K and several tiles per CTA: the epilogue, not the main loop, bounds a tile (4096x32768x512: 124 -> 93 us
+        // with eight warps); with longer K the lost pipeline stage costs more than the faster drain gains.
+        const uint64_t dense_tiles = (uint64_t)ceil_div_u32(d.m, kBlockM * c.cta_group) * ceil_div_u32(d.n, c.block_n);
+        const bool several_tiles = d.gemm_type != DG_GEMM_NORMAL || dense_tiles > num_sms / c.cta_group;
+        c.reserved[5] = (wide_possible && several_tiles && d.gemm_type != DG_GEMM_K_GROUPED_PSUM && nkb_tile <= 8 &&
+                         !feature_disabled("wide")) ? 2u : 1u;
+    }
+    const uint32_t epi_warps = wide_epilogue(c) ? 2 * kNumEpilogueWarps : kNumEpilogueWarps;
     const uint32_t accum_stages = (2 * c.block_n + sf_tmem_cols(c.block_n, atoms) <= 512) ? 2u : 1u;
     c.tmem_cols = tmem_cols_for(c.block_n, accum_stages, atoms);
     c.reserved[0] = accum_stages;
@@ -239,12 +256,12 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     // (4096x7168x16384: 5 -> 6 stages = +9 %), so one box per warp is taken when that buys a stage.
     if (c.reserved[1] == 0) {
         const uint32_t cs = in_cluster ? c.split_k : 1u;
-        c.reserved[1] = max_stages_for(c.block_n, c.cta_group, d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3, 1, cs, sf_atoms(d)) >
-                        max_stages_for(c.block_n, c.cta_group, d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3, 2, cs, sf_atoms(d)) ? 1u : 2u;
+        c.reserved[1] = max_stages_for(c.block_n, c.cta_group, d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3, 1, cs, sf_atoms(d), epi_warps) >
+                        max_stages_for(c.block_n, c.cta_group, d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3, 2, cs, sf_atoms(d), epi_warps) ? 1u : 2u;
     }
     DG_CHECK_ARG(c.reserved[1] >= 1 && c.reserved[1] <= kMaxStoreBufs, "store buffers per warp must be 1..4");
     const uint32_t store_bufs = c.reserved[1];
-    uint32_t max_stages = max_stages_for(c.block_n, c.cta_group, decode_b, store_bufs, cluster_split, atoms);
+    uint32_t max_stages = max_stages_for(c.block_n, c.cta_group, decode_b, store_bufs, cluster_split, atoms, epi_warps);
     if (c.num_stages == 0 || c.num_stages > max_stages) c.num_stages = max_stages;
     DG_CHECK_ARG(c.num_stages >= 1, "tile does not fit in shared memory");
     if (c.num_stages > nkb * 4 && c.num_stages > 2) c.num_stages = nkb * 4 > 2 ? nkb * 4 : 2;
@@ -264,7 +281,7 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     }
     // one CTA per SM: keep the dynamic shared memory above half of the SM's capacity
     const uint32_t need = make_smem_layout(c.block_n, c.num_stages, c.cta_group, decode_b, store_bufs,
-                                           splits_in_cluster(c) ? c.split_k : 1u, atoms).total;
+                                           splits_in_cluster(c) ? c.split_k : 1u, atoms, epi_warps).total;
     c.smem_bytes = need < 120u * 1024 ? 120u * 1024 : need;
 
     uint32_t grid_units;
@@ -285,6 +302,7 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     }
     if (grid_units == 0) grid_units = 1;
     c.num_ctas = grid_units * c.cta_group;
+    if (c.epilogue_mode == kEpiTmaStore && feature_disabled("tma_store")) c.epilogue_mode = kEpiPlainStore;
     // A CTA with a single tile cannot hide its epilogue behind a next tile, and there the TMA store (staging, proxy
     // fence, descriptor fetch) costs more latency than plain 16-byte stores straight from the registers.
     if (c.epilogue_mode == kEpiTmaStore && d.gemm_type == DG_GEMM_NORMAL && c.cta_group == 1 &&
@@ -497,8 +515,9 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     plan.decode_b = decodes_b(d);
     plan.fp4_pair = is_fp4_pair(d);
     plan.bf16_pair = is_bf16_pair(d);
+    plan.wide_epi = wide_epilogue(c);
     plan.lean = d.gemm_type == DG_GEMM_NORMAL && c.cta_group == 1 && !plan.decode_b && c.epilogue_mode == kEpiPlainStore &&
-                (d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_BIAS) && !plan.fp4_pair && !plan.bf16_pair && !feature_disabled("lean");
+                (d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_BIAS) && !plan.fp4_pair && !plan.bf16_pair && !plan.wide_epi && !feature_disabled("lean");
     // k-grouped, no accumulation: D of groups whose K range is empty must read as zero
     plan.zero_empty_groups = k_grouped && !d.accumulate;
     plan.zero_d = d.d;

@@ -14,6 +14,7 @@ struct LaunchPlan {
     int cta_group, major_a, major_b;
     bool decode_b;               // B is packed E2M1 and is decoded to E4M3 in shared memory
     uint32_t num_ctas, smem_bytes;
+    bool wide_epi;                    // eight epilogue warps (384 threads)
     bool bf16_pair;                   // both operands BF16 (kind::f16, no scale factors)
     bool fp4_pair;                    // both operands packed E2M1 (kind::mxf4)
     bool lean;                        // the instantiation without the staged-store / alpha / stochastic / FP8 epilogues

@@ -60,7 +60,11 @@ __global__ void zero_empty_k_groups_kernel(uint8_t* __restrict__ d, const int32_
 using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
                           const CUtensorMap, const CUtensorMap, const GemmKernelArgs);
 
-static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode_b, bool lean, bool fp4_pair, bool bf16_pair) {
+static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode_b, bool lean, bool fp4_pair, bool bf16_pair,
+                            bool wide_epi) {
+    if (wide_epi)
+        return cta_group == 2 ? mx_gemm_kernel<2, 0, 0, false, false, false, false, true>
+                              : mx_gemm_kernel<1, 0, 0, false, false, false, false, true>;
     if (bf16_pair) {
         static const KernelFn bf16_table[2][2][2] = {
             {{mx_gemm_kernel<1, 0, 0, false, false, false, true>, mx_gemm_kernel<1, 0, 1, false, false, false, true>},
@@ -106,7 +110,7 @@ int get_status_pointer(int32_t** out) {
 }
 
 int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
-    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b, plan.lean, plan.fp4_pair, plan.bf16_pair);
+    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b, plan.lean, plan.fp4_pair, plan.bf16_pair, plan.wide_epi);
     // The attribute is per device and per function; setting it is cheap, so do it on every launch.
     DG_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem_bytes));
 
@@ -132,7 +136,7 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
 
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(plan.num_ctas, 1, 1);
-    cfg.blockDim = dim3(plan.decode_b ? kNumThreadsDecode : kNumThreads, 1, 1);
+    cfg.blockDim = dim3((plan.decode_b || plan.wide_epi) ? kNumThreadsDecode : kNumThreads, 1, 1);
     cfg.dynamicSmemBytes = plan.smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];

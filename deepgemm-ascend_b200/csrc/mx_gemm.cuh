@@ -277,7 +277,7 @@ __host__ __device__ __forceinline__ uint32_t cluster_reduce_bytes(uint32_t block
 // 32), 2 when both operands are packed E2M1 (256 K-elements per stage).
 __host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_t num_stages, uint32_t cta_group,
                                                        bool decode_b, uint32_t store_bufs, uint32_t cluster_split = 1,
-                                                       uint32_t sf_atoms = 1) {
+                                                       uint32_t sf_atoms = 1, uint32_t epilogue_warps = kNumEpilogueWarps) {
     SmemLayout L;
     L.a_stage = kBlockM * kBlockK;
     L.b_stage = (block_n / cta_group) * kBlockK;
@@ -290,7 +290,7 @@ __host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_
         // slab per 32 columns) and the store staging behind them live there and the ring keeps the memory.
         L.store_bufs = (block_n / 32) * kReduceSlabBytes;
     } else {
-        L.store_bufs = off; off += kNumEpilogueWarps * store_bufs * kStoreBufBytes;
+        L.store_bufs = off; off += epilogue_warps * store_bufs * kStoreBufBytes;
     }
     L.a = off; off += num_stages * L.a_stage;
     L.b = off; off += num_stages * L.b_stage;
@@ -366,8 +366,13 @@ __device__ __forceinline__ uint2 stochastic_round_quartet(uint32_t v0, uint32_t 
 // kind::mxf4 with two scales per row per instruction, and a stage carries eight scale bytes per row instead of four.
 // kBf16: BF16 operands, no scale factors (kind::f16): a stage is 128 bytes = 64 K-elements per row; the packer
 // warp idles and the MMA thread waits for the operands directly.
-template <int kCtaGroup, int kMajorA, int kMajorB, bool kDecodeB, bool kLean = false, bool kFp4 = false, bool kBf16 = false>
-__global__ void __launch_bounds__(kDecodeB ? kNumThreadsDecode : kNumThreads, 1)
+// kWideEpi: eight epilogue warps instead of four (warps 8..11 take every other 64-column group of the tile). One warp
+// retires about one instruction every five to six cycles on the dependent chains of the epilogue (164 instructions per
+// 32x32 chunk), so for short K, where the epilogue and not the main loop bounds a tile, a second warp per scheduler
+// doubles the rate at which accumulators are drained.
+template <int kCtaGroup, int kMajorA, int kMajorB, bool kDecodeB, bool kLean = false, bool kFp4 = false, bool kBf16 = false,
+          bool kWideEpi = false>
+__global__ void __launch_bounds__((kDecodeB || kWideEpi) ? kNumThreadsDecode : kNumThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
                const __grid_constant__ CUtensorMap tm_d, const __grid_constant__ CUtensorMap tm_d_tail,
@@ -375,12 +380,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t cluster_split = (kCtaGroup == 1 && !kDecodeB) ? p.cluster_split : 1u;
+    const uint32_t cluster_split = (kCtaGroup == 1 && !kDecodeB && !kWideEpi) ? p.cluster_split : 1u;
     constexpr uint32_t kSfAtoms = kBf16 ? 0u : kFp4 ? 2u : 1u;
     constexpr uint32_t kElemBytes = kBf16 ? 2u : 1u;              // bytes per operand element as TMA counts them
     constexpr uint32_t kStageK = kBlockK / kElemBytes;            // TMA elements of K per stage (= K rows of an MN-major tile)
     constexpr uint32_t kAtomMn = 128 / kElemBytes;                // MN elements in one 128-byte swizzle atom
-    const SmemLayout L = make_smem_layout(p.block_n, p.num_stages, kCtaGroup, kDecodeB, p.store_bufs, cluster_split, kSfAtoms);
+    static_assert(!(kDecodeB && kWideEpi), "warps 8..11 are either decoders or epilogue warps");
+    constexpr uint32_t kEpiWarps = kWideEpi ? 2 * kNumEpilogueWarps : kNumEpilogueWarps;
+    const SmemLayout L = make_smem_layout(p.block_n, p.num_stages, kCtaGroup, kDecodeB, p.store_bufs, cluster_split, kSfAtoms, kEpiWarps);
 
     const uint32_t warp = threadIdx.x / 32, lane = lane_id();
     const uint32_t cta_rank = kCtaGroup == 2 ? cluster_ctarank() : 0u;
@@ -412,7 +419,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         }
         for (uint32_t e = 0; e < 2; ++e) {
             mbar_init(tmem_full_bar(e), 1);
-            mbar_init(tmem_empty_bar(e), kNumEpilogueWarps * kCtaGroup);   // one arrival per epilogue warp
+            mbar_init(tmem_empty_bar(e), kEpiWarps * kCtaGroup);   // one arrival per epilogue warp
         }
         if (cluster_split > 1) {
             // the chunks this rank finalises arrive as bulk copies from the other ranks, counted in bytes
@@ -436,7 +443,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // Warp 0 (whose first lane initialised the barriers and is the TMA producer) only checks in: its loads fill this
     // CTA's own ring and need nothing from the other warps or CTAs, so they start while TMEM is still being allocated.
     const bool in_cluster = kCtaGroup == 2 || cluster_split > 1;
-    const uint32_t num_threads = kDecodeB ? kNumThreadsDecode : kNumThreads;
+    const uint32_t num_threads = (kDecodeB || kWideEpi) ? kNumThreadsDecode : kNumThreads;
     if (in_cluster) {
         cluster_arrive();
         if (warp != 0) cluster_wait();
@@ -684,15 +691,17 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 if (++stage == num_stages) { stage = 0; phase ^= 1; }
             }
         }
-    } else if (warp >= 4 && warp < 8) {
+    } else if (warp >= 4 && warp < 4 + kEpiWarps) {
         // ======================================================================== epilogue
-        const uint32_t q = warp - 4;                         // TMEM lane quadrant == warp index % 4
+        const uint32_t q = warp % 4;                         // TMEM lane quadrant == warp index % 4
+        const uint32_t col_half = (warp - 4) / 4;            // wide epilogue: which 64-column groups this warp takes
+        constexpr uint32_t kColStep = kWideEpi ? 128u : 64u;
         Scheduler<kCtaGroup, kLean> sched(p);
         Tile t;
         uint32_t tile_iter = 0, buf = 0;
         bool ok = true;
-        const uint32_t store_base = smem_base + L.store_bufs + q * p.store_bufs * kStoreBufBytes;
-        uint8_t* store_gen = smem_gen + L.store_bufs + q * p.store_bufs * kStoreBufBytes;
+        const uint32_t store_base = smem_base + L.store_bufs + (warp - 4) * p.store_bufs * kStoreBufBytes;
+        uint8_t* store_gen = smem_gen + L.store_bufs + (warp - 4) * p.store_bufs * kStoreBufBytes;
         const uint32_t cols_per_box = p.d_is_fp32 ? 32u : 64u;
         const uint32_t leader_tmem_empty0 = kCtaGroup == 2 ? mapa_shared(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
         while (ok && sched.next(t)) {
@@ -931,14 +940,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             // clipped by the hardware instead).
             const bool plain = kLean || p.epilogue_mode == kEpiPlainStore || p.epilogue_mode == kEpiPlainAtomic;
             const uint32_t cols = plain ? min(p.block_n, (p.n - t.n0 + 31u) & ~31u) : p.block_n;
-            tmem_ld_32x32b_x32(taddr, va);
-            for (uint32_t c0 = 0; c0 < cols; c0 += 64) {
+            const uint32_t c_first = col_half * 64;
+            if (c_first < cols) tmem_ld_32x32b_x32(taddr + c_first, va);
+            for (uint32_t c0 = c_first; c0 < cols; c0 += kColStep) {
                 tmem_ld_wait();
                 if (c0 + 32 < cols) tmem_ld_32x32b_x32(taddr + c0 + 32, vb);
                 process_chunk(va, c0, false);
                 if (c0 + 32 < cols) {
                     tmem_ld_wait();
-                    if (c0 + 64 < cols) tmem_ld_32x32b_x32(taddr + c0 + 64, va);
+                    if (c0 + kColStep < cols) tmem_ld_32x32b_x32(taddr + c0 + kColStep, va);
                     process_chunk(vb, c0 + 32, false);
                 }
             }

@@ -404,3 +404,15 @@ def test_m_grouped_masked(max_m, masked):
     for i, mg in enumerate(masked):
         if mg:
             assert_close(d[i, :mg], ref[i, :mg], f'masked group {i} rows {mg}')
+
+
+def test_dense_eight_epilogue_warps():
+    """Warps 8..11 as a second set of epilogue warps (every other 64-column group of a tile)."""
+    for bn in (32, 64, 96, 128, 160, 192, 224, 256):
+        _dense(384, 768, 512, config={'block_n': bn, 'epilogue_warps': 8})
+        _dense(512, 768, 512, config={'cta_group': 2, 'block_n': bn, 'epilogue_warps': 8}, out=torch.float32, acc=True)
+    _dense(1024, 2048, 256, config={'cta_group': 2, 'block_n': 224, 'epilogue_warps': 8}, bias=True)
+    _dense(300, 500, 384, config={'block_n': 96, 'epilogue_warps': 8}, alpha=0.5)
+    _dense(4096, 4096, 512)            # the heuristic takes eight warps here
+    with pytest.raises(RuntimeError):
+        _dense(256, 256, 512, trans='nn', config={'block_n': 128, 'epilogue_warps': 8})
