@@ -28,6 +28,7 @@ def main() -> None:
     ap.add_argument('--stages', type=int, default=0)
     ap.add_argument('--out', default='bf16', choices=['bf16', 'f32'])
     ap.add_argument('--fp4', action='store_true', help='both operands packed E2M1 (dense only)')
+    ap.add_argument('--bf16', action='store_true', help='BF16 operands, no scale factors (dense only)')
     ap.add_argument('--quant', default='', choices=['', 'swiglu', 'cast'],
                     help='run the FP8 producer on [m, k] activations instead of a GEMM')
     args = ap.parse_args()
@@ -62,11 +63,16 @@ def main() -> None:
         a = torch.randint(-128, 128, (rows, k // 2), dtype=torch.int8, device=dev)
         b = torch.randint(-128, 128, (n, k // 2), dtype=torch.int8, device=dev)
     d = torch.empty(rows, n, dtype=torch.bfloat16 if args.out == 'bf16' else torch.float32, device=dev)
+    if args.bf16:
+        a_bf16 = torch.randn(rows, k, device=dev).bfloat16()
+        b_bf16 = torch.randn(n, k, device=dev).bfloat16()
     config = {key: val for key, val in (('block_n', args.block_n), ('cta_group', args.cta_group),
                                         ('split_k', args.split_k), ('num_stages', args.stages)) if val}
     layout = torch.arange(1, g + 1, dtype=torch.int32, device=dev) * m if g else None
     for _ in range(args.iters):
-        if g:
+        if args.bf16:
+            deep_gemm.bf16_gemm_nt(a_bf16, b_bf16, d, config=config or None)
+        elif g:
             deep_gemm.m_grouped_fp8_gemm_nt_contiguous((a, sfa), (b, sfb), d, layout, config=config or None)
         else:
             deep_gemm.fp8_gemm_nt((a, sfa), (b, sfb), d, config=config or None)
