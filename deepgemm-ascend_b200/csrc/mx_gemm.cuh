@@ -302,7 +302,7 @@ __host__ __device__ inline SmemLayout make_smem_layout(uint32_t block_n, uint32_
     L.sf_raw_b = off; L.sf_pack_b = off; off += num_stages * L.sfb_stage;
     off = (off + 127u) & ~127u;
     L.reduce = off; off += cluster_reduce_bytes(block_n, cluster_split);
-    L.barriers = off; off += (3 * kMaxStages + 4) * 8 + 16;
+    L.barriers = off; off += (4 * kMaxStages + 4) * 8 + 16;
     L.total = off + 1024;    // slack for the manual 1024-B alignment of the dynamic base
     return L;
 }
@@ -393,16 +393,17 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t cta_rank = kCtaGroup == 2 ? cluster_ctarank() : 0u;
     const bool is_leader = cta_rank == 0;
 
-    // Barrier block: full[s], sf_full[s], empty[s], tmem_full[2], tmem_empty[2], tmem ptr, abort flag
+    // Barrier block: full[s], sf_full[s], empty[s], sf_tma[s], tmem_full[2], tmem_empty[2], tmem ptr, abort flag
     const uint32_t bar_base = smem_base + L.barriers;
     auto full_bar = [&](uint32_t s) { return bar_base + s * 8; };
     auto sf_full_bar = [&](uint32_t s) { return bar_base + (kMaxStages + s) * 8; };
     auto empty_bar = [&](uint32_t s) { return bar_base + (2 * kMaxStages + s) * 8; };
-    auto tmem_full_bar = [&](uint32_t e) { return bar_base + (3 * kMaxStages + e) * 8; };
-    auto tmem_empty_bar = [&](uint32_t e) { return bar_base + (3 * kMaxStages + 2 + e) * 8; };
-    volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + L.barriers + (3 * kMaxStages + 4) * 8);
+    auto sf_tma_bar = [&](uint32_t s) { return bar_base + (3 * kMaxStages + s) * 8; };   // the scale columns of a stage have landed
+    auto tmem_full_bar = [&](uint32_t e) { return bar_base + (4 * kMaxStages + e) * 8; };
+    auto tmem_empty_bar = [&](uint32_t e) { return bar_base + (4 * kMaxStages + 2 + e) * 8; };
+    volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + L.barriers + (4 * kMaxStages + 4) * 8);
     const AbortFlag ab{tmem_ptr_smem + 1, p.status};
-    const uint32_t reduce_bar = bar_base + (3 * kMaxStages + 5) * 8;     // cluster split-K: partial sums have arrived
+    const uint32_t reduce_bar = bar_base + (4 * kMaxStages + 5) * 8;     // cluster split-K: partial sums have arrived
 
     const uint32_t num_stages = p.num_stages;
     const uint32_t load_n = p.block_n / kCtaGroup;            // rows of B this CTA fetches
@@ -416,6 +417,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             // one arrival per warp that prepares the stage for the MMA: the packer, and the decoders if any
             mbar_init(sf_full_bar(s), kCtaGroup * (1 + (kDecodeB ? kNumDecodeWarps : 0)));
             mbar_init(empty_bar(s), 1);
+            mbar_init(sf_tma_bar(s), 1);
         }
         for (uint32_t e = 0; e < 2; ++e) {
             mbar_init(tmem_full_bar(e), 1);
@@ -474,9 +476,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     if (ring_used && !(ok = wait_barrier(empty_bar(stage), phase ^ 1, ab, kStatusTimeoutProducer))) break;
                     if (first_issue) trace_mark(p, 10);
                     const uint32_t bar = full_bar(stage);
-                    const uint32_t bytes = L.a_stage + (kDecodeB ? L.b_raw_stage : load_n * kBlockK) + L.sfa_stage + L.sfb_stage;
+                    // The operands and the (much smaller) scale columns complete on barriers of their own, so that the
+                    // scales are usually packed by the time the last operand byte lands.
+                    const uint32_t bytes = L.a_stage + (kDecodeB ? L.b_raw_stage : load_n * kBlockK);
                     static_assert(!kBf16 || !kDecodeB, "BF16 operands are never decoded");
                     mbar_arrive_expect_tx(bar, bytes);
+                    const uint32_t sf_bar = sf_tma_bar(stage);
+                    if constexpr (!kBf16) mbar_arrive_expect_tx(sf_bar, L.sfa_stage + L.sfb_stage);
                     if (first_issue) { trace_mark(p, 3); first_issue = false; }
                     const uint32_t sa = smem_base + L.a + stage * L.a_stage;
                     const uint32_t sb = smem_base + L.b + stage * L.b_stage;
@@ -504,9 +510,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                     if (i == 0) trace_mark(p, 11);
                     if constexpr (!kBf16) {
-                        tma_load_3d(smem_base + L.sf_raw_a + stage * L.sfa_stage, &tm_sfa, bar,
+                        tma_load_3d(smem_base + L.sf_raw_a + stage * L.sfa_stage, &tm_sfa, sf_bar,
                                     (int32_t)t.row0, (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.row_z);
-                        tma_load_3d(smem_base + L.sf_raw_b + stage * L.sfb_stage, &tm_sfb, bar,
+                        tma_load_3d(smem_base + L.sf_raw_b + stage * L.sfb_stage, &tm_sfb, sf_bar,
                                     (int32_t)t.n0, (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.b_z);
                     }
                     if (i == 0) trace_mark(p, 12);
@@ -604,7 +610,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const uint32_t leader_sf_full0 = kCtaGroup == 2 ? mapa_shared(sf_full_bar(0), 0) : sf_full_bar(0);
         while (ok && sched.next(t)) {
             for (uint32_t kb = t.kb_begin; kb < t.kb_end; ++kb) {
-                if (!(ok = wait_barrier(full_bar(stage), phase, ab, kStatusTimeoutPacker))) break;
+                if constexpr (!kBf16) {
+                    if (!(ok = wait_barrier(sf_tma_bar(stage), phase, ab, kStatusTimeoutPacker))) break;
+                }
                 const uint16_t* raw_a = reinterpret_cast<const uint16_t*>(smem_gen + L.sf_raw_a + stage * L.sfa_stage);
                 uint4* pack_a = reinterpret_cast<uint4*>(smem_gen + L.sf_pack_a + stage * L.sfa_stage);
                 const uint32_t rows_b = sfb_slabs * 128;
@@ -641,6 +649,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         if (i < sfb_slabs) pack_b[(g * sfb_slabs + i) * 32 + lane] = vb[g][i];
                 }
                 fence_proxy_async_smem();
+                // the arrival below also tells the MMA thread (in a CTA pair: the leader's) that this CTA's operands are in
+                if (!(ok = wait_barrier(full_bar(stage), phase, ab, kStatusTimeoutPacker))) break;
                 __syncwarp();
                 // one (possibly remote) arrival per warp: remote arrivals are slow enough to matter per K block
                 if (lane == 0) {
