@@ -190,8 +190,9 @@ static bool wide_epilogue(const dg_gemm_config_t& c) { return c.reserved[5] == 2
 
 // Two ways to split K: partial sums reduced into an FP32 workspace that a second kernel casts (reserved[3] == 0), or
 // the splits of one tile form a thread-block cluster and reduce through shared memory (reserved[3] == 1).
-// DG_DISABLE=lean,cluster (debugging aid for A/B timing): keeps the heuristic away from cluster split-K and / or the
-// launch away from the lean kernel instantiations.
+// DG_DISABLE=lean,cluster,wide,tma_store (debugging aid for A/B timing): keeps the heuristic away from cluster
+// split-K, from eight epilogue warps, from TMA stores (plain stores instead), and / or the launch away from the lean
+// kernel instantiations. Every alternative computes the same values.
 static bool feature_disabled(const char* name) {
     static const std::string list = [] { const char* e = getenv("DG_DISABLE"); return std::string(e ? e : ""); }();
     return list.find(name) != std::string::npos;

@@ -125,11 +125,15 @@ typedef struct {
     uint32_t tmem_cols;
     uint32_t smem_bytes;
     uint32_t epilogue_mode;   /* 0 TMA store, 1 TMA reduce-add, 2 plain stores, 3 plain atomics */
-    uint32_t reserved[6];     /* [0] TMEM accumulators (1 or 2, derived); [1] epilogue staging boxes per warp (0 = auto, 2..4);
+    uint32_t reserved[6];     /* [0] TMEM accumulators (1 or 2, derived); [1] epilogue staging boxes per warp (0 = auto:
+                               *     one when that buys a pipeline stage, else two; 1..4);
                                * [2] K stagger: tile column j starts its K loop at block (j * value) % blocks (0 = off);
                                * [3] split_k > 1 only: 0 = partial sums go to the FP32 workspace and a second kernel casts
                                *     them, 1 = the splits of a tile run as one thread-block cluster (cta_group 1,
-                               *     split_k <= 8, B not packed) and reduce through shared memory: no workspace */
+                               *     split_k <= 8, B not packed) and reduce through shared memory: no workspace;
+                               * [4] unused, must be 0;
+                               * [5] epilogue warps: 0 = auto, 1 = four, 2 = eight (two warps per TMEM lane quarter, each
+                               *     taking alternate 32-column chunks; E4M3 x E4M3 with K-major operands only) */
 } dg_gemm_config_t;
 
 /* The B200 tiling heuristic. Replaces select_gemm_config, csrc/jit_kernels/heuristics.hpp:592-755. */
