@@ -190,7 +190,7 @@ static bool wide_epilogue(const dg_gemm_config_t& c) { return c.reserved[5] == 2
 
 // Two ways to split K: partial sums reduced into an FP32 workspace that a second kernel casts (reserved[3] == 0), or
 // the splits of one tile form a thread-block cluster and reduce through shared memory (reserved[3] == 1).
-// DG_DISABLE=lean,cluster,wide,tma_store (debugging aid for A/B timing): keeps the heuristic away from cluster
+// DG_DISABLE=lean,cluster,wide,simple,tma_store (debugging aid for A/B timing): keeps the heuristic away from cluster
 // split-K, from eight epilogue warps, from TMA stores (plain stores instead), and / or the launch away from the lean
 // kernel instantiations. Every alternative computes the same values.
 static bool feature_disabled(const char* name) {
@@ -243,8 +243,12 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
         // with eight warps); with longer K the lost pipeline stage costs more than the faster drain gains.
         const uint64_t dense_tiles = (uint64_t)ceil_div_u32(d.m, kBlockM * c.cta_group) * ceil_div_u32(d.n, c.block_n);
         const bool several_tiles = d.gemm_type != DG_GEMM_NORMAL || dense_tiles > num_sms / c.cta_group;
+        // A plain BF16 output runs the cast-and-store-only instantiation, whose four warps drain an accumulator as fast
+        // as eight do (4096x32768x512: 78 us with four warps, 81 us with eight).
+        const bool cast_and_store_only = d.d_dtype == DG_BF16 && !split && d.epilogue == DG_EPILOGUE_IDENTITY &&
+                                         c.epilogue_mode <= kEpiTmaReduce && !feature_disabled("simple");
         c.reserved[5] = (wide_possible && several_tiles && d.gemm_type != DG_GEMM_K_GROUPED_PSUM && nkb_tile <= 8 &&
-                         !feature_disabled("wide")) ? 2u : 1u;
+                         !cast_and_store_only && !feature_disabled("wide")) ? 2u : 1u;
     }
     const uint32_t epi_warps = wide_epilogue(c) ? 2 * kNumEpilogueWarps : kNumEpilogueWarps;
     const uint32_t accum_stages = (2 * c.block_n + sf_tmem_cols(c.block_n, atoms) <= 512) ? 2u : 1u;
@@ -484,6 +488,19 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.split_k = c.split_k;
     a.k_blocks_per_split = ceil_div_u32(a.num_k_blocks, c.split_k);
     a.raster_group = 8;
+    while (a.raster_group > 1 && (uint64_t)a.raster_group * a.num_n_blocks >= (1u << 16)) a.raster_group /= 2;
+    {
+        // the kernel divides tile indices by multiplying with these (fast_div): indices below 2^24, index x divisor below 2^40
+        const uint64_t repeats = (grouped && d.gemm_type != DG_GEMM_M_GROUPED_PSUM) ? d.num_groups : 1;
+        const uint64_t tile_bound = repeats * (a.num_m_blocks + (grouped ? d.num_groups : 0)) * a.num_n_blocks * c.split_k + c.num_ctas;
+        DG_CHECK_ARG(tile_bound < (1u << 24) && (uint64_t)a.raster_group * a.num_n_blocks < (1u << 16),
+                     "the problem has too many tiles (%llu)", (unsigned long long)tile_bound);
+        const uint32_t last_rows = a.num_m_blocks % a.raster_group;
+        a.magic_per_group = fast_div_magic(a.raster_group * a.num_n_blocks);
+        a.magic_rows_full = fast_div_magic(a.raster_group);
+        a.magic_rows_last = fast_div_magic(last_rows ? last_rows : a.raster_group);
+        a.magic_n_blocks = fast_div_magic(a.num_n_blocks);
+    }
     a.epilogue_mode = c.epilogue_mode;
     a.d_is_fp32 = (split || d.d_dtype == DG_F32) ? 1u : 0u;
     a.has_alpha = d.epilogue == DG_EPILOGUE_ALPHA ? 1u : 0u;
@@ -519,6 +536,11 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     plan.wide_epi = wide_epilogue(c);
     plan.lean = d.gemm_type == DG_GEMM_NORMAL && c.cta_group == 1 && !plan.decode_b && c.epilogue_mode == kEpiPlainStore &&
                 (d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_BIAS) && !plan.fp4_pair && !plan.bf16_pair && !plan.wide_epi && !feature_disabled("lean");
+    a.epi_simple = (d.epilogue == DG_EPILOGUE_IDENTITY && !a.has_alpha && !a.has_bias && !a.stochastic &&
+                    c.epilogue_mode <= kEpiTmaReduce && !splits_in_cluster(c) && !feature_disabled("straight")) ? 1u : 0u;
+    plan.simple_epi = !plan.lean && !plan.decode_b && !plan.fp4_pair && !plan.bf16_pair && d.major_a == DG_MAJOR_K && d.major_b == DG_MAJOR_K &&
+                      !a.d_is_fp32 && d.epilogue == DG_EPILOGUE_IDENTITY && !a.has_alpha && !a.has_bias && !a.stochastic &&
+                      c.epilogue_mode <= kEpiTmaReduce && !splits_in_cluster(c) && !feature_disabled("simple");
     // k-grouped, no accumulation: D of groups whose K range is empty must read as zero
     plan.zero_empty_groups = k_grouped && !d.accumulate;
     plan.zero_d = d.d;

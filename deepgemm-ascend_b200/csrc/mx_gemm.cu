@@ -61,7 +61,14 @@ using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMa
                           const CUtensorMap, const CUtensorMap, const GemmKernelArgs);
 
 static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode_b, bool lean, bool fp4_pair, bool bf16_pair,
-                            bool wide_epi) {
+                            bool wide_epi, bool simple_epi) {
+    if (simple_epi) {       // E4M3 x E4M3, K-major operands, plain BF16 output through TMA stores
+        if (wide_epi)
+            return cta_group == 2 ? mx_gemm_kernel<2, 0, 0, false, false, false, false, true, true>
+                                  : mx_gemm_kernel<1, 0, 0, false, false, false, false, true, true>;
+        return cta_group == 2 ? mx_gemm_kernel<2, 0, 0, false, false, false, false, false, true>
+                              : mx_gemm_kernel<1, 0, 0, false, false, false, false, false, true>;
+    }
     if (wide_epi)
         return cta_group == 2 ? mx_gemm_kernel<2, 0, 0, false, false, false, false, true>
                               : mx_gemm_kernel<1, 0, 0, false, false, false, false, true>;
@@ -110,7 +117,7 @@ int get_status_pointer(int32_t** out) {
 }
 
 int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
-    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b, plan.lean, plan.fp4_pair, plan.bf16_pair, plan.wide_epi);
+    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b, plan.lean, plan.fp4_pair, plan.bf16_pair, plan.wide_epi, plan.simple_epi);
     // The attribute is per device and per function; setting it is cheap, so do it on every launch.
     DG_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem_bytes));
 
@@ -121,8 +128,8 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
     static const bool trace_enabled = [] { const char* e = getenv("DG_TRACE"); return e && atoi(e) != 0; }();
     static unsigned long long* trace_buf = nullptr;
     if (trace_enabled) {
-        if (trace_buf == nullptr) DG_CHECK_CUDA(cudaMalloc(&trace_buf, 1024 * 16 * sizeof(unsigned long long)));
-        DG_CHECK_CUDA(cudaMemsetAsync(trace_buf, 0, 1024 * 16 * sizeof(unsigned long long), stream));
+        if (trace_buf == nullptr) DG_CHECK_CUDA(cudaMalloc(&trace_buf, 2048 * 16 * sizeof(unsigned long long)));
+        DG_CHECK_CUDA(cudaMemsetAsync(trace_buf, 0, 2048 * 16 * sizeof(unsigned long long), stream));
         args.trace = trace_buf;
     }
 
@@ -198,6 +205,21 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
                 sum[2] / n, mx[2], sum[3] / n, mx[3], sum[4] / n, mx[4], sum[5] / n, mx[5], sum[6] / n, mx[6], sum[7] / n, mx[7]);
     }
 
+#ifdef DG_EPI_PROF
+    if (trace_enabled) {
+        static unsigned long long h2[1024 * 16];
+        const uint32_t n = grid < 1024 ? grid : 1024;
+        DG_CHECK_CUDA(cudaMemcpy(h2, trace_buf + 1024 * 16, n * 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+        double s[16] = {0};
+        for (uint32_t i = 0; i < n; ++i) for (int j = 0; j < 16; ++j) s[j] += (double)h2[i * 16 + j];
+        const double ch = s[8] > 0 ? s[8] : 1, tl = s[12] > 0 ? s[12] : 1;
+        fprintf(stderr, "[dg_epi] tiles/cta %.1f chunks/tile %.1f | per chunk: ldissue %.0f ldwait %.0f pre %.0f cvt %.0f math %.0f storewait %.0f stsmem %.0f | per box-ish (per chunk avg): fence %.0f issue %.0f | per tile: accwait %.0f epilogue %.0f\n",
+                tl / n, ch / tl, s[10] / ch, s[0] / ch, s[11] / ch, s[9] / ch, s[1] / ch, s[2] / ch, s[3] / ch, s[4] / ch, s[5] / ch, s[6] / tl, s[7] / tl);
+        const double tiles_lead = tl / plan.cta_group;
+        fprintf(stderr, "[dg_mma] per tile: accumulator-free wait %.0f  data wait %.0f (first K block %.0f)\n",
+                s[13] / tiles_lead, s[14] / tiles_lead, s[15] / tiles_lead);
+    }
+#endif
     if (plan.finalize) {
         const uint64_t total = (uint64_t)plan.args.m * ((plan.args.n + 3) / 4);
         const uint32_t grid = (uint32_t)((total + 255) / 256 < 148ull * 8 ? (total + 255) / 256 : 148ull * 8);

@@ -21,6 +21,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cstdint>
+#include <type_traits>
 
 #include "ptx.cuh"
 
@@ -59,8 +60,12 @@ struct GemmKernelArgs {
     const int32_t* grouped_layout;    // psum[G] or masked_m[G]
     uint32_t split_k, k_blocks_per_split;
     uint32_t raster_group;            // m-blocks per rasterisation group (L2 reuse of B)
+    // floor(2^40 / d) + 1 for the three divisors of the tile walk (see fast_div): m-blocks x n-blocks of a raster
+    // group, m-blocks of a full and of the last raster group, n-blocks
+    uint64_t magic_per_group, magic_rows_full, magic_rows_last, magic_n_blocks;
     uint32_t epilogue_mode;
     uint32_t d_is_fp32;
+    uint32_t epi_simple;  // nothing but cast (or FP32) + staged TMA store / reduce: the epilogue takes its short loop
     uint32_t has_bias, has_alpha;
     uint32_t stochastic;              // BF16 output is rounded stochastically instead of to nearest
     uint8_t* sfd;                     // FP8-quantised output: UE8M0 scale bytes, two per int16 element
@@ -121,6 +126,18 @@ __device__ __forceinline__ bool wait_barrier_cluster(uint32_t bar, uint32_t pari
 // requested, first operands landed (MMA side), last MMA committed, first accumulator ready (epilogue side), epilogue
 // done; 8..12 producer: role entered, first tile known, first stage free, A and B requested, first stage requested;
 // 13..15 epilogue: partial sums sent (cluster split-K), partial sums received, all chunks of the first tile written.
+// -DDG_EPI_PROF (a build for measuring, never the shipped one): the first epilogue warp and the MMA thread of every CTA
+// add up, over all tiles, the clock cycles they spend in each phase (waiting for TMEM loads, converting, waiting for
+// a staging box, writing it, proxy fence, issuing the store; waiting for an accumulator or for operands), and a
+// launch with DG_TRACE=1 prints the averages.
+#ifdef DG_EPI_PROF
+__device__ __forceinline__ uint32_t rdclk() { uint32_t x; asm volatile("mov.u32 %0, %%clock;" : "=r"(x) :: "memory"); return x; }
+#define EPI_T(var) const uint32_t var = rdclk()
+#define EPI_ACC(i, a, b) prof[i] += (b) - (a)
+#else
+#define EPI_T(var)
+#define EPI_ACC(i, a, b)
+#endif
 __device__ __forceinline__ void trace_mark(const GemmKernelArgs& p, uint32_t slot) {
     if (p.trace != nullptr) p.trace[blockIdx.x * 16 + slot] = slot == 0 ? global_timer_ns() : (unsigned long long)clock64();
 }
@@ -137,6 +154,13 @@ struct Tile {
     uint32_t kb_begin, kb_end;
     uint32_t kb_rot;      // the loads walk the K blocks rotated by this much (CTAs that share A then read different lines)
 };
+
+// Every role walks the tile sequence on its own, once per tile, and that walk sits on the critical path between two
+// tiles (the MMA thread between the last MMA of a tile and the first of the next, the epilogue warps between two
+// accumulators), so the divisions by run-time constants are multiplications by host-made reciprocals:
+// n / d == (n * (floor(2^40 / d) + 1)) >> 40, exact for n < 2^24 and n * d < 2^40 (checked on the host).
+__host__ __device__ __forceinline__ uint64_t fast_div_magic(uint32_t d) { return (1ull << 40) / d + 1; }
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint64_t magic) { return (uint32_t)(((uint64_t)n * magic) >> 40); }
 
 // kLean: dense GEMM only (the other layouts are compiled out).
 template <int kCtaGroup, bool kLean = false>
@@ -186,12 +210,15 @@ struct Scheduler {
         if (kLean || p.gemm_type == kNormal) {
             const uint32_t total = p.num_m_blocks * p.num_n_blocks * p.split_k;
             if (tile >= total) return false;
-            const uint32_t ks = tile % p.split_k, mn = tile / p.split_k;
+            uint32_t ks = 0, mn = tile;
+            if (p.split_k > 1) { mn = tile / p.split_k; ks = tile - mn * p.split_k; }
             const uint32_t per_group = p.raster_group * p.num_n_blocks;
-            const uint32_t gi = mn / per_group, in_group = mn - gi * per_group;
+            const uint32_t gi = fast_div(mn, p.magic_per_group), in_group = mn - gi * per_group;
             const uint32_t first_m = gi * p.raster_group;
-            const uint32_t rows = min(p.raster_group, p.num_m_blocks - first_m);
-            const uint32_t mb = first_m + in_group % rows, nb = in_group / rows;
+            const bool full = first_m + p.raster_group <= p.num_m_blocks;
+            const uint32_t rows = full ? p.raster_group : p.num_m_blocks - first_m;
+            const uint32_t nb = fast_div(in_group, full ? p.magic_rows_full : p.magic_rows_last);
+            const uint32_t mb = first_m + in_group - nb * rows;
             t.row0 = (mb * kCtaGroup + rank) * kBlockM;
             t.row_z = 0;
             t.d_z = 0;
@@ -201,7 +228,7 @@ struct Scheduler {
             t.kb_end = min(t.kb_begin + p.k_blocks_per_split, p.num_k_blocks);
             t.kb_rot = p.k_stagger ? (nb * p.k_stagger) % (t.kb_end - t.kb_begin) : 0u;
         } else if constexpr (!kLean) {
-            const uint32_t mb_lin = tile / p.num_n_blocks, nb = tile - mb_lin * p.num_n_blocks;
+            const uint32_t mb_lin = fast_div(tile, p.magic_n_blocks), nb = tile - mb_lin * p.num_n_blocks;
             while (true) {
                 if (cur_group >= p.num_groups) return false;
                 if (!group_loaded) load_group();
@@ -370,8 +397,13 @@ __device__ __forceinline__ uint2 stochastic_round_quartet(uint32_t v0, uint32_t 
 // retires about one instruction every five to six cycles on the dependent chains of the epilogue (164 instructions per
 // 32x32 chunk), so for short K, where the epilogue and not the main loop bounds a tile, a second warp per scheduler
 // doubles the rate at which accumulators are drained.
+// kSimpleEpi: the output is BF16 written (or reduce-added) through staged TMA stores with no alpha, bias, stochastic
+// rounding, FP8 quantisation or cluster exchange. The generic epilogue decides all of that per chunk at run time, and
+// although every decision is a uniform branch, the code that is jumped over spreads the few instructions a chunk
+// really needs across kilobytes: the same sixteen conversions take three times as long as in a straight-line loop
+// (in-kernel clock reads), all of it instruction fetch. This instantiation keeps only the straight line.
 template <int kCtaGroup, int kMajorA, int kMajorB, bool kDecodeB, bool kLean = false, bool kFp4 = false, bool kBf16 = false,
-          bool kWideEpi = false>
+          bool kWideEpi = false, bool kSimpleEpi = false>
 __global__ void __launch_bounds__((kDecodeB || kWideEpi) ? kNumThreadsDecode : kNumThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
@@ -380,7 +412,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t cluster_split = (kCtaGroup == 1 && !kDecodeB && !kWideEpi) ? p.cluster_split : 1u;
+    static_assert(!(kLean && kSimpleEpi), "lean kernels store plainly, simple ones through TMA");
+    const uint32_t cluster_split = (kCtaGroup == 1 && !kDecodeB && !kWideEpi && !kSimpleEpi) ? p.cluster_split : 1u;
     constexpr uint32_t kSfAtoms = kBf16 ? 0u : kFp4 ? 2u : 1u;
     constexpr uint32_t kElemBytes = kBf16 ? 2u : 1u;              // bytes per operand element as TMA counts them
     constexpr uint32_t kStageK = kBlockK / kElemBytes;            // TMA elements of K per stage (= K rows of an MN-major tile)
@@ -535,21 +568,31 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             Tile t;
             uint32_t stage = 0, phase = 0, tile_iter = 0;
             bool ok = true;
+#ifdef DG_EPI_PROF
+            uint32_t prof[4] = {0, 0, 0, 0};
+#endif
             while (ok && sched.next(t)) {
                 const uint32_t e = p.accum_stages == 2 ? (tile_iter & 1u) : 0u;
                 const uint32_t e_phase = p.accum_stages == 2 ? ((tile_iter >> 1) & 1u) : (tile_iter & 1u);
+                EPI_T(tm0);
                 // the epilogue(s) must have drained this accumulator
                 if (kCtaGroup == 2) ok = wait_barrier_cluster(tmem_empty_bar(e), e_phase ^ 1, ab, kStatusTimeoutMma);
                 else ok = wait_barrier(tmem_empty_bar(e), e_phase ^ 1, ab, kStatusTimeoutMma);
                 if (!ok) break;
+                EPI_T(tm1); EPI_ACC(0, tm0, tm1);
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + e * p.block_n;
                 for (uint32_t kb = t.kb_begin; kb < t.kb_end; ++kb) {
                     // (BF16: the packer only forwards the arrival of the operands, which in a CTA pair is how the
                     // leader learns that the peer's half has landed too)
+                    EPI_T(tm2);
                     if (kCtaGroup == 2) ok = wait_barrier_cluster(sf_full_bar(stage), phase, ab, kStatusTimeoutMma);
                     else ok = wait_barrier(sf_full_bar(stage), phase, ab, kStatusTimeoutMma);
                     if (!ok) break;
+                    EPI_T(tm3); EPI_ACC(1, tm2, tm3);
+#ifdef DG_EPI_PROF
+                    if (kb == t.kb_begin) prof[2] += tm3 - tm2;
+#endif
                     if (tile_iter == 0 && kb == t.kb_begin) trace_mark(p, 4);
                     tc_fence_after_sync();
                     // scales: smem -> TMEM (A: 128 rows = one slab; B: one slab per 128 columns)
@@ -597,6 +640,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 trace_mark(p, 5);
                 ++tile_iter;
             }
+#ifdef DG_EPI_PROF
+            if (p.trace != nullptr) for (int i = 0; i < 3; ++i) p.trace[(1024 + blockIdx.x) * 16 + 13 + i] = prof[i];
+#endif
         }
         __syncwarp();
     } else if (warp == 2) {
@@ -710,14 +756,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         Tile t;
         uint32_t tile_iter = 0, buf = 0;
         bool ok = true;
+#ifdef DG_EPI_PROF
+        uint32_t prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+#endif
         const uint32_t store_base = smem_base + L.store_bufs + (warp - 4) * p.store_bufs * kStoreBufBytes;
         uint8_t* store_gen = smem_gen + L.store_bufs + (warp - 4) * p.store_bufs * kStoreBufBytes;
-        const uint32_t cols_per_box = p.d_is_fp32 ? 32u : 64u;
+        auto out_is_fp32 = [&]() -> bool { return !kSimpleEpi && p.d_is_fp32 != 0; };   // a kernel-argument read, not a register
         const uint32_t leader_tmem_empty0 = kCtaGroup == 2 ? mapa_shared(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
         while (ok && sched.next(t)) {
             const uint32_t e = p.accum_stages == 2 ? (tile_iter & 1u) : 0u;
             const uint32_t e_phase = p.accum_stages == 2 ? ((tile_iter >> 1) & 1u) : (tile_iter & 1u);
+            EPI_T(tw0);
             if (!(ok = wait_barrier(tmem_full_bar(e), e_phase, ab, kStatusTimeoutEpilogue))) break;
+            EPI_T(tw1); EPI_ACC(6, tw0, tw1);
             if (tile_iter == 0 && threadIdx.x == 128) trace_mark(p, 6);
             tc_fence_after_sync();
             const uint32_t row = t.row0 + q * 32 + lane;       // row of D held by this thread
@@ -725,23 +776,31 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
             // One 32-column chunk of this thread's row: alpha / bias, cast, stage, store.
             // `single`: the chunk goes out on its own (BF16 boxes normally pair two chunks).
-            auto process_chunk = [&](uint32_t (&v)[32], uint32_t c0, bool single) {
+            // `simple_tag`: std::true_type leaves only cast + staged TMA store (the caller has checked that nothing else
+            // is asked for), so that the loop over the chunks of such a tile is a short straight line of code.
+            auto process_chunk = [&](auto simple_tag, uint32_t (&v)[32], uint32_t c0, bool single) {
+                constexpr bool kSimple = kSimpleEpi || decltype(simple_tag)::value;
                 const uint32_t col0 = t.n0 + c0;
-                if (!kLean && p.has_alpha) {
+                EPI_T(tp0);
+#ifdef DG_EPI_PROF
+                prof[8] += 1;
+#endif
+                if (!kLean && !kSimple && p.has_alpha) {
                     #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * p.alpha);
                 }
-                if (p.has_bias) {
+                if (!kSimple && p.has_bias) {
                     #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         float bv = 0.f;
                         if (col0 + i < p.n)
-                            bv = p.d_is_fp32 ? __ldg(reinterpret_cast<const float*>(p.bias) + col0 + i)
+                            bv = out_is_fp32() ? __ldg(reinterpret_cast<const float*>(p.bias) + col0 + i)
                                              : __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0 + i));
                         v[i] = __float_as_uint(__uint_as_float(v[i]) + bv);
                     }
                 }
-                if (!kLean && p.epilogue_mode == kEpiFp8Quant) {
+                EPI_T(tpa); EPI_ACC(11, tp0, tpa);
+                if (!kLean && !kSimple && p.epilogue_mode == kEpiFp8Quant) {
                     // E4M3 output with one UE8M0 scale per row per 32 columns (exactly this thread's chunk). As the
                     // reference does (operators.hpp:368-411, tests/test_einsum.py:74-84): round to BF16 first, scale =
                     // 2^ceil(log2(max(amax, 1e-4) / 448)), divide, round to nearest E4M3.
@@ -775,8 +834,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
                 // BF16 output: sixteen packed pairs, rounded to nearest or stochastically
                 uint32_t w16[16];
-                if (!p.d_is_fp32) {
-                    if (!kLean && p.stochastic) {
+                if (!out_is_fp32()) {
+                    if (!kLean && !kSimple && p.stochastic) {
                         #pragma unroll
                         for (uint32_t g = 0; g < 8; ++g) {
                             uint32_t x[4];
@@ -794,12 +853,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         }
                     }
                 }
-                if (!kLean && p.epilogue_mode <= kEpiTmaReduce) {
+                asm volatile("" :: "r"(w16[0]), "r"(w16[5]), "r"(w16[10]), "r"(w16[15]) : "memory");
+                EPI_T(tpc); EPI_ACC(9, tpa, tpc);
+                if (kSimple || (!kLean && p.epilogue_mode <= kEpiTmaReduce)) {
                     // Stage a [32 rows x 128 B] box, 16-byte chunk c of row r at chunk (c ^ (r & 7)). A BF16 box holds two
                     // 32-column groups; when block_n is an odd multiple of 32 the last group goes out alone as a
                     // [32 rows x 64 B] box (64B swizzle: chunk c of row r at c ^ ((r >> 1) & 3)) through tm_d_tail.
-                    const uint32_t half = (p.d_is_fp32 || single) ? 0u : ((c0 / 32) & 1u);
-                    const bool tail = !p.d_is_fp32 && half == 0 && (single || c0 + 32 >= p.block_n);
+                    const uint32_t half = (out_is_fp32() || single) ? 0u : ((c0 / 32) & 1u);
+                    const bool tail = !out_is_fp32() && half == 0 && (single || c0 + 32 >= p.block_n);
+                    EPI_T(tp1); EPI_ACC(1, tp0, tp1);
                     if (half == 0) {
                         // the buffer may still be read by the store issued `store_bufs` boxes ago
                         if (p.store_bufs == 1) tma_store_wait_read<0>();
@@ -808,8 +870,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         else tma_store_wait_read<3>();
                         __syncwarp();
                     }
+                    EPI_T(tp2); EPI_ACC(2, tp1, tp2);
                     uint8_t* bufp = store_gen + buf * kStoreBufBytes;
-                    if (p.d_is_fp32) {
+                    if (out_is_fp32()) {
                         uint8_t* rowp = bufp + lane * 128;
                         #pragma unroll
                         for (uint32_t c = 0; c < 8; ++c)
@@ -823,12 +886,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             *reinterpret_cast<uint4*>(dst) = make_uint4(w16[c * 4], w16[c * 4 + 1], w16[c * 4 + 2], w16[c * 4 + 3]);
                         }
                     }
-                    const bool box_done = p.d_is_fp32 || half == 1 || tail;
+                    const bool box_done = out_is_fp32() || half == 1 || tail;
+                    EPI_T(tp3); EPI_ACC(3, tp2, tp3);
                     if (box_done) {
                         fence_proxy_async_smem();
                         __syncwarp();
+                        EPI_T(tp4); EPI_ACC(4, tp3, tp4);
                         if (lane == 0) {
-                            const int32_t x = (int32_t)(t.n0 + (tail ? c0 : (c0 / cols_per_box) * cols_per_box));
+                            const int32_t x = (int32_t)(t.n0 + (tail ? c0 : (out_is_fp32() ? c0 : (c0 & ~63u))));
                             const int32_t y = (int32_t)(t.row0 + q * 32);
                             const CUtensorMap* map = tail ? &tm_d_tail : &tm_d;
                             if (p.epilogue_mode == kEpiTmaStore)
@@ -837,6 +902,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                 tma_reduce_add_3d(map, store_base + buf * kStoreBufBytes, x, y, (int32_t)t.d_z);
                             tma_store_commit();
                         }
+#ifdef DG_EPI_PROF
+                        __syncwarp();
+#endif
+                        EPI_T(tp5); EPI_ACC(5, tp4, tp5);
                         if (++buf == p.store_bufs) buf = 0;
                     }
                 } else {
@@ -845,10 +914,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     const bool row_ok = row < p.m;
                     const uint64_t base = (uint64_t)t.d_z * p.d_group_stride + (uint64_t)row * p.d_stride;
                     if ((kLean || p.epilogue_mode == kEpiPlainStore) && col0 + 32 <= p.n) {
-                        uint8_t* dst = reinterpret_cast<uint8_t*>(p.d) + (base + col0) * (p.d_is_fp32 ? 4u : 2u);
+                        uint8_t* dst = reinterpret_cast<uint8_t*>(p.d) + (base + col0) * (out_is_fp32() ? 4u : 2u);
                         if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
                             if (row_ok) {
-                                if (p.d_is_fp32) {
+                                if (out_is_fp32()) {
                                     #pragma unroll
                                     for (uint32_t c = 0; c < 8; ++c)
                                         reinterpret_cast<uint4*>(dst)[c] = make_uint4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
@@ -865,7 +934,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     for (int i = 0; i < 32; ++i) {
                         if (row_ok && col0 + i < p.n) {
                             const float f = __uint_as_float(v[i]);
-                            if (p.d_is_fp32) {
+                            if (out_is_fp32()) {
                                 float* dst = reinterpret_cast<float*>(p.d) + base + col0 + i;
                                 if (!kLean && p.epilogue_mode == kEpiPlainAtomic) atomicAdd(dst, f); else *dst = f;
                             } else {
@@ -941,29 +1010,42 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                 }
                             }
                         }
-                        process_chunk(vb, c * 32, true);
+                        process_chunk(std::false_type{}, vb, c * 32, true);
                     }
                 }
             } else {
             // Two register sets: the TMEM load of the next chunk is in flight while this one is converted and staged.
             // With plain stores the columns of the tile that lie beyond N are not even read (the staged TMA boxes are
             // clipped by the hardware instead).
-            const bool plain = kLean || p.epilogue_mode == kEpiPlainStore || p.epilogue_mode == kEpiPlainAtomic;
+            const bool plain = !kSimpleEpi && (kLean || p.epilogue_mode == kEpiPlainStore || p.epilogue_mode == kEpiPlainAtomic);
             const uint32_t cols = plain ? min(p.block_n, (p.n - t.n0 + 31u) & ~31u) : p.block_n;
             const uint32_t c_first = col_half * 64;
-            if (c_first < cols) tmem_ld_32x32b_x32(taddr + c_first, va);
-            for (uint32_t c0 = c_first; c0 < cols; c0 += kColStep) {
-                tmem_ld_wait();
-                if (c0 + 32 < cols) tmem_ld_32x32b_x32(taddr + c0 + 32, vb);
-                process_chunk(va, c0, false);
-                if (c0 + 32 < cols) {
+            auto run_chunks = [&](auto simple_tag) {
+                if (c_first < cols) tmem_ld_32x32b_x32(taddr + c_first, va);
+                for (uint32_t c0 = c_first; c0 < cols; c0 += kColStep) {
+                    EPI_T(tl0);
                     tmem_ld_wait();
-                    if (c0 + kColStep < cols) tmem_ld_32x32b_x32(taddr + c0 + kColStep, va);
-                    process_chunk(vb, c0 + 32, false);
+                    EPI_T(tl1); EPI_ACC(0, tl0, tl1);
+                    if (c0 + 32 < cols) tmem_ld_32x32b_x32(taddr + c0 + 32, vb);
+                    EPI_T(tl1b); EPI_ACC(10, tl1, tl1b);
+                    process_chunk(simple_tag, va, c0, false);
+                    if (c0 + 32 < cols) {
+                        EPI_T(tl2);
+                        tmem_ld_wait();
+                        EPI_T(tl3); EPI_ACC(0, tl2, tl3);
+                        if (c0 + kColStep < cols) tmem_ld_32x32b_x32(taddr + c0 + kColStep, va);
+                        EPI_T(tl3b); EPI_ACC(10, tl3, tl3b);
+                        process_chunk(simple_tag, vb, c0 + 32, false);
+                    }
                 }
-            }
+            };
+            // (the 384-thread instantiations have 168 registers per thread: two copies of the loop make them spill)
+            constexpr bool kTwoLoops = !kSimpleEpi && !kLean && !kDecodeB && !kWideEpi;
+            if (kSimpleEpi || (kTwoLoops && p.epi_simple)) run_chunks(std::true_type{});
+            else if constexpr (!kSimpleEpi) run_chunks(std::false_type{});
             }
             if (tile_iter == 0 && threadIdx.x == 128) trace_mark(p, 15);
+            EPI_T(tw2); EPI_ACC(7, tw1, tw2);
             // this accumulator may be overwritten by the next-but-one tile
             tc_fence_before_sync();
             __syncwarp();
@@ -976,6 +1058,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         // shared memory must outlive the bulk stores that read it; their global writes complete with the grid
         tma_store_wait_read<0>();
         if (threadIdx.x == 128) trace_mark(p, 7);
+#ifdef DG_EPI_PROF
+        if (threadIdx.x == 128 && p.trace != nullptr) {
+            for (int i = 0; i < 9; ++i) p.trace[(1024 + blockIdx.x) * 16 + i] = prof[i];
+            p.trace[(1024 + blockIdx.x) * 16 + 12] = tile_iter;
+            p.trace[(1024 + blockIdx.x) * 16 + 10] = prof[10];
+            p.trace[(1024 + blockIdx.x) * 16 + 9] = prof[9];
+            p.trace[(1024 + blockIdx.x) * 16 + 11] = prof[11];
+        }
+#endif
     }
 
     // ============================================================================ teardown
