@@ -197,6 +197,12 @@ static bool feature_disabled(const char* name) {
     static const std::string list = [] { const char* e = getenv("DG_DISABLE"); return std::string(e ? e : ""); }();
     return list.find(name) != std::string::npos;
 }
+// Wide tiles (block_n in (256, 448]: two accumulators of block_n / 2 columns fed by one A tile per K step) exist for the
+// FP8 x FP8 kernels with K-major operands; 2 * 224 accumulator columns + 20 scale columns is what fits in TMEM.
+constexpr uint32_t kMaxWideBlockN = 448;
+static bool wide_tile_possible(const dg_gemm_desc_t& d) {
+    return d.a_dtype == DG_E4M3 && d.b_dtype == DG_E4M3 && d.major_a == DG_MAJOR_K && d.major_b == DG_MAJOR_K;
+}
 static bool splits_in_cluster(const dg_gemm_config_t& c) { return c.split_k > 1 && c.reserved[3] != 0; }
 static bool splits_in_workspace(const dg_gemm_config_t& c) { return c.split_k > 1 && c.reserved[3] == 0; }
 constexpr uint32_t kMaxClusterSplit = 8;        // portable cluster size
@@ -217,9 +223,14 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
 
     const uint32_t gran = 32u;
     DG_CHECK_ARG(c.cta_group == 1 || c.cta_group == 2, "cta_group must be 1 or 2");
-    DG_CHECK_ARG(c.block_n >= gran && c.block_n <= 256 && c.block_n % gran == 0,
-                 "block_n must be a multiple of %u in [%u, 256]", gran, gran);
-    DG_CHECK_ARG(c.block_n % (16 * c.cta_group) == 0, "block_n not valid for this cta_group");
+    if (c.block_n > 256) {
+        // wide tile: two column halves per K step that share the A operand
+        DG_CHECK_ARG(wide_tile_possible(d) && !in_cluster, "block_n > 256 needs E4M3 x E4M3 with K-major operands and no cluster split-K");
+        DG_CHECK_ARG(c.block_n <= kMaxWideBlockN && c.block_n % 64 == 0, "a wide block_n must be a multiple of 64 in (256, %u]", kMaxWideBlockN);
+    } else {
+        DG_CHECK_ARG(c.block_n >= gran && c.block_n % gran == 0, "block_n must be a multiple of %u in [%u, 256]", gran, gran);
+        DG_CHECK_ARG(c.block_n % (16 * c.cta_group) == 0, "block_n not valid for this cta_group");
+    }
     if (d.major_b == DG_MAJOR_MN)      // MN-major B comes in 128-byte atoms along N
         DG_CHECK_ARG((c.block_n / c.cta_group) % (128 / ab_elem_bytes(d)) == 0,
                      "MN-major B needs block_n / cta_group to be a multiple of %u", 128 / ab_elem_bytes(d));
@@ -247,8 +258,9 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
         // as eight do (4096x32768x512: 78 us with four warps, 81 us with eight).
         const bool cast_and_store_only = d.d_dtype == DG_BF16 && !split && d.epilogue == DG_EPILOGUE_IDENTITY &&
                                          c.epilogue_mode <= kEpiTmaReduce && !feature_disabled("simple");
-        c.reserved[5] = (wide_possible && several_tiles && d.gemm_type != DG_GEMM_K_GROUPED_PSUM && nkb_tile <= 8 &&
-                         !cast_and_store_only && !feature_disabled("wide")) ? 2u : 1u;
+        // (measured on wide tiles too: eight warps gain nothing there and their staging costs a pipeline stage)
+        const bool short_k = several_tiles && d.gemm_type != DG_GEMM_K_GROUPED_PSUM && nkb_tile <= 8 && !cast_and_store_only;
+        c.reserved[5] = (wide_possible && short_k && c.block_n <= 256 && !feature_disabled("wide")) ? 2u : 1u;
     }
     const uint32_t epi_warps = wide_epilogue(c) ? 2 * kNumEpilogueWarps : kNumEpilogueWarps;
     const uint32_t accum_stages = (2 * c.block_n + sf_tmem_cols(c.block_n, atoms) <= 512) ? 2u : 1u;
@@ -328,6 +340,18 @@ static double k_block_cycles(uint32_t cta_group, uint32_t bn, bool packed_b = fa
     return t > decode ? t : decode;
 }
 
+// Modelled cycles of the main loop of one whole tile for problems with many rows (the tensor-bound regime), from
+// in-kernel clock reads: everything that crosses the SM's port to L2 (operands, scales, and the tile of D going out)
+// moves at about 58 bytes per cycle whatever the tiling, and the tensor pipe needs 2 * block_n cycles per K block.
+static double tile_main_cycles(uint32_t cta_group, uint32_t bn, uint32_t k_blocks, uint32_t atoms, uint32_t d_elem_bytes, bool packed_b) {
+    const double mma = 2.0 * bn * k_blocks;
+    const double per_kb = (128.0 + (double)bn / cta_group / (packed_b ? 2 : 1)) * 128.0 + (128.0 + sfb_rows(bn)) * 4.0 * atoms;
+    const double ingest = (per_kb * k_blocks + 128.0 * bn * d_elem_bytes) / 58.0;
+    const double decode = packed_b ? 2.5 * bn / cta_group * k_blocks : 0.0;
+    double t = mma > ingest ? mma : ingest;
+    return t > decode ? t : decode;
+}
+
 static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     memset(&c, 0, sizeof(c));
     const uint32_t num_sms = effective_num_sms(d);
@@ -370,7 +394,9 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
                               d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16 || d.epilogue == DG_EPILOGUE_FP8_QUANT)) break;
             const bool out_fp32 = d_fp32 || split > 1;
             const uint32_t step = d.major_b == DG_MAJOR_MN ? (128u / ab_elem_bytes(d)) * cg : 32u;   // MN-major B comes in 128-byte atoms
-            for (uint32_t bn = step; bn <= 256; bn += step) {
+            // (single CTAs gain little from a wide tile: A + 2 x B per stage leaves them two or three stages)
+            const uint32_t bn_max = (split == 1 && cg == 2 && wide_tile_possible(d) && !feature_disabled("wide_tile")) ? kMaxWideBlockN : 256u;
+            for (uint32_t bn = step; bn <= bn_max; bn += (bn >= 256 ? 64u : step)) {
                 if (bn > step && bn - step >= d.n) continue;                 // a narrower legal tile already covers N
                 if (bn % (16 * cg) != 0) continue;
                 const uint32_t n_tiles = ceil_div_u32(d.n, bn);
@@ -378,8 +404,11 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
                 const uint64_t waves = (tiles + units - 1) / units;
                 const uint32_t kb_per = ceil_div_u32(nkb, split);
                 const bool single_accum = 2 * bn + sf_tmem_cols(bn, atoms) > 512;
-                const double t_epi = bn * (out_fp32 ? 8.0 : 6.0);
-                const double cycles = kb_per * k_block_cycles(cg, bn, decodes_b(d)) + ((single_accum || waves == 1) ? t_epi : 0.0) + 700.0;
+                // (a wide tile has one accumulator: ~290 cycles per 32-column chunk are not hidden behind the next tile)
+                const double t_epi = bn > 256 ? bn * 9.0 : bn * (out_fp32 ? 8.0 : 6.0);
+                const double main_loop = rows > kBlockM ? tile_main_cycles(cg, bn, kb_per, atoms, out_fp32 ? 4 : elem_size(d.d_dtype), decodes_b(d))
+                                                        : kb_per * k_block_cycles(cg, bn, decodes_b(d));
+                const double cycles = main_loop + ((single_accum || waves == 1) ? t_epi : 0.0) + 700.0;
                 double cost = (double)waves * cycles / 1.8;                   // ns at ~1.8 GHz
                 if (cost < t_hbm) cost = t_hbm + 1e-3 * cost;     // HBM-bound: the cheaper schedule still wins ties
                 // second kernel (launch gap, FP32 read + zero + write) and the FP32 reduce traffic of the partials
@@ -520,7 +549,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.cluster_split = splits_in_cluster(c) ? c.split_k : 1u;
     plan.cluster_x = c.cta_group > 1 ? c.cta_group : a.cluster_split;
     // Instruction descriptor (block-scaled, kind::mxf8f6f4): E4M3 x E4M3, UE8M0 scales, FP32 accumulate.
-    a.idesc = ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) | ((c.block_n >> 3) << 17) | (1u << 23) |
+    a.idesc = ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) | (((c.block_n / tile_halves(c.block_n)) >> 3) << 17) | (1u << 23) |
               (((kBlockM * c.cta_group) >> 4) << 24);
     if (is_fp4_pair(d)) a.idesc |= (1u << 7) | (1u << 10);       // kind::mxf4: both operand formats E2M1
     if (is_bf16_pair(d))                                         // kind::f16: FP32 accumulator, BF16 operands, no scale fields
@@ -568,7 +597,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     }
     if (!encode) return DG_OK;
 
-    const uint32_t load_n = c.block_n / c.cta_group;
+    const uint32_t load_n = c.block_n / tile_halves(c.block_n) / c.cta_group;      // rows of one B box
     const uint64_t k64 = (d.k + 63) / 64;
     const uint64_t rows_a = d.m;      // rows per group for masked, all rows otherwise
     // ---- A
@@ -639,7 +668,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
         const uint64_t gs = nonzero_stride(d.sfb_group_stride, k64 * d.sfb_stride);
         const uint64_t dims[3] = {d.n, k64, groups};
         const uint64_t str[2] = {d.sfb_stride * 2, gs * 2};
-        const uint32_t box[3] = {sfb_rows(c.block_n), 2 * sf_atoms(d), 1};
+        const uint32_t box[3] = {sfb_rows(c.block_n) / tile_halves(c.block_n), 2 * sf_atoms(d), 1};
         if (int rc = encode_map(&plan.tm_sfb, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, d.sfb, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE, "SFB")) return rc;
     }
     // ---- D (or the split-K workspace)

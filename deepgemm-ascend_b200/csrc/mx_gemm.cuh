@@ -285,7 +285,13 @@ __device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
     return d;
 }
 
-__host__ __device__ __forceinline__ uint32_t sfb_rows(uint32_t block_n) { return (block_n + 127u) / 128u * 128u; }
+// A tile wider than 256 columns is computed as two halves of block_n / 2 columns (two MMAs per K step that share the
+// A operand): each half has its own rows of B and its own scale-factor slabs.
+__host__ __device__ __forceinline__ uint32_t tile_halves(uint32_t block_n) { return block_n > 256u ? 2u : 1u; }
+__host__ __device__ __forceinline__ uint32_t sfb_rows(uint32_t block_n) {
+    const uint32_t h = tile_halves(block_n);
+    return (block_n / h + 127u) / 128u * 128u * h;
+}
 
 // Shared-memory carve-up, computed identically on host and device.
 struct SmemLayout {
@@ -441,6 +447,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t num_stages = p.num_stages;
     const uint32_t load_n = p.block_n / kCtaGroup;            // rows of B this CTA fetches
     const uint32_t sfb_slabs = sfb_rows(p.block_n) / 128;
+    // wide tiles (block_n > 256, K-major 8-bit operands only): two column halves per K step
+    const uint32_t n_halves = (kMajorB == 0 && !kDecodeB && !kFp4 && !kBf16) ? tile_halves(p.block_n) : 1u;
+    const uint32_t half_n = p.block_n / n_halves, load_half = load_n / n_halves, slabs_half = sfb_slabs / n_halves;
 
     if (threadIdx.x == 0) {
         trace_mark(p, 0); trace_mark(p, 1);
@@ -535,7 +544,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         if constexpr (kMajorB == 0) tma_load_3d(sraw, &tm_b, bar, k0 / 2, (int32_t)bn0, (int32_t)t.b_z);
                         else tma_load_3d(sraw, &tm_b, bar, (int32_t)(bn0 / 2), k0, (int32_t)t.b_z);
                     } else if constexpr (kMajorB == 0) {
-                        tma_load_3d(sb, &tm_b, bar, k0, (int32_t)bn0, (int32_t)t.b_z);
+                        // (in a CTA pair every half is split between the two CTAs, as its MMA expects)
+                        for (uint32_t h = 0; h < n_halves; ++h)
+                            tma_load_3d(sb + h * load_half * kBlockK, &tm_b, bar, k0,
+                                        (int32_t)(t.n0 + h * half_n + cta_rank * load_half), (int32_t)t.b_z);
                     } else {
                         // one box per 128-byte atom along N: [atom][K rows of the stage][128 B]
                         for (uint32_t a0 = 0; a0 < load_n; a0 += kAtomMn)
@@ -545,8 +557,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     if constexpr (!kBf16) {
                         tma_load_3d(smem_base + L.sf_raw_a + stage * L.sfa_stage, &tm_sfa, sf_bar,
                                     (int32_t)t.row0, (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.row_z);
-                        tma_load_3d(smem_base + L.sf_raw_b + stage * L.sfb_stage, &tm_sfb, sf_bar,
-                                    (int32_t)t.n0, (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.b_z);
+                        for (uint32_t h = 0; h < n_halves; ++h)
+                            tma_load_3d(smem_base + L.sf_raw_b + stage * L.sfb_stage + h * (L.sfb_stage / n_halves), &tm_sfb, sf_bar,
+                                        (int32_t)(t.n0 + h * half_n), (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.b_z);
                     }
                     if (i == 0) trace_mark(p, 12);
                     if (++stage == num_stages) { stage = 0; phase ^= 1; ring_used = true; }
@@ -627,6 +640,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             const uint32_t idesc = p.idesc | (k << 4) | (k << 29);   // scale ids of B and of A
                             umma_mxf8f6f4<kCtaGroup>(tmem_d, da, db, idesc, tmem_sfa, tmem_sfb,
                                                      (kb > t.kb_begin || k > 0) ? 1u : 0u);
+                            if constexpr (kMajorB == 0 && !kDecodeB) {
+                                // second column half of a wide tile: its own rows of B, scale slabs and accumulator columns
+                                if (n_halves == 2)
+                                    umma_mxf8f6f4<kCtaGroup>(tmem_d + half_n, da, make_kmajor_sw128_desc(sb + load_half * kBlockK + k * kUmmaK),
+                                                             idesc, tmem_sfa, tmem_sfb + slabs_half * 4,
+                                                             (kb > t.kb_begin || k > 0) ? 1u : 0u);
+                            }
                         }
                     }
                     // release the stage once these MMAs have read it
@@ -661,11 +681,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
                 const uint16_t* raw_a = reinterpret_cast<const uint16_t*>(smem_gen + L.sf_raw_a + stage * L.sfa_stage);
                 uint4* pack_a = reinterpret_cast<uint4*>(smem_gen + L.sf_pack_a + stage * L.sfa_stage);
-                const uint32_t rows_b = sfb_slabs * 128;
+                const uint32_t rows_b = slabs_half * 128;        // rows of one half's raw columns
                 const uint16_t* raw_b = reinterpret_cast<const uint16_t*>(smem_gen + L.sf_raw_b + stage * L.sfb_stage);
                 uint4* pack_b = reinterpret_cast<uint4*>(smem_gen + L.sf_pack_b + stage * L.sfb_stage);
                 // In place: everything is read into registers first, then the atoms overwrite the raw columns.
-                constexpr uint32_t kMaxSlabs = 2;                // block_n <= 256
+                constexpr uint32_t kMaxSlabs = (kMajorB == 0 && !kDecodeB && !kFp4 && !kBf16) ? 4 : 2;   // block_n <= 256, or two halves
                 uint4 va[kSfAtoms ? kSfAtoms : 1], vb[kSfAtoms ? kSfAtoms : 1][kMaxSlabs];
                 #pragma unroll
                 for (uint32_t g = 0; g + 1 <= kSfAtoms; ++g) {   // word g of a row = int16 columns 2g and 2g + 1
@@ -677,10 +697,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     #pragma unroll
                     for (uint32_t i = 0; i < kMaxSlabs; ++i) {
                         if (i < sfb_slabs) {
+                            // slab i belongs to half i / slabs_half, whose raw columns are an array of their own
+                            const uint32_t hh = i >= slabs_half ? 1u : 0u;
+                            const uint16_t* raw_h = raw_b + hh * (2 * kSfAtoms * rows_b);
                             #pragma unroll
                             for (uint32_t j = 0; j < 4; ++j) {
-                                const uint32_t r = i * 128 + j * 32 + lane;
-                                v[j] = (uint32_t)raw_b[(2 * g) * rows_b + r] | ((uint32_t)raw_b[(2 * g + 1) * rows_b + r] << 16);
+                                const uint32_t r = (i - hh * slabs_half) * 128 + j * 32 + lane;
+                                v[j] = (uint32_t)raw_h[(2 * g) * rows_b + r] | ((uint32_t)raw_h[(2 * g + 1) * rows_b + r] << 16);
                             }
                             vb[g][i] = make_uint4(v[0], v[1], v[2], v[3]);
                         }

@@ -416,3 +416,51 @@ def test_dense_eight_epilogue_warps():
     _dense(4096, 4096, 512)            # the heuristic takes eight warps here
     with pytest.raises(RuntimeError):
         _dense(256, 256, 512, trans='nn', config={'block_n': 128, 'epilogue_warps': 8})
+
+
+@pytest.mark.parametrize('bn', [320, 384, 448])
+@pytest.mark.parametrize('cg', [1, 2])
+def test_dense_wide_tiles(bn, cg):
+    """block_n > 256: two column halves per K step that share the A tile (one accumulator of block_n columns)."""
+    _dense(512, 1024, 1024, config={'cta_group': cg, 'block_n': bn})
+    _dense(300, 1000, 640, config={'cta_group': cg, 'block_n': bn}, out=torch.float32, acc=True)
+    _dense(130, 257, 384, config={'cta_group': cg, 'block_n': bn}, bias=True)                 # one ragged tile
+    _dense(256, 2 * bn + 40, 512, config={'cta_group': cg, 'block_n': bn, 'epilogue_warps': 8}, alpha=0.25)
+
+
+def test_dense_wide_tile_variants():
+    _dense(4096, 4096, 7168, dist='normal', recipe=(1, 128, 128))      # the heuristic takes a wide pair tile here
+    _dense(1024, 900, 2048, config={'cta_group': 2, 'block_n': 448}, acc=True)               # BF16 reduce-add
+    # same accumulation order as the narrow tiling: bit-identical results
+    seed_all(7)
+    a, sfa, _ = uniform_fp8((512, 1024), (1, 32))
+    b, sfb, _ = uniform_fp8((1344, 1024), (1, 32))
+    outs = []
+    for cfg in ({'cta_group': 2, 'block_n': 224}, {'cta_group': 2, 'block_n': 448}, {'cta_group': 1, 'block_n': 320}):
+        d = torch.full((512, 1344), float('nan'), dtype=torch.bfloat16, device='cuda')
+        deep_gemm.fp8_gemm_nt((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d, config=cfg)
+        outs.append(d)
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    assert torch.equal(outs[0].view(torch.int16), outs[2].view(torch.int16))
+    for bad in ({'block_n': 288}, {'block_n': 512}, {'block_n': 320, 'split_k': 2, 'cluster_split': 1}):
+        with pytest.raises(RuntimeError):
+            _dense(256, 1024, 1024, config=bad)
+    with pytest.raises(RuntimeError):                                                          # MN-major B
+        _dense(256, 1024, 1024, trans='nn', config={'block_n': 320})
+
+
+def test_m_grouped_wide_tiles():
+    total, psum = oracle.make_psum_layout([300, 0, 513, 256], 256)
+    seed_all(3)
+    a, sfa, a_ref = uniform_fp8((total, 768), (1, 32))
+    b, sfb, b_ref = uniform_fp8((4, 1000, 768), (1, 32))
+    for span in oracle.psum_padding_spans(psum):
+        a.view(torch.uint8)[span] = 0
+        a_ref[span] = 0
+    ref = oracle.m_grouped_psum_ref(a_ref, b_ref, psum, torch.bfloat16)
+    layout = torch.tensor(psum, dtype=torch.int32, device='cuda')
+    for cfg in ({'cta_group': 2, 'block_n': 384}, {'cta_group': 1, 'block_n': 448}):
+        d = torch.full((total, 1000), float('nan'), dtype=torch.bfloat16, device='cuda')
+        deep_gemm.m_grouped_fp8_gemm_nt_contiguous((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d, layout, config=cfg)
+        assert deep_gemm.device_status() == 0
+        assert_close(d, ref, f'm-grouped wide {cfg}')
