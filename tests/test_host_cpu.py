@@ -145,10 +145,13 @@ def test_heuristic_respects_hardware_limits():
             assert lib.dg_select_config(ctypes.byref(desc), ctypes.byref(cfg)) == 0, L.last_error()
             c = cfg.as_dict()
             assert c['block_m'] == 128 * c['cta_group'] and c['block_k'] == 128
-            assert 32 <= c['block_n'] <= 256 and c['block_n'] % 32 == 0
+            # up to 256 columns in steps of 32, or a wide tile of two halves (a CTA pair with many rows only)
+            assert (32 <= c['block_n'] <= 256 and c['block_n'] % 32 == 0) or \
+                   (c['block_n'] in (320, 384, 448) and c['cta_group'] == 2 and m > 128 and c['accum_stages'] == 1)
             assert c['smem_bytes'] <= 227 * 1024 and 1 <= c['num_stages'] <= 12
             assert c['tmem_cols'] in (32, 64, 128, 256, 512)
-            assert c['accum_stages'] * c['block_n'] + 12 <= 512
+            slabs = (c['block_n'] + 127) // 128 if c['block_n'] <= 256 else 2 * ((c['block_n'] // 2 + 127) // 128)
+            assert c['accum_stages'] * c['block_n'] + 4 + 4 * slabs <= c['tmem_cols']
             assert c['split_k'] >= 1 and (c['split_k'] == 1 or m <= 1024)
             ws = lib.dg_gemm_workspace_bytes(ctypes.byref(desc), ctypes.byref(cfg))
             if c['split_k'] > 1 and c['cluster_split']:
