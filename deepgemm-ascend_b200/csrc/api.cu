@@ -225,7 +225,8 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     DG_CHECK_ARG(c.cta_group == 1 || c.cta_group == 2, "cta_group must be 1 or 2");
     if (c.block_n > 256) {
         // wide tile: two column halves per K step that share the A operand
-        DG_CHECK_ARG(wide_tile_possible(d) && !in_cluster, "block_n > 256 needs E4M3 x E4M3 with K-major operands and no cluster split-K");
+        DG_CHECK_ARG(wide_tile_possible(d) && c.cta_group == 2 && !wide_epilogue(c),
+                     "block_n > 256 needs E4M3 x E4M3 with K-major operands, cta_group 2 and four epilogue warps");
         DG_CHECK_ARG(c.block_n <= kMaxWideBlockN && c.block_n % 64 == 0, "a wide block_n must be a multiple of 64 in (256, %u]", kMaxWideBlockN);
     } else {
         DG_CHECK_ARG(c.block_n >= gran && c.block_n % gran == 0, "block_n must be a multiple of %u in [%u, 256]", gran, gran);
@@ -567,6 +568,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
                 (d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_BIAS) && !plan.fp4_pair && !plan.bf16_pair && !plan.wide_epi && !feature_disabled("lean");
     a.epi_simple = (d.epilogue == DG_EPILOGUE_IDENTITY && !a.has_alpha && !a.has_bias && !a.stochastic &&
                     c.epilogue_mode <= kEpiTmaReduce && !splits_in_cluster(c) && !feature_disabled("straight")) ? 1u : 0u;
+    plan.wide_tile = c.block_n > 256;
     plan.simple_epi = !plan.lean && !plan.decode_b && !plan.fp4_pair && !plan.bf16_pair && d.major_a == DG_MAJOR_K && d.major_b == DG_MAJOR_K &&
                       !a.d_is_fp32 && d.epilogue == DG_EPILOGUE_IDENTITY && !a.has_alpha && !a.has_bias && !a.stochastic &&
                       c.epilogue_mode <= kEpiTmaReduce && !splits_in_cluster(c) && !feature_disabled("simple");

@@ -15,6 +15,7 @@ struct LaunchPlan {
     bool decode_b;               // B is packed E2M1 and is decoded to E4M3 in shared memory
     uint32_t num_ctas, smem_bytes;
     bool wide_epi;                    // eight epilogue warps (384 threads)
+    bool wide_tile;                   // block_n > 256: two column halves per K step
     bool simple_epi;                  // the instantiation whose epilogue only casts to BF16 and issues TMA stores
     bool bf16_pair;                   // both operands BF16 (kind::f16, no scale factors)
     bool fp4_pair;                    // both operands packed E2M1 (kind::mxf4)

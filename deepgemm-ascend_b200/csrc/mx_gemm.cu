@@ -61,7 +61,10 @@ using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMa
                           const CUtensorMap, const CUtensorMap, const GemmKernelArgs);
 
 static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode_b, bool lean, bool fp4_pair, bool bf16_pair,
-                            bool wide_epi, bool simple_epi) {
+                            bool wide_epi, bool simple_epi, bool wide_tile) {
+    if (wide_tile)          // E4M3 x E4M3, K-major operands, CTA pair, block_n > 256
+        return simple_epi ? mx_gemm_kernel<2, 0, 0, false, false, false, false, false, true, true>
+                          : mx_gemm_kernel<2, 0, 0, false, false, false, false, false, false, true>;
     if (simple_epi) {       // E4M3 x E4M3, K-major operands, plain BF16 output through TMA stores
         if (wide_epi)
             return cta_group == 2 ? mx_gemm_kernel<2, 0, 0, false, false, false, false, true, true>
@@ -117,7 +120,7 @@ int get_status_pointer(int32_t** out) {
 }
 
 int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
-    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b, plan.lean, plan.fp4_pair, plan.bf16_pair, plan.wide_epi, plan.simple_epi);
+    KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b, plan.lean, plan.fp4_pair, plan.bf16_pair, plan.wide_epi, plan.simple_epi, plan.wide_tile);
     // The attribute is per device and per function; setting it is cheap, so do it on every launch.
     DG_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem_bytes));
 

@@ -403,13 +403,17 @@ __device__ __forceinline__ uint2 stochastic_round_quartet(uint32_t v0, uint32_t 
 // retires about one instruction every five to six cycles on the dependent chains of the epilogue (164 instructions per
 // 32x32 chunk), so for short K, where the epilogue and not the main loop bounds a tile, a second warp per scheduler
 // doubles the rate at which accumulators are drained.
+// kWideTile: block_n in (256, 448]: the tile is two column halves of block_n / 2, each with its own rows of B, scale
+// slabs and MMAs, that share the A tile of every stage (28 % fewer bytes per flop into the SM than two narrow tiles);
+// one accumulator of block_n columns. A template parameter because the stage loop of every role is a latency chain
+// the ring's throughput depends on: the narrow kernels must not carry the extra loops.
 // kSimpleEpi: the output is BF16 written (or reduce-added) through staged TMA stores with no alpha, bias, stochastic
 // rounding, FP8 quantisation or cluster exchange. The generic epilogue decides all of that per chunk at run time, and
 // although every decision is a uniform branch, the code that is jumped over spreads the few instructions a chunk
 // really needs across kilobytes: the same sixteen conversions take three times as long as in a straight-line loop
 // (in-kernel clock reads), all of it instruction fetch. This instantiation keeps only the straight line.
 template <int kCtaGroup, int kMajorA, int kMajorB, bool kDecodeB, bool kLean = false, bool kFp4 = false, bool kBf16 = false,
-          bool kWideEpi = false, bool kSimpleEpi = false>
+          bool kWideEpi = false, bool kSimpleEpi = false, bool kWideTile = false>
 __global__ void __launch_bounds__((kDecodeB || kWideEpi) ? kNumThreadsDecode : kNumThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
@@ -448,7 +452,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t load_n = p.block_n / kCtaGroup;            // rows of B this CTA fetches
     const uint32_t sfb_slabs = sfb_rows(p.block_n) / 128;
     // wide tiles (block_n > 256, K-major 8-bit operands only): two column halves per K step
-    const uint32_t n_halves = (kMajorB == 0 && !kDecodeB && !kFp4 && !kBf16) ? tile_halves(p.block_n) : 1u;
+    static_assert(!kWideTile || (kCtaGroup == 2 && kMajorA == 0 && kMajorB == 0 && !kDecodeB && !kFp4 && !kBf16 && !kLean && !kWideEpi),
+                  "wide tiles: FP8 x FP8 CTA pairs with K-major operands");
+    constexpr uint32_t n_halves = kWideTile ? 2u : 1u;
     const uint32_t half_n = p.block_n / n_halves, load_half = load_n / n_halves, slabs_half = sfb_slabs / n_halves;
 
     if (threadIdx.x == 0) {
@@ -640,10 +646,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             const uint32_t idesc = p.idesc | (k << 4) | (k << 29);   // scale ids of B and of A
                             umma_mxf8f6f4<kCtaGroup>(tmem_d, da, db, idesc, tmem_sfa, tmem_sfb,
                                                      (kb > t.kb_begin || k > 0) ? 1u : 0u);
-                            if constexpr (kMajorB == 0 && !kDecodeB) {
+                            if constexpr (kWideTile) {
                                 // second column half of a wide tile: its own rows of B, scale slabs and accumulator columns
-                                if (n_halves == 2)
-                                    umma_mxf8f6f4<kCtaGroup>(tmem_d + half_n, da, make_kmajor_sw128_desc(sb + load_half * kBlockK + k * kUmmaK),
+                                umma_mxf8f6f4<kCtaGroup>(tmem_d + half_n, da, make_kmajor_sw128_desc(sb + load_half * kBlockK + k * kUmmaK),
                                                              idesc, tmem_sfa, tmem_sfb + slabs_half * 4,
                                                              (kb > t.kb_begin || k > 0) ? 1u : 0u);
                             }
@@ -685,7 +690,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 const uint16_t* raw_b = reinterpret_cast<const uint16_t*>(smem_gen + L.sf_raw_b + stage * L.sfb_stage);
                 uint4* pack_b = reinterpret_cast<uint4*>(smem_gen + L.sf_pack_b + stage * L.sfb_stage);
                 // In place: everything is read into registers first, then the atoms overwrite the raw columns.
-                constexpr uint32_t kMaxSlabs = (kMajorB == 0 && !kDecodeB && !kFp4 && !kBf16) ? 4 : 2;   // block_n <= 256, or two halves
+                constexpr uint32_t kMaxSlabs = kWideTile ? 4 : 2;           // block_n <= 256, or two halves
                 uint4 va[kSfAtoms ? kSfAtoms : 1], vb[kSfAtoms ? kSfAtoms : 1][kMaxSlabs];
                 #pragma unroll
                 for (uint32_t g = 0; g + 1 <= kSfAtoms; ++g) {   // word g of a row = int16 columns 2g and 2g + 1
@@ -698,7 +703,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     for (uint32_t i = 0; i < kMaxSlabs; ++i) {
                         if (i < sfb_slabs) {
                             // slab i belongs to half i / slabs_half, whose raw columns are an array of their own
-                            const uint32_t hh = i >= slabs_half ? 1u : 0u;
+                            const uint32_t hh = (kWideTile && i >= slabs_half) ? 1u : 0u;
                             const uint16_t* raw_h = raw_b + hh * (2 * kSfAtoms * rows_b);
                             #pragma unroll
                             for (uint32_t j = 0; j < 4; ++j) {

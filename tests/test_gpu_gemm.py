@@ -419,13 +419,13 @@ def test_dense_eight_epilogue_warps():
 
 
 @pytest.mark.parametrize('bn', [320, 384, 448])
-@pytest.mark.parametrize('cg', [1, 2])
-def test_dense_wide_tiles(bn, cg):
-    """block_n > 256: two column halves per K step that share the A tile (one accumulator of block_n columns)."""
-    _dense(512, 1024, 1024, config={'cta_group': cg, 'block_n': bn})
-    _dense(300, 1000, 640, config={'cta_group': cg, 'block_n': bn}, out=torch.float32, acc=True)
-    _dense(130, 257, 384, config={'cta_group': cg, 'block_n': bn}, bias=True)                 # one ragged tile
-    _dense(256, 2 * bn + 40, 512, config={'cta_group': cg, 'block_n': bn, 'epilogue_warps': 8}, alpha=0.25)
+def test_dense_wide_tiles(bn):
+    """block_n > 256 (CTA pairs): two column halves per K step that share the A tile, one accumulator of block_n columns."""
+    _dense(512, 1024, 1024, config={'cta_group': 2, 'block_n': bn})
+    _dense(300, 1000, 640, config={'cta_group': 2, 'block_n': bn}, out=torch.float32, acc=True)
+    _dense(130, 257, 384, config={'cta_group': 2, 'block_n': bn}, bias=True)                  # one ragged tile
+    _dense(256, 2 * bn + 40, 512, config={'cta_group': 2, 'block_n': bn}, alpha=0.25)
+    _dense(1024, 3 * bn, 2048, config={'cta_group': 2, 'block_n': bn, 'num_stages': 2})
 
 
 def test_dense_wide_tile_variants():
@@ -436,17 +436,18 @@ def test_dense_wide_tile_variants():
     a, sfa, _ = uniform_fp8((512, 1024), (1, 32))
     b, sfb, _ = uniform_fp8((1344, 1024), (1, 32))
     outs = []
-    for cfg in ({'cta_group': 2, 'block_n': 224}, {'cta_group': 2, 'block_n': 448}, {'cta_group': 1, 'block_n': 320}):
+    for cfg in ({'cta_group': 2, 'block_n': 224}, {'cta_group': 2, 'block_n': 448}, {'cta_group': 2, 'block_n': 320}):
         d = torch.full((512, 1344), float('nan'), dtype=torch.bfloat16, device='cuda')
         deep_gemm.fp8_gemm_nt((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d, config=cfg)
         outs.append(d)
     assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
     assert torch.equal(outs[0].view(torch.int16), outs[2].view(torch.int16))
-    for bad in ({'block_n': 288}, {'block_n': 512}, {'block_n': 320, 'split_k': 2, 'cluster_split': 1}):
+    for bad in ({'cta_group': 2, 'block_n': 288}, {'cta_group': 2, 'block_n': 512}, {'cta_group': 1, 'block_n': 320},
+                {'cta_group': 2, 'block_n': 320, 'epilogue_warps': 8}):
         with pytest.raises(RuntimeError):
             _dense(256, 1024, 1024, config=bad)
     with pytest.raises(RuntimeError):                                                          # MN-major B
-        _dense(256, 1024, 1024, trans='nn', config={'block_n': 320})
+        _dense(256, 1024, 1024, trans='nn', config={'cta_group': 2, 'block_n': 320})
 
 
 def test_m_grouped_wide_tiles():
@@ -459,7 +460,7 @@ def test_m_grouped_wide_tiles():
         a_ref[span] = 0
     ref = oracle.m_grouped_psum_ref(a_ref, b_ref, psum, torch.bfloat16)
     layout = torch.tensor(psum, dtype=torch.int32, device='cuda')
-    for cfg in ({'cta_group': 2, 'block_n': 384}, {'cta_group': 1, 'block_n': 448}):
+    for cfg in ({'cta_group': 2, 'block_n': 384}, {'cta_group': 2, 'block_n': 448}):
         d = torch.full((total, 1000), float('nan'), dtype=torch.bfloat16, device='cuda')
         deep_gemm.m_grouped_fp8_gemm_nt_contiguous((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d, layout, config=cfg)
         assert deep_gemm.device_status() == 0
