@@ -198,10 +198,12 @@ static bool feature_disabled(const char* name) {
     return list.find(name) != std::string::npos;
 }
 // Wide tiles (block_n in (256, 448]: two accumulators of block_n / 2 columns fed by one A tile per K step) exist for the
-// FP8 x FP8 kernels with K-major operands; 2 * 224 accumulator columns + 20 scale columns is what fits in TMEM.
+// FP8 x FP8 and FP4 x FP4 kernels with K-major operands; 2 * 224 accumulator columns + 20 (40) scale columns is what
+// fits in TMEM.
 constexpr uint32_t kMaxWideBlockN = 448;
 static bool wide_tile_possible(const dg_gemm_desc_t& d) {
-    return d.a_dtype == DG_E4M3 && d.b_dtype == DG_E4M3 && d.major_a == DG_MAJOR_K && d.major_b == DG_MAJOR_K;
+    return ((d.a_dtype == DG_E4M3 && d.b_dtype == DG_E4M3) || (d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E2M1X2)) &&
+           d.major_a == DG_MAJOR_K && d.major_b == DG_MAJOR_K;
 }
 static bool splits_in_cluster(const dg_gemm_config_t& c) { return c.split_k > 1 && c.reserved[3] != 0; }
 static bool splits_in_workspace(const dg_gemm_config_t& c) { return c.split_k > 1 && c.reserved[3] == 0; }
@@ -226,7 +228,7 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     if (c.block_n > 256) {
         // wide tile: two column halves per K step that share the A operand
         DG_CHECK_ARG(wide_tile_possible(d) && c.cta_group == 2 && !wide_epilogue(c),
-                     "block_n > 256 needs E4M3 x E4M3 with K-major operands, cta_group 2 and four epilogue warps");
+                     "block_n > 256 needs E4M3 x E4M3 or E2M1 x E2M1 with K-major operands, cta_group 2 and four epilogue warps");
         DG_CHECK_ARG(c.block_n <= kMaxWideBlockN && c.block_n % 64 == 0, "a wide block_n must be a multiple of 64 in (256, %u]", kMaxWideBlockN);
     } else {
         DG_CHECK_ARG(c.block_n >= gran && c.block_n % gran == 0, "block_n must be a multiple of %u in [%u, 256]", gran, gran);
@@ -345,7 +347,7 @@ static double k_block_cycles(uint32_t cta_group, uint32_t bn, bool packed_b = fa
 // in-kernel clock reads: everything that crosses the SM's port to L2 (operands, scales, and the tile of D going out)
 // moves at about 58 bytes per cycle whatever the tiling, and the tensor pipe needs 2 * block_n cycles per K block.
 static double tile_main_cycles(uint32_t cta_group, uint32_t bn, uint32_t k_blocks, uint32_t atoms, uint32_t d_elem_bytes, bool packed_b) {
-    const double mma = 2.0 * bn * k_blocks;
+    const double mma = (atoms == 2 ? 1.0 : 2.0) * bn * k_blocks;      // (kind::mxf4 runs a 128-byte K block in half the cycles)
     const double per_kb = (128.0 + (double)bn / cta_group / (packed_b ? 2 : 1)) * 128.0 + (128.0 + sfb_rows(bn)) * 4.0 * atoms;
     const double ingest = (per_kb * k_blocks + 128.0 * bn * d_elem_bytes) / 58.0;
     const double decode = packed_b ? 2.5 * bn / cta_group * k_blocks : 0.0;
@@ -400,6 +402,10 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
             for (uint32_t bn = step; bn <= bn_max; bn += (bn >= 256 ? 64u : step)) {
                 if (bn > step && bn - step >= d.n) continue;                 // a narrower legal tile already covers N
                 if (bn % (16 * cg) != 0) continue;
+                // (packed E2M1 pairs copy twice the scale atoms per K block: only full 224-column halves pay off.
+                //  Measured, 4096x4096x7168: 320 columns 71.7 us against 65.6 us with 256; 4096x7168x16384: 448 columns
+                //  191 us against 205 us with 224)
+                if (bn > 256 && atoms == 2 && bn != kMaxWideBlockN) continue;
                 const uint32_t n_tiles = ceil_div_u32(d.n, bn);
                 const uint64_t tiles = m_tiles * n_tiles * split;
                 const uint64_t waves = (tiles + units - 1) / units;

@@ -452,8 +452,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t load_n = p.block_n / kCtaGroup;            // rows of B this CTA fetches
     const uint32_t sfb_slabs = sfb_rows(p.block_n) / 128;
     // wide tiles (block_n > 256, K-major 8-bit operands only): two column halves per K step
-    static_assert(!kWideTile || (kCtaGroup == 2 && kMajorA == 0 && kMajorB == 0 && !kDecodeB && !kFp4 && !kBf16 && !kLean && !kWideEpi),
-                  "wide tiles: FP8 x FP8 CTA pairs with K-major operands");
+    static_assert(!kWideTile || (kCtaGroup == 2 && kMajorA == 0 && kMajorB == 0 && !kDecodeB && !kBf16 && !kLean && !kWideEpi),
+                  "wide tiles: FP8 x FP8 or FP4 x FP4 CTA pairs with K-major operands");
     constexpr uint32_t n_halves = kWideTile ? 2u : 1u;
     const uint32_t half_n = p.block_n / n_halves, load_half = load_n / n_halves, slabs_half = sfb_slabs / n_halves;
 
@@ -642,6 +642,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             const uint32_t id = (k & 1u) * 2u, g = k >> 1;
                             umma_mxf4<kCtaGroup>(tmem_d, da, db, p.idesc | (id << 4) | (id << 29), tmem_sfa + g * 4,
                                                  tmem_sfb + g * sfb_slabs * 4, (kb > t.kb_begin || k > 0) ? 1u : 0u);
+                            if constexpr (kWideTile)      // second column half: its own rows of B and scale slabs
+                                umma_mxf4<kCtaGroup>(tmem_d + half_n, da, make_kmajor_sw128_desc(sb + load_half * kBlockK + k * kUmmaK),
+                                                     p.idesc | (id << 4) | (id << 29), tmem_sfa + g * 4,
+                                                     tmem_sfb + (g * sfb_slabs + slabs_half) * 4, (kb > t.kb_begin || k > 0) ? 1u : 0u);
                         } else {
                             const uint32_t idesc = p.idesc | (k << 4) | (k << 29);   // scale ids of B and of A
                             umma_mxf8f6f4<kCtaGroup>(tmem_d, da, db, idesc, tmem_sfa, tmem_sfb,

@@ -465,3 +465,11 @@ def test_m_grouped_wide_tiles():
         deep_gemm.m_grouped_fp8_gemm_nt_contiguous((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d, layout, config=cfg)
         assert deep_gemm.device_status() == 0
         assert_close(d, ref, f'm-grouped wide {cfg}')
+
+
+def test_fp4_pair_wide_tiles():
+    """Both operands packed E2M1 with block_n > 256: two column halves per K step, two scale words per row and stage."""
+    for bn in (320, 448):
+        _fp4_pair(512, 1024, 1024, config={'cta_group': 2, 'block_n': bn})
+        _fp4_pair(300, 1000, 768, config={'cta_group': 2, 'block_n': bn}, out=torch.float32)
+    _fp4_pair(4096, 7168, 4096)          # the heuristic takes a wide tile here
