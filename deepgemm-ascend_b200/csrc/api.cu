@@ -198,11 +198,13 @@ static bool feature_disabled(const char* name) {
     return list.find(name) != std::string::npos;
 }
 // Wide tiles (block_n in (256, 448]: two accumulators of block_n / 2 columns fed by one A tile per K step) exist for the
-// FP8 x FP8 and FP4 x FP4 kernels with K-major operands; 2 * 224 accumulator columns + 20 (40) scale columns is what
-// fits in TMEM.
+// FP8 x FP8, FP4 x FP4 and BF16 kernels with K-major operands; 2 * 224 accumulator columns + 20 (40) scale columns is
+// what fits in TMEM (BF16 has no scale columns and goes to 2 * 256).
 constexpr uint32_t kMaxWideBlockN = 448;
+static uint32_t max_wide_block_n(const dg_gemm_desc_t& d) { return d.a_dtype == DG_BF16 ? 512u : kMaxWideBlockN; }
 static bool wide_tile_possible(const dg_gemm_desc_t& d) {
-    return ((d.a_dtype == DG_E4M3 && d.b_dtype == DG_E4M3) || (d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E2M1X2)) &&
+    return ((d.a_dtype == DG_E4M3 && d.b_dtype == DG_E4M3) || (d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E2M1X2) ||
+            (d.a_dtype == DG_BF16 && d.b_dtype == DG_BF16)) &&
            d.major_a == DG_MAJOR_K && d.major_b == DG_MAJOR_K;
 }
 static bool splits_in_cluster(const dg_gemm_config_t& c) { return c.split_k > 1 && c.reserved[3] != 0; }
@@ -228,8 +230,8 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     if (c.block_n > 256) {
         // wide tile: two column halves per K step that share the A operand
         DG_CHECK_ARG(wide_tile_possible(d) && c.cta_group == 2 && !wide_epilogue(c),
-                     "block_n > 256 needs E4M3 x E4M3 or E2M1 x E2M1 with K-major operands, cta_group 2 and four epilogue warps");
-        DG_CHECK_ARG(c.block_n <= kMaxWideBlockN && c.block_n % 64 == 0, "a wide block_n must be a multiple of 64 in (256, %u]", kMaxWideBlockN);
+                     "block_n > 256 needs E4M3 x E4M3, E2M1 x E2M1 or BF16 x BF16 with K-major operands, cta_group 2 and four epilogue warps");
+        DG_CHECK_ARG(c.block_n <= max_wide_block_n(d) && c.block_n % 64 == 0, "a wide block_n must be a multiple of 64 in (256, %u]", max_wide_block_n(d));
     } else {
         DG_CHECK_ARG(c.block_n >= gran && c.block_n % gran == 0, "block_n must be a multiple of %u in [%u, 256]", gran, gran);
         DG_CHECK_ARG(c.block_n % (16 * c.cta_group) == 0, "block_n not valid for this cta_group");
@@ -398,7 +400,7 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
             const bool out_fp32 = d_fp32 || split > 1;
             const uint32_t step = d.major_b == DG_MAJOR_MN ? (128u / ab_elem_bytes(d)) * cg : 32u;   // MN-major B comes in 128-byte atoms
             // (single CTAs gain little from a wide tile: A + 2 x B per stage leaves them two or three stages)
-            const uint32_t bn_max = (split == 1 && cg == 2 && wide_tile_possible(d) && !feature_disabled("wide_tile")) ? kMaxWideBlockN : 256u;
+            const uint32_t bn_max = (split == 1 && cg == 2 && wide_tile_possible(d) && !feature_disabled("wide_tile")) ? max_wide_block_n(d) : 256u;
             for (uint32_t bn = step; bn <= bn_max; bn += (bn >= 256 ? 64u : step)) {
                 if (bn > step && bn - step >= d.n) continue;                 // a narrower legal tile already covers N
                 if (bn % (16 * cg) != 0) continue;
@@ -406,6 +408,9 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
                 //  Measured, 4096x4096x7168: 320 columns 71.7 us against 65.6 us with 256; 4096x7168x16384: 448 columns
                 //  191 us against 205 us with 224)
                 if (bn > 256 && atoms == 2 && bn != kMaxWideBlockN) continue;
+                // (BF16: the narrow tiling already runs at 95 % of the cuBLAS figure; measured, a wide tile gains 4 % at
+                //  K = 7168 and loses 5 % at K = 2048, where its exposed epilogue weighs more)
+                if (bn > 256 && atoms == 0 && nkb < 48) continue;
                 const uint32_t n_tiles = ceil_div_u32(d.n, bn);
                 const uint64_t tiles = m_tiles * n_tiles * split;
                 const uint64_t waves = (tiles + units - 1) / units;
@@ -561,7 +566,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     if (is_fp4_pair(d)) a.idesc |= (1u << 7) | (1u << 10);       // kind::mxf4: both operand formats E2M1
     if (is_bf16_pair(d))                                         // kind::f16: FP32 accumulator, BF16 operands, no scale fields
         a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) |
-                  ((c.block_n >> 3) << 17) | (((kBlockM * c.cta_group) >> 4) << 24);
+                  (((c.block_n / tile_halves(c.block_n)) >> 3) << 17) | (((kBlockM * c.cta_group) >> 4) << 24);
 
     plan.cta_group = (int)c.cta_group;
     plan.major_a = d.major_a;

@@ -63,6 +63,7 @@ using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMa
 static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode_b, bool lean, bool fp4_pair, bool bf16_pair,
                             bool wide_epi, bool simple_epi, bool wide_tile) {
     if (wide_tile && fp4_pair) return mx_gemm_kernel<2, 0, 0, false, false, true, false, false, false, true>;
+    if (wide_tile && bf16_pair) return mx_gemm_kernel<2, 0, 0, false, false, false, true, false, false, true>;
     if (wide_tile)          // E4M3 x E4M3, K-major operands, CTA pair, block_n > 256
         return simple_epi ? mx_gemm_kernel<2, 0, 0, false, false, false, false, false, true, true>
                           : mx_gemm_kernel<2, 0, 0, false, false, false, false, false, false, true>;

@@ -452,8 +452,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t load_n = p.block_n / kCtaGroup;            // rows of B this CTA fetches
     const uint32_t sfb_slabs = sfb_rows(p.block_n) / 128;
     // wide tiles (block_n > 256, K-major 8-bit operands only): two column halves per K step
-    static_assert(!kWideTile || (kCtaGroup == 2 && kMajorA == 0 && kMajorB == 0 && !kDecodeB && !kBf16 && !kLean && !kWideEpi),
-                  "wide tiles: FP8 x FP8 or FP4 x FP4 CTA pairs with K-major operands");
+    static_assert(!kWideTile || (kCtaGroup == 2 && kMajorA == 0 && kMajorB == 0 && !kDecodeB && !kLean && !kWideEpi),
+                  "wide tiles: CTA pairs with K-major operands");
     constexpr uint32_t n_halves = kWideTile ? 2u : 1u;
     const uint32_t half_n = p.block_n / n_halves, load_half = load_n / n_halves, slabs_half = sfb_slabs / n_halves;
 
@@ -637,6 +637,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         else db = make_mnmajor_sw128_desc(sb + k * kMmaKRows * 128, kStageK * 128);
                         if constexpr (kBf16) {
                             umma_f16<kCtaGroup>(tmem_d, da, db, p.idesc, (kb > t.kb_begin || k > 0) ? 1u : 0u);
+                            if constexpr (kWideTile)      // second column half: its own rows of B
+                                umma_f16<kCtaGroup>(tmem_d + half_n, da, make_kmajor_sw128_desc(sb + load_half * kBlockK + k * kUmmaK),
+                                                    p.idesc, (kb > t.kb_begin || k > 0) ? 1u : 0u);
                         } else if constexpr (kFp4) {
                             // instruction k reads 64 K-elements: scale bytes 2(k&1), 2(k&1)+1 of word k/2
                             const uint32_t id = (k & 1u) * 2u, g = k >> 1;

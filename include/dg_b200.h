@@ -118,7 +118,7 @@ typedef struct {
 /* Tiling chosen for a problem. Replaces GemmConfig, csrc/jit_kernels/gemm_config.hpp:98-121. */
 typedef struct {
     uint32_t block_m, block_n, block_k;   /* block_m = 128 x cta_group, block_k = 128 bytes of K; block_n a multiple of 32 up to 256,
-                                           * or 320 / 384 / 448 (CTA pairs, E4M3 x E4M3 or E2M1 x E2M1, K-major operands): a wide
+                                           * or 320 / 384 / 448 (CTA pairs, E4M3 x E4M3, E2M1 x E2M1 or BF16 x BF16 (also 512), K-major operands): a wide
                                            * tile computed as two column halves per K step that share the A tile */
     uint32_t num_stages;
     uint32_t cta_group;       /* 1, or 2 = two CTAs of a cluster share one 256-row UMMA */

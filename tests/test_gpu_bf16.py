@@ -58,6 +58,12 @@ def test_dense_tilings():
     _dense(512, 512, 1024, trans='tn', config={'cta_group': 1, 'block_n': 64})
     _dense(128, 512, 4096, config={'block_n': 128, 'split_k': 4})
     _dense(128, 512, 4096, config={'block_n': 128, 'split_k': 4, 'cluster_split': 1})
+    # wide tiles: two column halves per K step sharing the A tile; without scale columns TMEM holds 2 x 256
+    for bn in (320, 384, 448, 512):
+        _dense(512, 1100, 1024, config={'cta_group': 2, 'block_n': bn})
+        _dense(300, 2 * bn + 8, 512, config={'cta_group': 2, 'block_n': bn}, out=torch.float32, acc=True)
+    with pytest.raises(RuntimeError):
+        _dense(512, 1024, 1024, trans='nn', config={'cta_group': 2, 'block_n': 320})
 
 
 def test_golden_fixtures(golden):
