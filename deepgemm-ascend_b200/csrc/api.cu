@@ -351,7 +351,8 @@ static double k_block_cycles(uint32_t cta_group, uint32_t bn, bool packed_b = fa
 static double tile_main_cycles(uint32_t cta_group, uint32_t bn, uint32_t k_blocks, uint32_t atoms, uint32_t d_elem_bytes, bool packed_b) {
     const double mma = (atoms == 2 ? 1.0 : 2.0) * bn * k_blocks;      // (kind::mxf4 runs a 128-byte K block in half the cycles)
     const double per_kb = (128.0 + (double)bn / cta_group / (packed_b ? 2 : 1)) * 128.0 + (128.0 + sfb_rows(bn)) * 4.0 * atoms;
-    const double ingest = (per_kb * k_blocks + 128.0 * bn * d_elem_bytes) / 58.0;
+    // (a wide tile keeps four or five 40-46 KB stages in flight instead of six 32 KB ones and measures nearer 55)
+    const double ingest = (per_kb * k_blocks + 128.0 * bn * d_elem_bytes) / (bn > 256 ? 55.0 : 58.0);
     const double decode = packed_b ? 2.5 * bn / cta_group * k_blocks : 0.0;
     double t = mma > ingest ? mma : ingest;
     return t > decode ? t : decode;
