@@ -88,3 +88,43 @@ def test_fp8_output_rules():
         deep_gemm.fp8_bmm((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), (d, sfd))
     with pytest.raises(RuntimeError, match='Unsupported einsum expression'):
         deep_gemm.fp8_einsum('bhr,hrd->bhd', (a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d)
+
+
+def test_wide_tiles_batched_quantised_and_stochastic():
+    """block_n > 256 (two column halves per K step) under the batched scheduler and the two epilogues that work on
+    32-column chunks: FP8-quantised output (bit-exact against quantising the BF16 result) and stochastic rounding
+    (bit-exact against the hash model applied to the FP32 result)."""
+    cfg = {'cta_group': 2, 'block_n': 384}
+    (a, sfa, a_ref), (b, sfb, b_ref) = _batched_operands(3, 300, 800, 512, seed=2)
+    ref = torch.einsum('bmk,bnk->bmn', a_ref, b_ref)
+    d = torch.full((3, 300, 800), float('nan'), dtype=torch.bfloat16, device='cuda')
+    deep_gemm.fp8_bmm((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d, config=cfg)
+    assert deep_gemm.device_status() == 0
+    assert_close(d, ref.bfloat16(), 'bmm wide tile')
+
+    b_, h, r, d_ = 64, 4, 256, 256                                                   # 'bhr,hdr->bhd': N = d_ per head
+    (a, sfa, _), (b, sfb, _) = _batched_operands(h, b_, d_, r, seed=4)
+    a_arg = (a.permute(1, 0, 2).cuda(), sfa.permute(1, 0, 2).cuda())
+    b_arg = (b.cuda(), sfb.cuda())
+    d16 = torch.full((b_, h, d_), float('nan'), dtype=torch.bfloat16, device='cuda')
+    deep_gemm.fp8_einsum('bhr,hdr->bhd', a_arg, b_arg, d16)
+    out8 = torch.zeros((b_, h, d_), dtype=torch.float8_e4m3fn, device='cuda')
+    sfd = torch.empty_strided((b_, h * d_ // 64), (1, b_), dtype=torch.int16, device='cuda')
+    deep_gemm.fp8_einsum('bhr,hdr->bhd', a_arg, b_arg, (out8, sfd), config={'cta_group': 2, 'block_n': 320})
+    assert deep_gemm.device_status() == 0
+    q, sf, _ = oracle.quantize_e4m3(d16.cpu().float().reshape(b_, h * d_), (1, 32))
+    sf_bytes = ((sf.view(torch.int32) >> 23) & 0xFF).reshape(b_, -1, 2)
+    assert torch.equal(out8.cpu().view(torch.uint8).reshape(b_, h * d_), q.view(torch.uint8))
+    assert torch.equal(sfd.contiguous().cpu(), (sf_bytes[..., 0] + sf_bytes[..., 1] * 256).to(torch.int16))
+
+    seed_all(9)
+    a, sfa, _ = uniform_fp8((384, 768), (1, 32))
+    b, sfb, _ = uniform_fp8((900, 768), (1, 32))
+    a_arg, b_arg = (a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda())
+    d32 = torch.empty(384, 900, dtype=torch.float32, device='cuda')
+    deep_gemm.fp8_gemm_nt(a_arg, b_arg, d32, config={'cta_group': 2, 'block_n': 448})
+    d16 = torch.empty(384, 900, dtype=torch.bfloat16, device='cuda')
+    deep_gemm.fp8_gemm_nt(a_arg, b_arg, d16, epilogue=deep_gemm.epilogue.BF16StochasticRounding(),
+                          config={'cta_group': 2, 'block_n': 448})
+    assert deep_gemm.device_status() == 0
+    assert torch.equal(d16.cpu().view(torch.int16), oracle.stochastic_round_bf16(d32).view(torch.int16))
