@@ -581,6 +581,14 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.epi_simple = (d.epilogue == DG_EPILOGUE_IDENTITY && !a.has_alpha && !a.has_bias && !a.stochastic &&
                     c.epilogue_mode <= kEpiTmaReduce && !splits_in_cluster(c) && !feature_disabled("straight")) ? 1u : 0u;
     plan.wide_tile = c.block_n > 256;
+    {
+        // Wide tiles, dense: when the last wave of tiles fills at most half of the CTA pairs, its tiles are handed out
+        // as single column halves (two work items per tile), which makes that wave half as long.
+        const uint32_t tiles = a.num_m_blocks * a.num_n_blocks, units = c.num_ctas / c.cta_group;
+        const uint32_t rem = tiles % units;
+        a.half_from = (plan.wide_tile && d.gemm_type == DG_GEMM_NORMAL && c.split_k == 1 && tiles > units && rem > 0 && 2 * rem <= units &&
+                       !feature_disabled("half_tiles")) ? tiles - rem : tiles;
+    }
     plan.simple_epi = !plan.lean && !plan.decode_b && !plan.fp4_pair && !plan.bf16_pair && d.major_a == DG_MAJOR_K && d.major_b == DG_MAJOR_K &&
                       !a.d_is_fp32 && d.epilogue == DG_EPILOGUE_IDENTITY && !a.has_alpha && !a.has_bias && !a.stochastic &&
                       c.epilogue_mode <= kEpiTmaReduce && !splits_in_cluster(c) && !feature_disabled("simple");

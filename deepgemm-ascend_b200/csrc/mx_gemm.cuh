@@ -65,6 +65,7 @@ struct GemmKernelArgs {
     uint64_t magic_per_group, magic_rows_full, magic_rows_last, magic_n_blocks;
     uint32_t epilogue_mode;
     uint32_t d_is_fp32;
+    uint32_t half_from;   // wide tiles, dense: tiles from this index on (the last, partial wave) run as two half tiles
     uint32_t epi_simple;  // nothing but cast (or FP32) + staged TMA store / reduce: the epilogue takes its short loop
     uint32_t has_bias, has_alpha;
     uint32_t stochastic;              // BF16 output is rounded stochastically instead of to nearest
@@ -149,6 +150,7 @@ struct Tile {
     uint32_t row0;        // first row of this CTA in A / SFA / D (within the group for masked)
     uint32_t row_z;       // third TMA coordinate of A / SFA (group for masked / batched, else 0)
     uint32_t d_z;         // third TMA coordinate of D (as row_z, but the group for the K-grouped layout)
+    uint32_t halves;      // wide tiles: bit h set = column half h of the tile is computed (3 = the whole tile)
     uint32_t n0;          // first column of D == first row of B
     uint32_t b_z;         // third TMA coordinate of B / SFB (group)
     uint32_t kb_begin, kb_end;
@@ -163,7 +165,7 @@ __host__ __device__ __forceinline__ uint64_t fast_div_magic(uint32_t d) { return
 __device__ __forceinline__ uint32_t fast_div(uint32_t n, uint64_t magic) { return (uint32_t)(((uint64_t)n * magic) >> 40); }
 
 // kLean: dense GEMM only (the other layouts are compiled out).
-template <int kCtaGroup, bool kLean = false>
+template <int kCtaGroup, bool kLean = false, bool kWideTile = false>
 struct Scheduler {
     const GemmKernelArgs& p;
     uint32_t tile, stride;
@@ -207,10 +209,21 @@ struct Scheduler {
 
     __device__ bool next(Tile& t) {
         const uint32_t rank = kCtaGroup == 2 ? (blockIdx.x & 1u) : 0u;
+        if constexpr (kWideTile) t.halves = 3u;
         if (kLean || p.gemm_type == kNormal) {
             const uint32_t total = p.num_m_blocks * p.num_n_blocks * p.split_k;
-            if (tile >= total) return false;
             uint32_t ks = 0, mn = tile;
+            if constexpr (kWideTile) {
+                // The tiles of the last, partial wave are handed out as single column halves, two indices per tile, so
+                // that twice as many CTA pairs share that wave and it takes half as long.
+                if (tile >= total + (total - p.half_from)) return false;
+                if (tile >= p.half_from) {
+                    t.halves = 1u << ((tile - p.half_from) & 1u);
+                    mn = p.half_from + ((tile - p.half_from) >> 1);
+                }
+            } else {
+                if (tile >= total) return false;
+            }
             if (p.split_k > 1) { mn = tile / p.split_k; ks = tile - mn * p.split_k; }
             const uint32_t per_group = p.raster_group * p.num_n_blocks;
             const uint32_t gi = fast_div(mn, p.magic_per_group), in_group = mn - gi * per_group;
@@ -511,7 +524,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         // ======================================================================== TMA producer
         if (lane == 0) {        // the thread that initialised the barriers
             trace_mark(p, 8);
-            Scheduler<kCtaGroup, kLean> sched(p);
+            Scheduler<kCtaGroup, kLean, kWideTile> sched(p);
             Tile t;
             uint32_t stage = 0, phase = 0;
             bool ok = true, first_issue = true, ring_used = false;
@@ -526,11 +539,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     const uint32_t bar = full_bar(stage);
                     // The operands and the (much smaller) scale columns complete on barriers of their own, so that the
                     // scales are usually packed by the time the last operand byte lands.
-                    const uint32_t bytes = L.a_stage + (kDecodeB ? L.b_raw_stage : load_n * kBlockK);
+                    // (half tiles of a wide-tile launch fetch one half's rows of B and scale columns only)
+                    const uint32_t act_halves = kWideTile ? (t.halves == 3u ? 2u : 1u) : 1u;
+                    const uint32_t bytes = L.a_stage + (kDecodeB ? L.b_raw_stage : kWideTile ? act_halves * load_half * kBlockK : load_n * kBlockK);
                     static_assert(!kBf16 || !kDecodeB, "BF16 operands are never decoded");
                     mbar_arrive_expect_tx(bar, bytes);
                     const uint32_t sf_bar = sf_tma_bar(stage);
-                    if constexpr (!kBf16) mbar_arrive_expect_tx(sf_bar, L.sfa_stage + L.sfb_stage);
+                    if constexpr (!kBf16) mbar_arrive_expect_tx(sf_bar, L.sfa_stage + (kWideTile ? act_halves * (L.sfb_stage / 2) : L.sfb_stage));
                     if (first_issue) { trace_mark(p, 3); first_issue = false; }
                     const uint32_t sa = smem_base + L.a + stage * L.a_stage;
                     const uint32_t sb = smem_base + L.b + stage * L.b_stage;
@@ -552,8 +567,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     } else if constexpr (kMajorB == 0) {
                         // (in a CTA pair every half is split between the two CTAs, as its MMA expects)
                         for (uint32_t h = 0; h < n_halves; ++h)
-                            tma_load_3d(sb + h * load_half * kBlockK, &tm_b, bar, k0,
-                                        (int32_t)(t.n0 + h * half_n + cta_rank * load_half), (int32_t)t.b_z);
+                            if (!kWideTile || ((t.halves >> h) & 1u))
+                                tma_load_3d(sb + h * load_half * kBlockK, &tm_b, bar, k0,
+                                            (int32_t)(t.n0 + h * half_n + cta_rank * load_half), (int32_t)t.b_z);
                     } else {
                         // one box per 128-byte atom along N: [atom][K rows of the stage][128 B]
                         for (uint32_t a0 = 0; a0 < load_n; a0 += kAtomMn)
@@ -564,8 +580,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         tma_load_3d(smem_base + L.sf_raw_a + stage * L.sfa_stage, &tm_sfa, sf_bar,
                                     (int32_t)t.row0, (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.row_z);
                         for (uint32_t h = 0; h < n_halves; ++h)
-                            tma_load_3d(smem_base + L.sf_raw_b + stage * L.sfb_stage + h * (L.sfb_stage / n_halves), &tm_sfb, sf_bar,
-                                        (int32_t)(t.n0 + h * half_n), (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.b_z);
+                            if (!kWideTile || ((t.halves >> h) & 1u))
+                                tma_load_3d(smem_base + L.sf_raw_b + stage * L.sfb_stage + h * (L.sfb_stage / n_halves), &tm_sfb, sf_bar,
+                                            (int32_t)(t.n0 + h * half_n), (int32_t)(kb * 2 * kSfAtoms), (int32_t)t.b_z);
                     }
                     if (i == 0) trace_mark(p, 12);
                     if (++stage == num_stages) { stage = 0; phase ^= 1; ring_used = true; }
@@ -583,7 +600,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     } else if (warp == 1) {
         // ======================================================================== MMA issuer
         if (is_leader && elect_one()) {
-            Scheduler<kCtaGroup, kLean> sched(p);
+            Scheduler<kCtaGroup, kLean, kWideTile> sched(p);
             Tile t;
             uint32_t stage = 0, phase = 0, tile_iter = 0;
             bool ok = true;
@@ -626,6 +643,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                     const uint32_t sa = smem_base + L.a + stage * L.a_stage;
                     const uint32_t sb = smem_base + L.b + stage * L.b_stage;
+                    const bool first_half = !kWideTile || (t.halves & 1u), second_half = kWideTile && (t.halves & 2u);   // (half tiles of the last wave)
                     #pragma unroll
                     for (uint32_t k = 0; k < kBlockK / kUmmaK; ++k) {
                         // every instruction consumes 32 bytes of K per row: 32 FP8, 64 FP4 or 16 BF16 elements
@@ -636,24 +654,26 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         if constexpr (kMajorB == 0) db = make_kmajor_sw128_desc(sb + k * kUmmaK);
                         else db = make_mnmajor_sw128_desc(sb + k * kMmaKRows * 128, kStageK * 128);
                         if constexpr (kBf16) {
-                            umma_f16<kCtaGroup>(tmem_d, da, db, p.idesc, (kb > t.kb_begin || k > 0) ? 1u : 0u);
-                            if constexpr (kWideTile)      // second column half: its own rows of B
+                            if (first_half) umma_f16<kCtaGroup>(tmem_d, da, db, p.idesc, (kb > t.kb_begin || k > 0) ? 1u : 0u);
+                            if (second_half)              // second column half: its own rows of B
                                 umma_f16<kCtaGroup>(tmem_d + half_n, da, make_kmajor_sw128_desc(sb + load_half * kBlockK + k * kUmmaK),
                                                     p.idesc, (kb > t.kb_begin || k > 0) ? 1u : 0u);
                         } else if constexpr (kFp4) {
                             // instruction k reads 64 K-elements: scale bytes 2(k&1), 2(k&1)+1 of word k/2
                             const uint32_t id = (k & 1u) * 2u, g = k >> 1;
-                            umma_mxf4<kCtaGroup>(tmem_d, da, db, p.idesc | (id << 4) | (id << 29), tmem_sfa + g * 4,
-                                                 tmem_sfb + g * sfb_slabs * 4, (kb > t.kb_begin || k > 0) ? 1u : 0u);
-                            if constexpr (kWideTile)      // second column half: its own rows of B and scale slabs
+                            if (first_half)
+                                umma_mxf4<kCtaGroup>(tmem_d, da, db, p.idesc | (id << 4) | (id << 29), tmem_sfa + g * 4,
+                                                     tmem_sfb + g * sfb_slabs * 4, (kb > t.kb_begin || k > 0) ? 1u : 0u);
+                            if (second_half)              // second column half: its own rows of B and scale slabs
                                 umma_mxf4<kCtaGroup>(tmem_d + half_n, da, make_kmajor_sw128_desc(sb + load_half * kBlockK + k * kUmmaK),
                                                      p.idesc | (id << 4) | (id << 29), tmem_sfa + g * 4,
                                                      tmem_sfb + (g * sfb_slabs + slabs_half) * 4, (kb > t.kb_begin || k > 0) ? 1u : 0u);
                         } else {
                             const uint32_t idesc = p.idesc | (k << 4) | (k << 29);   // scale ids of B and of A
-                            umma_mxf8f6f4<kCtaGroup>(tmem_d, da, db, idesc, tmem_sfa, tmem_sfb,
-                                                     (kb > t.kb_begin || k > 0) ? 1u : 0u);
-                            if constexpr (kWideTile) {
+                            if (first_half)
+                                umma_mxf8f6f4<kCtaGroup>(tmem_d, da, db, idesc, tmem_sfa, tmem_sfb,
+                                                         (kb > t.kb_begin || k > 0) ? 1u : 0u);
+                            if (second_half) {
                                 // second column half of a wide tile: its own rows of B, scale slabs and accumulator columns
                                 umma_mxf8f6f4<kCtaGroup>(tmem_d + half_n, da, make_kmajor_sw128_desc(sb + load_half * kBlockK + k * kUmmaK),
                                                              idesc, tmem_sfa, tmem_sfb + slabs_half * 4,
@@ -681,7 +701,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         // ======================================================================== scale-factor packer
         // raw slab (TMA): [2 K64 columns][rows] int16  ->  packed: [32][4] uint32, entry [l][j] = the four
         // UE8M0 bytes (K blocks 0..3 of this stage) of row j*32+l.
-        Scheduler<kCtaGroup, kLean> sched(p);
+        Scheduler<kCtaGroup, kLean, kWideTile> sched(p);
         Tile t;
         uint32_t stage = 0, phase = 0;
         bool ok = true;
@@ -744,7 +764,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     } else if (kDecodeB && warp >= 8) {
         // ======================================================================== FP4 decoders
         // One work item = 8 packed bytes (16 codes) -> one 16-byte chunk of the swizzled E4M3 tile.
-        Scheduler<kCtaGroup, kLean> sched(p);
+        Scheduler<kCtaGroup, kLean, kWideTile> sched(p);
         Tile t;
         uint32_t stage = 0, phase = 0;
         bool ok = true;
@@ -787,7 +807,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const uint32_t q = warp % 4;                         // TMEM lane quadrant == warp index % 4
         const uint32_t col_half = (warp - 4) / 4;            // wide epilogue: which 64-column groups this warp takes
         constexpr uint32_t kColStep = kWideEpi ? 128u : 64u;
-        Scheduler<kCtaGroup, kLean> sched(p);
+        Scheduler<kCtaGroup, kLean, kWideTile> sched(p);
         Tile t;
         uint32_t tile_iter = 0, buf = 0;
         bool ok = true;
@@ -808,6 +828,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             tc_fence_after_sync();
             const uint32_t row = t.row0 + q * 32 + lane;       // row of D held by this thread
             const uint32_t taddr = tmem_base + ((q * 32u) << 16) + e * p.block_n;
+            // columns of the tile this launch of the epilogue covers (a half tile of a wide-tile launch: one half)
+            const uint32_t col_begin = (kWideTile && t.halves == 2u) ? half_n : 0u;
+            const uint32_t col_end = (kWideTile && t.halves == 1u) ? half_n : p.block_n;
 
             // One 32-column chunk of this thread's row: alpha / bias, cast, stage, store.
             // `single`: the chunk goes out on its own (BF16 boxes normally pair two chunks).
@@ -895,7 +918,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     // 32-column groups; when block_n is an odd multiple of 32 the last group goes out alone as a
                     // [32 rows x 64 B] box (64B swizzle: chunk c of row r at c ^ ((r >> 1) & 3)) through tm_d_tail.
                     const uint32_t half = (out_is_fp32() || single) ? 0u : ((c0 / 32) & 1u);
-                    const bool tail = !out_is_fp32() && half == 0 && (single || c0 + 32 >= p.block_n);
+                    const bool tail = !out_is_fp32() && half == 0 && (single || c0 + 32 >= col_end);
                     EPI_T(tp1); EPI_ACC(1, tp0, tp1);
                     if (half == 0) {
                         // the buffer may still be read by the store issued `store_bufs` boxes ago
@@ -1053,9 +1076,16 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             // With plain stores the columns of the tile that lie beyond N are not even read (the staged TMA boxes are
             // clipped by the hardware instead).
             const bool plain = !kSimpleEpi && (kLean || p.epilogue_mode == kEpiPlainStore || p.epilogue_mode == kEpiPlainAtomic);
-            const uint32_t cols = plain ? min(p.block_n, (p.n - t.n0 + 31u) & ~31u) : p.block_n;
-            const uint32_t c_first = col_half * 64;
+            const uint32_t cols = plain ? min(col_end, (p.n - t.n0 + 31u) & ~31u) : col_end;
             auto run_chunks = [&](auto simple_tag) {
+                uint32_t c_first = kWideTile ? col_begin : col_half * 64;
+                if (kWideTile && (c_first & 32u) && c_first < cols) {
+                    // a second half that starts on an odd 32-column chunk: that chunk goes out on its own, the rest in pairs
+                    tmem_ld_32x32b_x32(taddr + c_first, va);
+                    tmem_ld_wait();
+                    process_chunk(simple_tag, va, c_first, true);
+                    c_first += 32;
+                }
                 if (c_first < cols) tmem_ld_32x32b_x32(taddr + c_first, va);
                 for (uint32_t c0 = c_first; c0 < cols; c0 += kColStep) {
                     EPI_T(tl0);

@@ -473,3 +473,23 @@ def test_fp4_pair_wide_tiles():
         _fp4_pair(512, 1024, 1024, config={'cta_group': 2, 'block_n': bn})
         _fp4_pair(300, 1000, 768, config={'cta_group': 2, 'block_n': bn}, out=torch.float32)
     _fp4_pair(4096, 7168, 4096)          # the heuristic takes a wide tile here
+
+
+@pytest.mark.parametrize('bn,n', [(448, 7168), (320, 6080), (384, 5376)])
+def test_dense_wide_tiles_last_wave_in_halves(bn, n):
+    """A wide-tile launch whose last wave fills at most half of the CTA pairs (16 x n / bn tiles on 74 pairs) hands
+    that wave's tiles out as single column halves: same results, bit for bit, as with whole tiles."""
+    cfg = {'cta_group': 2, 'block_n': bn}
+    _dense(4096, n, 256, config=cfg)
+    _dense(4096, n - 24, 384, config=cfg, out=torch.float32, acc=True)
+    _dense(4096, n, 128, config=cfg, bias=True)
+    seed_all(11)
+    a, sfa, _ = uniform_fp8((4096, 512), (1, 32))
+    b, sfb, _ = uniform_fp8((n, 512), (1, 32))
+    outs = []
+    for c in (cfg, {'cta_group': 2, 'block_n': 224}):
+        d = torch.full((4096, n), float('nan'), dtype=torch.bfloat16, device='cuda')
+        deep_gemm.fp8_gemm_nt((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d, config=c)
+        outs.append(d)
+    assert deep_gemm.device_status() == 0
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
