@@ -190,9 +190,10 @@ static bool wide_epilogue(const dg_gemm_config_t& c) { return c.reserved[5] == 2
 
 // Two ways to split K: partial sums reduced into an FP32 workspace that a second kernel casts (reserved[3] == 0), or
 // the splits of one tile form a thread-block cluster and reduce through shared memory (reserved[3] == 1).
-// DG_DISABLE=lean,cluster,wide,simple,tma_store (debugging aid for A/B timing): keeps the heuristic away from cluster
-// split-K, from eight epilogue warps, from TMA stores (plain stores instead), and / or the launch away from the lean
-// kernel instantiations. Every alternative computes the same values.
+// DG_DISABLE=lean,cluster,wide,simple,straight,wide_tile,half_tiles,tma_store (debugging aid for A/B timing): keeps the
+// heuristic away from cluster split-K, from eight epilogue warps, from wide tiles or from half tiles in their last wave,
+// from TMA stores (plain stores instead), and / or the launch away from the lean and the cast-and-store-only kernel
+// instantiations or from the short chunk loop. Every alternative computes the same values.
 static bool feature_disabled(const char* name) {
     static const std::string list = [] { const char* e = getenv("DG_DISABLE"); return std::string(e ? e : ""); }();
     return list.find(name) != std::string::npos;
