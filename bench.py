@@ -378,7 +378,7 @@ def run_dense(args, rank, world, device):
                               % args.steps if graph is not None else 'one CUDA-event pair around the steps, plain stream launches')
                              + '; per-shape and roofline figures from a second pass with one event pair per launch'},
         'roofline': {'bound': 'tensor', 'achieved': tf_big, 'peak': fp8_peak, 'unit': 'TFLOP/s', 'frac': tf_big / fp8_peak,
-                     'traffic': 512.7e6, 'traffic_of': 'dram__bytes_read.sum + dram__bytes_write.sum of the 4096x7168x16384 launch '
+                     'traffic': 489.5e6, 'traffic_of': 'dram__bytes_read.sum + dram__bytes_write.sum of the 4096x7168x16384 launch '
                      '(ncu capture in profiles/mx_gemm_wide_tile_pair.md; algorithmic 249.0 MB)',
                      'kernel': 'mx_gemm_kernel on the six M=4096 launches',
                      'peak_source': '2 x bf16 burst of MEASURED_PEAKS.json (%s)' % pk['source']},
