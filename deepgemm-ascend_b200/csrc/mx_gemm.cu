@@ -11,8 +11,9 @@
 
 namespace dg {
 
-// Device status word: 0, or the code of the first bounded wait that gave up.
-__device__ int32_t g_device_status;
+// Device status word: 0, or the code of the first bounded wait that gave up (zero from module load on: nothing has
+// to be cleared, and so nothing synchronises, before the first launch on a device).
+__device__ int32_t g_device_status = 0;
 
 // Split-K finalisation: D = cast(workspace (+ bias)) or D += workspace, and the workspace is zeroed
 // again so that the next launch can reduce into it without a memset.
@@ -104,6 +105,11 @@ static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode
     return table[cta_group - 1][major_a][major_b][decode_b ? 1 : 0];
 }
 
+// Caller-owned trace buffers, one per device (see dg_debug_set_trace_buffer).
+static std::mutex g_trace_mu;
+static unsigned long long* g_trace_buf[64] = {};
+static size_t g_trace_bytes[64] = {};
+
 int get_status_pointer(int32_t** out) {
     static std::mutex mu;
     static int32_t* ptrs[64] = {};
@@ -114,7 +120,6 @@ int get_status_pointer(int32_t** out) {
     if (ptrs[dev] == nullptr) {
         void* p = nullptr;
         DG_CHECK_CUDA(cudaGetSymbolAddress(&p, g_device_status));
-        DG_CHECK_CUDA(cudaMemset(p, 0, sizeof(int32_t)));
         ptrs[dev] = static_cast<int32_t*>(p);
     }
     *out = ptrs[dev];
@@ -127,15 +132,15 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
     DG_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem_bytes));
 
     GemmKernelArgs args = plan.args;
-    DG_CHECK_ARG(get_status_pointer(&args.status) == DG_OK, "%s", dg_last_error());
+    if (int rc = get_status_pointer(&args.status)) return rc;
 
-    // DG_TRACE=1 (debugging only): the launch becomes synchronous and prints where each CTA spent its time.
-    static const bool trace_enabled = [] { const char* e = getenv("DG_TRACE"); return e && atoi(e) != 0; }();
-    static unsigned long long* trace_buf = nullptr;
-    if (trace_enabled) {
-        if (trace_buf == nullptr) DG_CHECK_CUDA(cudaMalloc(&trace_buf, 2048 * 16 * sizeof(unsigned long long)));
-        DG_CHECK_CUDA(cudaMemsetAsync(trace_buf, 0, 2048 * 16 * sizeof(unsigned long long), stream));
-        args.trace = trace_buf;
+    // Debugging aid: per-CTA timestamps go to a buffer the caller handed over (dg_debug_set_trace_buffer), if any.
+    {
+        int dev = 0;
+        DG_CHECK_CUDA(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> lock(g_trace_mu);
+        args.trace = (dev >= 0 && dev < 64 && g_trace_bytes[dev] >= (size_t)plan.num_ctas * 16 * sizeof(unsigned long long))
+                         ? g_trace_buf[dev] : nullptr;
     }
 
     if (plan.zero_empty_groups) {
@@ -187,44 +192,6 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
     }
     DG_CHECK_CUDA(cudaLaunchKernelEx(&cfg, fn, plan.tm_a, plan.tm_b, plan.tm_sfa, plan.tm_sfb, plan.tm_d, plan.tm_d_tail, args));
     count_kernel_launch();
-    if (trace_enabled) {
-        DG_CHECK_CUDA(cudaStreamSynchronize(stream));
-        static unsigned long long host[1024 * 16];
-        const uint32_t n = grid < 1024 ? grid : 1024;
-        DG_CHECK_CUDA(cudaMemcpy(host, trace_buf, n * 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
-        unsigned long long t0 = ~0ull, t1 = 0;
-        double sum[16] = {0}, mx[16] = {0};
-        for (uint32_t i = 0; i < n; ++i) {
-            if (host[i * 16] < t0) t0 = host[i * 16];
-            if (host[i * 16] > t1) t1 = host[i * 16];
-            for (int j = 2; j < 16; ++j) {
-                const double d = host[i * 16 + j] ? (double)(host[i * 16 + j] - host[i * 16 + 1]) : 0.0;
-                sum[j] += d; if (d > mx[j]) mx[j] = d;
-            }
-        }
-        fprintf(stderr, "[dg_trace] producer: role-start %.0f sched %.0f wait %.0f ab-issued %.0f stage0-issued %.0f | epilogue: sent %.0f reduce-ready %.0f chunks-done %.0f\n",
-                sum[8] / n, sum[9] / n, sum[10] / n, sum[11] / n, sum[12] / n, sum[13] / n, sum[14] / n, sum[15] / n);
-        fprintf(stderr, "[dg_trace] m=%u n=%u k=%u bn=%u cg=%d split=%u ctas=%u start-skew=%.2f us | cycles since entry avg/max: "
-                "setup %.0f/%.0f  first-tma %.0f/%.0f  first-data %.0f/%.0f  last-mma %.0f/%.0f  first-acc %.0f/%.0f  epi-done %.0f/%.0f\n",
-                args.m, args.n, args.k, args.block_n, plan.cta_group, args.split_k, grid, (t1 - t0) / 1e3,
-                sum[2] / n, mx[2], sum[3] / n, mx[3], sum[4] / n, mx[4], sum[5] / n, mx[5], sum[6] / n, mx[6], sum[7] / n, mx[7]);
-    }
-
-#ifdef DG_EPI_PROF
-    if (trace_enabled) {
-        static unsigned long long h2[1024 * 16];
-        const uint32_t n = grid < 1024 ? grid : 1024;
-        DG_CHECK_CUDA(cudaMemcpy(h2, trace_buf + 1024 * 16, n * 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
-        double s[16] = {0};
-        for (uint32_t i = 0; i < n; ++i) for (int j = 0; j < 16; ++j) s[j] += (double)h2[i * 16 + j];
-        const double ch = s[8] > 0 ? s[8] : 1, tl = s[12] > 0 ? s[12] : 1;
-        fprintf(stderr, "[dg_epi] tiles/cta %.1f chunks/tile %.1f | per chunk: ldissue %.0f ldwait %.0f pre %.0f cvt %.0f math %.0f storewait %.0f stsmem %.0f | per box-ish (per chunk avg): fence %.0f issue %.0f | per tile: accwait %.0f epilogue %.0f\n",
-                tl / n, ch / tl, s[10] / ch, s[0] / ch, s[11] / ch, s[9] / ch, s[1] / ch, s[2] / ch, s[3] / ch, s[4] / ch, s[5] / ch, s[6] / tl, s[7] / tl);
-        const double tiles_lead = tl / plan.cta_group;
-        fprintf(stderr, "[dg_mma] per tile: accumulator-free wait %.0f  data wait %.0f (first K block %.0f)\n",
-                s[13] / tiles_lead, s[14] / tiles_lead, s[15] / tiles_lead);
-    }
-#endif
     if (plan.finalize) {
         const uint64_t total = (uint64_t)plan.args.m * ((plan.args.n + 3) / 4);
         const uint32_t grid = (uint32_t)((total + 255) / 256 < 148ull * 8 ? (total + 255) / 256 : 148ull * 8);
@@ -238,6 +205,17 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
 }
 
 }  // namespace dg
+
+extern "C" int dg_debug_set_trace_buffer(void* device_buffer, size_t bytes) {
+    int dev = 0;
+    DG_CHECK_CUDA(cudaGetDevice(&dev));
+    DG_CHECK_ARG(dev >= 0 && dev < 64, "device index out of range");
+    DG_CHECK_ARG((reinterpret_cast<uintptr_t>(device_buffer) & 7) == 0, "the trace buffer must be 8-byte aligned");
+    std::lock_guard<std::mutex> lock(dg::g_trace_mu);
+    dg::g_trace_buf[dev] = static_cast<unsigned long long*>(device_buffer);
+    dg::g_trace_bytes[dev] = device_buffer ? bytes : 0;
+    return DG_OK;
+}
 
 extern "C" int dg_device_status(int32_t* out_status) {
     DG_CHECK_ARG(out_status != nullptr, "dg_device_status: null output");

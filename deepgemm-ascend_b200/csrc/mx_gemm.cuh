@@ -127,18 +127,6 @@ __device__ __forceinline__ bool wait_barrier_cluster(uint32_t bar, uint32_t pari
 // requested, first operands landed (MMA side), last MMA committed, first accumulator ready (epilogue side), epilogue
 // done; 8..12 producer: role entered, first tile known, first stage free, A and B requested, first stage requested;
 // 13..15 epilogue: partial sums sent (cluster split-K), partial sums received, all chunks of the first tile written.
-// -DDG_EPI_PROF (a build for measuring, never the shipped one): the first epilogue warp and the MMA thread of every CTA
-// add up, over all tiles, the clock cycles they spend in each phase (waiting for TMEM loads, converting, waiting for
-// a staging box, writing it, proxy fence, issuing the store; waiting for an accumulator or for operands), and a
-// launch with DG_TRACE=1 prints the averages.
-#ifdef DG_EPI_PROF
-__device__ __forceinline__ uint32_t rdclk() { uint32_t x; asm volatile("mov.u32 %0, %%clock;" : "=r"(x) :: "memory"); return x; }
-#define EPI_T(var) const uint32_t var = rdclk()
-#define EPI_ACC(i, a, b) prof[i] += (b) - (a)
-#else
-#define EPI_T(var)
-#define EPI_ACC(i, a, b)
-#endif
 __device__ __forceinline__ void trace_mark(const GemmKernelArgs& p, uint32_t slot) {
     if (p.trace != nullptr) p.trace[blockIdx.x * 16 + slot] = slot == 0 ? global_timer_ns() : (unsigned long long)clock64();
 }
@@ -604,31 +592,21 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             Tile t;
             uint32_t stage = 0, phase = 0, tile_iter = 0;
             bool ok = true;
-#ifdef DG_EPI_PROF
-            uint32_t prof[4] = {0, 0, 0, 0};
-#endif
             while (ok && sched.next(t)) {
                 const uint32_t e = p.accum_stages == 2 ? (tile_iter & 1u) : 0u;
                 const uint32_t e_phase = p.accum_stages == 2 ? ((tile_iter >> 1) & 1u) : (tile_iter & 1u);
-                EPI_T(tm0);
                 // the epilogue(s) must have drained this accumulator
                 if (kCtaGroup == 2) ok = wait_barrier_cluster(tmem_empty_bar(e), e_phase ^ 1, ab, kStatusTimeoutMma);
                 else ok = wait_barrier(tmem_empty_bar(e), e_phase ^ 1, ab, kStatusTimeoutMma);
                 if (!ok) break;
-                EPI_T(tm1); EPI_ACC(0, tm0, tm1);
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + e * p.block_n;
                 for (uint32_t kb = t.kb_begin; kb < t.kb_end; ++kb) {
                     // (BF16: the packer only forwards the arrival of the operands, which in a CTA pair is how the
                     // leader learns that the peer's half has landed too)
-                    EPI_T(tm2);
                     if (kCtaGroup == 2) ok = wait_barrier_cluster(sf_full_bar(stage), phase, ab, kStatusTimeoutMma);
                     else ok = wait_barrier(sf_full_bar(stage), phase, ab, kStatusTimeoutMma);
                     if (!ok) break;
-                    EPI_T(tm3); EPI_ACC(1, tm2, tm3);
-#ifdef DG_EPI_PROF
-                    if (kb == t.kb_begin) prof[2] += tm3 - tm2;
-#endif
                     if (tile_iter == 0 && kb == t.kb_begin) trace_mark(p, 4);
                     tc_fence_after_sync();
                     // scales: smem -> TMEM (A: 128 rows = one slab; B: one slab per 128 columns)
@@ -692,9 +670,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 trace_mark(p, 5);
                 ++tile_iter;
             }
-#ifdef DG_EPI_PROF
-            if (p.trace != nullptr) for (int i = 0; i < 3; ++i) p.trace[(1024 + blockIdx.x) * 16 + 13 + i] = prof[i];
-#endif
         }
         __syncwarp();
     } else if (warp == 2) {
@@ -811,9 +786,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         Tile t;
         uint32_t tile_iter = 0, buf = 0;
         bool ok = true;
-#ifdef DG_EPI_PROF
-        uint32_t prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-#endif
         const uint32_t store_base = smem_base + L.store_bufs + (warp - 4) * p.store_bufs * kStoreBufBytes;
         uint8_t* store_gen = smem_gen + L.store_bufs + (warp - 4) * p.store_bufs * kStoreBufBytes;
         auto out_is_fp32 = [&]() -> bool { return !kSimpleEpi && p.d_is_fp32 != 0; };   // a kernel-argument read, not a register
@@ -821,9 +793,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         while (ok && sched.next(t)) {
             const uint32_t e = p.accum_stages == 2 ? (tile_iter & 1u) : 0u;
             const uint32_t e_phase = p.accum_stages == 2 ? ((tile_iter >> 1) & 1u) : (tile_iter & 1u);
-            EPI_T(tw0);
             if (!(ok = wait_barrier(tmem_full_bar(e), e_phase, ab, kStatusTimeoutEpilogue))) break;
-            EPI_T(tw1); EPI_ACC(6, tw0, tw1);
             if (tile_iter == 0 && threadIdx.x == 128) trace_mark(p, 6);
             tc_fence_after_sync();
             const uint32_t row = t.row0 + q * 32 + lane;       // row of D held by this thread
@@ -839,10 +809,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             auto process_chunk = [&](auto simple_tag, uint32_t (&v)[32], uint32_t c0, bool single) {
                 constexpr bool kSimple = kSimpleEpi || decltype(simple_tag)::value;
                 const uint32_t col0 = t.n0 + c0;
-                EPI_T(tp0);
-#ifdef DG_EPI_PROF
-                prof[8] += 1;
-#endif
                 if (!kLean && !kSimple && p.has_alpha) {
                     #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * p.alpha);
@@ -857,7 +823,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         v[i] = __float_as_uint(__uint_as_float(v[i]) + bv);
                     }
                 }
-                EPI_T(tpa); EPI_ACC(11, tp0, tpa);
                 if (!kLean && !kSimple && p.epilogue_mode == kEpiFp8Quant) {
                     // E4M3 output with one UE8M0 scale per row per 32 columns (exactly this thread's chunk). As the
                     // reference does (operators.hpp:368-411, tests/test_einsum.py:74-84): round to BF16 first, scale =
@@ -912,14 +877,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                 }
                 asm volatile("" :: "r"(w16[0]), "r"(w16[5]), "r"(w16[10]), "r"(w16[15]) : "memory");
-                EPI_T(tpc); EPI_ACC(9, tpa, tpc);
                 if (kSimple || (!kLean && p.epilogue_mode <= kEpiTmaReduce)) {
                     // Stage a [32 rows x 128 B] box, 16-byte chunk c of row r at chunk (c ^ (r & 7)). A BF16 box holds two
                     // 32-column groups; when block_n is an odd multiple of 32 the last group goes out alone as a
                     // [32 rows x 64 B] box (64B swizzle: chunk c of row r at c ^ ((r >> 1) & 3)) through tm_d_tail.
                     const uint32_t half = (out_is_fp32() || single) ? 0u : ((c0 / 32) & 1u);
                     const bool tail = !out_is_fp32() && half == 0 && (single || c0 + 32 >= col_end);
-                    EPI_T(tp1); EPI_ACC(1, tp0, tp1);
                     if (half == 0) {
                         // the buffer may still be read by the store issued `store_bufs` boxes ago
                         if (p.store_bufs == 1) tma_store_wait_read<0>();
@@ -928,7 +891,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         else tma_store_wait_read<3>();
                         __syncwarp();
                     }
-                    EPI_T(tp2); EPI_ACC(2, tp1, tp2);
                     uint8_t* bufp = store_gen + buf * kStoreBufBytes;
                     if (out_is_fp32()) {
                         uint8_t* rowp = bufp + lane * 128;
@@ -945,11 +907,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         }
                     }
                     const bool box_done = out_is_fp32() || half == 1 || tail;
-                    EPI_T(tp3); EPI_ACC(3, tp2, tp3);
                     if (box_done) {
                         fence_proxy_async_smem();
                         __syncwarp();
-                        EPI_T(tp4); EPI_ACC(4, tp3, tp4);
                         if (lane == 0) {
                             const int32_t x = (int32_t)(t.n0 + (tail ? c0 : (out_is_fp32() ? c0 : (c0 & ~63u))));
                             const int32_t y = (int32_t)(t.row0 + q * 32);
@@ -960,10 +920,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                 tma_reduce_add_3d(map, store_base + buf * kStoreBufBytes, x, y, (int32_t)t.d_z);
                             tma_store_commit();
                         }
-#ifdef DG_EPI_PROF
-                        __syncwarp();
-#endif
-                        EPI_T(tp5); EPI_ACC(5, tp4, tp5);
                         if (++buf == p.store_bufs) buf = 0;
                     }
                 } else {
@@ -1088,18 +1044,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
                 if (c_first < cols) tmem_ld_32x32b_x32(taddr + c_first, va);
                 for (uint32_t c0 = c_first; c0 < cols; c0 += kColStep) {
-                    EPI_T(tl0);
                     tmem_ld_wait();
-                    EPI_T(tl1); EPI_ACC(0, tl0, tl1);
                     if (c0 + 32 < cols) tmem_ld_32x32b_x32(taddr + c0 + 32, vb);
-                    EPI_T(tl1b); EPI_ACC(10, tl1, tl1b);
                     process_chunk(simple_tag, va, c0, false);
                     if (c0 + 32 < cols) {
-                        EPI_T(tl2);
                         tmem_ld_wait();
-                        EPI_T(tl3); EPI_ACC(0, tl2, tl3);
                         if (c0 + kColStep < cols) tmem_ld_32x32b_x32(taddr + c0 + kColStep, va);
-                        EPI_T(tl3b); EPI_ACC(10, tl3, tl3b);
                         process_chunk(simple_tag, vb, c0 + 32, false);
                     }
                 }
@@ -1110,7 +1060,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             else if constexpr (!kSimpleEpi) run_chunks(std::false_type{});
             }
             if (tile_iter == 0 && threadIdx.x == 128) trace_mark(p, 15);
-            EPI_T(tw2); EPI_ACC(7, tw1, tw2);
             // this accumulator may be overwritten by the next-but-one tile
             tc_fence_before_sync();
             __syncwarp();
@@ -1123,15 +1072,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         // shared memory must outlive the bulk stores that read it; their global writes complete with the grid
         tma_store_wait_read<0>();
         if (threadIdx.x == 128) trace_mark(p, 7);
-#ifdef DG_EPI_PROF
-        if (threadIdx.x == 128 && p.trace != nullptr) {
-            for (int i = 0; i < 9; ++i) p.trace[(1024 + blockIdx.x) * 16 + i] = prof[i];
-            p.trace[(1024 + blockIdx.x) * 16 + 12] = tile_iter;
-            p.trace[(1024 + blockIdx.x) * 16 + 10] = prof[10];
-            p.trace[(1024 + blockIdx.x) * 16 + 9] = prof[9];
-            p.trace[(1024 + blockIdx.x) * 16 + 11] = prof[11];
-        }
-#endif
     }
 
     // ============================================================================ teardown

@@ -79,3 +79,27 @@ def assert_close(out: torch.Tensor, ref: torch.Tensor, what: str = '') -> tuple[
     assert diff <= COS_TOL, f'{what}: 1-cos = {diff:.3e}'
     assert rel <= REL_TOL, f'{what}: max rel err = {rel:.3e}'
     return diff, rel
+
+
+def assert_close_device(out: torch.Tensor, ref: torch.Tensor, what: str = '') -> tuple[float, float]:
+    """Same two checks as `assert_close` for tensors too large to compare comfortably on the host: `out` stays on
+    its CUDA device, the oracle's `ref` is copied there, and only the metrics (plumbing, not the oracle) are
+    evaluated on the device, in row chunks so that the FP64 temporaries stay small."""
+    assert out.shape == ref.shape, f'{what}: shape {out.shape} vs {ref.shape}'
+    out2, ref2 = out.reshape(-1, out.shape[-1]), ref.reshape(-1, ref.shape[-1])
+    rows = max(1, (1 << 24) // max(1, out2.shape[-1]))
+    dot = sq = 0.0
+    scale = float(ref2.abs().max()) if ref2.numel() else 0.0
+    worst = 0.0
+    for r0 in range(0, out2.shape[0], rows):
+        x = out2[r0:r0 + rows].double()
+        y = ref2[r0:r0 + rows].to(out.device).double()
+        assert torch.isfinite(x).all(), f'{what}: non-finite output'
+        dot += float((x * y).sum())
+        sq += float((x * x + y * y).sum())
+        den = torch.clamp(y.abs(), min=scale / 64) if scale > 0 else torch.ones_like(y)
+        worst = max(worst, float(((x - y).abs() / den).max()))
+    diff = 0.0 if sq == 0 else 1 - 2 * dot / sq
+    assert diff <= COS_TOL, f'{what}: 1-cos = {diff:.3e}'
+    assert worst <= REL_TOL, f'{what}: max rel err = {worst:.3e}'
+    return diff, worst
