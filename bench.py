@@ -1,18 +1,25 @@
 """Benchmark of the block-scaled FP8 GEMM hot path on B200.
 
-One "step" is one pass over the dense FP8 NT sweep named by the baseline: M in {64, 128, 4096} times six (N, K)
-pairs, BF16 output, A quantised per 1x128 and B per 128x128 from N(0,1) data (synthetic, seeded). Every GEMM has its
-own operands, so a step touches about 1.5 GB and no launch finds its inputs in L2. The steps are timed on the device
-with one CUDA-event pair around all of them, each step being one replay of a CUDA graph of the 18 launches; a second
-pass with one event pair per launch gives the per-shape table and the roofline figures.
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload auto|dense|grouped|masked|mixed|fp4|bf16|quant]
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload dense|grouped|masked|mixed|fp4|bf16|quant]
+One GPU (`--workload auto` = `dense`): one "step" is one pass over the dense FP8 NT sweep the baseline names: M in
+{64, 128, 4096} times six (N, K) pairs, BF16 output, A quantised per 1x128 and B per 128x128 from N(0,1) data
+(synthetic, seeded). Every GEMM has its own operands, so a step touches about 1.5 GB and no launch finds its inputs
+in L2. The K steps are K replays of a CUDA graph of the 18 launches between one CUDA-event pair (`value`). Per-shape
+times, and the two roofline figures built from them, come from a second measurement in which every shape is launched
+back to back on rotating operand sets (again larger than L2) as a graph of its own. The same line carries short legs
+for the other three configurations (mixed FP8xFP4, m-grouped contiguous with 32 experts, m-grouped masked), each with
+its own roofline, `e2e` (the sweep through the public Python API from pinned host buffers, copies inside the timed
+region), `cpu_baseline` (the CPU oracle on the host cores over the same 18 shapes) and `verified`: after the timed
+region a row sample of every output is compared with the CPU oracle.
 
-Prints one JSON line (rank 0). `value` is whole-job TFLOP/s with operands resident in HBM; `e2e` is the same metric
-through the public Python API with pinned host buffers, host<->device copies inside the timed region.
-With N > 1 (torchrun, one rank per GPU) the dense shapes are sharded along N: the global problem has N_global =
-ranks x N columns and each rank owns one N-wide slab, so per-GPU work is fixed (weak scaling) and no collective is
-needed. `--workload grouped` shards experts across ranks instead and reports the optional NCCL gather separately.
+Several GPUs (torchrun, one rank per GPU; `--workload auto` = `grouped`): the m-grouped contiguous GEMM with a fixed
+global expert count sharded over the ranks (strong scaling), no collective on the data path; the NCCL all-gather of
+the outputs is timed separately (`gather_ms`). `--workload dense` at N > 1 runs N independent N-slabs instead.
+
+`--impl reference` times the reference's CPU implementation of the path (its dequantise-then-matmul test oracle) on
+the host cores over the same 18 shapes.
 """
 
 from __future__ import annotations
@@ -21,6 +28,7 @@ import argparse
 import ctypes
 import json
 import os
+import random
 import subprocess
 import sys
 import threading
@@ -34,7 +42,18 @@ import torch  # noqa: E402
 
 NK_LIST = [(2112, 7168), (24576, 1536), (32768, 512), (7168, 16384), (4096, 7168), (7168, 2048)]
 M_LIST = [64, 128, 4096]
+SWEEP = [(m, n, k) for m in M_LIST for (n, k) in NK_LIST]
 FP8_MAX = 448.0
+NOMINAL_FP8_TFLOPS, NOMINAL_HBM_GBS = 4500.0, 8000.0
+GLOBAL_EXPERTS = 32
+
+DENSE_WORKLOAD = ('dense FP8 NT sweep: M in {64,128,4096} x (N,K) in ' + str(NK_LIST) +
+                  ', BF16 out, A scaled per 1x128, B per 128x128 (UE8M0)')
+
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of single launches taken from ncu captures of this
+# library, keyed by (m, n, k, block_n): reported as `roofline.traffic` only when the launch timed here uses the same
+# tiling as the captured one, otherwise null.
+NCU_DRAM_TRAFFIC = {(4096, 7168, 16384, 448): 489.5e6, (4096, 7168, 16384, 320): 513.0e6, (4096, 7168, 16384, 224): 558.0e6}
 
 
 def peaks() -> dict:
@@ -44,6 +63,13 @@ def peaks() -> dict:
         return {'hbm_gbs': p['hbm_gbs'], 'bf16_tflops': p['bf16_tflops'],
                 'bf16_tflops_sustained': p.get('bf16_tflops_sustained', p['bf16_tflops']), 'source': 'measured'}
     return {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0, 'source': 'fallback'}
+
+
+def dense_config(world: int) -> dict:
+    """The `config` object of the dense workload; the reference arm prints the same one."""
+    return {'workload': DENSE_WORKLOAD,
+            'l2': 'inputs larger than L2: every GEMM has its own operands (1.5 GB per step against 126 MB of L2)',
+            'sharding': 'none' if world == 1 else 'N-slabs, one per rank, no collective'}
 
 
 # ----------------------------------------------------------------------------------------------------------------
@@ -69,16 +95,27 @@ def quantize_fp8(x: torch.Tensor, gran: tuple[int, int]):
     return (x / full).to(torch.float8_e4m3fn), sf.contiguous()
 
 
+def dense_bytes(m, n, k) -> int:
+    k64 = -(-k // 64)
+    return m * k + n * k + (m + n) * k64 * 2 + m * n * 2
+
+
 class DenseCase:
     """One (M, N, K) problem with operands on the device, canonical scale factors, and a prepared C-ABI call."""
 
-    def __init__(self, m, n, k, device, seed):
+    def __init__(self, m, n, k, device, seed, data=None):
         import deep_gemm
         from deep_gemm import _api
         g = torch.Generator(device=device).manual_seed(seed)
         self.m, self.n, self.k = m, n, k
-        self.a, self.sfa32 = quantize_fp8(torch.randn(m, k, device=device, generator=g), (1, 128))
-        self.b, self.sfb32 = quantize_fp8(torch.randn(n, k, device=device, generator=g), (128, 128))
+        if data is None:
+            self.a, self.sfa32 = quantize_fp8(torch.randn(m, k, device=device, generator=g), (1, 128))
+            self.b, self.sfb32 = quantize_fp8(torch.randn(n, k, device=device, generator=g), (128, 128))
+        else:       # another operand set of the same shape: codes and scales drawn directly (timing only)
+            self.a = torch.randint(0, 120, (m, k), dtype=torch.uint8, device=device, generator=g).view(torch.float8_e4m3fn)
+            self.b = torch.randint(0, 120, (n, k), dtype=torch.uint8, device=device, generator=g).view(torch.float8_e4m3fn)
+            self.sfa32 = torch.ones(m, k // 128, device=device)
+            self.sfb32 = torch.ones(-(-n // 128), k // 128, device=device)
         self.d = torch.empty(m, n, dtype=torch.bfloat16, device=device)
         # scale factors already in the required layout: the kernel-only number excludes the relayout
         self.sfa = deep_gemm.transform_sf_into_required_layout(self.sfa32, m, k, (1, 128, 128), is_sfa=True)
@@ -86,8 +123,7 @@ class DenseCase:
         self.desc = _api._run_gemm(_api.L.GEMM_NORMAL, self.a, self.b, self.d, None, _api.Identity(), self.sfa, self.sfb,
                                    (1, 1, 32), None, None, None, 'nk', False)
         self.flops = 2.0 * m * n * k
-        k64 = -(-k // 64)
-        self.bytes = m * k + n * k + (m + n) * k64 * 2 + m * n * 2
+        self.bytes = dense_bytes(m, n, k)
         self.ws = None
         lib = _api.L.lib()
         ws_bytes = lib.dg_gemm_workspace_bytes(ctypes.byref(self.desc), None)
@@ -111,6 +147,17 @@ class DenseCase:
         self.h_d = torch.empty(self.m, self.n, dtype=torch.bfloat16).pin_memory()
         self.h2d = self.h_a.numel() + self.h_b.numel() + 4 * (self.h_sfa.numel() + self.h_sfb.numel())
         self.d2h = self.h_d.numel() * 2
+
+    def verify(self, rows: int = 16) -> bool:
+        """A row sample of D against the CPU oracle (dequantise, FP32 matmul, one cast), within the parity tolerance."""
+        import oracle
+        idx = torch.randperm(self.m, generator=torch.Generator().manual_seed(self.m + self.n))[:rows].sort().values
+        a_deq = oracle.dequantize(oracle.decode_e4m3(self.a[idx.to(self.a.device)].cpu()), self.sfa32.cpu()[idx], 1, 128)
+        b_deq = oracle.dequantize(oracle.decode_e4m3(self.b.cpu()), self.sfb32.cpu(), 128, 128)
+        ref = oracle.gemm_ref(a_deq, b_deq, torch.bfloat16)
+        out = self.d[idx.to(self.d.device)].cpu()
+        return bool(torch.isfinite(out.float()).all()) and oracle.calc_diff(out, ref) <= 1e-3 and \
+            oracle.max_rel_err(out, ref) <= 2e-2
 
 
 # ----------------------------------------------------------------------------------------------------------------
@@ -160,26 +207,34 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------------------------------
 # CPU baseline: the reference's dequantise-then-matmul oracle on the host cores
 # ----------------------------------------------------------------------------------------------------------------
-def cpu_oracle_sample(shapes, repeats=1):
-    """Times oracle.gemm_ref (dequantise + FP32 matmul + BF16 cast) on `shapes`; returns (TFLOP/s, seconds)."""
+CPU_SAMPLE_TEXT = 'dequantise + FP32 matmul + BF16 cast (torch CPU) of all 18 shapes of the sweep, inputs quantised before the clock starts'
+
+
+def cpu_inputs(shapes):
+    """Quantised operands of `shapes` on the host (seeded), B shared by the shapes with the same (N, K)."""
     import oracle
     torch.manual_seed(0)
-    total_flops, total_s = 0.0, 0.0
+    weights, out = {}, []
     for (m, n, k) in shapes:
+        if (n, k) not in weights:
+            b, sfb, _ = oracle.quantize_e4m3(torch.randn(n, k), (128, 128))
+            weights[(n, k)] = (b, sfb)
         a, sfa, _ = oracle.quantize_e4m3(torch.randn(m, k), (1, 128))
-        b, sfb, _ = oracle.quantize_e4m3(torch.randn(n, k), (128, 128))
-        for _ in range(repeats):
-            t0 = time.perf_counter()
-            a_deq = oracle.dequantize(oracle.decode_e4m3(a), sfa, 1, 128)
-            b_deq = oracle.dequantize(oracle.decode_e4m3(b), sfb, 128, 128)
-            oracle.gemm_ref(a_deq, b_deq, torch.bfloat16)
-            total_s += time.perf_counter() - t0
-            total_flops += 2.0 * m * n * k
-    return total_flops / total_s / 1e12, total_s
+        out.append((a, sfa) + weights[(n, k)])
+    return out
 
 
-CPU_SAMPLE = [(128, n, k) for n, k in NK_LIST] + [(4096, 7168, 2048)]
-CPU_SAMPLE_TEXT = 'dequantise + FP32 matmul + BF16 cast of the six M=128 shapes and 4096x7168x2048, torch CPU'
+def cpu_oracle_pass(inputs) -> tuple[float, float]:
+    """One pass of the oracle over prepared inputs: (flops, seconds). Only dequantise + matmul + cast is timed."""
+    import oracle
+    flops = 0.0
+    t0 = time.perf_counter()
+    for (a, sfa, b, sfb) in inputs:
+        a_deq = oracle.dequantize(oracle.decode_e4m3(a), sfa, 1, 128)
+        b_deq = oracle.dequantize(oracle.decode_e4m3(b), sfb, 128, 128)
+        oracle.gemm_ref(a_deq, b_deq, torch.bfloat16)
+        flops += 2.0 * a.shape[0] * b.shape[0] * a.shape[1]
+    return flops, time.perf_counter() - t0
 
 
 def run_reference(args, rank, world):
@@ -187,31 +242,43 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
-    for _ in range(args.warmup):
-        cpu_oracle_sample(CPU_SAMPLE[:2])
-    t0 = time.perf_counter()
-    flops = 0.0
+    inputs = cpu_inputs(SWEEP)
+    for _ in range(min(args.warmup, 1)):
+        cpu_oracle_pass(inputs[:6])
+    flops, seconds = 0.0, 0.0
     for _ in range(args.steps):
-        tf, s = cpu_oracle_sample(CPU_SAMPLE)
-        flops += tf * s * 1e12
-    elapsed = time.perf_counter() - t0
-    value = flops / elapsed / 1e12
-    line = {
+        f, s = cpu_oracle_pass(inputs)
+        flops += f
+        seconds += s
+    value = flops / seconds / 1e12
+    emit({
         'impl': 'reference', 'metric': 'fp8_block_scaled_gemm_tflops', 'value': value, 'unit': 'TFLOP/s',
-        'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': elapsed / args.steps * 1e3,
+        'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': seconds / args.steps * 1e3,
         'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
-        'config': {'workload': 'dense FP8 NT sweep, M in {64,128,4096} x 6 (N,K), BF16 out', 'sample': CPU_SAMPLE_TEXT},
+        'config': dense_config(1),
         'cpu_baseline': {'value': value, 'unit': 'TFLOP/s', 'cores': torch.get_num_threads(), 'kind': 'port',
                          'sample': CPU_SAMPLE_TEXT},
         'e2e': {'value': value, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
-    }
-    emit(line)
+    })
 
 
 # ----------------------------------------------------------------------------------------------------------------
-# Main arm
+# Dense sweep
 # ----------------------------------------------------------------------------------------------------------------
+def per_shape_times(lib, device, base_cases) -> list[float]:
+    """Mean microseconds per launch of every shape of the sweep: each shape runs as a CUDA graph of back-to-back
+    launches over rotating operand sets that together exceed L2 several times, between one CUDA-event pair."""
+    from deep_gemm.testing import bench_graph
+    out = []
+    for ci, c in enumerate(base_cases):
+        copies = max(3, min(32, -(-512_000_000 // c.bytes)))
+        sets = [c] + [DenseCase(c.m, c.n, c.k, device, seed=7000 + 37 * ci + j, data='codes') for j in range(copies - 1)]
+        out.append(bench_graph([(lambda sptr, s=s: s.launch(lib, sptr)) for s in sets], 3, 10).dur_us)
+        del sets
+    return out
+
+
 def run_dense(args, rank, world, device):
     import deep_gemm
     from deep_gemm import _lib as L
@@ -219,24 +286,18 @@ def run_dense(args, rank, world, device):
     pk = peaks()
     stream = torch.cuda.current_stream(device)
     sptr = stream.cuda_stream
-    cases = [DenseCase(m, n, k, device, seed=1000 * rank + i)
-             for i, (m, (n, k)) in enumerate((m, nk) for m in M_LIST for nk in NK_LIST)]
+    cases = [DenseCase(m, n, k, device, seed=1000 * rank + i) for i, (m, n, k) in enumerate(SWEEP)]
     torch.cuda.synchronize(device)
 
     # One step = the 18 GEMMs back to back. Every GEMM has its own operands and the sweep touches far more than the
-    # L2 holds between two uses of the same buffer (`footprint` below), so every launch finds its inputs in HBM
-    # without a flush kernel in between.
+    # L2 holds between two uses of the same buffer, so every launch finds its inputs in HBM without a flush kernel.
     footprint = sum(c.bytes for c in cases)
     l2_bytes = torch.cuda.get_device_properties(device).L2_cache_size
     assert footprint > 4 * l2_bytes, 'the sweep must not fit in L2'
 
-    def sweep(stream_ptr, record=None):
-        for ci, c in enumerate(cases):
-            if record is not None:
-                record[ci][0].record(stream)
+    def sweep(stream_ptr):
+        for c in cases:
             c.launch(lib, stream_ptr)
-            if record is not None:
-                record[ci][1].record(stream)
 
     def barrier():
         if world > 1:
@@ -283,19 +344,14 @@ def run_dense(args, rank, world, device):
     barrier()
     launches = launches_per_step * args.steps if graph is not None else lib.dg_kernel_launch_count() - launches0
     step_ms = t_begin.elapsed_time(t_end) / args.steps
+    verified = all(c.verify() for c in cases) if rank == 0 else None
 
-    # Second pass, same sweep with one CUDA-event pair around every launch: the per-shape table and the roofline
-    # figures (a launch timed this way includes the gap to its neighbours, so these are upper bounds on kernel time).
-    events = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in cases]
-              for _ in range(args.steps)]
-    for s in range(args.steps):
-        sweep(sptr, events[s])
+    # Per-shape times and the roofline figures
+    per_case_us = per_shape_times(lib, device, cases)
     barrier()
     clocks = sampler.stop() if sampler else None
     status = deep_gemm.device_status()
 
-    per_case_us = [sum(events[s][ci][0].elapsed_time(events[s][ci][1]) for s in range(args.steps)) / args.steps * 1e3
-                   for ci in range(len(cases))]
     step_ms_t = torch.tensor([step_ms], dtype=torch.float64, device=device)
     if world > 1:
         torch.distributed.all_reduce(step_ms_t, op=torch.distributed.ReduceOp.MAX)
@@ -314,6 +370,7 @@ def run_dense(args, rank, world, device):
     s_in, s_mm, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device), torch.cuda.Stream(device)
     done_mm = [None] * len(cases)      # last GEMM that read case i's device inputs / wrote its D
     done_out = [None] * len(cases)     # last D2H copy of case i's D
+    host_us = []
 
     def e2e_step():
         for i, c in enumerate(cases):
@@ -330,7 +387,9 @@ def run_dense(args, rank, world, device):
                 s_mm.wait_event(ready)
                 if done_out[i] is not None:
                     s_mm.wait_event(done_out[i])         # D is still being copied out from the previous step
+                h0 = time.perf_counter()
                 deep_gemm.fp8_gemm_nt((c.a, c.sfa32), (c.b, c.sfb32), c.d, recipe=(1, 128, 128))
+                host_us.append((time.perf_counter() - h0) * 1e6)
                 done_mm[i] = torch.cuda.Event()
                 done_mm[i].record(s_mm)
             with torch.cuda.stream(s_out):
@@ -341,6 +400,7 @@ def run_dense(args, rank, world, device):
 
     e2e_step()
     barrier()
+    host_us.clear()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         e2e_step()
@@ -349,52 +409,101 @@ def run_dense(args, rank, world, device):
     if world > 1:
         torch.distributed.all_reduce(e2e_s, op=torch.distributed.ReduceOp.MAX)
     e2e_value = world * flops_step / float(e2e_s.item()) / 1e12
+    # host cost of one GEMM call with scale factors already in the required layout (no transform launched)
+    c0 = cases[6]
+    for _ in range(20):
+        deep_gemm.fp8_gemm_nt((c0.a, c0.sfa), (c0.b, c0.sfb), c0.d)
+    h0 = time.perf_counter()
+    for _ in range(200):
+        deep_gemm.fp8_gemm_nt((c0.a, c0.sfa), (c0.b, c0.sfb), c0.d)
+    host_call_us = (time.perf_counter() - h0) / 200 * 1e6
+    torch.cuda.synchronize(device)
 
     if rank != 0:
         return
-    # ---- roofline of the dominant kernel (the GEMM kernel on the tensor-bound M = 4096 shapes) and of the
-    #      HBM-bound small-M launches
+    legs = other_config_legs(args, device, pk) if world == 1 and not args.no_legs else None
+
     big = [i for i, c in enumerate(cases) if c.m == 4096]
     small = [i for i, c in enumerate(cases) if c.m <= 128]
     tf_big = sum(cases[i].flops for i in big) / sum(per_case_us[i] for i in big) / 1e6
     gbs_small = sum(cases[i].bytes for i in small) / sum(per_case_us[i] for i in small) / 1e3
     fp8_peak = 2.0 * pk['bf16_tflops']
+    top = max(big, key=lambda i: cases[i].flops)
     shapes = [{'m': c.m, 'n': c.n, 'k': c.k, 'us': round(per_case_us[i], 2),
                'tflops': round(c.flops / per_case_us[i] / 1e6, 1), 'gbs': round(c.bytes / per_case_us[i] / 1e3, 1),
                'block_n': c.config['block_n'], 'cta_group': c.config['cta_group'], 'split_k': c.config['split_k'],
                'split_in_cluster': bool(c.config['cluster_split']),
                'stages': c.config['num_stages']} for i, c in enumerate(cases)]
-    cpu_tf, cpu_s = cpu_oracle_sample(CPU_SAMPLE) if world == 1 else (None, None)
     line = {
         'metric': 'fp8_block_scaled_gemm_tflops', 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world,
         'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': step_ms_max, 'higher_is_better': True,
         'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp8_e4m3 x ue8m0, fp32 accumulate', 'data': 'synthetic',
-        'config': {'workload': 'dense FP8 NT sweep: M in {64,128,4096} x (N,K) in ' + str(NK_LIST) +
-                               ', BF16 out, A scaled per 1x128, B per 128x128 (UE8M0)',
-                   'l2': 'inputs larger than L2: every GEMM has its own operands, %d MB per step against %d MB of L2'
-                         % (footprint // 10**6, l2_bytes // 10**6),
-                   'sharding': 'none' if world == 1 else 'N-slabs, one per rank, no collective',
-                   'timing': ('one CUDA-event pair around the %d steps, each step one replay of a CUDA graph of the 18 launches'
-                              % args.steps if graph is not None else 'one CUDA-event pair around the steps, plain stream launches')
-                             + '; per-shape and roofline figures from a second pass with one event pair per launch'},
+        'config': dense_config(world),
+        'timing': ('one CUDA-event pair around the %d steps, each step one replay of a CUDA graph of the 18 launches'
+                   % args.steps if graph is not None else 'one CUDA-event pair around the steps, plain stream launches')
+                  + '; per-shape and roofline figures: every shape as a graph of back-to-back launches over rotating '
+                    'operand sets (more than 4x L2 in total), one event pair around 10 replays',
+        'verified': verified,
         'roofline': {'bound': 'tensor', 'achieved': tf_big, 'peak': fp8_peak, 'unit': 'TFLOP/s', 'frac': tf_big / fp8_peak,
-                     'traffic': 489.5e6, 'traffic_of': 'dram__bytes_read.sum + dram__bytes_write.sum of the 4096x7168x16384 launch '
-                     '(ncu capture in profiles/mx_gemm_wide_tile_pair.md; algorithmic 249.0 MB)',
+                     'traffic': NCU_DRAM_TRAFFIC.get((cases[top].m, cases[top].n, cases[top].k, cases[top].config['block_n'])),
+                     'traffic_of': 'one launch of %dx%dx%d (algorithmic %.1f MB), ncu capture of the same tiling'
+                                   % (cases[top].m, cases[top].n, cases[top].k, cases[top].bytes / 1e6),
                      'kernel': 'mx_gemm_kernel on the six M=4096 launches',
-                     'peak_source': '2 x bf16 burst of MEASURED_PEAKS.json (%s)' % pk['source']},
-        'roofline_small_m': {'bound': 'hbm', 'achieved': gbs_small, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
-                             'frac': gbs_small / pk['hbm_gbs'], 'kernel': 'mx_gemm_kernel (+ split-K finalisation) on the twelve M<=128 launches'},
+                     'peak_source': '2 x the BF16 burst figure of MEASURED_PEAKS.json (%s): derived, no FP8 figure is measured'
+                                    % pk['source'],
+                     'frac_of_nominal': tf_big / NOMINAL_FP8_TFLOPS, 'nominal_peak': NOMINAL_FP8_TFLOPS,
+                     'hbm': {'bound': 'hbm', 'achieved': gbs_small, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
+                             'frac': gbs_small / pk['hbm_gbs'], 'frac_of_nominal': gbs_small / NOMINAL_HBM_GBS,
+                             'kernel': 'mx_gemm_kernel (+ split-K finalisation where used) on the twelve M<=128 launches',
+                             'peak_source': 'copy bandwidth of MEASURED_PEAKS.json (%s)' % pk['source']}},
         'e2e': {'value': e2e_value, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': sum(c.h2d for c in cases),
                 'd2h_bytes_per_step': sum(c.d2h for c in cases), 'steps': e2e_steps},
+        'host_us_per_call': {'fp8_gemm_nt, scales in the required layout (plan reused)': round(host_call_us, 1),
+                             'fp8_gemm_nt with FP32 scales (two transforms launched), median':
+                                 round(sorted(host_us)[len(host_us) // 2], 1) if host_us else None},
         'gpu_launches': int(launches),
         'clocks': clocks,
         'device_status': status,
         'shapes': shapes,
     }
-    if cpu_tf is not None:
-        line['cpu_baseline'] = {'value': cpu_tf, 'unit': 'TFLOP/s', 'cores': torch.get_num_threads(), 'kind': 'port',
-                                'sample': CPU_SAMPLE_TEXT + ' (%.1f s)' % cpu_s}
+    if world == 1:
+        torch.set_num_threads(os.cpu_count() or 1)
+        flops, seconds = cpu_oracle_pass(cpu_inputs(SWEEP))
+        line['cpu_baseline'] = {'value': flops / seconds / 1e12, 'unit': 'TFLOP/s', 'cores': torch.get_num_threads(),
+                                'kind': 'port', 'sample': CPU_SAMPLE_TEXT + ' (%.1f s)' % seconds}
+    if legs is not None:
+        line['configs'] = legs
+        line['verified'] = bool(verified and all(v.get('verified', True) for v in legs.values()))
     emit(line)
+
+
+def other_config_legs(args, device, pk) -> dict:
+    """Short legs for the configurations the sweep does not contain: mixed FP8xFP4 (config 3), m-grouped contiguous
+    with 32 experts (config 4) and m-grouped masked 32 x 256 (config 5), each timed per launch after an untimed L2
+    flush, verified on a row sample, with the roofline that bounds it."""
+    from deep_gemm.testing import moe_bench
+    fp8_peak = 2.0 * pk['bf16_tflops']
+    steps = max(3, min(args.steps, 10))
+    out = {}
+    r = moe_bench.time_mixed(device, steps)
+    out['mixed_fp8_fp4_nn_4096x7168x2048'] = {
+        'us': round(r['us'], 2), 'tflops': round(r['tflops'], 1), 'verified': r['verified'], 'tiling': r['tiling'],
+        'roofline': {'bound': 'tensor', 'achieved': r['tflops'], 'peak': fp8_peak, 'unit': 'TFLOP/s',
+                     'frac': r['tflops'] / fp8_peak, 'frac_of_nominal': r['tflops'] / NOMINAL_FP8_TFLOPS, 'traffic': None}}
+    random.seed(1234)
+    sizes = [int(random.uniform(0.7, 1.3) * 8192) for _ in range(GLOBAL_EXPERTS)]
+    r = moe_bench.time_grouped(device, sizes, steps, masked=False)
+    out['m_grouped_contiguous_32_experts'] = {
+        'shapes': r['shapes'], 'tflops': round(r['tflops'], 1), 'verified': r['verified'],
+        'roofline': {'bound': 'tensor', 'achieved': r['tflops'], 'peak': fp8_peak, 'unit': 'TFLOP/s',
+                     'frac': r['tflops'] / fp8_peak, 'frac_of_nominal': r['tflops'] / NOMINAL_FP8_TFLOPS, 'traffic': None}}
+    masked = [random.randint(0, 256) for _ in range(GLOBAL_EXPERTS)]
+    r = moe_bench.time_grouped(device, masked, steps, masked=True)
+    out['m_grouped_masked_32x256'] = {
+        'shapes': r['shapes'], 'tflops': round(r['tflops'], 1), 'gbs': round(r['gbs'], 1), 'verified': r['verified'],
+        'roofline': {'bound': 'hbm', 'achieved': r['gbs'], 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
+                     'frac': r['gbs'] / pk['hbm_gbs'], 'frac_of_nominal': r['gbs'] / NOMINAL_HBM_GBS, 'traffic': None}}
+    return out
 
 
 def emit(line: dict) -> None:
@@ -416,11 +525,13 @@ def main():
     ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='dense', choices=['dense', 'grouped', 'masked', 'mixed', 'fp4', 'bf16', 'quant'])
-    ap.add_argument('--experts-per-gpu', type=int, default=0, help='grouped / masked workloads (default 8 / 32)')
+    ap.add_argument('--workload', default='auto',
+                    choices=['auto', 'dense', 'grouped', 'masked', 'mixed', 'fp4', 'bf16', 'quant'])
+    ap.add_argument('--experts', type=int, default=0, help='grouped / masked workloads: global expert count (default 32)')
     ap.add_argument('--no-graph', action='store_true',
                     help='dense workload: plain stream launches instead of a CUDA graph (for profilers that cannot follow a capture)')
-    ap.add_argument('--gather', action='store_true', help='grouped workload, N > 1: also time an NCCL all-gather of D')
+    ap.add_argument('--no-legs', action='store_true', help='dense workload: skip the legs for the other configurations')
+    ap.add_argument('--no-gather', action='store_true', help='grouped workload, N > 1: skip the NCCL all-gather of D')
     args = ap.parse_args()
 
     rank = int(os.environ.get('RANK', '0'))
@@ -436,12 +547,14 @@ def main():
     if world > 1:
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         torch.distributed.init_process_group('nccl', device_id=device)
+    workload = args.workload if args.workload != 'auto' else ('dense' if world == 1 else 'grouped')
+    args.workload = workload
     try:
-        if args.workload == 'dense':
+        if workload == 'dense':
             run_dense(args, rank, world, device)
         else:
             from deep_gemm.testing import moe_bench
-            moe_bench.run(args, rank, world, device, emit)
+            moe_bench.run(args, rank, world, device, emit, peaks())
     finally:
         if world > 1:
             torch.distributed.destroy_process_group()

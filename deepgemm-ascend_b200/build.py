@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, 'csrc')
 OUT = os.path.join(HERE, 'deep_gemm', 'libdg_b200.so')
-SOURCES = ['api.cu', 'mx_gemm.cu', 'transform_sf.cu', 'quant_ops.cu']
+SOURCES = ['api.cu', 'mx_gemm.cu', 'transform_sf.cu', 'quant_ops.cu', 'sleep.cu']
 NVCC_FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3', '-std=c++17',
               '-Xcompiler', '-fPIC', '-Xcompiler', '-fvisibility=hidden', '--expt-relaxed-constexpr']
 

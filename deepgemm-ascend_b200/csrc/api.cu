@@ -233,6 +233,8 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
         DG_CHECK_ARG(wide_tile_possible(d) && c.cta_group == 2 && !wide_epilogue(c),
                      "block_n > 256 needs E4M3 x E4M3, E2M1 x E2M1 or BF16 x BF16 with K-major operands, cta_group 2 and four epilogue warps");
         DG_CHECK_ARG(c.block_n <= max_wide_block_n(d) && c.block_n % 64 == 0, "a wide block_n must be a multiple of 64 in (256, %u]", max_wide_block_n(d));
+        // (the wide-tile walk hands out half tiles by tile index and knows nothing of K splits)
+        DG_CHECK_ARG(c.split_k <= 1, "block_n > 256 cannot be combined with split_k > 1");
     } else {
         DG_CHECK_ARG(c.block_n >= gran && c.block_n % gran == 0, "block_n must be a multiple of %u in [%u, 256]", gran, gran);
         DG_CHECK_ARG(c.block_n % (16 * c.cta_group) == 0, "block_n not valid for this cta_group");
@@ -244,6 +246,9 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     DG_CHECK_ARG(!split || d.epilogue != DG_EPILOGUE_FP8_QUANT, "FP8 quantization cannot be combined with split-K");
     DG_CHECK_ARG(c.split_k <= 1 || d.gemm_type == DG_GEMM_NORMAL, "split-K is only available for the dense GEMM");
     DG_CHECK_ARG(!split || d.epilogue != DG_EPILOGUE_STOCHASTIC_BF16, "stochastic rounding cannot be combined with split-K");
+    // The workspace reduction adds the partial sums of a tile in arrival order; the cluster reduction adds them in rank order.
+    DG_CHECK_ARG(!split || !d.deterministic, "deterministic algorithms: split-K through the workspace adds in arrival order; "
+                 "use the cluster reduction (reserved[3] = 1) or split_k = 1");
     DG_CHECK_ARG(!in_cluster || (c.cta_group == 1 && c.split_k <= kMaxClusterSplit && !decodes_b(d)),
                  "cluster split-K needs cta_group 1, unpacked B and at most %u splits", kMaxClusterSplit);
     const uint32_t cluster_split = in_cluster ? c.split_k : 1u;
@@ -397,7 +402,7 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
         else
             m_tiles = (rows + tile_m - 1) / tile_m;
         for (uint32_t split = 1; split <= 16; ++split) {
-            if (split > 1 && (d.gemm_type != DG_GEMM_NORMAL || nkb / split < 2 || cg == 2 ||
+            if (split > 1 && (d.gemm_type != DG_GEMM_NORMAL || nkb / split < 2 || cg == 2 || d.deterministic ||
                               d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16 || d.epilogue == DG_EPILOGUE_FP8_QUANT)) break;
             const bool out_fp32 = d_fp32 || split > 1;
             const uint32_t step = d.major_b == DG_MAJOR_MN ? (128u / ab_elem_bytes(d)) * cg : 32u;   // MN-major B comes in 128-byte atoms
@@ -744,6 +749,70 @@ static int resolve_config(const dg_gemm_desc_t& d, const dg_gemm_config_t* in, d
 }
 
 // ------------------------------------------------------------------------------------------------
+// Launch-plan cache
+// ------------------------------------------------------------------------------------------------
+// The reference re-runs its tiling search on every call and notes that as a gap (csrc/jit_kernels/heuristics.hpp:593).
+// Here everything the host derives from a call (validated problem, tiling, the six encoded tensor maps, kernel
+// arguments) is a pure function of the descriptor, the optional configuration, the workspace, the device and the
+// SM limit, so a repeated call (a decode loop over the same buffers) finds its plan by comparing those bytes.
+struct PlanKey {
+    dg_gemm_desc_t d;
+    dg_gemm_config_t c;
+    const void* workspace;
+    size_t workspace_bytes;
+    int32_t has_config, device, num_sms, pad;
+};
+struct PlanSlot {
+    bool used = false;
+    uint64_t hash = 0;
+    PlanKey key;
+    LaunchPlan plan;
+    dg_gemm_config_t cfg;
+};
+constexpr uint32_t kPlanSlots = 256;
+static std::mutex g_plan_mu;
+static PlanSlot* g_plan_slots = nullptr;       // allocated on first use, lives until process exit
+static std::atomic<unsigned long long> g_plan_hits{0}, g_plan_misses{0};
+
+static uint64_t hash_bytes(const void* p, size_t n) {
+    const unsigned char* b = static_cast<const unsigned char*>(p);
+    uint64_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < n; ++i) { h ^= b[i]; h *= 1099511628211ull; }
+    return h;
+}
+
+static void make_plan_key(PlanKey& key, const dg_gemm_desc_t& d, const dg_gemm_config_t* c, const void* ws, size_t ws_bytes, int dev) {
+    memset(&key, 0, sizeof(key));
+    key.d = d;
+    if (c != nullptr) { key.c = *c; key.has_config = 1; }
+    key.workspace = ws;
+    key.workspace_bytes = ws_bytes;
+    key.device = dev;
+    key.num_sms = g_num_sms.load();
+}
+
+static bool plan_cache_find(const PlanKey& key, uint64_t hash, LaunchPlan& plan, dg_gemm_config_t& cfg) {
+    std::lock_guard<std::mutex> lock(g_plan_mu);
+    if (g_plan_slots == nullptr) return false;
+    const PlanSlot& slot = g_plan_slots[hash % kPlanSlots];
+    if (!slot.used || slot.hash != hash || memcmp(&slot.key, &key, sizeof(key)) != 0) return false;
+    plan = slot.plan;
+    cfg = slot.cfg;
+    return true;
+}
+
+static void plan_cache_store(const PlanKey& key, uint64_t hash, const LaunchPlan& plan, const dg_gemm_config_t& cfg) {
+    std::lock_guard<std::mutex> lock(g_plan_mu);
+    if (g_plan_slots == nullptr) g_plan_slots = new PlanSlot[kPlanSlots];
+    PlanSlot& slot = g_plan_slots[hash % kPlanSlots];
+    slot.used = true;
+    slot.hash = hash;
+    slot.key = key;
+    slot.plan = plan;
+    slot.cfg = cfg;
+}
+
+// ------------------------------------------------------------------------------------------------
 // Fixed split-K scratch for callers that cannot allocate (dg_gemm_launch_static_scratch)
 // ------------------------------------------------------------------------------------------------
 // Lives in every GPU's memory from module load to process exit. In host code the name below is only a handle for
@@ -839,13 +908,29 @@ int dg_gemm_dry_run(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config) 
 int dg_gemm_launch(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config,
                    void* workspace, size_t workspace_bytes, void* stream) {
     DG_CHECK_ARG(desc != nullptr, "dg_gemm_launch: null descriptor");
-    if (int rc = validate(*desc)) return rc;
-    dg_gemm_config_t c;
-    if (int rc = resolve_config(*desc, config, c)) return rc;
+    int dev = 0;
+    DG_CHECK_CUDA(cudaGetDevice(&dev));
+    PlanKey key;
+    make_plan_key(key, *desc, config, workspace, workspace_bytes, dev);
+    const uint64_t hash = hash_bytes(&key, sizeof(key));
     LaunchPlan plan;
-    if (int rc = build_plan(*desc, c, workspace, workspace_bytes, /*encode=*/true, plan)) return rc;
+    dg_gemm_config_t c;
+    if (plan_cache_find(key, hash, plan, c)) {
+        g_plan_hits.fetch_add(1, std::memory_order_relaxed);
+    } else {
+        g_plan_misses.fetch_add(1, std::memory_order_relaxed);
+        if (int rc = validate(*desc)) return rc;
+        if (int rc = resolve_config(*desc, config, c)) return rc;
+        if (int rc = build_plan(*desc, c, workspace, workspace_bytes, /*encode=*/true, plan)) return rc;
+        plan_cache_store(key, hash, plan, c);
+    }
     maybe_print_config(*desc, c);
     return launch_gemm_kernel(plan, static_cast<cudaStream_t>(stream));
+}
+
+void dg_plan_cache_stats(uint64_t* hits, uint64_t* misses) {
+    if (hits) *hits = g_plan_hits.load(std::memory_order_relaxed);
+    if (misses) *misses = g_plan_misses.load(std::memory_order_relaxed);
 }
 
 }  // extern "C"

@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
 
 #include "host_common.h"
@@ -110,6 +111,19 @@ static std::mutex g_trace_mu;
 static unsigned long long* g_trace_buf[64] = {};
 static size_t g_trace_bytes[64] = {};
 
+// 1: GEMM kernels are launched with programmatic stream serialisation (default; DG_OVERLAP_LAUNCHES=0 or
+// dg_set_overlap_launches(0) turns it off).
+static std::atomic<int> g_overlap_launches{-1};
+bool overlap_launches_enabled() {
+    int v = g_overlap_launches.load(std::memory_order_relaxed);
+    if (v < 0) {
+        const char* e = getenv("DG_OVERLAP_LAUNCHES");
+        v = (e == nullptr || atoi(e) != 0) ? 1 : 0;
+        g_overlap_launches.store(v, std::memory_order_relaxed);
+    }
+    return v != 0;
+}
+
 int get_status_pointer(int32_t** out) {
     static std::mutex mu;
     static int32_t* ptrs[64] = {};
@@ -128,18 +142,34 @@ int get_status_pointer(int32_t** out) {
 
 int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
     KernelFn fn = pick_kernel(plan.cta_group, plan.major_a, plan.major_b, plan.decode_b, plan.lean, plan.fp4_pair, plan.bf16_pair, plan.wide_epi, plan.simple_epi, plan.wide_tile);
-    // The attribute is per device and per function; setting it is cheap, so do it on every launch.
-    DG_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem_bytes));
+    int dev = 0;
+    DG_CHECK_CUDA(cudaGetDevice(&dev));
+    DG_CHECK_ARG(dev >= 0 && dev < 64, "device index out of range");
+    // The dynamic shared-memory limit is an attribute per device and per function: raise it when a launch needs more
+    // than any earlier launch of that function on that device did.
+    {
+        struct Raised { const void* fn; int dev; uint32_t bytes; };
+        static std::mutex mu;
+        static Raised raised[128];
+        static int count = 0;
+        std::lock_guard<std::mutex> lock(mu);
+        int slot = -1;
+        for (int i = 0; i < count; ++i)
+            if (raised[i].fn == (const void*)fn && raised[i].dev == dev) { slot = i; break; }
+        if (slot < 0 || raised[slot].bytes < plan.smem_bytes) {
+            DG_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem_bytes));
+            if (slot < 0 && count < 128) slot = count++;
+            if (slot >= 0) raised[slot] = Raised{(const void*)fn, dev, plan.smem_bytes};
+        }
+    }
 
     GemmKernelArgs args = plan.args;
     if (int rc = get_status_pointer(&args.status)) return rc;
 
     // Debugging aid: per-CTA timestamps go to a buffer the caller handed over (dg_debug_set_trace_buffer), if any.
     {
-        int dev = 0;
-        DG_CHECK_CUDA(cudaGetDevice(&dev));
         std::lock_guard<std::mutex> lock(g_trace_mu);
-        args.trace = (dev >= 0 && dev < 64 && g_trace_bytes[dev] >= (size_t)plan.num_ctas * 16 * sizeof(unsigned long long))
+        args.trace = (dev >= 0 && dev < 64 && g_trace_bytes[dev] >= (size_t)plan.num_ctas * kTraceSlots * sizeof(unsigned long long))
                          ? g_trace_buf[dev] : nullptr;
     }
 
@@ -156,13 +186,20 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
     cfg.blockDim = dim3((plan.decode_b || plan.wide_epi) ? kNumThreadsDecode : kNumThreads, 1, 1);
     cfg.dynamicSmemBytes = plan.smem_bytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = plan.cluster_x;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    // Programmatic dependent launch: the kernel may be scheduled while the kernel in front of it in the stream is
+    // still draining; it waits for that kernel (griddepcontrol.wait) before it reads or writes any global data.
+    if (overlap_launches_enabled()) {
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 2;
+    }
     // A persistent grid must be fully co-resident: a CTA (pair) that only starts after another one has finished its
     // whole tile sequence doubles the run time. Not every SM pair can host a 2-CTA cluster, so ask the runtime.
     uint32_t grid = plan.num_ctas;
@@ -171,8 +208,6 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
         static std::mutex mu;
         static Key cache[32];
         static int cached = 0;
-        int dev = 0;
-        DG_CHECK_CUDA(cudaGetDevice(&dev));
         int clusters = -1;
         {
             std::lock_guard<std::mutex> lock(mu);
@@ -205,6 +240,12 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
 }
 
 }  // namespace dg
+
+extern "C" int dg_set_overlap_launches(int enabled) {
+    dg::g_overlap_launches.store(enabled ? 1 : 0, std::memory_order_relaxed);
+    return DG_OK;
+}
+extern "C" int dg_get_overlap_launches(void) { return dg::overlap_launches_enabled() ? 1 : 0; }
 
 extern "C" int dg_debug_set_trace_buffer(void* device_buffer, size_t bytes) {
     int dev = 0;

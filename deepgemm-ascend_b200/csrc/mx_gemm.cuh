@@ -127,8 +127,11 @@ __device__ __forceinline__ bool wait_barrier_cluster(uint32_t bar, uint32_t pari
 // requested, first operands landed (MMA side), last MMA committed, first accumulator ready (epilogue side), epilogue
 // done; 8..12 producer: role entered, first tile known, first stage free, A and B requested, first stage requested;
 // 13..15 epilogue: partial sums sent (cluster split-K), partial sums received, all chunks of the first tile written.
+// 16, 17: globaltimer ns when the wait for the preceding kernel returned and at the end of the kernel; 18: clock64 at the end.
+constexpr uint32_t kTraceSlots = 32;         // 8-byte slots per CTA
 __device__ __forceinline__ void trace_mark(const GemmKernelArgs& p, uint32_t slot) {
-    if (p.trace != nullptr) p.trace[blockIdx.x * 16 + slot] = slot == 0 ? global_timer_ns() : (unsigned long long)clock64();
+    if (p.trace != nullptr)
+        p.trace[blockIdx.x * kTraceSlots + slot] = (slot == 0 || slot == 16 || slot == 17) ? global_timer_ns() : (unsigned long long)clock64();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -502,6 +505,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (warp == 0) named_bar_arrive(1, num_threads); else named_bar_sync(1, num_threads);
     }
     tc_fence_after_sync();
+    // Programmatic dependent launch: everything above (barriers, TMEM, descriptor prefetch) touches no global data and
+    // may run while the preceding kernel of the stream is still finishing; everything below reads operands or writes
+    // D and waits for that kernel. The kernel behind this one may start its own set-up as soon as SMs free up.
+    griddep_wait();
+    griddep_launch_dependents();
+    if (threadIdx.x == 0) trace_mark(p, 16);
     const uint32_t tmem_base = tmem_ptr_smem[0];      // (not yet written when warp 0 gets here; warp 0 never uses it)
     if (threadIdx.x == 0) trace_mark(p, 2);
     // TMEM columns: accumulators first, then the scale factors of A and of B.
@@ -1081,6 +1090,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         tc_fence_after_sync();
         tmem_dealloc<kCtaGroup>(tmem_base, p.tmem_cols);
     }
+    if (threadIdx.x == 0) { trace_mark(p, 17); trace_mark(p, 18); }
 }
 
 }  // namespace dg

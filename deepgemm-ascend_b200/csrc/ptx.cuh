@@ -52,6 +52,17 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
     return r;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Blocks until every grid this one was launched behind (with the programmatic-serialisation launch attribute) has
+// finished and its writes are visible; returns at once when the grid was launched the ordinary way.
+__device__ __forceinline__ void griddep_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Lets a grid that was launched behind this one start (it runs its own set-up, then blocks in griddep_wait).
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));

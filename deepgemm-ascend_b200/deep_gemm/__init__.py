@@ -43,6 +43,7 @@ from ._api import (  # noqa: F401
     m_grouped_fp8_gemm_nn_contiguous,
     m_grouped_fp8_gemm_nt_contiguous,
     m_grouped_fp8_gemm_nt_masked,
+    npu_sleep,
     set_dry_run,
     set_mk_alignment_for_contiguous_layout,
     set_npu_arch,

@@ -12,6 +12,7 @@ heuristic, TMA descriptors and the launches live in libdg_b200.so.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import threading
 import warnings
 from typing import Optional
@@ -24,6 +25,7 @@ PACKED_FP4 = torch.int8           # csrc/utils/dtype.hpp:9
 MK_ALIGNMENT = 256                # csrc/jit/jit.hpp:59-73
 
 _state = threading.local()
+_DEBUG = os.environ.get('DG_JIT_DEBUG', '0') not in ('', '0')
 _global = {'dry_run': False, 'deterministic': False, 'arch': 100}
 _workspaces: dict = {}
 _ws_lock = threading.Lock()
@@ -163,7 +165,18 @@ def get_dry_run() -> bool:
 
 
 def init(version: str = '', library_root_path: str = '') -> None:
-    """Kept for import compatibility; importing never touches the device (csrc/apis/runtime.hpp:41-44)."""
+    """csrc/apis/runtime.hpp:41-44. The reference points its JIT at the installed headers here; this build has no
+    JIT, so the call only checks that the compiled library is present and of the expected ABI (no device is touched)."""
+    L.lib()
+
+
+def npu_sleep(sleep_cycles: int, *, marker: int = 0) -> None:
+    """csrc/apis/runtime.hpp:64-79: enqueue a kernel of one block per SM that spins for `sleep_cycles` SM clock
+    cycles (at most 4e9). `marker` selects the kernel's name so that a profiler can find begin / end marks."""
+    if get_dry_run():
+        return
+    device = torch.device('cuda', torch.cuda.current_device())
+    L.check(L.lib().dg_sleep_launch(int(sleep_cycles), int(marker), get_num_sms(), _stream_ptr(device)))
 
 
 def _stream_ptr(device: torch.device) -> int:
@@ -290,6 +303,25 @@ def _check_psum_layout(psum_layout, sf) -> int:
     return psum_layout.numel()
 
 
+_SF_INVALID_MESSAGE = "Float32 SF must be non-negative and can't have non-zero mantissa"
+STATUS_INVALID_SCALE_FACTOR = 201
+_sf_flags: dict = {}
+
+
+def _sf_invalid_flag(device: torch.device) -> torch.Tensor:
+    """One int32 per device that the transform kernel sets when it meets an FP32 scale that is negative or not a
+    power of two. The reference asserts on the device (deep_gemm/include/deep_gemm/transform_sf.hpp:13-21); a
+    CUDA kernel that traps loses the context, so the flag is reported by `device_status()` at the caller's next
+    synchronisation point, or at once when DG_JIT_DEBUG is set."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    with _ws_lock:
+        flag = _sf_flags.get(key)
+        if flag is None:
+            flag = torch.zeros(1, dtype=torch.int32, device=device)
+            _sf_flags[key] = flag
+        return flag
+
+
 def _launch_transform_sf(sf, mn, k, gran_mn, gran_k, psum_layout, tma_aligned: bool, k_psum_layout=None):
     """csrc/jit_kernels/transform_sf.hpp:15-105. With `tma_aligned` the column stride of the result is
     rounded up to 8 elements (what the GEMM's TMA descriptor needs); the public entry point never does that.
@@ -317,13 +349,18 @@ def _launch_transform_sf(sf, mn, k, gran_mn, gran_k, psum_layout, tma_aligned: b
     storage = torch.empty((batches, dst_cols, col_stride), dtype=torch.int16, device=sf.device)
     out = storage[:, :, :mn].transpose(-2, -1)
     if out.numel() and not get_dry_run() and not sf.is_meta:
+        flag = _sf_invalid_flag(sf.device) if is_fp32 else None
         rc = L.lib().dg_transform_sf_launch(
             sf.data_ptr(), int(is_fp32), sf.stride(-2), sf.stride(-1), sf.stride(0), sf.size(-2), sf.size(-1),
             storage.data_ptr(), col_stride, dst_cols * col_stride, mn, k32, gran_mn, gran_k // 32, batches,
             psum_layout.data_ptr() if psum_layout is not None else None, num_groups, MK_ALIGNMENT,
-            None, k_psum_layout.data_ptr() if k_psum_layout is not None else None, num_k_groups,
+            flag.data_ptr() if flag is not None else None,
+            k_psum_layout.data_ptr() if k_psum_layout is not None else None, num_k_groups,
             _stream_ptr(sf.device))
         L.check(rc)
+        if flag is not None and _DEBUG and int(flag.item()) != 0:
+            flag.zero_()
+            raise RuntimeError(_SF_INVALID_MESSAGE)
     return out.squeeze(0) if squeeze else out
 
 
@@ -425,6 +462,13 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
         return ws
 
 
+def _drop_workspaces(device_index: int) -> None:
+    """Forget the cached split-K scratch of a device (its zero invariant can no longer be trusted)."""
+    with _ws_lock:
+        for key in [k for k in _workspaces if k[0] == device_index]:
+            del _workspaces[key]
+
+
 def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recipe_a, recipe_b,
               grouped_layout, compiled_dims, disable_ue8m0_cast, expected_m=None, config=None):
     """csrc/apis/gemm.hpp:60-197 followed by the dispatch of :22-33."""
@@ -519,6 +563,7 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
     else:
         desc.epilogue = L.EPILOGUE_IDENTITY
     desc.num_sms = 0
+    desc.deterministic = int(_global['deterministic'])
 
     cfg = None
     if config is not None:
@@ -725,7 +770,19 @@ def fp8_einsum(expr, a, b, d, c=None, recipe=(1, 1, 32), epilogue=None, *, confi
 
 
 def device_status() -> int:
-    """0, or the code recorded by a kernel whose bounded wait gave up. Synchronises the device."""
+    """0, or the code of the first problem a kernel recorded since the last call: 101..107 = a bounded wait inside a
+    GEMM kernel gave up (its output is incomplete), 201 = a scale-factor transform met an FP32 scale that is negative
+    or not a power of two (the reference's device assert, transform_sf.hpp:13-21). Synchronises the device; the
+    record is cleared. After a wait that gave up the split-K scratch may hold partial sums, so it is dropped and
+    the next split-K launch starts from a fresh zeroed buffer."""
     out = C.c_int32(0)
     L.check(L.lib().dg_device_status(C.byref(out)))
-    return out.value
+    code = out.value
+    device = torch.cuda.current_device()
+    if code != 0:
+        _drop_workspaces(device)
+    flag = _sf_flags.get(device)
+    if flag is not None and int(flag.item()) != 0:
+        flag.zero_()
+        code = code or STATUS_INVALID_SCALE_FACTOR
+    return code

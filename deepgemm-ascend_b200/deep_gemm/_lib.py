@@ -37,6 +37,7 @@ class GemmDesc(C.Structure):
         ('bias', C.c_void_p),
         ('num_sms', C.c_uint32),
         ('sfd', C.c_void_p), ('sfd_stride', C.c_uint64),
+        ('deterministic', C.c_int32), ('reserved0', C.c_int32),
     ]
 
 
@@ -70,6 +71,11 @@ _PROTOTYPES = {
     'dg_pad_rows_launch': (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p]),
     'dg_l2_flush_launch': (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
     'dg_device_status': (C.c_int, [C.POINTER(C.c_int32)]),
+    'dg_plan_cache_stats': (None, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    'dg_sleep_launch': (C.c_int, [C.c_int64, C.c_uint32, C.c_int, C.c_void_p]),
+    'dg_set_overlap_launches': (C.c_int, [C.c_int]),
+    'dg_get_overlap_launches': (C.c_int, []),
+    'dg_debug_set_trace_buffer': (C.c_int, [C.c_void_p, C.c_size_t]),
     'dg_kernel_launch_count': (C.c_uint64, []),
     'dg_get_num_sms': (C.c_int, []),
     'dg_set_num_sms': (C.c_int, [C.c_int]),
@@ -79,7 +85,7 @@ _PROTOTYPES = {
 }
 
 STATIC_SCRATCH_BYTES = 4 << 20
-ABI_VERSION = 2
+ABI_VERSION = 3
 EXPORTED_SYMBOLS = tuple(_PROTOTYPES)
 _lib = None
 

@@ -63,3 +63,36 @@ def bench_events(fn, num_warmups: int = 10, num_tests: int = 30, flush_l2: bool 
     torch.cuda.synchronize(device)
     times = [s.elapsed_time(e) * 1e3 for s, e in zip(starts, ends)]
     return KernelProfile(sum(times) / len(times), min(times), max(times), num_tests)
+
+
+def bench_graph(launchers, num_warmups: int = 3, num_tests: int = 10) -> KernelProfile:
+    """Time a sequence of launches as one CUDA graph replayed `num_tests` times between one CUDA-event pair, and
+    return the mean duration per launch.
+
+    `launchers` are callables taking a raw stream pointer; each must work on operands of its own, and together they
+    must touch several times the L2 capacity, so that no launch finds its inputs cached (inputs larger than L2
+    instead of a flush kernel between launches). Timing a stream of launches this way leaves out the CUDA-event
+    records between kernels that `bench_events` pays per launch and lets consecutive kernels overlap their launch
+    latencies exactly as they do in an application that enqueues them back to back."""
+    device = torch.device('cuda', torch.cuda.current_device())
+    for fn in launchers:                                   # loads kernels, sets attributes: not capturable work
+        fn(torch.cuda.current_stream(device).cuda_stream)
+    torch.cuda.synchronize(device)
+    side = torch.cuda.Stream(device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        sptr = torch.cuda.current_stream(device).cuda_stream
+        for fn in launchers:
+            fn(sptr)
+    stream = torch.cuda.current_stream(device)
+    for _ in range(num_warmups):
+        graph.replay()
+    torch.cuda.synchronize(device)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(num_tests):
+        graph.replay()
+    end.record(stream)
+    torch.cuda.synchronize(device)
+    per_launch = start.elapsed_time(end) * 1e3 / (num_tests * len(launchers))
+    return KernelProfile(per_launch, per_launch, per_launch, num_tests * len(launchers))

@@ -68,7 +68,125 @@ class GroupedCase:
             raise RuntimeError(L.last_error())
 
 
-def run(args, rank, world, device, emit=None):
+def _flush_timed(lib, device, launch, steps, warmup=3):
+    """Mean microseconds of `launch(sptr)` over `steps` launches, each after an untimed write of a buffer larger
+    than L2, one CUDA-event pair per launch."""
+    stream = torch.cuda.current_stream(device)
+    sptr = stream.cuda_stream
+    flush = l2_flush_buffer(device)
+    for _ in range(warmup):
+        L.check(lib.dg_l2_flush_launch(flush.data_ptr(), flush.numel(), sptr))
+        launch(sptr)
+    torch.cuda.synchronize(device)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for e0, e1 in ev:
+        L.check(lib.dg_l2_flush_launch(flush.data_ptr(), flush.numel(), sptr))
+        e0.record(stream)
+        launch(sptr)
+        e1.record(stream)
+    torch.cuda.synchronize(device)
+    return sum(e0.elapsed_time(e1) for e0, e1 in ev) / steps * 1e3
+
+
+def _close(out: torch.Tensor, ref: torch.Tensor) -> bool:
+    import oracle
+    out, ref = out.cpu(), ref.cpu()
+    return bool(torch.isfinite(out.float()).all()) and oracle.calc_diff(out, ref) <= 1e-3 and oracle.max_rel_err(out, ref) <= 2e-2
+
+
+def _unpacked_scales(sf16: torch.Tensor, k: int) -> torch.Tensor:
+    """Required-layout int16 scales [..., MN, K64] (any strides) -> FP32 scales [..., MN, ceil(K/32)] on the host."""
+    import oracle
+    return oracle.unpack_required_sf(sf16.cpu().contiguous(), k)
+
+
+class MixedCase:
+    """FP8 x packed-FP4 GEMM "NN" (configuration 3): A [M, K] E4M3, B [K, N/2] packed E2M1 (uniform codes), per-32
+    UE8M0 scales already in the required layout, BF16 out."""
+
+    def __init__(self, device, seed=7, m=4096, n=7168, k=2048):
+        gen = torch.Generator(device=device).manual_seed(seed)
+        self.m, self.n, self.k = m, n, k
+        self.a = _codes((m, k), device, gen)
+        self.b = torch.randint(-128, 128, (k, n // 2), dtype=torch.int8, device=device, generator=gen)
+        self.sfa = _scales((), m, k, device, gen)
+        self.sfb = _scales((), n, k, device, gen)
+        self.d = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+        self.desc = _api._run_gemm(L.GEMM_NORMAL, self.a, self.b.transpose(0, 1), self.d, None, _api.Identity(), self.sfa,
+                                   self.sfb, (1, 1, 32), None, None, None, 'nk', False)
+        cfg = L.GemmConfig()
+        L.check(L.lib().dg_select_config(ctypes.byref(self.desc), ctypes.byref(cfg)))
+        self.config = cfg.as_dict()
+        self.flops = 2.0 * m * n * k
+        self.bytes = m * k + n * k // 2 + (m + n) * ((k + 63) // 64) * 2 + m * n * 2
+
+    def launch(self, lib, sptr):
+        L.check(lib.dg_gemm_launch(ctypes.byref(self.desc), None, None, 0, sptr))
+
+    def verify(self, rows: int = 16) -> bool:
+        import oracle
+        idx = torch.randperm(self.m, generator=torch.Generator().manual_seed(3))[:rows].sort().values
+        a_deq = oracle.dequantize(oracle.decode_e4m3(self.a[idx.to(self.a.device)].cpu()),
+                                  _unpacked_scales(self.sfa, self.k)[idx], 1, 32)
+        b_vals = oracle.decode_e2m1_packed(self.b.cpu(), axis=-1).transpose(0, 1)            # [N, K]
+        b_deq = oracle.dequantize(b_vals, _unpacked_scales(self.sfb, self.k), 1, 32)
+        return _close(self.d[idx.to(self.d.device)], oracle.gemm_ref(a_deq, b_deq, torch.bfloat16))
+
+
+def time_mixed(device, steps: int) -> dict:
+    lib = L.lib()
+    case = MixedCase(device)
+    us = _flush_timed(lib, device, lambda sptr: case.launch(lib, sptr), steps)
+    return {'us': us, 'tflops': case.flops / us / 1e6, 'gbs': case.bytes / us / 1e3, 'tiling': case.config,
+            'verified': case.verify()}
+
+
+def _verify_grouped(case: 'GroupedCase', sizes, masked: bool, samples: int = 6) -> bool:
+    """Row blocks of a few groups against the CPU oracle: the first 64 valid rows and the last 64 of each sampled group."""
+    import oracle
+    g_all = [g for g, s in enumerate(sizes) if s > 0]
+    picks = g_all[:: max(1, len(g_all) // samples)][:samples]
+    ok = True
+    psum_start = 0
+    starts = []
+    for s in sizes:
+        starts.append(psum_start)
+        psum_start = (psum_start + s + 255) // 256 * 256
+    for g in picks:
+        rows = sizes[g]
+        b_deq = oracle.dequantize(oracle.decode_e4m3(case.b[g].cpu()), _unpacked_scales(case.sfb[g], case.k), 1, 32)
+        for lo in {0, max(0, rows - 64)}:
+            hi = min(rows, lo + 64)
+            if masked:
+                a_blk, sf_blk, d_blk = case.a[g, lo:hi], case.sfa[g, lo:hi], case.d[g, lo:hi]
+            else:
+                r0 = starts[g]
+                a_blk, sf_blk, d_blk = case.a[r0 + lo:r0 + hi], case.sfa[r0 + lo:r0 + hi], case.d[r0 + lo:r0 + hi]
+            a_deq = oracle.dequantize(oracle.decode_e4m3(a_blk.cpu()), _unpacked_scales(sf_blk, case.k), 1, 32)
+            ok = ok and _close(d_blk, oracle.gemm_ref(a_deq, b_deq, torch.bfloat16))
+    return ok
+
+
+def time_grouped(device, sizes, steps: int, masked: bool) -> dict:
+    """Both (N, K) of the MoE configurations on one GPU for the given per-expert row counts."""
+    lib = L.lib()
+    shapes, flops, us_total, nbytes, ok = [], 0.0, 0.0, 0.0, True
+    for i, (n, k) in enumerate(NK_LIST):
+        case = GroupedCase(sizes, n, k, device, seed=100 + i, masked_max_m=256 if masked else 0)
+        us = _flush_timed(lib, device, lambda sptr: case.launch(lib, sptr), steps)
+        ok = ok and _verify_grouped(case, sizes, masked)
+        shapes.append({'rows': case.rows, 'valid_rows': case.valid_rows, 'n': n, 'k': k, 'us': round(us, 1),
+                       'tflops': round(case.flops / us / 1e6, 1), 'gbs': round(case.bytes / us / 1e3, 1),
+                       'block_n': case.config['block_n'], 'cta_group': case.config['cta_group']})
+        flops += case.flops
+        nbytes += case.bytes
+        us_total += us
+        del case
+        torch.cuda.empty_cache()
+    return {'shapes': shapes, 'tflops': flops / us_total / 1e6, 'gbs': nbytes / us_total / 1e3, 'verified': ok}
+
+
+def run(args, rank, world, device, emit=None, pk=None):
     if args.workload == 'mixed':
         return run_mixed(args, rank, world, device, emit)
     if args.workload == 'fp4':
@@ -77,19 +195,30 @@ def run(args, rank, world, device, emit=None):
         return run_bf16(args, rank, world, device, emit)
     if args.workload == 'quant':
         return run_quant(args, rank, world, device, emit)
+    return run_grouped(args, rank, world, device, emit, pk or {'bf16_tflops': 1590.0, 'hbm_gbs': 6650.0, 'source': 'fallback'})
+
+
+def run_grouped(args, rank, world, device, emit, pk):
+    """m-grouped contiguous (or masked) FP8 GEMM with a FIXED global expert count sharded over the ranks: every rank
+    owns a contiguous block of experts (`sharding.expert_range`) and runs the single-GPU kernel on its local psum
+    layout; nothing is exchanged on the data path. The NCCL all-gather of the outputs (equal, padded chunks) is timed
+    on its own. The end-to-end leg copies the rank's A, B and scales from pinned host memory, calls the public API and
+    copies D back, inside the timed region."""
+    import deep_gemm
+    from .sharding import expert_range
     lib = L.lib()
     stream = torch.cuda.current_stream(device)
     sptr = stream.cuda_stream
     flush = l2_flush_buffer(device)
     masked = args.workload == 'masked'
-    per_rank = getattr(args, 'experts_per_gpu', 0) or (32 if masked else 8)
+    g_total = getattr(args, 'experts', 0) or 32
     random.seed(1234)                       # the global problem is the same on every rank
-    g_total = per_rank * world
     if masked:
         sizes = [random.randint(0, 256) for _ in range(g_total)]
     else:
         sizes = [int(random.uniform(0.7, 1.3) * 8192) for _ in range(g_total)]
-    mine = sizes[rank * per_rank:(rank + 1) * per_rank]
+    g0, g1 = expert_range(g_total, world, rank)
+    mine = sizes[g0:g1]
     cases = [GroupedCase(mine, n, k, device, seed=100 * rank + i, masked_max_m=256 if masked else 0)
              for i, (n, k) in enumerate(NK_LIST)]
     torch.cuda.synchronize(device)
@@ -108,7 +237,8 @@ def run(args, rank, world, device, emit=None):
             if events is not None:
                 events[ci][1].record(stream)
 
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         step(None)
     barrier()
     ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in cases]
@@ -120,50 +250,119 @@ def run(args, rank, world, device, emit=None):
     launches = lib.dg_kernel_launch_count() - launches0
     per_case_us = [sum(ev[s][ci][0].elapsed_time(ev[s][ci][1]) for s in range(args.steps)) / args.steps * 1e3
                    for ci in range(len(cases))]
-    step_ms = torch.tensor([sum(per_case_us) / 1e3], dtype=torch.float64, device=device)
-    flops = torch.tensor([sum(c.flops for c in cases)], dtype=torch.float64, device=device)
+    verified = all(_verify_grouped(c, mine, masked, samples=2) for c in cases)
+
+    def reduce_max(x):
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        if world > 1:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return float(t.item())
+
+    def reduce_sum(x):
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        if world > 1:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.SUM)
+        return float(t.item())
+
+    gemm_ms = reduce_max(sum(per_case_us) / 1e3)
+    flops = reduce_sum(sum(c.flops for c in cases))
+    nbytes = reduce_sum(sum(c.bytes for c in cases))
+    verified = reduce_sum(0.0 if verified else 1.0) == 0.0
+
+    # ---- the optional gather of the outputs, timed separately (both (N, K), one after the other)
     gather_ms = None
-    if world > 1:
-        torch.distributed.all_reduce(step_ms, op=torch.distributed.ReduceOp.MAX)
-        torch.distributed.all_reduce(flops, op=torch.distributed.ReduceOp.SUM)
-        if getattr(args, 'gather', False):
-            # outputs have rank-dependent row counts: gather equal-sized padded chunks
-            rows = torch.tensor([cases[0].rows], dtype=torch.int64, device=device)
-            torch.distributed.all_reduce(rows, op=torch.distributed.ReduceOp.MAX)
-            chunk = torch.zeros(int(rows.item()), cases[0].n, dtype=torch.bfloat16, device=device)
-            chunk[:cases[0].rows].copy_(cases[0].d.reshape(-1, cases[0].n))
-            out = torch.empty(world * chunk.size(0), chunk.size(1), dtype=torch.bfloat16, device=device)
+    if world > 1 and not getattr(args, 'no_gather', False):
+        chunks, outs = [], []
+        for c in cases:
+            rows = int(reduce_max(float(c.rows)))
+            chunk = torch.zeros(rows, c.n, dtype=torch.bfloat16, device=device)
+            chunk[:c.rows].copy_(c.d.reshape(-1, c.n))
+            chunks.append(chunk)
+            outs.append(torch.empty(world * rows, c.n, dtype=torch.bfloat16, device=device))
+        for out, chunk in zip(outs, chunks):
             torch.distributed.all_gather_into_tensor(out, chunk)
-            barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            torch.distributed.all_gather_into_tensor(out, chunk)
-            e1.record(stream)
-            barrier()
-            g_ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
-            torch.distributed.all_reduce(g_ms, op=torch.distributed.ReduceOp.MAX)
-            gather_ms = float(g_ms.item())
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
+        e0.record(stream)
+        for _ in range(reps):
+            for out, chunk in zip(outs, chunks):
+                torch.distributed.all_gather_into_tensor(out, chunk)
+        e1.record(stream)
+        barrier()
+        gather_ms = reduce_max(e0.elapsed_time(e1) / reps)
+        gathered_bytes = sum(o.numel() * 2 for o in outs)
+        del chunks, outs
+
+    # ---- end to end: host buffers -> device, the public API call, D back to the host
+    hosts = []
+    for c in cases:
+        hosts.append({'a': c.a.view(torch.uint8).cpu().pin_memory(), 'b': c.b.view(torch.uint8).cpu().pin_memory(),
+                      # (scales stay in the required layout: MN contiguous, so the host copy is of the transposed view)
+                      'sfa': c.sfa.transpose(-2, -1).contiguous().cpu().pin_memory(),
+                      'sfb': c.sfb.transpose(-2, -1).contiguous().cpu().pin_memory(),
+                      'd': torch.empty(c.d.shape, dtype=torch.bfloat16).pin_memory()})
+    sfa_dev = [torch.empty_like(c.sfa.transpose(-2, -1).contiguous()) for c in cases]
+    sfb_dev = [torch.empty_like(c.sfb.transpose(-2, -1).contiguous()) for c in cases]
+    h2d = sum(h['a'].numel() + h['b'].numel() + 2 * (h['sfa'].numel() + h['sfb'].numel()) for h in hosts)
+    d2h = sum(h['d'].numel() * 2 for h in hosts)
+
+    def e2e_step():
+        for c, h, sa, sb in zip(cases, hosts, sfa_dev, sfb_dev):
+            c.a.view(torch.uint8).copy_(h['a'], non_blocking=True)
+            c.b.view(torch.uint8).copy_(h['b'], non_blocking=True)
+            sa.copy_(h['sfa'], non_blocking=True)
+            sb.copy_(h['sfb'], non_blocking=True)
+            sa_t, sb_t = sa.transpose(-2, -1), sb.transpose(-2, -1)
+            if masked:
+                deep_gemm.m_grouped_fp8_gemm_nt_masked((c.a, sa_t), (c.b, sb_t), c.d, c.layout, max(1, c.valid_rows // len(mine)))
+            else:
+                deep_gemm.m_grouped_fp8_gemm_nt_contiguous((c.a, sa_t), (c.b, sb_t), c.d, c.layout)
+            h['d'].copy_(c.d, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    import time
+    e2e_steps = max(1, min(args.steps, 3))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = reduce_max((time.perf_counter() - t0) / e2e_steps)
     status = _api.device_status()
     if rank != 0:
         return
-    value = float(flops.item()) / (float(step_ms.item()) * 1e-3) / 1e12
+    value = flops / (gemm_ms * 1e-3) / 1e12
+    fp8_peak = 2.0 * pk['bf16_tflops'] * world
     line = {
         'metric': 'fp8_block_scaled_gemm_tflops', 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world,
-        'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': float(step_ms.item()),
-        'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+        'steps': args.steps, 'warmup': warmup, 'ms_per_step': gemm_ms,
+        'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
         'dtype': 'fp8_e4m3 x ue8m0, fp32 accumulate', 'data': 'synthetic',
-        'config': {'workload': ('m-grouped masked FP8 GEMM, %d experts x max_m 256 per GPU' if masked else
-                                'm-grouped contiguous FP8 GEMM (psum layout), %d experts per GPU, m ~ U(0.7,1.3) x 8192')
-                               % per_rank + ', (N,K) in ' + str(NK_LIST) + ', BF16 out',
-                   'sharding': 'experts, contiguous blocks per rank, no data-path collective',
+        'config': {'workload': ('m-grouped masked FP8 GEMM, %d experts x max_m 256, valid rows ~ U[0,256]' if masked else
+                                'm-grouped contiguous FP8 GEMM (psum layout), %d experts in total, rows per expert ~ U(0.7,1.3) x 8192')
+                               % g_total + ', (N,K) in ' + str(NK_LIST) + ', BF16 out',
+                   'sharding': 'experts in contiguous blocks over %d rank(s), no data-path collective' % world,
                    'l2': 'flushed before every GEMM, untimed', 'flops': 'valid rows only'},
+        'verified': verified,
+        'gemm_ms': gemm_ms, 'gather_ms': gather_ms,
+        'gemm_plus_gather_ms': (gemm_ms + gather_ms) if gather_ms is not None else None,
+        'roofline': ({'bound': 'hbm', 'achieved': nbytes / (gemm_ms * 1e-3) / 1e9, 'peak': pk['hbm_gbs'] * world, 'unit': 'GB/s',
+                      'frac': nbytes / (gemm_ms * 1e-3) / 1e9 / (pk['hbm_gbs'] * world), 'traffic': None,
+                      'peak_source': 'copy bandwidth of MEASURED_PEAKS.json x ranks (%s)' % pk['source']} if masked else
+                     {'bound': 'tensor', 'achieved': value, 'peak': fp8_peak, 'unit': 'TFLOP/s', 'frac': value / fp8_peak,
+                      'frac_of_nominal': value / (4500.0 * world), 'traffic': None,
+                      'peak_source': '2 x the BF16 burst figure of MEASURED_PEAKS.json x ranks (%s): derived' % pk['source']}),
+        'e2e': {'value': flops / e2e_s / 1e12, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
+                'steps': e2e_steps, 'bytes_are': 'per rank (rank 0)'},
         'gpu_launches': int(launches), 'device_status': status,
         'shapes': [{'rows': c.rows, 'valid_rows': c.valid_rows, 'n': c.n, 'k': c.k, 'us': round(per_case_us[i], 1),
                     'tflops': round(c.flops / per_case_us[i] / 1e6, 1), 'gbs': round(c.bytes / per_case_us[i] / 1e3, 1),
                     'block_n': c.config['block_n'], 'cta_group': c.config['cta_group']} for i, c in enumerate(cases)],
+        'shapes_are': 'rank 0',
     }
     if gather_ms is not None:
-        line['gather_ms'] = gather_ms
+        line['gather_gbs_per_rank'] = gathered_bytes * (world - 1) / world / (gather_ms * 1e-3) / 1e9
     (emit or (lambda l: print(json.dumps(l), flush=True)))(line)
 
 
@@ -171,47 +370,18 @@ def run_mixed(args, rank, world, device, emit=None):
     """FP8 x packed-FP4 GEMM "NN": A [M,K] E4M3 with per-128 scales, B [K, N/2] packed E2M1 (uniform codes) with
     per-32 scales, BF16 out; M=4096, N=7168, K=2048. Normalised by the FP8 peak (the MMA runs on E4M3 operands)."""
     lib = L.lib()
-    stream = torch.cuda.current_stream(device)
-    sptr = stream.cuda_stream
-    flush = l2_flush_buffer(device)
-    gen = torch.Generator(device=device).manual_seed(7 + rank)
-    m, n, k = 4096, 7168, 2048
-    a = _codes((m, k), device, gen)
-    b = torch.randint(-128, 128, (k, n // 2), dtype=torch.int8, device=device, generator=gen)
-    sfa = _scales((), m, k, device, gen)
-    sfb = _scales((), n, k, device, gen)
-    d = torch.empty(m, n, dtype=torch.bfloat16, device=device)
-    desc = _api._run_gemm(L.GEMM_NORMAL, a, b.transpose(0, 1), d, None, _api.Identity(), sfa, sfb,
-                          (1, 1, 32), None, None, None, 'nk', False)
-    cfg = L.GemmConfig()
-    L.check(lib.dg_select_config(ctypes.byref(desc), ctypes.byref(cfg)))
-
-    def once(events=None):
-        L.check(lib.dg_l2_flush_launch(flush.data_ptr(), flush.numel(), sptr))
-        if events:
-            events[0].record(stream)
-        L.check(lib.dg_gemm_launch(ctypes.byref(desc), None, None, 0, sptr))
-        if events:
-            events[1].record(stream)
-
-    for _ in range(max(args.warmup, 3)):
-        once()
-    torch.cuda.synchronize(device)
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    for e in ev:
-        once(e)
-    torch.cuda.synchronize(device)
-    us = sum(a_.elapsed_time(b_) for a_, b_ in ev) / args.steps * 1e3
+    case = MixedCase(device, seed=7 + rank)
+    us = _flush_timed(lib, device, lambda sptr: case.launch(lib, sptr), args.steps, max(args.warmup, 3))
     if rank != 0:
         return
-    flops = 2.0 * m * n * k
-    nbytes = m * k + n * k // 2 + (m + n) * ((k + 63) // 64) * 2 + m * n * 2
-    line = {'metric': 'fp8_block_scaled_gemm_tflops', 'value': world * flops / us / 1e6, 'unit': 'TFLOP/s', 'n_gpus': world,
+    m, n, k = case.m, case.n, case.k
+    line = {'metric': 'fp8_block_scaled_gemm_tflops', 'value': world * case.flops / us / 1e6, 'unit': 'TFLOP/s', 'n_gpus': world,
             'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': us / 1e3, 'higher_is_better': True,
             'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp8_e4m3 x fp4_e2m1 (decoded to e4m3), ue8m0 scales',
             'data': 'synthetic',
-            'config': {'workload': 'mixed FP8xFP4 GEMM NN, M=4096 N=7168 K=2048, BF16 out', 'l2': 'flushed, untimed'},
-            'gbs': nbytes / us / 1e3, 'tiling': cfg.as_dict(), 'device_status': _api.device_status()}
+            'config': {'workload': 'mixed FP8xFP4 GEMM NN, M=%d N=%d K=%d, BF16 out' % (m, n, k), 'l2': 'flushed, untimed'},
+            'gbs': case.bytes / us / 1e3, 'tiling': case.config, 'verified': case.verify(),
+            'device_status': _api.device_status()}
     (emit or (lambda l: print(json.dumps(l), flush=True)))(line)
 
 

@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define DG_B200_ABI_VERSION 2
+#define DG_B200_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #pragma GCC visibility push(default)
@@ -113,6 +113,11 @@ typedef struct {
      * element, element (row, col) at sfd[col * sfd_stride + row]; batch g owns columns [g*N/64, (g+1)*N/64) */
     int16_t* sfd;
     uint64_t sfd_stride;
+    /* use_deterministic_algorithms, csrc/apis/runtime.hpp:56-62: non-zero keeps the heuristic away from every tiling
+     * whose result depends on timing (split-K through the FP32 workspace, which adds partial sums in arrival order)
+     * and makes an explicit config that asks for one an error. Everything else is bit-reproducible as it is. */
+    int32_t deterministic;
+    int32_t reserved0;                        /* must be 0 */
 } dg_gemm_desc_t;
 
 /* Tiling chosen for a problem. Replaces GemmConfig, csrc/jit_kernels/gemm_config.hpp:98-121. */
@@ -150,6 +155,11 @@ size_t dg_gemm_workspace_bytes(const dg_gemm_desc_t* desc, const dg_gemm_config_
  * `config` may be NULL (the heuristic is used). */
 int dg_gemm_launch(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config,
                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* dg_gemm_launch memoises what it derives on the host (validation, tiling, encoded tensor maps, kernel arguments) on
+ * the bytes of (desc, config, workspace, device, SM limit): a call that repeats an earlier one only enqueues. The
+ * reference re-runs its search per call (csrc/jit_kernels/heuristics.hpp:593). Counters for tests and benchmarks. */
+void dg_plan_cache_stats(uint64_t* hits, uint64_t* misses);
 
 /*
  * Split-K GEMM for callers that cannot allocate device memory. No counterpart in the reference.
@@ -233,6 +243,25 @@ int dg_device_status(int32_t* out_status);
 /* Number of kernels this library has enqueued in this process (all devices, all threads). Benchmarks
  * read it before and after a timed region to report how many of the library's kernels ran. */
 uint64_t dg_kernel_launch_count(void);
+
+/* Busy-wait marker kernel, one block per SM for `sleep_cycles` SM clock cycles (at most 4e9, about two seconds):
+ * replaces npu_sleep, csrc/apis/runtime.hpp:64-79 + deep_gemm/include/deep_gemm/sleep.hpp:5-15. `marker` only selects
+ * the kernel's name (sleep_kernel<0>, <1>, <2>; any other value shares <3>) so that a profiler can find begin / end
+ * marks; `num_blocks` is the grid size (the reference launches one block per core). */
+int dg_sleep_launch(int64_t sleep_cycles, uint32_t marker, int num_blocks, void* stream);
+
+/* GEMM kernels are launched with programmatic stream serialisation by default: a GEMM may be scheduled while the
+ * kernel in front of it in the stream is still draining, runs its set-up (barriers, TMEM allocation, descriptor
+ * prefetch) and then waits for that kernel before it touches operands or outputs, so results are unchanged. 0 turns
+ * it off (also: environment DG_OVERLAP_LAUNCHES=0). No counterpart in the reference. */
+int dg_set_overlap_launches(int enabled);
+int dg_get_overlap_launches(void);
+
+/* Debugging aid, no counterpart in the reference: hand the library a device buffer of at least 256 bytes per CTA and
+ * every GEMM kernel launched on the current device afterwards records per-CTA timestamps in it (32 slots of 8 bytes
+ * per CTA: kernel entry, set-up done, first operands landed, last MMA, epilogue done, kernel end, ...); NULL stops it. The
+ * library neither allocates, reads nor synchronises for this. */
+int dg_debug_set_trace_buffer(void* device_buffer, size_t bytes);
 
 /* Runtime knobs, csrc/apis/runtime.hpp:12-62 / csrc/jit/jit.hpp:18-76. */
 int dg_get_num_sms(void);

@@ -1,0 +1,188 @@
+"""Runtime behaviour around the GEMM on the GPU: invalid scale factors, the sleep marker kernel, deterministic mode,
+the launch-plan cache, operands and outputs that are column slices of wider tensors, launch overlap on and off."""
+
+import ctypes as C
+
+import pytest
+import torch
+
+import deep_gemm
+import oracle
+from deep_gemm import _lib as L
+from helpers import assert_close, seed_all, uniform_fp8, with_major
+
+pytestmark = pytest.mark.gpu
+
+
+def test_invalid_fp32_scale_factor_is_reported_not_trapped():
+    """The reference asserts on the device when an FP32 scale is negative or not a power of two
+    (deep_gemm/include/deep_gemm/transform_sf.hpp:13-21). Here the transform records it and `device_status()`
+    reports code 201 once; the context stays usable."""
+    assert deep_gemm.device_status() == 0
+    mn, k = 256, 512
+    sf = torch.ones(mn, k // 32, device='cuda')
+    deep_gemm.transform_sf_into_required_layout(sf, mn, k, (1, 1, 32), is_sfa=True)
+    assert deep_gemm.device_status() == 0
+    for bad in (1.5, -1.0):
+        sf2 = sf.clone()
+        sf2[17, 3] = bad
+        deep_gemm.transform_sf_into_required_layout(sf2, mn, k, (1, 1, 32), is_sfa=True)
+        assert deep_gemm.device_status() == deep_gemm._api.STATUS_INVALID_SCALE_FACTOR
+        assert deep_gemm.device_status() == 0                # reported once
+    # the same through a GEMM call that is handed FP32 scales
+    seed_all(1)
+    a, sfa, _ = uniform_fp8((128, 512), (1, 32))
+    b, sfb, _ = uniform_fp8((256, 512), (1, 32))
+    sfa[5, 2] = 3.0
+    d = torch.empty(128, 256, dtype=torch.bfloat16, device='cuda')
+    deep_gemm.fp8_gemm_nt((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d)
+    assert deep_gemm.device_status() == deep_gemm._api.STATUS_INVALID_SCALE_FACTOR
+    # and the library still works afterwards
+    sfa[5, 2] = 0.5
+    deep_gemm.fp8_gemm_nt((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), d)
+    assert deep_gemm.device_status() == 0
+
+
+def test_npu_sleep_runs_and_takes_about_the_requested_time():
+    """csrc/apis/runtime.hpp:64-79: one block per SM spinning for the given number of cycles."""
+    deep_gemm.npu_sleep(0)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    deep_gemm.npu_sleep(2_000_000, marker=1)                # about 1 ms at 1.9 GHz
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    assert 0.5 < ms < 20.0, ms
+    with pytest.raises(RuntimeError, match='sleep_cycles'):
+        deep_gemm.npu_sleep(10 ** 10)
+    assert deep_gemm.device_status() == 0
+
+
+def test_deterministic_mode_gives_the_same_bits_every_time():
+    """MN-major B with few rows and a long K is where the heuristic otherwise splits K through the FP32 workspace
+    (partial sums added in arrival order). With use_deterministic_algorithms(True) repeated runs agree bit for bit
+    and still match the oracle."""
+    seed_all(5)
+    m, n, k = 128, 512, 16384
+    a, sfa, a_ref = uniform_fp8((m, k), (1, 32))
+    b, sfb, b_ref = uniform_fp8((n, k), (1, 32))
+    ref = oracle.gemm_ref(a_ref, b_ref, torch.float32)
+    b_dev = with_major(b, True).cuda()
+    a_arg, b_arg = (a.cuda(), sfa.cuda()), (b_dev.transpose(0, 1), sfb.cuda().transpose(0, 1))
+    deep_gemm.use_deterministic_algorithms(True)
+    try:
+        outs = []
+        for _ in range(4):
+            d = torch.empty(m, n, dtype=torch.float32, device='cuda')
+            deep_gemm.fp8_gemm_nn(a_arg, b_arg, d)
+            outs.append(d)
+        assert deep_gemm.device_status() == 0
+        assert all(torch.equal(outs[0], o) for o in outs[1:])
+        assert_close(outs[0], ref, 'deterministic nn')
+        # K-major B takes the cluster reduction (rank order), with or without the flag
+        outs = []
+        for _ in range(3):
+            d = torch.empty(m, n, dtype=torch.float32, device='cuda')
+            deep_gemm.fp8_gemm_nt(a_arg, (b.cuda(), sfb.cuda()), d)
+            outs.append(d)
+        assert all(torch.equal(outs[0], o) for o in outs[1:])
+        assert_close(outs[0], ref, 'deterministic nt')
+    finally:
+        deep_gemm.use_deterministic_algorithms(False)
+
+
+def test_repeated_calls_reuse_the_launch_plan():
+    seed_all(2)
+    a, sfa, a_ref = uniform_fp8((256, 1024), (1, 32))
+    b, sfb, b_ref = uniform_fp8((384, 1024), (1, 32))
+    a_dev, b_dev = a.cuda(), b.cuda()
+    sfa_dev = deep_gemm.transform_sf_into_required_layout(sfa.cuda(), 256, 1024, (1, 1, 32), is_sfa=True)
+    sfb_dev = deep_gemm.transform_sf_into_required_layout(sfb.cuda(), 384, 1024, (1, 1, 32), is_sfa=False)
+    d = torch.empty(256, 384, dtype=torch.bfloat16, device='cuda')
+    hits, misses = C.c_uint64(), C.c_uint64()
+    lib = L.lib()
+    deep_gemm.fp8_gemm_nt((a_dev, sfa_dev), (b_dev, sfb_dev), d)
+    lib.dg_plan_cache_stats(C.byref(hits), C.byref(misses))
+    h0, m0 = hits.value, misses.value
+    for _ in range(5):
+        d.fill_(float('nan'))
+        deep_gemm.fp8_gemm_nt((a_dev, sfa_dev), (b_dev, sfb_dev), d)
+    lib.dg_plan_cache_stats(C.byref(hits), C.byref(misses))
+    assert hits.value == h0 + 5 and misses.value == m0
+    assert_close(d, oracle.gemm_ref(a_ref, b_ref, torch.bfloat16), 'cached plan')
+    # another output buffer is another plan
+    d2 = torch.empty(256, 384, dtype=torch.bfloat16, device='cuda')
+    deep_gemm.fp8_gemm_nt((a_dev, sfa_dev), (b_dev, sfb_dev), d2)
+    lib.dg_plan_cache_stats(C.byref(hits), C.byref(misses))
+    assert misses.value == m0 + 1
+    assert torch.equal(d.view(torch.int16), d2.view(torch.int16))
+    assert deep_gemm.device_status() == 0
+
+
+@pytest.mark.parametrize('m,n,k,out', [(128, 512, 2048, torch.bfloat16), (4096, 1024, 1024, torch.bfloat16),
+                                       (300, 520, 1024, torch.float32)])
+def test_output_and_operands_as_column_slices_of_wider_tensors(m, n, k, out):
+    """Dense N-sharding writes D[:, n0:n1] of a wider D (outer_stride_d > n; csrc/jit_kernels/gemm_config.hpp:68-75);
+    A and B may be K-slices of wider tensors. Columns outside the slice must stay untouched."""
+    seed_all(m + n)
+    a, sfa, a_ref = uniform_fp8((m, k), (1, 32))
+    b, sfb, b_ref = uniform_fp8((n, k), (1, 32))
+    ref = oracle.gemm_ref(a_ref, b_ref, out)
+    # D as columns [n0, n0 + n) of a tensor three slabs wide
+    n0 = n + 64
+    wide_d = torch.full((m, 3 * n + 128), 7.0, dtype=out, device='cuda')
+    d = wide_d[:, n0:n0 + n]
+    # A and B as column ranges of wider byte tensors
+    wide_a = torch.zeros(m, k + 256, dtype=torch.uint8, device='cuda')
+    wide_a[:, 128:128 + k] = a.view(torch.uint8).cuda()
+    wide_b = torch.zeros(n, 2 * k, dtype=torch.uint8, device='cuda')
+    wide_b[:, k:] = b.view(torch.uint8).cuda()
+    a_arg = (wide_a[:, 128:128 + k].view(torch.float8_e4m3fn), sfa.cuda())
+    b_arg = (wide_b[:, k:].view(torch.float8_e4m3fn), sfb.cuda())
+    deep_gemm.fp8_gemm_nt(a_arg, b_arg, d)
+    assert deep_gemm.device_status() == 0
+    assert_close(d, ref, f'column slices {m}x{n}x{k}')
+    assert bool((wide_d[:, :n0] == 7.0).all()) and bool((wide_d[:, n0 + n:] == 7.0).all()), 'columns outside the slab were written'
+    # accumulate into the slab
+    if out == torch.float32:
+        c = torch.randn(m, n)
+        d.copy_(c)
+        deep_gemm.fp8_gemm_nt(a_arg, b_arg, d, c=d)
+        assert_close(d, oracle.gemm_ref(a_ref, b_ref, out, c=c), 'column slab accumulate')
+        assert bool((wide_d[:, :n0] == 7.0).all()) and bool((wide_d[:, n0 + n:] == 7.0).all())
+
+
+def test_results_do_not_depend_on_launch_overlap():
+    """GEMMs queued back to back, each reading the previous one's output as its A operand: with programmatic
+    dependent launch (the default) a kernel starts before its predecessor has finished and must still see all of
+    its output. Same bits with the overlap switched off."""
+    seed_all(9)
+    m, n, k = 128, 512, 512
+    x, sfx, _ = uniform_fp8((m, k), (1, 32))
+    ws = [uniform_fp8((n, k), (1, 32)) for _ in range(6)]
+    lib = L.lib()
+
+    def chain():
+        cur = (x.cuda(), sfx.cuda())
+        outs = []
+        for w, sfw, _ in ws:
+            d = torch.empty(m, n, dtype=torch.bfloat16, device='cuda')
+            deep_gemm.fp8_gemm_nt(cur, (w.cuda(), sfw.cuda()), d)
+            outs.append(d)
+            # next A: the output's bytes reinterpreted as E4M3 codes (NaN codes masked), unit scales
+            codes = d.view(torch.uint8).reshape(m, 2 * n)[:, :k] & 0x77
+            cur = (codes.view(torch.float8_e4m3fn), torch.ones(m, k // 32, device='cuda'))
+        torch.cuda.synchronize()
+        return outs
+
+    assert lib.dg_get_overlap_launches() == 1
+    first = chain()
+    try:
+        lib.dg_set_overlap_launches(0)
+        second = chain()
+    finally:
+        lib.dg_set_overlap_launches(1)
+    assert deep_gemm.device_status() == 0
+    for x1, x2 in zip(first, second):
+        assert torch.equal(x1.view(torch.int16), x2.view(torch.int16))

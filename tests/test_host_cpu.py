@@ -37,12 +37,12 @@ def test_library_exports_every_declared_symbol():
     for name in sorted(declared):
         assert hasattr(handle, name), f'{name} is declared but not exported'
     assert declared == set(L.EXPORTED_SYMBOLS)
-    assert L.lib().dg_abi_version() == L.ABI_VERSION == 2
+    assert L.lib().dg_abi_version() == L.ABI_VERSION == 3
 
 
 def test_struct_sizes_match_the_header():
-    # 5 pointers, 8 x 4-byte, 10 x 8-byte, 2 x 4, pointer, 2 x 4, 2 x 4, pointer, 4 (+4 padding), pointer, 8
-    assert ctypes.sizeof(L.GemmDesc) == 216
+    # 5 pointers, 8 x 4-byte, 10 x 8-byte, 2 x 4, pointer, 2 x 4, 2 x 4, pointer, 4 (+4 padding), pointer, 8, 2 x 4
+    assert ctypes.sizeof(L.GemmDesc) == 224
     assert ctypes.sizeof(L.GemmConfig) == 64
 
 
@@ -182,3 +182,72 @@ def test_c_abi_validation_messages():
     forced.block_n, forced.cta_group, forced.split_k = 100, 1, 1
     assert lib.dg_gemm_dry_run(ctypes.byref(_desc(128, 256, 256)), ctypes.byref(forced)) == L.DG_ERR_INVALID
     assert 'block_n' in L.last_error()
+
+
+def test_wide_tile_with_split_k_is_rejected():
+    """A tile wider than 256 columns is walked by tile index alone; with K splits the walk would mix the two up."""
+    lib = L.lib()
+    forced = L.GemmConfig()
+    forced.block_n, forced.cta_group, forced.split_k = 448, 2, 2
+    assert lib.dg_gemm_dry_run(ctypes.byref(_desc(4096, 4096, 4096)), ctypes.byref(forced)) == L.DG_ERR_INVALID
+    assert 'cannot be combined with split_k' in L.last_error()
+    forced.split_k = 1
+    assert lib.dg_gemm_dry_run(ctypes.byref(_desc(4096, 4096, 4096)), ctypes.byref(forced)) == 0, L.last_error()
+
+
+def test_deterministic_flag_keeps_away_from_arrival_order_reductions():
+    """use_deterministic_algorithms (csrc/apis/runtime.hpp:56-62): split-K through the FP32 workspace adds partial
+    sums in arrival order, so the heuristic must not pick it and an explicit request for it is an error; the
+    cluster reduction (rank order) stays available."""
+    lib = L.lib()
+    for m, n, k, major_b in ((128, 512, 16384, L.MAJOR_MN), (64, 2112, 7168, L.MAJOR_K), (128, 256, 32768, L.MAJOR_MN)):
+        desc = _desc(m, n, k, major_b=major_b, deterministic=1)
+        if major_b == L.MAJOR_MN:
+            desc.outer_stride_b = n
+        cfg = L.GemmConfig()
+        assert lib.dg_select_config(ctypes.byref(desc), ctypes.byref(cfg)) == 0, L.last_error()
+        c = cfg.as_dict()
+        assert c['split_k'] == 1 or c['cluster_split'] == 1
+        assert lib.dg_gemm_workspace_bytes(ctypes.byref(desc), ctypes.byref(cfg)) == 0
+    forced = L.GemmConfig()
+    forced.block_n, forced.cta_group, forced.split_k = 128, 1, 4
+    desc = _desc(128, 512, 4096, deterministic=1)
+    assert lib.dg_gemm_dry_run(ctypes.byref(desc), ctypes.byref(forced)) == L.DG_ERR_INVALID
+    assert 'deterministic' in L.last_error()
+    forced.reserved[3] = 1
+    assert lib.dg_gemm_dry_run(ctypes.byref(desc), ctypes.byref(forced)) == 0, L.last_error()
+    # the Python knob reaches the descriptor
+    deep_gemm.use_deterministic_algorithms(True)
+    try:
+        a, b = _meta_pair(128, 4096), _meta_pair(512, 4096)
+        d = torch.empty(128, 512, dtype=torch.bfloat16, device='meta')
+        with pytest.raises(RuntimeError, match='deterministic'):
+            deep_gemm.fp8_gemm_nt(a, b, d, config={'block_n': 128, 'cta_group': 1, 'split_k': 4})
+        deep_gemm.fp8_gemm_nt(a, b, d)
+    finally:
+        deep_gemm.use_deterministic_algorithms(False)
+    assert deep_gemm.get_deterministic_algorithms() is False
+
+
+def test_status_report_drops_the_split_k_scratch():
+    """After a kernel reported a wait that gave up, the cached split-K scratch of that device may hold partial sums:
+    the host layer must forget it so that the next split-K launch gets a fresh zeroed buffer."""
+    from deep_gemm import _api
+    _api._workspaces[(0, 123)] = object()
+    _api._workspaces[(0, 456)] = object()
+    _api._workspaces[(1, 123)] = object()
+    try:
+        _api._drop_workspaces(0)
+        assert list(_api._workspaces) == [(1, 123)]
+    finally:
+        _api._workspaces.clear()
+
+
+def test_npu_sleep_and_init_exist_and_dry_run_is_a_no_op():
+    deep_gemm.init('', '')
+    deep_gemm.npu_sleep(0)                      # dry run (autouse fixture): nothing is launched
+    deep_gemm.npu_sleep(1000, marker=1)
+    lib = L.lib()
+    assert lib.dg_sleep_launch(-1, 0, 148, None) == L.DG_ERR_INVALID
+    assert lib.dg_sleep_launch(5 * 10 ** 9, 0, 148, None) == L.DG_ERR_INVALID
+    assert 'sleep_cycles' in L.last_error()

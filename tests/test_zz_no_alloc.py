@@ -14,6 +14,7 @@ import pytest
 import torch
 
 import deep_gemm
+import oracle
 from deep_gemm import _api
 from deep_gemm import _lib as L
 from helpers import assert_close, seed_all, uniform_fp8
@@ -29,19 +30,23 @@ def _split_k_config(split: int, block_n: int) -> L.GemmConfig:
 
 def _case(m, n, k, seed):
     seed_all(seed)
-    a, sfa, _ = uniform_fp8((m, k), (1, 32))
-    b, sfb, _ = uniform_fp8((n, k), (1, 32))
+    a, sfa, a_ref = uniform_fp8((m, k), (1, 32))
+    b, sfb, b_ref = uniform_fp8((n, k), (1, 32))
+    ref = oracle.gemm_ref(a_ref, b_ref, torch.bfloat16)
     a, b = a.cuda(), b.cuda()
     sfa = deep_gemm.transform_sf_into_required_layout(sfa.cuda(), m, k, (1, 1, 32), is_sfa=True)
     sfb = deep_gemm.transform_sf_into_required_layout(sfb.cuda(), n, k, (1, 1, 32), is_sfa=False)
-    return a, sfa, b, sfb
+    return a, sfa, b, sfb, ref
 
 
 def test_static_scratch_matches_workspace_entry_point_twice():
+    """Two calls in a row (the array is shared and keeps the first call's contents), each compared with the ordinary
+    entry point and with the CPU oracle. Free device memory as the driver reports it (which sees every allocation,
+    not only torch's) must not move across a call once the kernels are loaded."""
     lib = L.lib()
     stream = torch.cuda.current_stream().cuda_stream
     for call, (m, n, k, split, bn) in enumerate([(128, 640, 4096, 4, 128), (96, 1000, 2048, 8, 96)]):
-        a, sfa, b, sfb = _case(m, n, k, seed=10 + call)
+        a, sfa, b, sfb, ref = _case(m, n, k, seed=10 + call)
         d_ref = torch.full((m, n), float('nan'), dtype=torch.bfloat16, device='cuda')
         d_new = torch.full((m, n), float('nan'), dtype=torch.bfloat16, device='cuda')
         config = {'block_n': bn, 'cta_group': 1, 'split_k': split}
@@ -51,17 +56,44 @@ def test_static_scratch_matches_workspace_entry_point_twice():
         # new entry point: same descriptor, other output, no workspace argument at all
         desc.d = d_new.data_ptr()
         cfg = _split_k_config(split, bn)
-        before = torch.cuda.memory_allocated()
+        L.check(lib.dg_gemm_launch_static_scratch(C.byref(desc), C.byref(cfg), stream))      # loads what it needs
+        torch.cuda.synchronize()
+        d_new.fill_(float('nan'))
+        free_before, torch_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
         L.check(lib.dg_gemm_launch_static_scratch(C.byref(desc), C.byref(cfg), stream))
-        assert torch.cuda.memory_allocated() == before
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before and torch.cuda.memory_allocated() == torch_before
         assert deep_gemm.device_status() == 0
-        assert_close(d_new, d_ref, f'static scratch, call {call}')
+        assert_close(d_new, d_ref, f'static scratch against the workspace entry point, call {call}')
+        assert_close(d_new, ref, f'static scratch against the oracle, call {call}')
+
+
+def test_static_scratch_with_the_heuristic_and_with_the_cluster_reduction():
+    """`config = NULL` (the library picks the tiling) on a few-rows, long-K shape, and an explicit cluster split-K
+    (which needs no scratch at all): both must go through and match the oracle."""
+    lib = L.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    m, n, k = 64, 512, 8192
+    a, sfa, b, sfb, ref = _case(m, n, k, seed=21)
+    d = torch.full((m, n), float('nan'), dtype=torch.bfloat16, device='cuda')
+    desc = _api._run_gemm(L.GEMM_NORMAL, a, b, d, None, _api.Identity(), sfa, sfb, (1, 1, 32), None, None,
+                          None, 'nk', False)
+    assert_close(d, ref, 'ordinary entry point')
+    d.fill_(float('nan'))
+    L.check(lib.dg_gemm_launch_static_scratch(C.byref(desc), None, stream))
+    assert_close(d, ref, 'static scratch, heuristic tiling')
+    cfg = _split_k_config(4, 128)
+    cfg.reserved[3] = 1
+    d.fill_(float('nan'))
+    L.check(lib.dg_gemm_launch_static_scratch(C.byref(desc), C.byref(cfg), stream))
+    assert_close(d, ref, 'static scratch entry point, cluster reduction')
+    assert deep_gemm.device_status() == 0
 
 
 def test_static_scratch_rejects_problems_beyond_its_size():
     lib = L.lib()
     m, n, k = 128, 16384, 1024                      # 128 x 16384 x 4 bytes = 8 MiB of partial sums > 4 MiB
-    a, sfa, b, sfb = _case(m, n, k, seed=3)
+    a, sfa, b, sfb, _ = _case(m, n, k, seed=3)
     d = torch.zeros(m, n, dtype=torch.bfloat16, device='cuda')
     desc = _api._run_gemm(L.GEMM_NORMAL, a, b, d, None, _api.Identity(), sfa, sfb, (1, 1, 32), None, None,
                           None, 'nk', False, config={'block_n': 128, 'cta_group': 1, 'split_k': 1})
