@@ -90,7 +90,20 @@ static uint32_t sf_atoms(const dg_gemm_desc_t& d) { return is_bf16_pair(d) ? 0u 
 // K elements in one 128-byte stage row
 static uint32_t stage_k(const dg_gemm_desc_t& d) { return is_fp4_pair(d) ? 256u : kBlockK / ab_elem_bytes(d); }
 // packed E2M1 B next to an E4M3 A is decoded to E4M3 in shared memory
-static bool decodes_b(const dg_gemm_desc_t& d) { return d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3; }
+static bool feature_disabled(const char* name);
+// Packed E2M1 B next to an E4M3 A. tcgen05.mma kind::mxf8f6f4 reads E2M1 operands itself when shared memory holds
+// them as groups of sixteen 4-bit values in 16-byte containers (8 bytes of codes, 8 bytes of padding), and TMA
+// expands the packed global bytes into exactly that form (CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B): no decoding in
+// the kernel, and B crosses HBM and the SM's port at half a byte per element. That tensor-map type wants a 32-byte
+// aligned base, strides that are multiples of 32 bytes and a contiguous extent that is a multiple of 128 elements;
+// anything else takes the decoder warps (the packed bytes are expanded to E4M3 in shared memory).
+static bool native_fp4_b(const dg_gemm_desc_t& d) {
+    if (!(d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3) || feature_disabled("native_fp4")) return false;
+    const uint32_t inner = d.major_b == DG_MAJOR_K ? d.k : d.n;           // elements along B's contiguous axis
+    return (reinterpret_cast<uintptr_t>(d.b) & 31) == 0 && d.outer_stride_b % 32 == 0 && d.group_stride_b % 32 == 0 &&
+           inner % 128 == 0;
+}
+static bool decodes_b(const dg_gemm_desc_t& d) { return d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3 && !native_fp4_b(d); }
 
 static int validate(const dg_gemm_desc_t& d) {
     DG_CHECK_ARG(d.gemm_type == DG_GEMM_NORMAL || is_grouped(d.gemm_type) ||
@@ -190,7 +203,7 @@ static bool wide_epilogue(const dg_gemm_config_t& c) { return c.reserved[5] == 2
 
 // Two ways to split K: partial sums reduced into an FP32 workspace that a second kernel casts (reserved[3] == 0), or
 // the splits of one tile form a thread-block cluster and reduce through shared memory (reserved[3] == 1).
-// DG_DISABLE=lean,cluster,wide,simple,straight,wide_tile,half_tiles,tma_store (debugging aid for A/B timing): keeps the
+// DG_DISABLE=lean,cluster,wide,simple,straight,wide_tile,half_tiles,tma_store,native_fp4 (debugging aid for A/B timing): keeps the
 // heuristic away from cluster split-K, from eight epilogue warps, from wide tiles or from half tiles in their last wave,
 // from TMA stores (plain stores instead), and / or the launch away from the lean and the cast-and-store-only kernel
 // instantiations or from the short chunk loop. Every alternative computes the same values.
@@ -343,10 +356,10 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
 // 2 * block_n cycles for 128 x block_n x 128 (16384 FP8 flop per cycle per SM). Operand bytes enter an SM at about
 // 50 bytes per cycle (measured: 43-56 B/clk/SM across tilings, the L2-to-SM path), which is what bounds every tiling
 // that does not share operands across SMs; a CTA pair halves the B bytes per SM.
-static double k_block_cycles(uint32_t cta_group, uint32_t bn, bool packed_b = false) {
+static double k_block_cycles(uint32_t cta_group, uint32_t bn, bool packed_b = false, bool decoded = true) {
     const double mma = 2.0 * bn;
     const double ingest = (128.0 + (double)bn / cta_group / (packed_b ? 2 : 1)) * 128.0 / 50.0;
-    const double decode = packed_b ? 2.5 * bn / cta_group : 0.0;       // four decoder warps, ~40 instructions per 16 codes
+    const double decode = (packed_b && decoded) ? 2.5 * bn / cta_group : 0.0;       // four decoder warps, ~40 instructions per 16 codes
     double t = mma > ingest ? mma : ingest;
     return t > decode ? t : decode;
 }
@@ -354,12 +367,13 @@ static double k_block_cycles(uint32_t cta_group, uint32_t bn, bool packed_b = fa
 // Modelled cycles of the main loop of one whole tile for problems with many rows (the tensor-bound regime), from
 // in-kernel clock reads: everything that crosses the SM's port to L2 (operands, scales, and the tile of D going out)
 // moves at about 58 bytes per cycle whatever the tiling, and the tensor pipe needs 2 * block_n cycles per K block.
-static double tile_main_cycles(uint32_t cta_group, uint32_t bn, uint32_t k_blocks, uint32_t atoms, uint32_t d_elem_bytes, bool packed_b) {
+static double tile_main_cycles(uint32_t cta_group, uint32_t bn, uint32_t k_blocks, uint32_t atoms, uint32_t d_elem_bytes, bool packed_b,
+                               bool decoded = true) {
     const double mma = (atoms == 2 ? 1.0 : 2.0) * bn * k_blocks;      // (kind::mxf4 runs a 128-byte K block in half the cycles)
     const double per_kb = (128.0 + (double)bn / cta_group / (packed_b ? 2 : 1)) * 128.0 + (128.0 + sfb_rows(bn)) * 4.0 * atoms;
     // (a wide tile keeps four or five 40-46 KB stages in flight instead of six 32 KB ones and measures nearer 55)
     const double ingest = (per_kb * k_blocks + 128.0 * bn * d_elem_bytes) / (bn > 256 ? 55.0 : 58.0);
-    const double decode = packed_b ? 2.5 * bn / cta_group * k_blocks : 0.0;
+    const double decode = (packed_b && decoded) ? 2.5 * bn / cta_group * k_blocks : 0.0;
     double t = mma > ingest ? mma : ingest;
     return t > decode ? t : decode;
 }
@@ -425,8 +439,9 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
                 const bool single_accum = 2 * bn + sf_tmem_cols(bn, atoms) > 512;
                 // (a wide tile has one accumulator: ~290 cycles per 32-column chunk are not hidden behind the next tile)
                 const double t_epi = bn > 256 ? bn * 9.0 : bn * (out_fp32 ? 8.0 : 6.0);
-                const double main_loop = rows > kBlockM ? tile_main_cycles(cg, bn, kb_per, atoms, out_fp32 ? 4 : elem_size(d.d_dtype), decodes_b(d))
-                                                        : kb_per * k_block_cycles(cg, bn, decodes_b(d));
+                const bool packed_b = d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3;
+                const double main_loop = rows > kBlockM ? tile_main_cycles(cg, bn, kb_per, atoms, out_fp32 ? 4 : elem_size(d.d_dtype), packed_b, decodes_b(d))
+                                                        : kb_per * k_block_cycles(cg, bn, packed_b, decodes_b(d));
                 const double cycles = main_loop + ((single_accum || waves == 1) ? t_epi : 0.0) + 700.0;
                 double cost = (double)waves * cycles / 1.8;                   // ns at ~1.8 GHz
                 if (cost < t_hbm) cost = t_hbm + 1e-3 * cost;     // HBM-bound: the cheaper schedule still wins ties
@@ -571,6 +586,8 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.idesc = ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) | (((c.block_n / tile_halves(c.block_n)) >> 3) << 17) | (1u << 23) |
               (((kBlockM * c.cta_group) >> 4) << 24);
     if (is_fp4_pair(d)) a.idesc |= (1u << 7) | (1u << 10);       // kind::mxf4: both operand formats E2M1
+    if (native_fp4_b(d)) a.idesc |= (5u << 10);                  // kind::mxf8f6f4: B format E2M1 (A stays E4M3)
+    a.b_tx_shift = native_fp4_b(d) ? 1u : 0u;
     if (is_bf16_pair(d))                                         // kind::f16: FP32 accumulator, BF16 operands, no scale fields
         a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) |
                   (((c.block_n / tile_halves(c.block_n)) >> 3) << 17) | (((kBlockM * c.cta_group) >> 4) << 24);
@@ -665,6 +682,21 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
             const uint64_t str[2] = {d.outer_stride_b, gs};
             const uint32_t box[3] = {load_n / 2, kBlockK, 1};
             if (int rc = encode_map(&plan.tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE, "B (packed FP4)")) return rc;
+        }
+    } else if (native_fp4_b(d)) {
+        // packed E2M1 expanded by TMA into 16-byte containers of sixteen codes: dimensions count 4-bit elements, strides bytes
+        if (d.major_b == DG_MAJOR_K) {
+            const uint64_t gs = nonzero_stride(d.group_stride_b, (uint64_t)d.n * d.outer_stride_b);
+            const uint64_t dims[3] = {d.k, d.n, groups};
+            const uint64_t str[2] = {d.outer_stride_b, gs};
+            const uint32_t box[3] = {kBlockK, load_n, 1};
+            if (int rc = encode_map(&plan.tm_b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, d.b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "B (E2M1)")) return rc;
+        } else {
+            const uint64_t gs = nonzero_stride(d.group_stride_b, (uint64_t)d.k * d.outer_stride_b);
+            const uint64_t dims[3] = {d.n, d.k, groups};
+            const uint64_t str[2] = {d.outer_stride_b, gs};
+            const uint32_t box[3] = {128, kBlockK, 1};
+            if (int rc = encode_map(&plan.tm_b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, d.b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "B (E2M1)")) return rc;
         }
     } else {
         if (d.major_b == DG_MAJOR_K) {

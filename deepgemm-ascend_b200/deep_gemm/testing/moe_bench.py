@@ -377,7 +377,7 @@ def run_mixed(args, rank, world, device, emit=None):
     m, n, k = case.m, case.n, case.k
     line = {'metric': 'fp8_block_scaled_gemm_tflops', 'value': world * case.flops / us / 1e6, 'unit': 'TFLOP/s', 'n_gpus': world,
             'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': us / 1e3, 'higher_is_better': True,
-            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp8_e4m3 x fp4_e2m1 (decoded to e4m3), ue8m0 scales',
+            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp8_e4m3 x fp4_e2m1 (kind::mxf8f6f4), ue8m0 scales',
             'data': 'synthetic',
             'config': {'workload': 'mixed FP8xFP4 GEMM NN, M=%d N=%d K=%d, BF16 out' % (m, n, k), 'l2': 'flushed, untimed'},
             'gbs': case.bytes / us / 1e3, 'tiling': case.config, 'verified': case.verify(),
