@@ -61,6 +61,45 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return OUT
 
 
+EXT_OUT = os.path.join(HERE, 'deep_gemm', '_C.so')
+
+
+def ext_is_stale() -> bool:
+    if not os.path.exists(EXT_OUT):
+        return True
+    built = os.path.getmtime(EXT_OUT)
+    deps = [os.path.join(CSRC, 'python_api.cpp'), os.path.join(HERE, '..', 'include', 'dg_b200.h')]
+    deps += [os.path.join(CSRC, 'apis', f) for f in os.listdir(os.path.join(CSRC, 'apis'))]
+    return any(os.path.getmtime(d) > built for d in deps) or os.path.getmtime(OUT) > built
+
+
+def build_extension(force: bool = False, verbose: bool = False) -> str:
+    """The `_C` torch extension (pybind11 + torch headers, g++): the reference's csrc/python_api.cpp surface over the
+    C ABI. Needs libdg_b200.so next to it (linked with an $ORIGIN run path)."""
+    if not force and not ext_is_stale():
+        return EXT_OUT
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension
+    cxx = shutil.which('g++') or 'g++'
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), 'lib')
+    cmd = [cxx, '-O2', '-std=c++17', '-shared', '-fPIC', '-fvisibility=hidden', '-Wno-attributes',
+           '-DTORCH_EXTENSION_NAME=_C', '-DTORCH_API_INCLUDE_EXTENSION_H',
+           '-D_GLIBCXX_USE_CXX11_ABI=%d' % int(torch._C._GLIBCXX_USE_CXX11_ABI),
+           os.path.join(CSRC, 'python_api.cpp'), '-o', EXT_OUT,
+           *['-I' + p for p in cpp_extension.include_paths()], '-I' + sysconfig.get_paths()['include'],
+           '-I/usr/local/cuda/include',
+           '-L' + torch_lib, '-ltorch_python', '-ltorch', '-ltorch_cpu', '-lc10', '-lc10_cuda',
+           '-L' + os.path.dirname(OUT), '-l:libdg_b200.so', '-Wl,-rpath,$ORIGIN', '-Wl,-rpath,' + torch_lib]
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if verbose or proc.returncode != 0:
+        sys.stderr.write(proc.stdout)
+    if proc.returncode != 0:
+        raise RuntimeError('g++ failed on python_api.cpp')
+    return EXT_OUT
+
+
 if __name__ == '__main__':
     path = build(force='--force' in sys.argv, verbose='--verbose' in sys.argv)
     print(path)
+    print(build_extension(force='--force' in sys.argv, verbose='--verbose' in sys.argv))

@@ -21,6 +21,15 @@ import torch
 
 from . import _lib as L
 
+# The compiled host layer, when it has been built (`python deepgemm-ascend_b200/build.py`); DG_PYTHON_HOST=1 keeps to
+# this module. Its process-wide knobs are kept in step with the ones below.
+_C = None
+if os.environ.get('DG_PYTHON_HOST', '0') in ('', '0'):
+    try:
+        from . import _C  # type: ignore[attr-defined,no-redef]
+    except ImportError:
+        _C = None
+
 PACKED_FP4 = torch.int8           # csrc/utils/dtype.hpp:9
 MK_ALIGNMENT = 256                # csrc/jit/jit.hpp:59-73
 
@@ -130,6 +139,8 @@ def set_num_sms(n: int) -> None:
 
 def set_npu_arch(arch: int) -> None:
     _global['arch'] = int(arch)
+    if _C is not None:
+        _C.set_npu_arch(int(arch))
 
 
 def get_npu_arch() -> int:
@@ -150,6 +161,8 @@ def get_theoretical_mk_alignment_for_contiguous_layout() -> int:
 
 def use_deterministic_algorithms(enabled: bool) -> None:
     _global['deterministic'] = bool(enabled)
+    if _C is not None:
+        _C.use_deterministic_algorithms(bool(enabled))
 
 
 def get_deterministic_algorithms() -> bool:
@@ -158,6 +171,8 @@ def get_deterministic_algorithms() -> bool:
 
 def set_dry_run(value: bool) -> None:
     _global['dry_run'] = bool(value)
+    if _C is not None:
+        _C.set_dry_run(bool(value))
 
 
 def get_dry_run() -> bool:
@@ -785,4 +800,10 @@ def device_status() -> int:
     if flag is not None and int(flag.item()) != 0:
         flag.zero_()
         code = code or STATUS_INVALID_SCALE_FACTOR
+    if _C is not None:
+        # (the compiled host layer keeps a flag and a scratch cache of its own)
+        if out.value != 0:
+            _C._drop_workspaces(device)
+        c_code = _C.device_status()
+        code = code or c_code
     return code

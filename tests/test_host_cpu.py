@@ -251,3 +251,38 @@ def test_npu_sleep_and_init_exist_and_dry_run_is_a_no_op():
     assert lib.dg_sleep_launch(-1, 0, 148, None) == L.DG_ERR_INVALID
     assert lib.dg_sleep_launch(5 * 10 ** 9, 0, 148, None) == L.DG_ERR_INVALID
     assert 'sleep_cycles' in L.last_error()
+
+
+def test_compiled_host_layer_is_in_use_and_agrees_with_the_python_one():
+    """When the `_C` extension is built the public entry points are its functions; the Python host layer stays
+    importable and must accept and reject the same calls with the same messages (both end in the same C ABI)."""
+    from deep_gemm import _api
+    if _api._C is None:
+        pytest.skip('the _C extension has not been built')
+    assert deep_gemm.BACKEND == '_C'
+    assert deep_gemm.fp8_gemm_nt is _api._C.fp8_fp4_gemm_nt
+    assert deep_gemm.epilogue.Alpha is _api._C.epilogue.Alpha
+    a, b = _meta_pair(128, 256), _meta_pair(64, 256)
+    d = torch.empty(128, 64, dtype=torch.bfloat16, device='meta')
+    bias = torch.empty(1, 64, dtype=torch.bfloat16, device='meta')
+    cases = [
+        (dict(c=bias, alpha=0.5), 'alpha and bias cannot be used together'),
+        (dict(c=torch.empty(2, 64, dtype=torch.bfloat16, device='meta')), "C must match D's pointer and shape"),
+        (dict(recipe=(1, 1, 32), recipe_a=(1, 32)), 'mutually exclusive'),
+        (dict(config={'block_n': 100}), 'block_n'),
+        (dict(), None), (dict(c=bias), None), (dict(alpha=2.0), None), (dict(config={'block_n': 64, 'cta_group': 1}), None),
+    ]
+    for kwargs, message in cases:
+        for fn in (_api._C.fp8_gemm_nt, _api.fp8_gemm_nt):
+            if message is None:
+                fn(a, b, d, **kwargs)
+            else:
+                with pytest.raises(RuntimeError, match=message):
+                    fn(a, b, d, **kwargs)
+    with pytest.raises(RuntimeError, match="Conflicting shape dimension 'k'"):
+        _api._C.fp8_gemm_nt(a, _meta_pair(64, 128), d)
+    # the knobs set through the package reach both layers
+    deep_gemm.set_dry_run(False)
+    assert _api._C.get_dry_run() is False and _api.get_dry_run() is False
+    deep_gemm.set_dry_run(True)
+    assert _api._C.get_dry_run() is True and _api.get_dry_run() is True
