@@ -1,7 +1,7 @@
 """Benchmark of the block-scaled FP8 GEMM hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload auto|dense|grouped|masked|mixed|fp4|bf16|quant]
+                    [--workload auto|dense|grouped|masked|mixed|fp4|bf16|quant|layout]
 
 One GPU (`--workload auto` = `dense`): one "step" is one pass over the dense FP8 NT sweep the baseline names: M in
 {64, 128, 4096} times six (N, K) pairs, BF16 output, A quantised per 1x128 and B per 128x128 from N(0,1) data
@@ -63,6 +63,23 @@ def peaks() -> dict:
         return {'hbm_gbs': p['hbm_gbs'], 'bf16_tflops': p['bf16_tflops'],
                 'bf16_tflops_sustained': p.get('bf16_tflops_sustained', p['bf16_tflops']), 'source': 'measured'}
     return {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0, 'source': 'fallback'}
+
+
+def measure_write_bandwidth(device) -> float:
+    """GB/s of a pure write stream on this GPU (a 1 GiB fill, best of 5, CUDA events): HBM takes writes at roughly
+    half the rate of the read+write copy that MEASURED_PEAKS.json records, which is what bounds a GEMM whose output
+    is most of its traffic (4096 x 32768 x 512: 268 MB of D against 19 MB of operands)."""
+    buf = torch.empty(1 << 30, dtype=torch.uint8, device=device)
+    best = float('inf')
+    for _ in range(6):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        buf.fill_(1)
+        e1.record()
+        torch.cuda.synchronize(device)
+        best = min(best, e0.elapsed_time(e1))
+    del buf
+    return (1 << 30) / best / 1e6
 
 
 def dense_config(world: int) -> dict:
@@ -429,11 +446,19 @@ def run_dense(args, rank, world, device):
     gbs_small = sum(cases[i].bytes for i in small) / sum(per_case_us[i] for i in small) / 1e3
     fp8_peak = 2.0 * pk['bf16_tflops']
     top = max(big, key=lambda i: cases[i].flops)
+    write_gbs = measure_write_bandwidth(device)
+
+    def roofs(c, us):
+        # the three lower bounds of one launch, in microseconds, and the fraction of the tightest one that was reached
+        floors = {'tensor': c.flops / fp8_peak / 1e6, 'hbm': c.bytes / pk['hbm_gbs'] / 1e3,
+                  'hbm_write': c.m * c.n * 2 / write_gbs / 1e3}
+        bound = max(floors, key=floors.get)
+        return {'bound': bound, 'floor_us': round(floors[bound], 2), 'frac': round(floors[bound] / us, 3)}
     shapes = [{'m': c.m, 'n': c.n, 'k': c.k, 'us': round(per_case_us[i], 2),
                'tflops': round(c.flops / per_case_us[i] / 1e6, 1), 'gbs': round(c.bytes / per_case_us[i] / 1e3, 1),
                'block_n': c.config['block_n'], 'cta_group': c.config['cta_group'], 'split_k': c.config['split_k'],
                'split_in_cluster': bool(c.config['cluster_split']),
-               'stages': c.config['num_stages']} for i, c in enumerate(cases)]
+               'stages': c.config['num_stages'], 'roof': roofs(c, per_case_us[i])} for i, c in enumerate(cases)]
     line = {
         'metric': 'fp8_block_scaled_gemm_tflops', 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world,
         'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': step_ms_max, 'higher_is_better': True,
@@ -461,6 +486,7 @@ def run_dense(args, rank, world, device):
         'host_us_per_call': {'fp8_gemm_nt, scales in the required layout (plan reused)': round(host_call_us, 1),
                              'fp8_gemm_nt with FP32 scales (two transforms launched), median':
                                  round(sorted(host_us)[len(host_us) // 2], 1) if host_us else None},
+        'hbm_write_gbs': round(write_gbs, 1),
         'gpu_launches': int(launches),
         'clocks': clocks,
         'device_status': status,
@@ -479,8 +505,10 @@ def run_dense(args, rank, world, device):
 
 def other_config_legs(args, device, pk) -> dict:
     """Short legs for the configurations the sweep does not contain: mixed FP8xFP4 (config 3), m-grouped contiguous
-    with 32 experts (config 4) and m-grouped masked 32 x 256 (config 5), each timed per launch after an untimed L2
-    flush, verified on a row sample, with the roofline that bounds it."""
+    with 32 experts (config 4) and m-grouped masked 32 x 256 (config 5), verified on a row sample, with the roofline
+    that bounds each. The mixed and the masked GEMM (tens to hundreds of microseconds) are timed like the sweep's
+    shapes, as graphs of back-to-back launches over rotating operand sets larger than L2; the contiguous one
+    (milliseconds) per launch after an untimed L2 flush."""
     from deep_gemm.testing import moe_bench
     fp8_peak = 2.0 * pk['bf16_tflops']
     steps = max(3, min(args.steps, 10))
@@ -526,7 +554,7 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--workload', default='auto',
-                    choices=['auto', 'dense', 'grouped', 'masked', 'mixed', 'fp4', 'bf16', 'quant'])
+                    choices=['auto', 'dense', 'grouped', 'masked', 'mixed', 'fp4', 'bf16', 'quant', 'layout'])
     ap.add_argument('--experts', type=int, default=0, help='grouped / masked workloads: global expert count (default 32)')
     ap.add_argument('--no-graph', action='store_true',
                     help='dense workload: plain stream launches instead of a CUDA graph (for profilers that cannot follow a capture)')

@@ -478,11 +478,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             mbar_init(tmem_empty_bar(e), kEpiWarps * kCtaGroup);   // one arrival per epilogue warp
         }
         if (cluster_split > 1) {
-            // the chunks this rank finalises arrive as bulk copies from the other ranks, counted in bytes
-            const uint32_t chunks = p.block_n / 32, r = cluster_ctarank();
-            const uint32_t owned = r < chunks ? (chunks - r + cluster_split - 1) / cluster_split : 0u;
+            // the chunks this rank finalises arrive as bulk copies from the other ranks, counted in bytes; how many bytes
+            // depends on how many of the tile's rows exist, so the epilogue posts the expected count
             mbar_init(reduce_bar, 1);
-            if (owned) mbar_arrive_expect_tx(reduce_bar, owned * (cluster_split - 1) * kReduceSlabBytes);
         }
         fence_mbar_init();
         fence_proxy_async_smem();
@@ -981,11 +979,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 const uint32_t S = cluster_split, r = cluster_ctarank();
                 const uint32_t chunks = p.block_n / 32;
                 const uint32_t row_off = (q * 32 + lane) * 128, sw = lane & 7u;
+                // Only the 32-row quarters of the tile that hold rows of D take part (M = 64: two of four).
+                const uint32_t rows_here = p.m > t.row0 ? p.m - t.row0 : 0u;
+                const uint32_t live_quarters = min(4u, (rows_here + 31u) / 32u);
+                const bool live = q < live_quarters;
+                if (threadIdx.x == 128) {
+                    const uint32_t owned = r < chunks ? (chunks - r + S - 1) / S : 0u;
+                    if (owned) mbar_arrive_expect_tx(reduce_bar, owned * (S - 1) * live_quarters * 4096u);
+                }
                 // Outgoing chunks are staged in the operand ring (this CTA's only tile has been multiplied, so the
                 // ring is free) and leave as one 4 KB bulk copy per warp; the staging must stay untouched until the
                 // copy has been read, which the cluster barrier at the end of the kernel guarantees.
                 uint32_t sent = 0;
-                for (uint32_t c = 0; c < chunks; ++c) {
+                for (uint32_t c = 0; live && c < chunks; ++c) {
                     const uint32_t owner = c % S;
                     if (owner == r) continue;
                     tmem_ld_32x32b_x32(taddr + c * 32, va);
@@ -998,7 +1004,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) {
+                if (lane == 0 && live) {
                     sent = 0;
                     for (uint32_t c = 0; c < chunks; ++c) {
                         const uint32_t owner = c % S;
@@ -1011,7 +1017,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                 }
                 if (threadIdx.x == 128) trace_mark(p, 13);
-                if (r < chunks) {
+                if (r < chunks && live) {
                     if (!(ok = wait_barrier(reduce_bar, tile_iter & 1u, ab, kStatusTimeoutReduce))) break;
                     if (threadIdx.x == 128) trace_mark(p, 14);
                     for (uint32_t slot = 0, c = r; c < chunks; ++slot, c += S) {

@@ -133,10 +133,18 @@ class MixedCase:
         return _close(self.d[idx.to(self.d.device)], oracle.gemm_ref(a_deq, b_deq, torch.bfloat16))
 
 
+def _graph_timed(lib, cases, steps) -> float:
+    """Mean microseconds per launch of `cases` (same problem, operands of their own, together several times the L2
+    capacity) launched back to back as one CUDA graph: the method the dense sweep's per-shape figures use."""
+    from .bench import bench_graph
+    return bench_graph([(lambda sptr, c=c: c.launch(lib, sptr)) for c in cases], 3, steps).dur_us
+
+
 def time_mixed(device, steps: int) -> dict:
     lib = L.lib()
-    case = MixedCase(device)
-    us = _flush_timed(lib, device, lambda sptr: case.launch(lib, sptr), steps)
+    cases = [MixedCase(device, seed=7 + i) for i in range(7)]           # 7 x 75 MB of operands and outputs
+    us = _graph_timed(lib, cases, steps)
+    case = cases[0]
     return {'us': us, 'tflops': case.flops / us / 1e6, 'gbs': case.bytes / us / 1e3, 'tiling': case.config,
             'verified': case.verify()}
 
@@ -173,7 +181,12 @@ def time_grouped(device, sizes, steps: int, masked: bool) -> dict:
     shapes, flops, us_total, nbytes, ok = [], 0.0, 0.0, 0.0, True
     for i, (n, k) in enumerate(NK_LIST):
         case = GroupedCase(sizes, n, k, device, seed=100 + i, masked_max_m=256 if masked else 0)
-        us = _flush_timed(lib, device, lambda sptr: case.launch(lib, sptr), steps)
+        if masked:      # 100-200 us per launch: graph of three operand sets (0.5-1 GB each); the contiguous layout runs for milliseconds
+            extra = [GroupedCase(sizes, n, k, device, seed=200 + 10 * i + j, masked_max_m=256) for j in range(2)]
+            us = _graph_timed(lib, [case] + extra, steps)
+            del extra
+        else:
+            us = _flush_timed(lib, device, lambda sptr: case.launch(lib, sptr), steps)
         ok = ok and _verify_grouped(case, sizes, masked)
         shapes.append({'rows': case.rows, 'valid_rows': case.valid_rows, 'n': n, 'k': k, 'us': round(us, 1),
                        'tflops': round(case.flops / us / 1e6, 1), 'gbs': round(case.bytes / us / 1e3, 1),
@@ -195,6 +208,8 @@ def run(args, rank, world, device, emit=None, pk=None):
         return run_bf16(args, rank, world, device, emit)
     if args.workload == 'quant':
         return run_quant(args, rank, world, device, emit)
+    if args.workload == 'layout':
+        return run_layout(args, rank, world, device, emit, pk)
     return run_grouped(args, rank, world, device, emit, pk or {'bf16_tflops': 1590.0, 'hbm_gbs': 6650.0, 'source': 'fallback'})
 
 
@@ -545,4 +560,64 @@ def run_bf16(args, rank, world, device, emit=None):
             'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16 x bf16, fp32 accumulate (kind::f16)', 'data': 'synthetic',
             'config': {'workload': 'BF16 GEMM NT, BF16 out: ' + str(shapes), 'l2': 'flushed before every GEMM, untimed'},
             'shapes': rows, 'device_status': _api.device_status()}
+    (emit or (lambda l: print(json.dumps(l), flush=True)))(line)
+
+
+def run_layout(args, rank, world, device, emit=None, pk=None):
+    """Scale-factor relayout (`transform_sf_into_required_layout`) on large cases of the reference's layout
+    performance list (tests/generators.py:725-747): batched FP32 scales [8, 32768, K/32], an m-grouped psum layout of
+    262144 rows in 128 groups, per-row, per-32-row and per-128-row granularity, FP32 and packed int16 sources, K- and
+    MN-major. HBM-bound: bytes = source read + int16 result written."""
+    import deep_gemm
+    from .bench import bench_events
+    peak = (pk or {}).get('hbm_gbs', 6453.4)
+    gen = torch.Generator(device=device).manual_seed(3 + rank)
+    rows_out, total_bytes, total_us = [], 0.0, 0.0
+    batches, batch_mn, k = 8, 32768, 7168
+    total_mn = batches * batch_mn
+    group_sizes = [total_mn // 128 - 1] * 128
+    psum, acc = [], 0
+    for sz in group_sizes:
+        psum.append(acc + sz)
+        acc = (acc + sz + 255) // 256 * 256
+    layout = torch.tensor(psum, dtype=torch.int32, device=device)
+    cases = []
+    for gran in (1, 32, 128):
+        cases.append(('batched fp32 K-major gran_mn=%d' % gran, torch.float32, False, gran, None))
+    cases.append(('m-grouped (128 groups) fp32 K-major gran_mn=1', torch.float32, False, 1, layout))
+    cases.append(('m-grouped (128 groups) fp32 MN-major gran_mn=1', torch.float32, True, 1, layout))
+    cases.append(('m-grouped (128 groups) int16 K-major gran_mn=1', torch.int16, False, 1, layout))
+    for name, dtype, mn_major, gran, lay in cases:
+        cols = k // 32 if dtype == torch.float32 else k // 64
+        lead = (batches, batch_mn // gran) if lay is None else (total_mn // gran,)
+        if dtype == torch.float32:
+            src = (torch.randint(100, 140, (*lead, cols), dtype=torch.int32, device=device, generator=gen) << 23).view(torch.float32)
+        else:
+            src = torch.randint(0, 32000, (*lead, cols), dtype=torch.int16, device=device, generator=gen)
+        if mn_major:
+            src = src.transpose(-2, -1).contiguous().transpose(-2, -1)
+        mn = batch_mn if lay is None else total_mn
+
+        def fn():
+            return deep_gemm.transform_sf_into_required_layout(src, mn, k, (gran, gran, 32), batches if lay is None else None,
+                                                               True, False, lay)
+        out = fn()
+        p = bench_events(fn, max(args.warmup, 3), args.steps)
+        nbytes = src.numel() * src.element_size() + out.numel() * 2
+        rows_out.append({'case': name, 'us': round(p.dur_us, 1), 'gbs': round(nbytes / p.dur_us / 1e3, 1),
+                         'mb': round(nbytes / 1e6, 1)})
+        total_bytes += nbytes
+        total_us += p.dur_us
+        del src, out
+    if rank != 0:
+        return
+    achieved = total_bytes / total_us / 1e3
+    line = {'metric': 'sf_transform_gbs', 'value': world * achieved, 'unit': 'GB/s', 'n_gpus': world, 'steps': args.steps,
+            'warmup': max(args.warmup, 3), 'ms_per_step': total_us / 1e3, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': 'u8 (UE8M0 exponent bytes)', 'data': 'synthetic',
+            'config': {'workload': 'transform_sf_into_required_layout, 262144 rows x K=7168, six large cases of the '
+                                   "reference's layout performance list", 'l2': 'flushed before every launch, untimed'},
+            'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
+                         'traffic': None, 'kernel': 'transform_sf_kernel'},
+            'cases': rows_out, 'device_status': _api.device_status()}
     (emit or (lambda l: print(json.dumps(l), flush=True)))(line)
