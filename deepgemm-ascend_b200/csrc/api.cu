@@ -310,7 +310,9 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     // cluster split-K stages its outgoing partial sums (16 KB per 32 columns) and its output boxes in the operand ring
     if (in_cluster) {
         const uint32_t ring = c.num_stages * (kBlockM * kBlockK + c.block_n * kBlockK);
-        const uint32_t need = (c.block_n / 32) * kReduceSlabBytes + kNumEpilogueWarps * store_bufs * kStoreBufBytes;
+        // (outgoing partial sums, the staging boxes of the epilogue warps, and one more box each for the second set of warps
+        //  a lean kernel uses)
+        const uint32_t need = (c.block_n / 32) * kReduceSlabBytes + kNumEpilogueWarps * (store_bufs + 1) * kStoreBufBytes;
         DG_CHECK_ARG(ring >= need, "cluster split-K needs a pipeline of at least %u bytes, %u stages give %u", need, c.num_stages, ring);
     }
     if (c.split_k > 1) {

@@ -787,17 +787,28 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 if (++stage == num_stages) { stage = 0; phase ^= 1; }
             }
         }
-    } else if (warp >= 4 && warp < 4 + kEpiWarps) {
+    }
+    // A lean kernel has one tile per CTA: when that tile has been multiplied, warps 0..3 have nothing left to do, and one
+    // warp alone retires the ~160 dependent instructions of a 32-column chunk in about 900 cycles. So they join as a second
+    // set of epilogue warps (warp w reads the same TMEM lane quarter as warp w + 4) and the two sets take alternate chunks.
+    if ((warp >= 4 && warp < 4 + kEpiWarps) || (kLean && warp < 4)) {
         // ======================================================================== epilogue
         const uint32_t q = warp % 4;                         // TMEM lane quadrant == warp index % 4
-        const uint32_t col_half = (warp - 4) / 4;            // wide epilogue: which 64-column groups this warp takes
+        const uint32_t eset = (kLean && warp < 4) ? 1u : 0u; // lean kernels: the second set of epilogue warps
+        const uint32_t col_half = kLean ? 0u : (warp - 4) / 4;   // wide epilogue: which 64-column groups this warp takes
         constexpr uint32_t kColStep = kWideEpi ? 128u : 64u;
         Scheduler<kCtaGroup, kLean, kWideTile> sched(p);
         Tile t;
         uint32_t tile_iter = 0, buf = 0;
         bool ok = true;
-        const uint32_t store_base = smem_base + L.store_bufs + (warp - 4) * p.store_bufs * kStoreBufBytes;
-        uint8_t* store_gen = smem_gen + L.store_bufs + (warp - 4) * p.store_bufs * kStoreBufBytes;
+        // Staging boxes: one set per warp of the first set in the region laid out for them; the second set of a lean kernel
+        // takes boxes in the operand ring, which is free once the only tile has been multiplied (behind the outgoing partial
+        // sums and the first set's boxes when the K splits reduce through the cluster).
+        const uint32_t box_off = eset == 0 ? L.store_bufs + (warp - 4) * p.store_bufs * kStoreBufBytes
+                                           : (cluster_split > 1 ? L.store_bufs + (4 * p.store_bufs + warp) * kStoreBufBytes
+                                                                : L.a + warp * kStoreBufBytes);
+        const uint32_t store_base = smem_base + box_off;
+        uint8_t* store_gen = smem_gen + box_off;
         auto out_is_fp32 = [&]() -> bool { return !kSimpleEpi && p.d_is_fp32 != 0; };   // a kernel-argument read, not a register
         const uint32_t leader_tmem_empty0 = kCtaGroup == 2 ? mapa_shared(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
         while (ok && sched.next(t)) {
@@ -811,6 +822,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             // columns of the tile this launch of the epilogue covers (a half tile of a wide-tile launch: one half)
             const uint32_t col_begin = (kWideTile && t.halves == 2u) ? half_n : 0u;
             const uint32_t col_end = (kWideTile && t.halves == 1u) ? half_n : p.block_n;
+
+            // Lean kernels write D with plain stores. A thread holds one row of the tile, so storing straight from the
+            // registers makes every store instruction touch 32 rows (32 separate sectors): measured, about 900 cycles per
+            // 32-column chunk per CTA, all of it transaction issue. Instead a warp stages its 32 rows x 64 (or 32) columns
+            // in its staging box, then every store instruction writes whole 128-byte (64-byte) row segments.
+            uint32_t col_stop = col_end;            // the chunk loop of the plain-store path ends at the last column of D
+            const bool lean_vec_ok = kLean && (reinterpret_cast<uintptr_t>(p.d) & 15u) == 0 &&
+                                     ((p.d_stride * (p.d_is_fp32 ? 4u : 2u)) & 15u) == 0;
 
             // One 32-column chunk of this thread's row: alpha / bias, cast, stage, store.
             // `single`: the chunk goes out on its own (BF16 boxes normally pair two chunks).
@@ -935,6 +954,53 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 } else {
                     // plain path: bounds-checked element stores / atomics, any N and any stride; a whole chunk that lies
                     // inside D on a 16-byte boundary goes out as 16-byte stores
+                    if constexpr (kLean) {
+                        if (lean_vec_ok && col0 + 32 <= p.n) {
+                            const uint32_t es = out_is_fp32() ? 4u : 2u;
+                            // BF16: two chunks share a box of 128-byte rows when both lie inside D, else the chunk goes alone
+                            const uint32_t pair_c0 = c0 & ~63u;
+                            const bool pair = !out_is_fp32() && !single && t.n0 + pair_c0 + 64 <= p.n && pair_c0 + 64 <= col_stop;
+                            const uint32_t half = pair ? ((c0 >> 5) & 1u) : 0u;
+                            uint8_t* bufp = store_gen;
+                            if (out_is_fp32()) {
+                                #pragma unroll
+                                for (uint32_t c = 0; c < 8; ++c)
+                                    *reinterpret_cast<uint4*>(bufp + lane * 128 + ((c ^ (lane & 7u)) * 16)) =
+                                        make_uint4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+                            } else {
+                                #pragma unroll
+                                for (uint32_t c = 0; c < 4; ++c) {
+                                    uint8_t* dst = pair ? bufp + lane * 128 + (((half * 4 + c) ^ (lane & 7u)) * 16)
+                                                        : bufp + lane * 64 + ((c ^ ((lane >> 1) & 3u)) * 16);
+                                    *reinterpret_cast<uint4*>(dst) = make_uint4(w16[c * 4], w16[c * 4 + 1], w16[c * 4 + 2], w16[c * 4 + 3]);
+                                }
+                            }
+                            if (pair && half == 0) return;              // the box is written out with its second half
+                            __syncwarp();
+                            uint8_t* out = reinterpret_cast<uint8_t*>(p.d) +
+                                           ((uint64_t)t.d_z * p.d_group_stride + t.n0 + (pair ? pair_c0 : c0)) * es;
+                            const uint32_t row_base = t.row0 + q * 32;
+                            if (out_is_fp32() || pair) {
+                                #pragma unroll
+                                for (uint32_t it = 0; it < 8; ++it) {          // four rows of 128 bytes per instruction
+                                    const uint32_t r = it * 4 + (lane >> 3), c = lane & 7u;
+                                    const uint4 x = *reinterpret_cast<const uint4*>(bufp + r * 128 + ((c ^ (r & 7u)) * 16));
+                                    if (row_base + r < p.m)
+                                        *reinterpret_cast<uint4*>(out + (uint64_t)(row_base + r) * p.d_stride * es + c * 16) = x;
+                                }
+                            } else {
+                                #pragma unroll
+                                for (uint32_t it = 0; it < 4; ++it) {          // eight rows of 64 bytes per instruction
+                                    const uint32_t r = it * 8 + (lane >> 2), c = lane & 3u;
+                                    const uint4 x = *reinterpret_cast<const uint4*>(bufp + r * 64 + ((c ^ ((r >> 1) & 3u)) * 16));
+                                    if (row_base + r < p.m)
+                                        *reinterpret_cast<uint4*>(out + (uint64_t)(row_base + r) * p.d_stride * es + c * 16) = x;
+                                }
+                            }
+                            __syncwarp();                                   // the box is free again
+                            return;
+                        }
+                    }
                     const bool row_ok = row < p.m;
                     const uint64_t base = (uint64_t)t.d_z * p.d_group_stride + (uint64_t)row * p.d_stride;
                     if ((kLean || p.epilogue_mode == kEpiPlainStore) && col0 + 32 <= p.n) {
@@ -990,18 +1056,22 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 // Outgoing chunks are staged in the operand ring (this CTA's only tile has been multiplied, so the
                 // ring is free) and leave as one 4 KB bulk copy per warp; the staging must stay untouched until the
                 // copy has been read, which the cluster barrier at the end of the kernel guarantees.
+                // (the two sets of epilogue warps of a lean kernel take alternate outgoing chunks)
                 uint32_t sent = 0;
                 for (uint32_t c = 0; live && c < chunks; ++c) {
                     const uint32_t owner = c % S;
                     if (owner == r) continue;
-                    tmem_ld_32x32b_x32(taddr + c * 32, va);
-                    tmem_ld_wait();
-                    uint8_t* out = smem_gen + L.a + sent * kReduceSlabBytes + row_off;
-                    #pragma unroll
-                    for (uint32_t u = 0; u < 8; ++u)
-                        *reinterpret_cast<uint4*>(out + ((u ^ sw) * 16)) = make_uint4(va[u * 4], va[u * 4 + 1], va[u * 4 + 2], va[u * 4 + 3]);
+                    if (!kLean || (sent & 1u) == eset) {
+                        tmem_ld_32x32b_x32(taddr + c * 32, va);
+                        tmem_ld_wait();
+                        uint8_t* out = smem_gen + L.a + sent * kReduceSlabBytes + row_off;
+                        #pragma unroll
+                        for (uint32_t u = 0; u < 8; ++u)
+                            *reinterpret_cast<uint4*>(out + ((u ^ sw) * 16)) = make_uint4(va[u * 4], va[u * 4 + 1], va[u * 4 + 2], va[u * 4 + 3]);
+                    }
                     ++sent;
                 }
+                if (kLean && threadIdx.x == 128) trace_mark(p, 21);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0 && live) {
@@ -1010,9 +1080,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         const uint32_t owner = c % S;
                         if (owner == r) continue;
                         const uint32_t slab = (c / S) * (S - 1) + (r < owner ? r : r - 1);
-                        bulk_copy_to_cluster(mapa_shared(smem_base + L.reduce + slab * kReduceSlabBytes + q * 4096, owner),
-                                             smem_base + L.a + sent * kReduceSlabBytes + q * 4096, 4096,
-                                             mapa_shared(reduce_bar, owner));
+                        if (!kLean || (sent & 1u) == eset)
+                            bulk_copy_to_cluster(mapa_shared(smem_base + L.reduce + slab * kReduceSlabBytes + q * 4096, owner),
+                                                 smem_base + L.a + sent * kReduceSlabBytes + q * 4096, 4096,
+                                                 mapa_shared(reduce_bar, owner));
                         ++sent;
                     }
                 }
@@ -1022,8 +1093,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     if (threadIdx.x == 128) trace_mark(p, 14);
                     for (uint32_t slot = 0, c = r; c < chunks; ++slot, c += S) {
                         if (t.n0 + c * 32 >= p.n && (kLean || p.epilogue_mode >= kEpiPlainStore)) break;   // beyond N
+                        if (kLean && (slot & 1u) != eset) continue;                                       // the other set's chunk
                         tmem_ld_32x32b_x32(taddr + c * 32, va);
                         tmem_ld_wait();
+                        if (kLean && slot == 0 && threadIdx.x == 128) trace_mark(p, 22);
                         #pragma unroll
                         for (int i = 0; i < 32; ++i) vb[i] = 0u;        // +0.0f
                         for (uint32_t s = 0; s < S; ++s) {
@@ -1042,7 +1115,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                 }
                             }
                         }
+                        if (kLean && slot == 0 && threadIdx.x == 128) trace_mark(p, 23);
                         process_chunk(std::false_type{}, vb, c * 32, true);
+                        if (kLean && slot == 0 && threadIdx.x == 128) trace_mark(p, 24);
                     }
                 }
             } else {
@@ -1051,6 +1126,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             // clipped by the hardware instead).
             const bool plain = !kSimpleEpi && (kLean || p.epilogue_mode == kEpiPlainStore || p.epilogue_mode == kEpiPlainAtomic);
             const uint32_t cols = plain ? min(col_end, (p.n - t.n0 + 31u) & ~31u) : col_end;
+            col_stop = cols;
             auto run_chunks = [&](auto simple_tag) {
                 uint32_t c_first = kWideTile ? col_begin : col_half * 64;
                 if (kWideTile && (c_first & 32u) && c_first < cols) {
@@ -1074,14 +1150,31 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             };
             // (the 384-thread instantiations have 168 registers per thread: two copies of the loop make them spill)
             constexpr bool kTwoLoops = !kSimpleEpi && !kLean && !kDecodeB && !kWideEpi;
-            if (kSimpleEpi || (kTwoLoops && p.epi_simple)) run_chunks(std::true_type{});
+            if constexpr (kLean) {
+                // one tile, two sets of warps: chunk c goes to set c % 2, every chunk as a box of its own
+                (void)run_chunks;
+                uint32_t c0 = eset * 32;
+                if (c0 < cols) tmem_ld_32x32b_x32(taddr + c0, va);
+                for (; c0 < cols; c0 += 128) {
+                    tmem_ld_wait();
+                    if (c0 == 0 && threadIdx.x == 128) trace_mark(p, 19);
+                    if (c0 + 64 < cols) tmem_ld_32x32b_x32(taddr + c0 + 64, vb);
+                    process_chunk(std::false_type{}, va, c0, true);
+                    if (c0 == 0 && threadIdx.x == 128) trace_mark(p, 20);
+                    if (c0 + 64 < cols) {
+                        tmem_ld_wait();
+                        if (c0 + 128 < cols) tmem_ld_32x32b_x32(taddr + c0 + 128, va);
+                        process_chunk(std::false_type{}, vb, c0 + 64, true);
+                    }
+                }
+            } else if (kSimpleEpi || (kTwoLoops && p.epi_simple)) run_chunks(std::true_type{});
             else if constexpr (!kSimpleEpi) run_chunks(std::false_type{});
             }
             if (tile_iter == 0 && threadIdx.x == 128) trace_mark(p, 15);
             // this accumulator may be overwritten by the next-but-one tile
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) {
+            if (lane == 0 && eset == 0) {
                 if constexpr (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty0 + e * 8);
                 else mbar_arrive(tmem_empty_bar(e));
             }
