@@ -283,15 +283,29 @@ def run_reference(args, rank, world):
 # ----------------------------------------------------------------------------------------------------------------
 # Dense sweep
 # ----------------------------------------------------------------------------------------------------------------
-def per_shape_times(lib, device, base_cases) -> list[float]:
+def per_shape_times(lib, device, base_cases, use_graph=True) -> list[float]:
     """Mean microseconds per launch of every shape of the sweep: each shape runs as a CUDA graph of back-to-back
-    launches over rotating operand sets that together exceed L2 several times, between one CUDA-event pair."""
+    launches over rotating operand sets that together exceed L2 several times, between one CUDA-event pair.
+    Without graphs (`--no-graph`, for profilers): the same launches on the stream, one event pair around them."""
     from deep_gemm.testing import bench_graph
     out = []
     for ci, c in enumerate(base_cases):
         copies = max(3, min(32, -(-512_000_000 // c.bytes)))
         sets = [c] + [DenseCase(c.m, c.n, c.k, device, seed=7000 + 37 * ci + j, data='codes') for j in range(copies - 1)]
-        out.append(bench_graph([(lambda sptr, s=s: s.launch(lib, sptr)) for s in sets], 3, 10).dur_us)
+        if use_graph:
+            out.append(bench_graph([(lambda sptr, s=s: s.launch(lib, sptr)) for s in sets], 3, 10).dur_us)
+        else:
+            stream = torch.cuda.current_stream(device)
+            for s in sets:
+                s.launch(lib, stream.cuda_stream)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(3):
+                for s in sets:
+                    s.launch(lib, stream.cuda_stream)
+            e1.record(stream)
+            torch.cuda.synchronize(device)
+            out.append(e0.elapsed_time(e1) * 1e3 / (3 * len(sets)))
         del sets
     return out
 
@@ -364,7 +378,7 @@ def run_dense(args, rank, world, device):
     verified = all(c.verify() for c in cases) if rank == 0 else None
 
     # Per-shape times and the roofline figures
-    per_case_us = per_shape_times(lib, device, cases)
+    per_case_us = per_shape_times(lib, device, cases, use_graph=graph is not None)
     barrier()
     clocks = sampler.stop() if sampler else None
     status = deep_gemm.device_status()
@@ -438,7 +452,7 @@ def run_dense(args, rank, world, device):
 
     if rank != 0:
         return
-    legs = other_config_legs(args, device, pk) if world == 1 and not args.no_legs else None
+    legs = other_config_legs(args, device, pk) if world == 1 and not args.no_legs and not args.no_graph else None
 
     big = [i for i, c in enumerate(cases) if c.m == 4096]
     small = [i for i, c in enumerate(cases) if c.m <= 128]

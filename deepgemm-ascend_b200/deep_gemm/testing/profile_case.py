@@ -31,6 +31,10 @@ def main() -> None:
     ap.add_argument('--bf16', action='store_true', help='BF16 operands, no scale factors (dense only)')
     ap.add_argument('--quant', default='', choices=['', 'swiglu', 'cast'],
                     help='run the FP8 producer on [m, k] activations instead of a GEMM')
+    ap.add_argument('--mixed', action='store_true', help='FP8 x packed FP4 "NN": B is [k, n / 2] packed E2M1 (dense only)')
+    ap.add_argument('--masked', type=int, default=0, help='>0: m-grouped masked with this many groups of at most m rows')
+    ap.add_argument('--layout', action='store_true',
+                    help='run transform_sf_into_required_layout on FP32 scales [m, k / 32] instead of a GEMM')
     args = ap.parse_args()
 
     torch.manual_seed(0)
@@ -46,6 +50,14 @@ def main() -> None:
                 deep_gemm.swiglu_apply_weight_to_fp8(x)
             else:
                 deep_gemm.cast_to_fp8(x)
+        torch.cuda.synchronize()
+        print('status', deep_gemm.device_status(), 'launches', args.iters)
+        return
+
+    if args.layout:
+        sf = (torch.randint(100, 140, (m, k // 32), dtype=torch.int32, device=dev) << 23).view(torch.float32)
+        for _ in range(args.iters):
+            deep_gemm.transform_sf_into_required_layout(sf, m, k, (1, 1, 32), is_sfa=True)
         torch.cuda.synchronize()
         print('status', deep_gemm.device_status(), 'launches', args.iters)
         return
@@ -69,8 +81,20 @@ def main() -> None:
     config = {key: val for key, val in (('block_n', args.block_n), ('cta_group', args.cta_group),
                                         ('split_k', args.split_k), ('num_stages', args.stages)) if val}
     layout = torch.arange(1, g + 1, dtype=torch.int32, device=dev) * m if g else None
+    if args.mixed:
+        b_packed = torch.randint(-128, 128, (k, n // 2), dtype=torch.int8, device=dev)
+    if args.masked:
+        gm = args.masked
+        a3, sfa3 = codes(gm, m, k), scales((gm,), m)
+        b3, sfb3 = codes(gm, n, k), scales((gm,), n)
+        d3 = torch.empty(gm, m, n, dtype=torch.bfloat16, device=dev)
+        mask = torch.randint(0, m + 1, (gm,), dtype=torch.int32, device=dev)
     for _ in range(args.iters):
-        if args.bf16:
+        if args.masked:
+            deep_gemm.m_grouped_fp8_gemm_nt_masked((a3, sfa3), (b3, sfb3), d3, mask, m // 2, config=config or None)
+        elif args.mixed:
+            deep_gemm.fp8_fp4_gemm_nn((a, sfa), (b_packed, sfb.transpose(0, 1)), d, config=config or None)
+        elif args.bf16:
             deep_gemm.bf16_gemm_nt(a_bf16, b_bf16, d, config=config or None)
         elif g:
             deep_gemm.m_grouped_fp8_gemm_nt_contiguous((a, sfa), (b, sfb), d, layout, config=config or None)
