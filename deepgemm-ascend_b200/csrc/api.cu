@@ -440,7 +440,7 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
                 const uint32_t kb_per = ceil_div_u32(nkb, split);
                 const bool single_accum = 2 * bn + sf_tmem_cols(bn, atoms) > 512;
                 // (a wide tile has one accumulator: ~290 cycles per 32-column chunk are not hidden behind the next tile)
-                const double t_epi = bn > 256 ? bn * 9.0 : bn * (out_fp32 ? 8.0 : 6.0);
+                const double t_epi = bn > 256 ? bn * 12.0 : bn * (out_fp32 ? 8.0 : 6.0);
                 const bool packed_b = d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3;
                 const double main_loop = rows > kBlockM ? tile_main_cycles(cg, bn, kb_per, atoms, out_fp32 ? 4 : elem_size(d.d_dtype), packed_b, decodes_b(d))
                                                         : kb_per * k_block_cycles(cg, bn, packed_b, decodes_b(d));
