@@ -301,6 +301,7 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
                         max_stages_for(c.block_n, c.cta_group, d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3, 2, cs, sf_atoms(d), epi_warps) ? 1u : 2u;
     }
     DG_CHECK_ARG(c.reserved[1] >= 1 && c.reserved[1] <= kMaxStoreBufs, "store buffers per warp must be 1..4");
+    DG_CHECK_ARG(c.reserved[4] <= 64, "raster group must be at most 64 row blocks");
     const uint32_t store_bufs = c.reserved[1];
     uint32_t max_stages = max_stages_for(c.block_n, c.cta_group, decode_b, store_bufs, cluster_split, atoms, epi_warps);
     if (c.num_stages == 0 || c.num_stages > max_stages) c.num_stages = max_stages;
@@ -552,7 +553,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.grouped_layout = d.grouped_layout;
     a.split_k = c.split_k;
     a.k_blocks_per_split = ceil_div_u32(a.num_k_blocks, c.split_k);
-    a.raster_group = 8;
+    a.raster_group = c.reserved[4] ? c.reserved[4] : 8;
     while (a.raster_group > 1 && (uint64_t)a.raster_group * a.num_n_blocks >= (1u << 16)) a.raster_group /= 2;
     {
         // the kernel divides tile indices by multiplying with these (fast_div): indices below 2^24, index x divisor below 2^40

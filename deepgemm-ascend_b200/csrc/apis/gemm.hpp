@@ -83,6 +83,7 @@ inline void apply_config_override(const OptConfig& config, dg_gemm_config_t& cfg
         else if (key == "store_bufs") cfg.reserved[1] = (uint32_t)value;
         else if (key == "k_stagger") cfg.reserved[2] = (uint32_t)value;
         else if (key == "cluster_split") cfg.reserved[3] = (uint32_t)value;
+        else if (key == "raster_group") cfg.reserved[4] = (uint32_t)value;
         else if (key == "epilogue_warps") {
             host_assert(value == 4 || value == 8, "epilogue_warps must be 4 or 8");
             cfg.reserved[5] = value == 8 ? 2u : 1u;

@@ -590,6 +590,8 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
                 cfg.reserved[2] = int(value)
             elif key == 'cluster_split':
                 cfg.reserved[3] = int(value)
+            elif key == 'raster_group':
+                cfg.reserved[4] = int(value)
             elif key == 'epilogue_warps':
                 cfg.reserved[5] = {4: 1, 8: 2}[int(value)]
             else:

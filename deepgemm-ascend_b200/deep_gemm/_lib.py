@@ -52,7 +52,7 @@ class GemmConfig(C.Structure):
     def as_dict(self) -> dict:
         return {name: getattr(self, name) for name, _ in self._fields_ if name != 'reserved'} | {
             'accum_stages': self.reserved[0], 'store_bufs': self.reserved[1], 'k_stagger': self.reserved[2],
-            'cluster_split': self.reserved[3], 'epilogue_warps': 8 if self.reserved[5] == 2 else 4}
+            'cluster_split': self.reserved[3], 'raster_group': self.reserved[4], 'epilogue_warps': 8 if self.reserved[5] == 2 else 4}
 
 
 _PROTOTYPES = {

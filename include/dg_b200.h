@@ -138,7 +138,9 @@ typedef struct {
                                * [3] split_k > 1 only: 0 = partial sums go to the FP32 workspace and a second kernel casts
                                *     them, 1 = the splits of a tile run as one thread-block cluster (cta_group 1,
                                *     split_k <= 8, B not packed) and reduce through shared memory: no workspace;
-                               * [4] unused, must be 0;
+                               * [4] dense GEMM: row blocks per rasterisation group (tiles are handed out row block fastest
+                               *     inside groups of this many row blocks, so that CTAs running together share their
+                               *     B panels in L2); 0 = 8;
                                * [5] epilogue warps: 0 = auto, 1 = four, 2 = eight (two warps per TMEM lane quarter, each
                                *     taking alternate 32-column chunks; E4M3 x E4M3 with K-major operands only) */
 } dg_gemm_config_t;
@@ -152,7 +154,9 @@ size_t dg_gemm_workspace_bytes(const dg_gemm_desc_t* desc, const dg_gemm_config_
 
 /* Enqueue the GEMM. Replaces launch_fp8_gemm / launch_fp4_gemm / launch_fp8_dequant_gemm,
  * csrc/jit_kernels/fp8_gemm.hpp:11-79,83-151 and csrc/jit_kernels/fp8_dequant_gemm.hpp:24-95.
- * `config` may be NULL (the heuristic is used). */
+ * `config` may be NULL (the heuristic is used). The first launch of a kernel variant on a device loads it, looks up
+ * the status word's address and raises the variant's shared-memory limit: make one launch of every problem a stream
+ * capture will contain before the capture begins (a warm-up pass does). */
 int dg_gemm_launch(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config,
                    void* workspace, size_t workspace_bytes, void* stream);
 
