@@ -493,3 +493,51 @@ def test_dense_wide_tiles_last_wave_in_halves(bn, n):
         outs.append(d)
     assert deep_gemm.device_status() == 0
     assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+
+
+@pytest.mark.parametrize('trans_b', [False, True])
+def test_m_grouped_mixed_fp8_fp4(trans_b):
+    """m-grouped contiguous and masked GEMM with a packed-FP4 B: [G, N, K/2] (K-major) or [G, K, N/2] (MN-major codes).
+    N and K are multiples of 128, so the tensor cores read B as E2M1 (one 3-D tensor map over all groups); a second
+    problem with N = 392 takes the decoder warps instead."""
+    seed_all(21)
+    sizes = [300, 0, 513]
+    total, psum = oracle.make_psum_layout(sizes, 256)
+    layout = torch.tensor(psum, dtype=torch.int32, device='cuda')
+    for n, k in ((384, 512), (392, 640)):
+        a, sfa, a_ref = uniform_fp8((total, k), (1, 32))
+        for span in oracle.psum_padding_spans(psum):
+            a.view(torch.uint8)[span] = 0
+            a_ref[span] = 0
+        parts = [uniform_fp4(n, k, (1, 32), mn_major=trans_b) for _ in sizes]
+        b_ref = torch.stack([p[2] for p in parts])
+        sfb = torch.stack([p[1] for p in parts])
+        if trans_b:      # storage [G, K, N/2]; the API takes the [G, K, N/2] tensor and transposes it itself
+            b_store = torch.stack([p[0].transpose(0, 1).contiguous() for p in parts]).cuda()
+            b_arg = (b_store, sfb.cuda().transpose(1, 2))
+            fn = deep_gemm.m_grouped_fp8_fp4_gemm_nn_contiguous
+        else:
+            b_arg = (torch.stack([p[0] for p in parts]).cuda(), sfb.cuda())
+            fn = deep_gemm.m_grouped_fp8_fp4_gemm_nt_contiguous
+        d = torch.full((total, n), float('nan'), dtype=torch.bfloat16, device='cuda')
+        fn((a.cuda(), sfa.cuda()), b_arg, d, layout, recipe_a=(1, 32), recipe_b=(1, 32))
+        assert deep_gemm.device_status() == 0
+        ref = oracle.m_grouped_psum_ref(a_ref, b_ref, psum, torch.bfloat16)
+        for span in oracle.psum_valid_spans(psum, 256):
+            if span.stop > span.start:
+                assert_close(d[span], ref[span], f'm-grouped fp8xfp4 n={n} k={k} trans_b={trans_b}')
+    if not trans_b:
+        masked = [200, 0, 77]
+        n, k = 384, 512
+        am, sfam, am_ref = uniform_fp8((3, 256, k), (1, 32))
+        parts = [uniform_fp4(n, k, (1, 32), mn_major=False) for _ in masked]
+        d = torch.zeros((3, 256, n), dtype=torch.bfloat16, device='cuda')
+        deep_gemm.m_grouped_fp8_fp4_gemm_nt_masked((am.cuda(), sfam.cuda()),
+                                                   (torch.stack([p[0] for p in parts]).cuda(), torch.stack([p[1] for p in parts]).cuda()),
+                                                   d, torch.tensor(masked, dtype=torch.int32, device='cuda'), 100,
+                                                   recipe_a=(1, 32), recipe_b=(1, 32))
+        assert deep_gemm.device_status() == 0
+        ref = oracle.m_grouped_masked_ref(am_ref, torch.stack([p[2] for p in parts]), masked, torch.bfloat16)
+        for g, mg in enumerate(masked):
+            if mg:
+                assert_close(d[g, :mg], ref[g, :mg], f'masked fp8xfp4 group {g}')
