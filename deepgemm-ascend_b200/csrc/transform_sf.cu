@@ -165,9 +165,14 @@ __global__ void __launch_bounds__(kTsfThreads) transform_sf_kernel(const Transfo
 // same staging in shared memory, but every thread moves 16 bytes at a time: four FP32 scales (or eight packed scale
 // bytes) in, eight int16 results of eight consecutive rows out, so the instruction count per byte drops by about six
 // and the kernel follows HBM instead of the issue rate.
-template <bool kFp32>
+// kPerRow (gran_mn = 1, the scales of activations and of per-row quantised weights): the staging area is kept
+// transposed, one array of int16 results per output column, so that the eight consecutive rows a thread writes are two
+// 8-byte shared-memory loads instead of sixteen byte gathers.
+constexpr uint32_t kColPitch = kTileRows + 4;      // int16 elements per staged column (8-byte aligned, spreads the banks)
+template <bool kFp32, bool kPerRow>
 __global__ void __launch_bounds__(kTsfThreads, 4) transform_sf_stream_kernel(const TransformSfArgs a) {
-    __shared__ __align__(16) uint8_t bytes[kTileRows][64 + 4];
+    __shared__ __align__(16) uint8_t bytes[kPerRow ? 1 : kTileRows][64 + 4];
+    __shared__ __align__(16) uint16_t cols[kPerRow ? kTileCols : 1][kColPitch];
     __shared__ uint8_t padded[kTileRows];
 
     const uint32_t tiles_per_batch = a.tiles_m * a.tiles_c;
@@ -219,7 +224,7 @@ __global__ void __launch_bounds__(kTsfThreads, 4) transform_sf_stream_kernel(con
         #pragma unroll
         for (uint32_t it = 0; it < kUnitsPerThread; ++it) {
             const uint32_t i = threadIdx.x + it * kTsfThreads;
-            if (i >= units) continue;
+            if (i >= (kPerRow ? (kTileRows << unit_shift) : units)) continue;      // (transposed staging: rows without a source get zeros)
             const uint32_t r = i >> unit_shift, u = i & ((1u << unit_shift) - 1u);
             uint32_t word = in[it].x;
             if constexpr (kFp32) {
@@ -231,7 +236,21 @@ __global__ void __launch_bounds__(kTsfThreads, 4) transform_sf_stream_kernel(con
                     if ((v[j] & 0x807fffffu) != 0u) bad = true;       // negative or not a power of two
                 }
             }
-            *reinterpret_cast<uint32_t*>(&bytes[r][4u * u]) = word;
+            if constexpr (kPerRow) {
+                if (a.k_repeat_shift == 0) {          // bytes 0..3 = K blocks 4u..4u+3 -> int16 columns 2u, 2u + 1
+                    cols[2u * u][r] = (uint16_t)(word & 0xffffu);
+                    cols[2u * u + 1u][r] = (uint16_t)(word >> 16);
+                } else {                               // each byte covers four K blocks -> two equal int16 columns
+                    #pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j) {
+                        const uint16_t both = (uint16_t)(((word >> (8u * j)) & 0xffu) * 0x0101u);
+                        cols[8u * u + 2u * j][r] = both;
+                        cols[8u * u + 2u * j + 1u][r] = both;
+                    }
+                }
+            } else {
+                *reinterpret_cast<uint32_t*>(&bytes[r][4u * u]) = word;
+            }
         }
         __syncthreads();
 
@@ -242,20 +261,29 @@ __global__ void __launch_bounds__(kTsfThreads, 4) transform_sf_stream_kernel(con
             const uint32_t ml0 = g8 * 8u, mn = mn0 + ml0, col = c0 + c;
             if (mn >= a.dst_mn || col >= a.dst_cols) continue;
             const uint32_t kb = 2u * col;
-            const uint32_t rel0 = (kb >> a.k_repeat_shift) - s0, rel1 = ((kb + 1u) >> a.k_repeat_shift) - s0;
             const uint32_t keep = ((passthrough || kb < a.k32_blocks) ? 0x00ffu : 0u) | ((passthrough || kb + 1u < a.k32_blocks) ? 0xff00u : 0u);
-            uint32_t out[8];
-            #pragma unroll
-            for (uint32_t j = 0; j < 8; ++j) {
-                const uint32_t r = (ml0 + j) >> a.gran_shift;
-                out[j] = r < rows ? (((uint32_t)bytes[r][rel0] | ((uint32_t)bytes[r][rel1] << 8)) & keep) : 0u;
+            uint4 packed;
+            if constexpr (kPerRow) {
+                const uint2 lo = *reinterpret_cast<const uint2*>(&cols[c][ml0]);
+                const uint2 hi = *reinterpret_cast<const uint2*>(&cols[c][ml0 + 4u]);
+                const uint32_t keep2 = keep | (keep << 16);
+                packed = make_uint4(lo.x & keep2, lo.y & keep2, hi.x & keep2, hi.y & keep2);
+            } else {
+                const uint32_t rel0 = (kb >> a.k_repeat_shift) - s0, rel1 = ((kb + 1u) >> a.k_repeat_shift) - s0;
+                uint32_t out[8];
+                #pragma unroll
+                for (uint32_t j = 0; j < 8; ++j) {
+                    const uint32_t r = (ml0 + j) >> a.gran_shift;
+                    out[j] = r < rows ? (((uint32_t)bytes[r][rel0] | ((uint32_t)bytes[r][rel1] << 8)) & keep) : 0u;
+                }
+                packed = make_uint4(out[0] | (out[1] << 16), out[2] | (out[3] << 16), out[4] | (out[5] << 16), out[6] | (out[7] << 16));
             }
             int16_t* dst = a.dst + batch * a.dst_batch_stride + (uint64_t)col * a.dst_col_stride + mn;
             if (mn + 8u <= a.dst_mn) {
-                *reinterpret_cast<uint4*>(dst) = make_uint4(out[0] | (out[1] << 16), out[2] | (out[3] << 16),
-                                                            out[4] | (out[5] << 16), out[6] | (out[7] << 16));
+                *reinterpret_cast<uint4*>(dst) = packed;
             } else {
-                for (uint32_t j = 0; mn + j < a.dst_mn; ++j) dst[j] = (int16_t)out[j];
+                const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
+                for (uint32_t j = 0; mn + j < a.dst_mn; ++j) dst[j] = (int16_t)(w[j >> 1] >> (16u * (j & 1u)));
             }
         }
     }
@@ -327,8 +355,11 @@ extern "C" int dg_transform_sf_launch(const void* src, int src_is_fp32,
                            (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && dst_col_stride % 8 == 0 && dst_batch_stride % 8 == 0 &&
                            getenv("DG_TRANSFORM_GENERIC") == nullptr;
     auto s = static_cast<cudaStream_t>(stream);
-    if (stream_ok && src_is_fp32) transform_sf_stream_kernel<true><<<dim3(grid_x, num_batches), kTsfThreads, 0, s>>>(a);
-    else if (stream_ok) transform_sf_stream_kernel<false><<<dim3(grid_x, num_batches), kTsfThreads, 0, s>>>(a);
+    const bool per_row = gran_mn == 1;
+    if (stream_ok && src_is_fp32 && per_row) transform_sf_stream_kernel<true, true><<<dim3(grid_x, num_batches), kTsfThreads, 0, s>>>(a);
+    else if (stream_ok && src_is_fp32) transform_sf_stream_kernel<true, false><<<dim3(grid_x, num_batches), kTsfThreads, 0, s>>>(a);
+    else if (stream_ok && per_row) transform_sf_stream_kernel<false, true><<<dim3(grid_x, num_batches), kTsfThreads, 0, s>>>(a);
+    else if (stream_ok) transform_sf_stream_kernel<false, false><<<dim3(grid_x, num_batches), kTsfThreads, 0, s>>>(a);
     else transform_sf_kernel<<<dim3(grid_x, num_batches), kTsfThreads, 0, s>>>(a);
     DG_CHECK_CUDA(cudaGetLastError());
     count_kernel_launch();

@@ -220,7 +220,7 @@ def run_grouped(args, rank, world, device, emit, pk):
     on its own. The end-to-end leg copies the rank's A, B and scales from pinned host memory, calls the public API and
     copies D back, inside the timed region."""
     import deep_gemm
-    from .sharding import expert_range
+    from .sharding import balanced_expert_ranges, expert_range
     lib = L.lib()
     stream = torch.cuda.current_stream(device)
     sptr = stream.cuda_stream
@@ -232,7 +232,9 @@ def run_grouped(args, rank, world, device, emit, pk):
         sizes = [random.randint(0, 256) for _ in range(g_total)]
     else:
         sizes = [int(random.uniform(0.7, 1.3) * 8192) for _ in range(g_total)]
-    g0, g1 = expert_range(g_total, world, rank)
+    # contiguous blocks of experts: balanced by rows for the contiguous layout, by count for the masked one (whose cost
+    # is the experts' B, the same for every expert)
+    g0, g1 = expert_range(g_total, world, rank) if masked else balanced_expert_ranges(sizes, world)[rank]
     mine = sizes[g0:g1]
     cases = [GroupedCase(mine, n, k, device, seed=100 * rank + i, masked_max_m=256 if masked else 0)
              for i, (n, k) in enumerate(NK_LIST)]
@@ -357,7 +359,8 @@ def run_grouped(args, rank, world, device, emit, pk):
         'config': {'workload': ('m-grouped masked FP8 GEMM, %d experts x max_m 256, valid rows ~ U[0,256]' if masked else
                                 'm-grouped contiguous FP8 GEMM (psum layout), %d experts in total, rows per expert ~ U(0.7,1.3) x 8192')
                                % g_total + ', (N,K) in ' + str(NK_LIST) + ', BF16 out',
-                   'sharding': 'experts in contiguous blocks over %d rank(s), no data-path collective' % world,
+                   'sharding': 'experts in contiguous blocks over %d rank(s)%s, no data-path collective'
+                               % (world, '' if masked else ', block boundaries balanced by rows'),
                    'l2': 'flushed before every GEMM, untimed', 'flops': 'valid rows only'},
         'verified': verified,
         'gemm_ms': gemm_ms, 'gather_ms': gather_ms,

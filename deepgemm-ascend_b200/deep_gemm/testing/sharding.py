@@ -22,6 +22,44 @@ def expert_range(num_experts: int, world: int, rank: int) -> tuple[int, int]:
     return begin, begin + base + (1 if rank < extra else 0)
 
 
+def balanced_expert_ranges(sizes: list[int], world: int) -> list[tuple[int, int]]:
+    """Contiguous blocks of experts, one per rank, that minimise the largest number of (256-aligned) rows any rank
+    gets: the step time of the sharded grouped GEMM is the slowest rank's. Per-expert sizes ~ U(0.7, 1.3) x 8192 make
+    equal expert counts up to 15 % uneven in rows. Every rank computes the same answer from the same `sizes`."""
+    rows = [_align(s) for s in sizes]
+    n = len(rows)
+    if world <= 1 or n == 0:
+        return [(0, n)] + [(n, n)] * max(0, world - 1)
+
+    def blocks_needed(cap: int) -> int:
+        count, load = 1, 0
+        for r in rows:
+            if load + r > cap and load > 0:
+                count, load = count + 1, 0
+            load += r
+        return count
+
+    lo, hi = max(rows), sum(rows)
+    while lo < hi:                                   # smallest cap that fits in `world` contiguous blocks
+        mid = (lo + hi) // 2
+        if blocks_needed(mid) <= world:
+            hi = mid
+        else:
+            lo = mid + 1
+    ranges, begin, load = [], 0, 0
+    for i, r in enumerate(rows):
+        remaining_ranks = world - len(ranges) - 1
+        # close the block when the next expert would exceed the cap, or when every remaining rank needs an expert
+        if i > begin and (load + r > lo) and remaining_ranks > 0:
+            ranges.append((begin, i))
+            begin, load = i, 0
+        load += r
+    ranges.append((begin, n))
+    while len(ranges) < world:                       # fewer blocks than ranks: the last ranks get nothing
+        ranges.append((n, n))
+    return ranges
+
+
 def psum_from_sizes(sizes: list[int]) -> tuple[int, list[int]]:
     """Per-group row counts -> (total rows incl. padding, psum list of end rows); tests/generators.py:212-220."""
     psum, out = 0, []

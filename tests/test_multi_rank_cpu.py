@@ -23,6 +23,24 @@ def test_expert_and_column_ranges_partition_exactly():
     assert all(a[1] == b[0] for a, b in zip(cols, cols[1:]))
 
 
+def test_balanced_expert_ranges_partition_and_balance():
+    import random
+    random.seed(1234)
+    sizes = [int(random.uniform(0.7, 1.3) * 8192) for _ in range(32)]
+    for world in (1, 2, 4, 8):
+        ranges = sharding.balanced_expert_ranges(sizes, world)
+        assert len(ranges) == world and ranges[0][0] == 0 and ranges[-1][1] == 32
+        assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+        assert all(e > b for b, e in ranges)                         # nobody idles with 32 experts
+        loads = [sum(sizes[b:e]) for b, e in ranges]
+        even = [sum(sizes[b:e]) for b, e in (sharding.expert_range(32, world, r) for r in range(world))]
+        assert max(loads) <= max(even)                                # never worse than equal counts
+    # more ranks than experts, and an empty problem
+    assert sharding.balanced_expert_ranges([100, 200], 4)[:2] == [(0, 1), (1, 2)]
+    assert sharding.balanced_expert_ranges([100, 200], 4)[2:] == [(2, 2), (2, 2)]
+    assert sharding.balanced_expert_ranges([], 2) == [(0, 0), (0, 0)]
+
+
 def test_local_psum_layout_matches_global_rows():
     sizes = [300, 0, 513, 255, 256, 1, 700, 90]
     total, psum = sharding.psum_from_sizes(sizes)
