@@ -6,7 +6,9 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <torch/extension.h>
 
+#include <atomic>
 #include <cstdint>
+#include <cstdlib>
 #include <mutex>
 #include <optional>
 #include <sstream>

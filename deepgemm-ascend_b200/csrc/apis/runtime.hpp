@@ -1,6 +1,8 @@
 // Runtime knobs: the counterpart of csrc/apis/runtime.hpp:12-80 (same names and argument names).
 #pragma once
 
+#include <map>
+
 #include "common.hpp"
 
 namespace dg_host {

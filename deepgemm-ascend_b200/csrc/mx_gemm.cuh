@@ -511,7 +511,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     griddep_wait();
     griddep_launch_dependents();
     if (threadIdx.x == 0) trace_mark(p, 16);
-    const uint32_t tmem_base = tmem_ptr_smem[0];      // (not yet written when warp 0 gets here; warp 0 never uses it)
+    const uint32_t tmem_base = tmem_ptr_smem[0];      // (possibly not yet written when warp 0 gets here: see the epilogue)
     if (threadIdx.x == 0) trace_mark(p, 2);
     // TMEM columns: accumulators first, then the scale factors of A and of B.
     const uint32_t tmem_sfa = tmem_base + p.accum_stages * p.block_n;
@@ -818,7 +818,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             if (tile_iter == 0 && threadIdx.x == 128) trace_mark(p, 6);
             tc_fence_after_sync();
             const uint32_t row = t.row0 + q * 32 + lane;       // row of D held by this thread
-            const uint32_t taddr = tmem_base + ((q * 32u) << 16) + e * p.block_n;
+            // Warp 0 read tmem_base right after checking in at the set-up barrier, possibly before the allocation had
+            // written it; the accumulator barrier it has just passed orders this read behind the allocation.
+            const uint32_t taddr = (eset != 0 ? tmem_ptr_smem[0] : tmem_base) + ((q * 32u) << 16) + e * p.block_n;
             // columns of the tile this launch of the epilogue covers (a half tile of a wide-tile launch: one half)
             const uint32_t col_begin = (kWideTile && t.halves == 2u) ? half_n : 0u;
             const uint32_t col_end = (kWideTile && t.halves == 1u) ? half_n : p.block_n;

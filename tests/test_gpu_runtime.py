@@ -186,3 +186,30 @@ def test_results_do_not_depend_on_launch_overlap():
     assert deep_gemm.device_status() == 0
     for x1, x2 in zip(first, second):
         assert torch.equal(x1.view(torch.int16), x2.view(torch.int16))
+
+
+def test_lean_gemm_after_kernels_that_dirty_shared_memory():
+    """A small-M GEMM (one tile per CTA, warps 0..3 join the epilogue) launched straight behind kernels that leave other
+    contents in shared memory: every warp must take the accumulator's TMEM address from this CTA's own allocation, never
+    from whatever the previous kernel left at that shared-memory word. Same bits as the first, undisturbed, call."""
+    seed_all(10)
+    m, n, k = 128, 7168, 2048
+    a, sfa, _ = uniform_fp8((m, k), (1, 128))
+    b, sfb, _ = uniform_fp8((n, k), (128, 128))
+    a, sfa, b, sfb = a.cuda(), sfa.cuda(), b.cuda(), sfb.cuda()
+    sfa_t = deep_gemm.transform_sf_into_required_layout(sfa, m, k, (1, 128), None)
+    sfb_t = deep_gemm.transform_sf_into_required_layout(sfb, n, k, (128, 128), None)
+    want = torch.empty(m, n, dtype=torch.bfloat16, device='cuda')
+    deep_gemm.fp8_gemm_nt((a, sfa_t), (b, sfb_t), want)
+    torch.cuda.synchronize()
+    noise = torch.randn(148 * 8, 4096, device='cuda')
+    for i in range(40):
+        got = torch.empty_like(want)
+        # softmax, sort and a small matmul keep data in shared memory on every SM
+        torch.softmax(noise, dim=-1)
+        torch.sort(noise, dim=-1)
+        noise[:512, :512] @ noise[:512, :512]
+        deep_gemm.fp8_gemm_nt((a, sfa_t), (b, sfb_t), got)
+        torch.cuda.synchronize()
+        assert deep_gemm.device_status() == 0
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f'iteration {i}'
