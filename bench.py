@@ -310,6 +310,27 @@ def per_shape_times(lib, device, base_cases, use_graph=True) -> list[float]:
     return out
 
 
+def copies_of_same_bytes(device, base_cases) -> dict:
+    """For every few-rows shape: microseconds per copy when device-to-device copies that move the same number of bytes
+    (half read, half written) run back to back in a graph over rotating buffers, exactly like the GEMM launches of
+    `per_shape_times`. A launch that moves 16-45 MB cannot reach the bandwidth of a long copy: this is what a plain copy
+    of that size achieves on this box, start-up and tail included."""
+    from deep_gemm.testing import bench_graph
+    out = {}
+    for c in base_cases:
+        if c.m > 128:
+            continue
+        half = c.bytes // 2
+        copies = max(3, min(32, -(-512_000_000 // c.bytes)))
+        bufs = [(torch.empty(half, dtype=torch.uint8, device=device), torch.empty(half, dtype=torch.uint8, device=device))
+                for _ in range(copies)]
+        for src, _ in bufs:
+            src.zero_()
+        out[(c.m, c.n, c.k)] = bench_graph([(lambda sptr, sd=sd: sd[1].copy_(sd[0])) for sd in bufs], 3, 10).dur_us
+        del bufs
+    return out
+
+
 def run_dense(args, rank, world, device):
     import deep_gemm
     from deep_gemm import _lib as L
@@ -379,6 +400,7 @@ def run_dense(args, rank, world, device):
 
     # Per-shape times and the roofline figures
     per_case_us = per_shape_times(lib, device, cases, use_graph=graph is not None)
+    copy_us = copies_of_same_bytes(device, cases) if rank == 0 and graph is not None else {}
     barrier()
     clocks = sampler.stop() if sampler else None
     status = deep_gemm.device_status()
@@ -458,6 +480,9 @@ def run_dense(args, rank, world, device):
     small = [i for i, c in enumerate(cases) if c.m <= 128]
     tf_big = sum(cases[i].flops for i in big) / sum(per_case_us[i] for i in big) / 1e6
     gbs_small = sum(cases[i].bytes for i in small) / sum(per_case_us[i] for i in small) / 1e3
+    # the same twelve byte counts as plain device-to-device copies, launched and timed the same way
+    gbs_copies = (sum(cases[i].bytes for i in small) / sum(copy_us[(cases[i].m, cases[i].n, cases[i].k)] for i in small) / 1e3
+                  if copy_us else None)
     fp8_peak = 2.0 * pk['bf16_tflops']
     top = max(big, key=lambda i: cases[i].flops)
     write_gbs = measure_write_bandwidth(device)
@@ -467,7 +492,11 @@ def run_dense(args, rank, world, device):
         floors = {'tensor': c.flops / fp8_peak / 1e6, 'hbm': c.bytes / pk['hbm_gbs'] / 1e3,
                   'hbm_write': c.m * c.n * 2 / write_gbs / 1e3}
         bound = max(floors, key=floors.get)
-        return {'bound': bound, 'floor_us': round(floors[bound], 2), 'frac': round(floors[bound] / us, 3)}
+        out = {'bound': bound, 'floor_us': round(floors[bound], 2), 'frac': round(floors[bound] / us, 3)}
+        if (c.m, c.n, c.k) in copy_us:      # a device-to-device copy of the same bytes, timed the same way
+            out['copy_of_same_bytes_us'] = round(copy_us[(c.m, c.n, c.k)], 2)
+            out['frac_of_that_copy'] = round(copy_us[(c.m, c.n, c.k)] / us, 3)
+        return out
     shapes = [{'m': c.m, 'n': c.n, 'k': c.k, 'us': round(per_case_us[i], 2),
                'tflops': round(c.flops / per_case_us[i] / 1e6, 1), 'gbs': round(c.bytes / per_case_us[i] / 1e3, 1),
                'block_n': c.config['block_n'], 'cta_group': c.config['cta_group'], 'split_k': c.config['split_k'],
@@ -494,7 +523,9 @@ def run_dense(args, rank, world, device):
                      'hbm': {'bound': 'hbm', 'achieved': gbs_small, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
                              'frac': gbs_small / pk['hbm_gbs'], 'frac_of_nominal': gbs_small / NOMINAL_HBM_GBS,
                              'kernel': 'mx_gemm_kernel (+ split-K finalisation where used) on the twelve M<=128 launches',
-                             'peak_source': 'copy bandwidth of MEASURED_PEAKS.json (%s)' % pk['source']}},
+                             'peak_source': 'copy bandwidth of MEASURED_PEAKS.json (%s)' % pk['source'],
+                             'copies_of_same_bytes_gbs': round(gbs_copies, 1) if gbs_copies else None,
+                             'frac_of_copies_of_same_bytes': round(gbs_small / gbs_copies, 3) if gbs_copies else None}},
         'e2e': {'value': e2e_value, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': sum(c.h2d for c in cases),
                 'd2h_bytes_per_step': sum(c.d2h for c in cases), 'steps': e2e_steps},
         'host_us_per_call': {'fp8_gemm_nt, scales in the required layout (plan reused)': round(host_call_us, 1),
