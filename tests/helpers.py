@@ -36,6 +36,23 @@ def uniform_fp8(shape, gran, sf_choices=(2.0 ** -9, 2.0 ** -8, 2.0 ** -7)):
     return data, sf, oracle.dequantize(data.float(), sf, gran[0], gran[1])
 
 
+def uniform_codes(shape) -> torch.Tensor:
+    """Random E4M3 bytes (uint8) without the two NaN codes: the distribution of tests/generators.py:137-153, drawn
+    eight bytes at a time because some tensors of the full-size tests hold up to two billion codes."""
+    numel = 1
+    for s in shape:
+        numel *= s
+    raw = torch.randint(-2 ** 63, 2 ** 63 - 1, ((numel + 7) // 8,), dtype=torch.int64).view(torch.uint8)[:numel].view(shape)
+    raw -= ((raw & 0x7F) == 0x7F).to(torch.uint8)           # 0x7f -> 0x7e, 0xff -> 0xfe
+    return raw
+
+
+def pow2_scales(shape) -> torch.Tensor:
+    """One of {2^-9, 2^-8, 2^-7} per element (tests/generators.py:141), FP32."""
+    table = torch.tensor([2.0 ** -9, 2.0 ** -8, 2.0 ** -7], dtype=torch.float32)
+    return table[torch.randint(0, 3, shape)].contiguous()
+
+
 def uniform_fp4(mn, k, gran, mn_major: bool, sf_choices=(0.25, 0.5, 1.0)):
     """Uniform random packed E2M1 (tests/generators.py:155-164): returns (packed int8 whose logical shape is
     [MN, K] with two codes per byte along the contiguous axis, sf fp32, dequantised fp32 [MN, K]).

@@ -17,27 +17,12 @@ import torch
 
 import deep_gemm
 import oracle
-from helpers import assert_close, assert_close_device, seed_all, uniform_fp4, uniform_fp8, with_major
+from helpers import (assert_close, assert_close_device, pow2_scales, seed_all, uniform_codes, uniform_fp4, uniform_fp8,
+                     with_major)
 
 pytestmark = pytest.mark.gpu
 
 NK_LIST = [(2112, 7168), (24576, 1536), (32768, 512), (7168, 16384), (4096, 7168), (7168, 2048)]
-
-
-def _uniform_codes(shape) -> torch.Tensor:
-    """Random E4M3 bytes without the two NaN codes (the distribution of tests/generators.py:137-153, drawn eight
-    bytes at a time because these tensors hold up to two billion codes)."""
-    numel = 1
-    for s in shape:
-        numel *= s
-    raw = torch.randint(-2 ** 63, 2 ** 63 - 1, ((numel + 7) // 8,), dtype=torch.int64).view(torch.uint8)[:numel].view(shape)
-    raw -= ((raw & 0x7F) == 0x7F).to(torch.uint8)           # 0x7f -> 0x7e, 0xff -> 0xfe
-    return raw
-
-
-def _pow2_scales(shape) -> torch.Tensor:
-    table = torch.tensor([2.0 ** -9, 2.0 ** -8, 2.0 ** -7], dtype=torch.float32)
-    return table[torch.randint(0, 3, shape)].contiguous()
 
 
 # ----------------------------------------------------------------------------------------------------------------
@@ -174,13 +159,13 @@ def test_m_grouped_contiguous_32_experts_sampled_blocks(n, k):
     sizes = _expert_sizes(g, seed=32)
     total, psum = oracle.make_psum_layout(sizes, 256)
     seed_all(k + g)
-    a = _uniform_codes((total, k))
-    sfa = _pow2_scales((total, k // 32))
+    a = uniform_codes((total, k))
+    sfa = pow2_scales((total, k // 32))
     for span in oracle.psum_padding_spans(psum, 256):
         a[span] = 0
         sfa[span] = torch.randn_like(sfa[span])
-    b = _uniform_codes((g, n, k))
-    sfb = _pow2_scales((g, n, k // 32))
+    b = uniform_codes((g, n, k))
+    sfb = pow2_scales((g, n, k // 32))
     a_dev, sfa_dev = a.view(torch.float8_e4m3fn).cuda(), sfa.cuda()
     layout = torch.tensor(psum, dtype=torch.int32, device='cuda')
     # blocks to check: (group, first row)
@@ -226,10 +211,10 @@ def test_m_grouped_masked_32_experts_at_benchmark_size(n, k):
     masked = [random.randint(0, max_m) for _ in range(g)]
     masked[3], masked[7] = 0, max_m                       # an empty and a full expert are always among them
     seed_all(n)
-    a = _uniform_codes((g, max_m, k))
-    sfa = _pow2_scales((g, max_m, k // 32))
-    b = _uniform_codes((g, n, k))
-    sfb = _pow2_scales((g, n, k // 32))
+    a = uniform_codes((g, max_m, k))
+    sfa = pow2_scales((g, max_m, k // 32))
+    b = uniform_codes((g, n, k))
+    sfb = pow2_scales((g, n, k // 32))
     d = torch.full((g, max_m, n), float('nan'), dtype=torch.bfloat16, device='cuda')
     mask = torch.tensor(masked, dtype=torch.int32, device='cuda')
     deep_gemm.m_grouped_fp8_gemm_nt_masked((a.view(torch.float8_e4m3fn).cuda(), sfa.cuda()),
