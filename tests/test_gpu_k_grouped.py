@@ -13,7 +13,7 @@ import torch
 
 import deep_gemm
 import oracle
-from helpers import assert_close, seed_all, uniform_fp8
+from helpers import assert_close, assert_close_device, seed_all, uniform_fp8
 
 pytestmark = pytest.mark.gpu
 
@@ -60,7 +60,7 @@ def _run(m, n, sizes, out=torch.bfloat16, acc=False, ks_hint='list', epilogue=No
         deep_gemm.k_grouped_fp8_gemm_tn_contiguous(a_arg, b_arg, d, ks, layout, recipe=(1, 1, 32), epilogue=epilogue,
                                                    config=config, **kwargs)
     assert deep_gemm.device_status() == 0
-    assert_close(d, ref, f'k-grouped {m}x{n} sizes={sizes} out={out} acc={acc}')
+    (assert_close_device if d.numel() > (1 << 24) else assert_close)(d, ref, f'k-grouped {m}x{n} sizes={sizes} out={out} acc={acc}')
     return d, (a_arg, b_arg, layout, ks)
 
 

@@ -132,3 +132,30 @@ def test_m_grouped_contiguous_reference_settings(num_groups, expected_m, n, k):
         for span in oracle.psum_padding_spans(psum, 256):
             assert bool((d[span] == 0).all()), 'padding rows of D must be exactly zero'
         del d, b_arg
+
+
+# tests/generators.py:620-627: (groups, M, N, expected K per group) of the weight-gradient GEMM at its EP64 / EP32 / EP16
+# sizes; A [K, M] and B [K, N] hold the groups along K on the 256-row psum layout
+K_GROUPED = [(4, 4096, 7168, 8192), (4, 7168, 2048, 8192), (8, 4096, 7168, 4096), (8, 7168, 2048, 4096),
+             (16, 4096, 7168, 2048), (16, 7168, 2048, 2048)]
+
+
+@pytest.mark.parametrize('num_groups,m,n,expected_k', K_GROUPED)
+def test_k_grouped_reference_settings(num_groups, m, n, expected_k):
+    """Group sizes as the reference draws them (`max(1, int(expected_k * U(0.7, 1.3)))`), then its three variants
+    (tests/generators.py:606-613): all groups, a quarter of them empty (the first always, the last never), and a single
+    non-empty group in the middle: all three with four groups (FP32 accumulation, direct BF16, BF16 accumulation), the
+    second with eight and the first with sixteen. The whole [G, M, N] output is compared with the oracle (an empty group
+    leaves zeros, or C untouched when accumulating)."""
+    from test_gpu_k_grouped import _run
+    random.seed(num_groups + m)
+    real = [max(1, int(expected_k * random.uniform(0.7, 1.3))) for _ in range(num_groups)]
+    empty = [0 if random.random() < 0.25 else s for s in real]
+    empty[0], empty[-1] = 0, real[-1]
+    single = [s if g == num_groups // 2 else 0 for g, s in enumerate(real)]
+    if num_groups == 4:
+        _run(m, n, tuple(real), out=torch.float32, acc=True, ks_hint='list', seed=1)
+        _run(m, n, tuple(empty), out=torch.bfloat16, acc=False, ks_hint='none', seed=2)
+        _run(m, n, tuple(single), out=torch.bfloat16, acc=True, ks_hint='empty', seed=3)
+    else:                                       # 8 and 16 groups: one variant each, to keep the oracle's share short
+        _run(m, n, tuple(empty if num_groups == 8 else real), out=torch.bfloat16, acc=False, ks_hint='list', seed=1)
