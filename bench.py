@@ -1,7 +1,7 @@
 """Benchmark of the block-scaled FP8 GEMM hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload auto|dense|grouped|masked|mixed|fp4|bf16|quant|layout]
+                    [--workload auto|dense|grouped|masked|mixed|fp4|bf16|quant|layout|published]
 
 One GPU (`--workload auto` = `dense`): one "step" is one pass over the dense FP8 NT sweep the baseline names: M in
 {64, 128, 4096} times six (N, K) pairs, BF16 output, A quantised per 1x128 and B per 128x128 from N(0,1) data
@@ -10,7 +10,7 @@ in L2. The K steps are K replays of a CUDA graph of the 18 launches between one 
 times, and the two roofline figures built from them, come from a second measurement in which every shape is launched
 back to back on rotating operand sets (again larger than L2) as a graph of its own. The same line carries short legs
 for the other three configurations (mixed FP8xFP4, m-grouped contiguous with 32 experts, m-grouped masked), each with
-its own roofline, `e2e` (the sweep through the public Python API from pinned host buffers, copies inside the timed
+its own roofline, a leg over every row of the reference's own published tables (`--workload published` alone), `e2e` (the sweep through the public Python API from pinned host buffers, copies inside the timed
 region), `cpu_baseline` (the CPU oracle on the host cores over the same 18 shapes) and `verified`: after the timed
 region a row sample of every output is compared with the CPU oracle.
 
@@ -576,6 +576,12 @@ def other_config_legs(args, device, pk) -> dict:
         'shapes': r['shapes'], 'tflops': round(r['tflops'], 1), 'gbs': round(r['gbs'], 1), 'verified': r['verified'],
         'roofline': {'bound': 'hbm', 'achieved': r['gbs'], 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
                      'frac': r['gbs'] / pk['hbm_gbs'], 'frac_of_nominal': r['gbs'] / NOMINAL_HBM_GBS, 'traffic': None}}
+    # every row of the reference's own published tables (other hardware), for the ratio a reader will want to see
+    from deep_gemm.testing import published_bench
+    r = published_bench.time_published(device, steps)
+    out['reference_published_tables'] = {
+        'tflops': round(r['tflops'], 1), 'published_tflops_other_hardware': round(r['published_tflops'], 1),
+        'geomean_speedup_vs_published': round(r['geomean_speedup'], 2), 'verified': r['verified'], 'rows': r['rows']}
     return out
 
 
@@ -599,7 +605,7 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--workload', default='auto',
-                    choices=['auto', 'dense', 'grouped', 'masked', 'mixed', 'fp4', 'bf16', 'quant', 'layout'])
+                    choices=['auto', 'dense', 'grouped', 'masked', 'mixed', 'fp4', 'bf16', 'quant', 'layout', 'published'])
     ap.add_argument('--experts', type=int, default=0, help='grouped / masked workloads: global expert count (default 32)')
     ap.add_argument('--no-graph', action='store_true',
                     help='dense workload: plain stream launches instead of a CUDA graph (for profilers that cannot follow a capture)')

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <cudaTypedefs.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -468,8 +469,12 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
             for (uint32_t bn = 32; bn <= 256; bn += 32) {
                 if (bn > 32 && bn - 32 >= d.n) continue;
                 if (max_stages_for(bn, 1, false, 2, split, atoms) < 4) continue;
-                const uint64_t tiles = m_tiles * ceil_div_u32(d.n, bn) * split;
-                const uint64_t waves = (tiles + num_sms - 1) / num_sms;
+                // A cluster lives inside one GPC, so fewer clusters than SMs / split are resident at once. Assumed GPC
+                // sizes (two of 20 SMs, six of 18), consistent with what was measured: 33 clusters of 4, 45 of 3 and 18 of 6
+                // run as one wave, 18 clusters of 7 or of 8 take two.
+                const uint64_t clusters = m_tiles * ceil_div_u32(d.n, bn);
+                const uint64_t resident = std::max<uint64_t>(1, (uint64_t)(2 * (20 / split) + 6 * (18 / split)) * num_sms / 148);
+                const uint64_t waves = (clusters + resident - 1) / resident;
                 const uint32_t kb_per = ceil_div_u32(nkb, split);
                 // exchange: staging and sending the chunks a rank does not own, the cluster barrier, the summation
                 const uint32_t chunks = bn / 32, sent = chunks - chunks / split;

@@ -210,6 +210,9 @@ def run(args, rank, world, device, emit=None, pk=None):
         return run_quant(args, rank, world, device, emit)
     if args.workload == 'layout':
         return run_layout(args, rank, world, device, emit, pk)
+    if args.workload == 'published':
+        from .published_bench import run_published
+        return run_published(args, rank, world, device, emit)
     return run_grouped(args, rank, world, device, emit, pk or {'bf16_tflops': 1590.0, 'hbm_gbs': 6650.0, 'source': 'fallback'})
 
 
