@@ -19,7 +19,8 @@ global expert count sharded over the ranks (strong scaling), no collective on th
 the outputs is timed separately (`gather_ms`). `--workload dense` at N > 1 runs N independent N-slabs instead.
 
 `--impl reference` times the reference's CPU implementation of the path (its dequantise-then-matmul test oracle) on
-the host cores over the same 18 shapes.
+the host cores on the workload this build's arm runs with the same arguments: the same 18 shapes on one GPU, a bounded
+sample of the same sharded grouped problem (and the same `config` object) with `--gpus N`, N > 1.
 """
 
 from __future__ import annotations
@@ -254,11 +255,68 @@ def cpu_oracle_pass(inputs) -> tuple[float, float]:
     return flops, time.perf_counter() - t0
 
 
+def run_reference_grouped(args, world, masked: bool):
+    """The grouped workload of the multi-GPU arm on the host cores: the oracle (dequantise per 1x32 + FP32 matmul + BF16
+    cast) over a bounded sample of the same global problem: every eighth expert, its first 1024 valid rows (all valid
+    rows of a masked expert), both (N, K). Operands are drawn before the clock starts."""
+    import oracle
+    from deep_gemm.testing import moe_bench
+    g_total = args.experts or GLOBAL_EXPERTS
+    sizes = moe_bench.grouped_sizes(g_total, masked)
+    torch.manual_seed(0)
+    table = torch.tensor([2.0 ** -9, 2.0 ** -8, 2.0 ** -7])
+    inputs = []
+    for (n, k) in moe_bench.NK_LIST:
+        for g in range(0, g_total, 8):
+            rows = min(sizes[g], 1024)
+            if rows == 0:
+                continue
+            def operand(mn):
+                raw = torch.randint(0, 254, (mn, k), dtype=torch.uint8)
+                raw += (raw >= 0x7F).to(torch.uint8)
+                return raw.view(torch.float8_e4m3fn), table[torch.randint(0, 3, (mn, k // 32))].contiguous()
+            inputs.append(operand(rows) + operand(n))
+
+    def one_pass():
+        flops, t0 = 0.0, time.perf_counter()
+        for (a, sfa, b, sfb) in inputs:
+            oracle.gemm_ref(oracle.dequantize(oracle.decode_e4m3(a), sfa, 1, 32), oracle.dequantize(oracle.decode_e4m3(b), sfb, 1, 32),
+                            torch.bfloat16)
+            flops += 2.0 * a.shape[0] * b.shape[0] * a.shape[1]
+        return flops, time.perf_counter() - t0
+
+    for _ in range(min(args.warmup, 1)):
+        one_pass()
+    flops = seconds = 0.0
+    for _ in range(args.steps):
+        f, s = one_pass()
+        flops += f
+        seconds += s
+    value = flops / seconds / 1e12
+    sample = ('dequantise + FP32 matmul + BF16 cast (torch CPU) of every eighth expert, first 1024 valid rows, both (N, K): '
+              '%.2f TFLOP per step of the %.1f TFLOP problem, operands drawn before the clock starts'
+              % (flops / args.steps / 1e12, sum(2.0 * sum(sizes) * n * k for n, k in moe_bench.NK_LIST) / 1e12))
+    emit({
+        'impl': 'reference', 'metric': 'fp8_block_scaled_gemm_tflops', 'value': value, 'unit': 'TFLOP/s',
+        'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': seconds / args.steps * 1e3,
+        'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': moe_bench.grouped_config(world, g_total, masked),
+        'cpu_baseline': {'value': value, 'unit': 'TFLOP/s', 'cores': torch.get_num_threads(), 'kind': 'port', 'sample': sample},
+        'e2e': {'value': value, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    })
+
+
 def run_reference(args, rank, world):
-    """The reference's CPU implementation of the path (its test oracle) on this box's host cores."""
+    """The reference's CPU implementation of the path (its test oracle) on this box's host cores, on the workload this
+    build's arm runs with the same arguments: the dense sweep on one GPU, the sharded grouped GEMM on several."""
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
+    ranks = max(world, args.gpus)
+    workload = args.workload if args.workload != 'auto' else ('dense' if ranks == 1 else 'grouped')
+    if workload in ('grouped', 'masked'):
+        return run_reference_grouped(args, ranks, workload == 'masked')
     inputs = cpu_inputs(SWEEP)
     for _ in range(min(args.warmup, 1)):
         cpu_oracle_pass(inputs[:6])

@@ -68,6 +68,24 @@ class GroupedCase:
             raise RuntimeError(L.last_error())
 
 
+def grouped_config(world: int, g_total: int, masked: bool) -> dict:
+    """The `config` object of the grouped workloads; the reference arm of the benchmark prints the same one."""
+    return {'workload': ('m-grouped masked FP8 GEMM, %d experts x max_m 256, valid rows ~ U[0,256]' if masked else
+                         'm-grouped contiguous FP8 GEMM (psum layout), %d experts in total, rows per expert ~ U(0.7,1.3) x 8192')
+                        % g_total + ', (N,K) in ' + str(NK_LIST) + ', BF16 out',
+            'sharding': 'experts in contiguous blocks over %d rank(s)%s, no data-path collective'
+                        % (world, '' if masked else ', block boundaries balanced by rows'),
+            'l2': 'flushed before every GEMM, untimed', 'flops': 'valid rows only'}
+
+
+def grouped_sizes(g_total: int, masked: bool) -> list:
+    """Rows per expert of the global problem: the same on every rank and in the reference arm."""
+    random.seed(1234)
+    if masked:
+        return [random.randint(0, 256) for _ in range(g_total)]
+    return [int(random.uniform(0.7, 1.3) * 8192) for _ in range(g_total)]
+
+
 def _flush_timed(lib, device, launch, steps, warmup=3):
     """Mean microseconds of `launch(sptr)` over `steps` launches, each after an untimed write of a buffer larger
     than L2, one CUDA-event pair per launch."""
@@ -230,11 +248,7 @@ def run_grouped(args, rank, world, device, emit, pk):
     flush = l2_flush_buffer(device)
     masked = args.workload == 'masked'
     g_total = getattr(args, 'experts', 0) or 32
-    random.seed(1234)                       # the global problem is the same on every rank
-    if masked:
-        sizes = [random.randint(0, 256) for _ in range(g_total)]
-    else:
-        sizes = [int(random.uniform(0.7, 1.3) * 8192) for _ in range(g_total)]
+    sizes = grouped_sizes(g_total, masked)  # the global problem is the same on every rank
     # contiguous blocks of experts: balanced by rows for the contiguous layout, by count for the masked one (whose cost
     # is the experts' B, the same for every expert)
     g0, g1 = expert_range(g_total, world, rank) if masked else balanced_expert_ranges(sizes, world)[rank]
@@ -359,12 +373,7 @@ def run_grouped(args, rank, world, device, emit, pk):
         'steps': args.steps, 'warmup': warmup, 'ms_per_step': gemm_ms,
         'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
         'dtype': 'fp8_e4m3 x ue8m0, fp32 accumulate', 'data': 'synthetic',
-        'config': {'workload': ('m-grouped masked FP8 GEMM, %d experts x max_m 256, valid rows ~ U[0,256]' if masked else
-                                'm-grouped contiguous FP8 GEMM (psum layout), %d experts in total, rows per expert ~ U(0.7,1.3) x 8192')
-                               % g_total + ', (N,K) in ' + str(NK_LIST) + ', BF16 out',
-                   'sharding': 'experts in contiguous blocks over %d rank(s)%s, no data-path collective'
-                               % (world, '' if masked else ', block boundaries balanced by rows'),
-                   'l2': 'flushed before every GEMM, untimed', 'flops': 'valid rows only'},
+        'config': grouped_config(world, g_total, masked),
         'verified': verified,
         'gemm_ms': gemm_ms, 'gather_ms': gather_ms,
         'gemm_plus_gather_ms': (gemm_ms + gather_ms) if gather_ms is not None else None,
