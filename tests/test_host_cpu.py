@@ -286,3 +286,32 @@ def test_compiled_host_layer_is_in_use_and_agrees_with_the_python_one():
     assert _api._C.get_dry_run() is False and _api.get_dry_run() is False
     deep_gemm.set_dry_run(True)
     assert _api._C.get_dry_run() is True and _api.get_dry_run() is True
+
+
+def _run_bench(*argv):
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc = subprocess.run([sys.executable, os.path.join(root, 'bench.py'), *argv], capture_output=True, text=True, timeout=600)
+    return proc, (json.loads(proc.stdout.strip().splitlines()[-1]) if proc.stdout.strip() else None)
+
+
+def test_reference_arm_of_the_benchmark_follows_the_multi_gpu_workload():
+    """`bench.py --impl reference --gpus 2` times the oracle on a sample of the grouped problem the two-GPU arm shards
+    and prints that arm's `config` object, the contract's keys and no GPU launches."""
+    from deep_gemm.testing import moe_bench
+    proc, line = _run_bench('--impl', 'reference', '--gpus', '2', '--steps', '1', '--warmup', '0')
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert line['impl'] == 'reference' and line['n_gpus'] == 2 and line['gpu_launches'] == 0
+    assert line['config'] == moe_bench.grouped_config(2, 32, False)
+    assert line['metric'] == 'fp8_block_scaled_gemm_tflops' and line['unit'] == 'TFLOP/s' and line['higher_is_better'] is True
+    assert line['value'] > 0 and line['cpu_baseline']['kind'] == 'port' and line['cpu_baseline']['value'] == line['value']
+    assert line['e2e'] == {'value': line['value'], 'unit': 'TFLOP/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason='checks the behaviour of a box without a GPU')
+def test_benchmark_refuses_to_run_without_a_gpu():
+    proc, line = _run_bench('--steps', '1')
+    assert proc.returncode != 0 and line is None
+    assert 'no CPU fallback' in proc.stderr
