@@ -81,8 +81,13 @@ static bool tma_store_ok(const dg_gemm_desc_t& d) {
            ((!has_row_groups(d.gemm_type) && d.gemm_type != DG_GEMM_K_GROUPED_PSUM) || (d.group_stride_d * es) % 16 == 0);
 }
 
-// Both operands packed E2M1: the kind::mxf4 path. The kernel then counts K in bytes (two elements each).
-static bool is_fp4_pair(const dg_gemm_desc_t& d) { return d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E2M1X2; }
+// Both operands packed E2M1 and K-major: the kind::mxf4 path (which reads K-major operands only). The kernel then
+// counts K in bytes (two elements each). Packed E2M1 operands in any other arrangement (an MN-major one among them,
+// the k-grouped layout, an E4M3 A) go through kind::mxf8f6f4, see native_fp4_a / native_fp4_b.
+static bool is_fp4_pair(const dg_gemm_desc_t& d) {
+    return d.a_dtype == DG_E2M1X2 && d.b_dtype == DG_E2M1X2 && d.major_a == DG_MAJOR_K && d.major_b == DG_MAJOR_K &&
+           d.gemm_type != DG_GEMM_K_GROUPED_PSUM;
+}
 // Both operands BF16: kind::f16, no scale factors; strides are in BF16 elements.
 static bool is_bf16_pair(const dg_gemm_desc_t& d) { return d.a_dtype == DG_BF16 && d.b_dtype == DG_BF16; }
 static uint32_t ab_elem_bytes(const dg_gemm_desc_t& d) { return is_bf16_pair(d) ? 2u : 1u; }
@@ -98,13 +103,18 @@ static bool feature_disabled(const char* name);
 // the kernel, and B crosses HBM and the SM's port at half a byte per element. That tensor-map type wants a 32-byte
 // aligned base, strides that are multiples of 32 bytes and a contiguous extent that is a multiple of 128 elements;
 // anything else takes the decoder warps (the packed bytes are expanded to E4M3 in shared memory).
-static bool native_fp4_b(const dg_gemm_desc_t& d) {
-    if (!(d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3) || feature_disabled("native_fp4")) return false;
-    const uint32_t inner = d.major_b == DG_MAJOR_K ? d.k : d.n;           // elements along B's contiguous axis
-    return (reinterpret_cast<uintptr_t>(d.b) & 31) == 0 && d.outer_stride_b % 32 == 0 && d.group_stride_b % 32 == 0 &&
-           inner % 128 == 0;
+static bool tma_can_expand_fp4(const void* base, uint64_t outer_stride, uint64_t group_stride, uint32_t inner_elems) {
+    return (reinterpret_cast<uintptr_t>(base) & 31) == 0 && outer_stride % 32 == 0 && group_stride % 32 == 0 && inner_elems % 128 == 0;
 }
-static bool decodes_b(const dg_gemm_desc_t& d) { return d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3 && !native_fp4_b(d); }
+static bool native_fp4_b(const dg_gemm_desc_t& d) {
+    if (d.b_dtype != DG_E2M1X2 || is_fp4_pair(d)) return false;
+    if (d.a_dtype == DG_E4M3 && feature_disabled("native_fp4")) return false;      // (an E2M1 A has no decoder to fall back to)
+    return tma_can_expand_fp4(d.b, d.outer_stride_b, d.group_stride_b, d.major_b == DG_MAJOR_K ? d.k : d.n);
+}
+static bool decodes_b(const dg_gemm_desc_t& d) { return d.b_dtype == DG_E2M1X2 && !is_fp4_pair(d) && !native_fp4_b(d); }
+// A packed E2M1 A outside the kind::mxf4 path is always expanded by TMA; operands that break the rules of that
+// tensor-map type are refused (the caller expands them to E4M3 first: dg_expand_fp4_launch).
+static bool unpacks_fp4_a(const dg_gemm_desc_t& d) { return d.a_dtype == DG_E2M1X2 && !is_fp4_pair(d); }
 
 static int validate(const dg_gemm_desc_t& d) {
     DG_CHECK_ARG(d.gemm_type == DG_GEMM_NORMAL || is_grouped(d.gemm_type) ||
@@ -116,14 +126,19 @@ static int validate(const dg_gemm_desc_t& d) {
     } else {
         DG_CHECK_ARG(d.epilogue != DG_EPILOGUE_FP8_QUANT, "BF16 matmul has no FP8 output");
     }
-    if (is_fp4_pair(d)) {
-        // csrc/jit_kernels/fp8_gemm.hpp:81: "K-major A/B only"
-        DG_CHECK_ARG(d.major_a == DG_MAJOR_K && d.major_b == DG_MAJOR_K, "FP4 x FP4 GEMM takes K-major A and B only");
-        DG_UNSUPPORTED(d.gemm_type == DG_GEMM_K_GROUPED_PSUM, "k-grouped matmul is built for FP8 operands only");
-    }
     if (d.b_dtype == DG_E2M1X2) {
         DG_CHECK_ARG(d.k % 2 == 0, "packed FP4 needs an even K");
         DG_CHECK_ARG(d.major_b == DG_MAJOR_K || d.n % 2 == 0, "MN-major packed FP4 needs an even N");
+    }
+    if (d.a_dtype == DG_E2M1X2)
+        DG_CHECK_ARG(d.major_a == DG_MAJOR_K || d.m % 2 == 0, "MN-major packed FP4 needs an even M");
+    if (unpacks_fp4_a(d)) {
+        DG_UNSUPPORTED(!tma_can_expand_fp4(d.a, d.outer_stride_a, d.group_stride_a, d.major_a == DG_MAJOR_K ? d.k : d.m),
+                       "A (packed FP4 with an MN-major or k-grouped operand): base and strides must be multiples of 32 bytes and the "
+                       "contiguous extent a multiple of 128 elements (expand A to E4M3 otherwise)");
+        DG_UNSUPPORTED(decodes_b(d) && d.gemm_type == DG_GEMM_K_GROUPED_PSUM,
+                       "B (packed FP4, k-grouped): base and strides must be multiples of 32 bytes and N a multiple of 128 "
+                       "(expand B to E4M3 otherwise)");
     }
     if (d.epilogue == DG_EPILOGUE_FP8_QUANT) {
         DG_CHECK_ARG(d.d_dtype == DG_E4M3 && !d.accumulate, "FP8 quantization requires a direct E4M3 output");
@@ -150,7 +165,8 @@ static int validate(const dg_gemm_desc_t& d) {
         DG_CHECK_ARG(d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_STOCHASTIC_BF16,
                      "k-grouped matmul takes no epilogue besides accumulation and stochastic BF16 rounding");
         DG_CHECK_ARG(d.k % 256 == 0, "k-grouped psum layout: total K must be a multiple of the 256 alignment");
-        DG_CHECK_ARG(d.b_dtype == DG_E4M3 || is_bf16_pair(d), "k-grouped matmul is built for FP8 and BF16 operands only");
+        DG_UNSUPPORTED(decodes_b(d), "B (packed FP4, k-grouped): base and strides must be multiples of 32 bytes and N a multiple "
+                                     "of 128 (expand B to E4M3 otherwise)");
     } else if (d.gemm_type == DG_GEMM_BATCHED) {
         DG_CHECK_ARG(d.num_groups > 0, "batched GEMM needs num_groups (the batch count)");
         DG_CHECK_ARG(d.epilogue != DG_EPILOGUE_BIAS, "batched matmul doesn't support bias");
@@ -298,8 +314,8 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     // (4096x7168x16384: 5 -> 6 stages = +9 %), so one box per warp is taken when that buys a stage.
     if (c.reserved[1] == 0) {
         const uint32_t cs = in_cluster ? c.split_k : 1u;
-        c.reserved[1] = max_stages_for(c.block_n, c.cta_group, d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3, 1, cs, sf_atoms(d), epi_warps) >
-                        max_stages_for(c.block_n, c.cta_group, d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3, 2, cs, sf_atoms(d), epi_warps) ? 1u : 2u;
+        c.reserved[1] = max_stages_for(c.block_n, c.cta_group, d.b_dtype == DG_E2M1X2 && !is_fp4_pair(d), 1, cs, sf_atoms(d), epi_warps) >
+                        max_stages_for(c.block_n, c.cta_group, d.b_dtype == DG_E2M1X2 && !is_fp4_pair(d), 2, cs, sf_atoms(d), epi_warps) ? 1u : 2u;
     }
     DG_CHECK_ARG(c.reserved[1] >= 1 && c.reserved[1] <= kMaxStoreBufs, "store buffers per warp must be 1..4");
     DG_CHECK_ARG(c.reserved[4] <= 64, "raster group must be at most 64 row blocks");
@@ -443,7 +459,7 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
                 const bool single_accum = 2 * bn + sf_tmem_cols(bn, atoms) > 512;
                 // (a wide tile has one accumulator: ~290 cycles per 32-column chunk are not hidden behind the next tile)
                 const double t_epi = bn > 256 ? bn * 12.0 : bn * (out_fp32 ? 8.0 : 6.0);
-                const bool packed_b = d.b_dtype == DG_E2M1X2 && d.a_dtype == DG_E4M3;
+                const bool packed_b = d.b_dtype == DG_E2M1X2 && !is_fp4_pair(d);
                 const double main_loop = rows > kBlockM ? tile_main_cycles(cg, bn, kb_per, atoms, out_fp32 ? 4 : elem_size(d.d_dtype), packed_b, decodes_b(d))
                                                         : kb_per * k_block_cycles(cg, bn, packed_b, decodes_b(d));
                 const double cycles = main_loop + ((single_accum || waves == 1) ? t_epi : 0.0) + 700.0;
@@ -594,8 +610,10 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     a.idesc = ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) | (((c.block_n / tile_halves(c.block_n)) >> 3) << 17) | (1u << 23) |
               (((kBlockM * c.cta_group) >> 4) << 24);
     if (is_fp4_pair(d)) a.idesc |= (1u << 7) | (1u << 10);       // kind::mxf4: both operand formats E2M1
-    if (native_fp4_b(d)) a.idesc |= (5u << 10);                  // kind::mxf8f6f4: B format E2M1 (A stays E4M3)
+    if (native_fp4_b(d)) a.idesc |= (5u << 10);                  // kind::mxf8f6f4: B format E2M1
+    if (unpacks_fp4_a(d)) a.idesc |= (5u << 7);                  // kind::mxf8f6f4: A format E2M1
     a.b_tx_shift = native_fp4_b(d) ? 1u : 0u;
+    a.a_tx_shift = unpacks_fp4_a(d) ? 1u : 0u;
     if (is_bf16_pair(d))                                         // kind::f16: FP32 accumulator, BF16 operands, no scale fields
         a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) |
                   (((c.block_n / tile_halves(c.block_n)) >> 3) << 17) | (((kBlockM * c.cta_group) >> 4) << 24);
@@ -660,7 +678,22 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     const CUtensorMapDataType ab_type = is_bf16_pair(d) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     const uint64_t k_elems = k_bytes(d) / eb;
     const uint32_t box_k = kBlockK / eb, atom_mn = 128 / eb;
-    {
+    if (unpacks_fp4_a(d)) {
+        // packed E2M1 expanded by TMA into 16-byte containers of sixteen codes: dimensions count 4-bit elements, strides bytes
+        if (d.major_a == DG_MAJOR_K) {
+            const uint64_t gs = nonzero_stride(d.group_stride_a, rows_a * d.outer_stride_a);
+            const uint64_t dims[3] = {d.k, rows_a, masked ? groups : 1};
+            const uint64_t str[2] = {d.outer_stride_a, gs};
+            const uint32_t box[3] = {kBlockK, kBlockM, 1};
+            if (int rc = encode_map(&plan.tm_a, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, d.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "A (E2M1)")) return rc;
+        } else {
+            const uint64_t dims[3] = {rows_a, d.k, masked ? groups : 1};
+            const uint64_t str[2] = {d.outer_stride_a, masked ? nonzero_stride(d.group_stride_a, (uint64_t)d.k * d.outer_stride_a)
+                                                               : align_u64((uint64_t)d.k * d.outer_stride_a, 32)};
+            const uint32_t box[3] = {128, kBlockK, 1};
+            if (int rc = encode_map(&plan.tm_a, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, d.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B, "A (E2M1)")) return rc;
+        }
+    } else {
         const uint64_t gs = nonzero_stride(d.group_stride_a, rows_a * d.outer_stride_a);
         if (d.major_a == DG_MAJOR_K) {
             const uint64_t dims[3] = {k_elems, rows_a, masked ? groups : 1};
@@ -966,6 +999,14 @@ int dg_gemm_launch(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config,
     }
     maybe_print_config(*desc, c);
     return launch_gemm_kernel(plan, static_cast<cudaStream_t>(stream));
+}
+
+int dg_fp4_expansion_needed(const dg_gemm_desc_t* desc, int* expand_a, int* expand_b) {
+    DG_CHECK_ARG(desc != nullptr && expand_a != nullptr && expand_b != nullptr, "dg_fp4_expansion_needed: null argument");
+    const dg_gemm_desc_t& d = *desc;
+    *expand_a = (unpacks_fp4_a(d) && !tma_can_expand_fp4(d.a, d.outer_stride_a, d.group_stride_a, d.major_a == DG_MAJOR_K ? d.k : d.m)) ? 1 : 0;
+    *expand_b = (decodes_b(d) && d.gemm_type == DG_GEMM_K_GROUPED_PSUM) ? 1 : 0;
+    return DG_OK;
 }
 
 void dg_plan_cache_stats(uint64_t* hits, uint64_t* misses) {

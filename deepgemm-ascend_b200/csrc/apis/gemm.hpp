@@ -69,6 +69,29 @@ inline torch::Tensor tma_ready_operand(const torch::Tensor& t, int major) {
     return major == DG_MAJOR_K ? view : view.transpose(-2, -1);
 }
 
+// Packed E2M1 operand (int8, two codes per byte along its contiguous axis) -> the same logical matrix as E4M3 bytes,
+// exactly, with the same major: for packed operands whose base, strides or extent break the rules of TMA's 4-bit
+// unpacking where the kernel has no decoder (dg_fp4_expansion_needed).
+inline torch::Tensor expand_fp4_operand(const torch::Tensor& t, int major) {
+    const auto src = major == DG_MAJOR_K ? t : t.transpose(-2, -1);
+    host_assert(src.dim() == 2 || src.dim() == 3, "operands have at most one leading (group) dimension");
+    const int64_t rows = src.size(-2), cols = src.size(-1), pitch = align_up(2 * cols, 32);
+    std::vector<int64_t> shape(src.sizes().begin(), src.sizes().end());
+    shape.back() = pitch;
+    auto buf = torch::empty(shape, t.options().dtype(torch::kUInt8));
+    if (!t.is_meta()) {
+        void* stream = stream_of(t);
+        const int64_t groups = src.dim() == 3 ? src.size(0) : 1;
+        for (int64_t g = 0; g < groups; ++g) {
+            const auto s = src.dim() == 3 ? src[g] : src;
+            const auto b = src.dim() == 3 ? buf[g] : buf;
+            check(dg_expand_fp4_launch(s.data_ptr(), (uint64_t)s.stride(0), b.data_ptr(), (uint64_t)pitch, (uint64_t)rows, (uint64_t)cols, stream));
+        }
+    }
+    auto view = buf.slice(-1, 0, 2 * cols).view(torch::kFloat8_e4m3fn);
+    return major == DG_MAJOR_K ? view : view.transpose(-2, -1);
+}
+
 inline void apply_config_override(const OptConfig& config, dg_gemm_config_t& cfg) {
     memset(&cfg, 0, sizeof(cfg));
     for (auto item : config.value()) {
@@ -158,8 +181,8 @@ inline void run_gemm(int gemm_type, const torch::Tensor& a, const torch::Tensor&
     desc.b_dtype = dtype_code(b);
     desc.d_dtype = d.scalar_type() == torch::kFloat8_e4m3fn ? DG_E4M3 : dtype_code(d);
     // (BF16 operands are not repacked: the library answers "strides must be multiples of 16 bytes" for odd views)
-    const auto a_use = bf16 ? a : tma_ready_operand(a, major_a);
-    const auto b_use = bf16 ? b : tma_ready_operand(b, major_b);
+    auto a_use = bf16 ? a : tma_ready_operand(a, major_a);
+    auto b_use = bf16 ? b : tma_ready_operand(b, major_b);
     desc.a = ptr_of(a_use);
     desc.b = ptr_of(b_use);
     desc.d = ptr_of(d);
@@ -179,8 +202,25 @@ inline void run_gemm(int gemm_type, const torch::Tensor& a, const torch::Tensor&
     desc.group_stride_a = masked ? (uint64_t)a_use.stride(0) : 0;
     desc.group_stride_b = b_use.dim() == 3 ? (uint64_t)b_use.stride(0) : 0;
     desc.group_stride_d = (masked || gemm_type == DG_GEMM_K_GROUPED_PSUM) ? (uint64_t)d.stride(0) : 0;
-    desc.accumulate = (c.has_value() && !with_bias) ? 1 : 0;
     desc.gemm_type = gemm_type;
+    if (!bf16 && (a.scalar_type() == kPackedFp4 || b.scalar_type() == kPackedFp4)) {
+        // packed operands the kernels cannot read as they are become E4M3 first (exact)
+        int expand_a = 0, expand_b = 0;
+        check(dg_fp4_expansion_needed(&desc, &expand_a, &expand_b));
+        if (expand_a) {
+            a_use = expand_fp4_operand(a_use, major_a);
+            desc.a = ptr_of(a_use); desc.a_dtype = DG_E4M3;
+            desc.outer_stride_a = (uint64_t)outer_stride(a_use, major_a);
+            desc.group_stride_a = masked ? (uint64_t)a_use.stride(0) : 0;
+        }
+        if (expand_b) {
+            b_use = expand_fp4_operand(b_use, major_b);
+            desc.b = ptr_of(b_use); desc.b_dtype = DG_E4M3;
+            desc.outer_stride_b = (uint64_t)outer_stride(b_use, major_b);
+            desc.group_stride_b = b_use.dim() == 3 ? (uint64_t)b_use.stride(0) : 0;
+        }
+    }
+    desc.accumulate = (c.has_value() && !with_bias) ? 1 : 0;
     desc.grouped_layout = grouped_layout.has_value() ? static_cast<const int32_t*>(ptr_of(grouped_layout.value())) : nullptr;
     desc.num_groups = (uint32_t)g;
     // (for the k-grouped layout `expected_m` carries the expected K of one group, csrc/apis/gemm.hpp:35-43)
@@ -273,8 +313,8 @@ static void k_grouped_fp8_gemm_tn_contiguous(const TensorPair& a, const TensorPa
                                              const std::string& compiled_dims, const bool& use_psum_layout,
                                              const std::shared_ptr<EpilogueClass>& epilogue, const OptConfig& config) {
     const auto at = transposed(a, true, 0, 1), bt = transposed(b, true, 0, 1);
-    host_assert(at.first.scalar_type() == torch::kFloat8_e4m3fn && bt.first.scalar_type() == torch::kFloat8_e4m3fn,
-                "k-grouped matmul is built for FP8 operands");
+    const auto ok = [](const torch::Tensor& t) { return t.scalar_type() == torch::kFloat8_e4m3fn || t.scalar_type() == kPackedFp4; };
+    host_assert(ok(at.first) && ok(bt.first), "Unsupported operand dtypes");
     host_assert(d.scalar_type() == torch::kBFloat16 || d.scalar_type() == torch::kFloat32);
     host_assert(use_psum_layout);
     run_gemm(DG_GEMM_K_GROUPED_PSUM, at.first, bt.first, d, c, resolve_epilogue(epilogue, c, d), at.second, bt.second, recipe, std::nullopt,

@@ -241,6 +241,39 @@ int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream) {
 
 }  // namespace dg
 
+namespace dg {
+// One thread per pair of packed bytes: four codes in, four E4M3 bytes out (two 2-byte stores).
+__global__ void expand_fp4_kernel(const uint8_t* __restrict__ src, uint64_t src_pitch, uint8_t* __restrict__ dst, uint64_t dst_pitch,
+                                  uint64_t rows, uint64_t packed_bytes) {
+    const uint64_t pairs = (packed_bytes + 1) / 2, total = rows * pairs;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t r = i / pairs, c = (i - r * pairs) * 2;
+        const uint8_t* s = src + r * src_pitch + c;
+        const bool two = c + 1 < packed_bytes;
+        const uint32_t codes = (uint32_t)s[0] | (two ? (uint32_t)s[1] << 8 : 0u);
+        const uint32_t out = e2m1x4_to_e4m3x4(codes);
+        uint16_t* d = reinterpret_cast<uint16_t*>(dst + r * dst_pitch + 2 * c);
+        d[0] = (uint16_t)(out & 0xFFFFu);
+        if (two) d[1] = (uint16_t)(out >> 16);
+    }
+}
+}  // namespace dg
+
+extern "C" int dg_expand_fp4_launch(const void* src, uint64_t src_pitch_bytes, void* dst, uint64_t dst_pitch_bytes,
+                                    uint64_t rows, uint64_t packed_bytes, void* stream) {
+    DG_CHECK_ARG(src != nullptr && dst != nullptr, "expand_fp4: null pointer");
+    DG_CHECK_ARG(dst_pitch_bytes >= 2 * packed_bytes && dst_pitch_bytes % 2 == 0 && (reinterpret_cast<uintptr_t>(dst) & 1) == 0,
+                 "expand_fp4: destination rows must hold two bytes per packed byte and be 2-byte aligned");
+    if (rows == 0 || packed_bytes == 0) return DG_OK;
+    const uint64_t total = rows * ((packed_bytes + 1) / 2);
+    const uint32_t grid = (uint32_t)((total + 255) / 256 < 148ull * 16 ? (total + 255) / 256 : 148ull * 16);
+    dg::expand_fp4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(src), src_pitch_bytes, static_cast<uint8_t*>(dst), dst_pitch_bytes, rows, packed_bytes);
+    DG_CHECK_CUDA(cudaGetLastError());
+    dg::count_kernel_launch();
+    return DG_OK;
+}
+
 extern "C" int dg_set_overlap_launches(int enabled) {
     dg::g_overlap_launches.store(enabled ? 1 : 0, std::memory_order_relaxed);
     return DG_OK;

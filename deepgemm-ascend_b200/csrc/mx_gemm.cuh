@@ -82,6 +82,7 @@ struct GemmKernelArgs {
     uint32_t k_stagger;               // dense GEMM: tile with column index nb starts its K loop at block (nb * k_stagger) % len
     uint32_t b_tx_shift;              // 1 when TMA expands packed E2M1 rows of B into 16-byte containers: the barrier then
                                       // counts the packed bytes it read (half of what lands in shared memory), else 0
+    uint32_t a_tx_shift;              // the same for a packed E2M1 A
     int32_t* status;
     unsigned long long* trace;        // debugging aid: per-CTA timestamps (8 slots each), or nullptr
 };
@@ -538,7 +539,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     // scales are usually packed by the time the last operand byte lands.
                     // (half tiles of a wide-tile launch fetch one half's rows of B and scale columns only)
                     const uint32_t act_halves = kWideTile ? (t.halves == 3u ? 2u : 1u) : 1u;
-                    const uint32_t bytes = L.a_stage + (kDecodeB ? L.b_raw_stage : kWideTile ? act_halves * load_half * kBlockK
+                    const uint32_t bytes = (L.a_stage >> p.a_tx_shift) + (kDecodeB ? L.b_raw_stage : kWideTile ? act_halves * load_half * kBlockK
                                                                                            : (load_n * kBlockK) >> p.b_tx_shift);
                     static_assert(!kBf16 || !kDecodeB, "BF16 operands are never decoded");
                     mbar_arrive_expect_tx(bar, bytes);

@@ -466,6 +466,23 @@ def _tma_ready_operand(t: torch.Tensor, major: int) -> torch.Tensor:
     return view if major == L.MAJOR_K else view.transpose(-2, -1)
 
 
+def _expand_fp4_operand(t: torch.Tensor, major: int) -> torch.Tensor:
+    """Packed E2M1 operand (int8, two codes per byte along its contiguous axis) -> the same logical matrix as E4M3
+    bytes, exactly, with the same major. For packed operands whose base, strides or extent break the rules of TMA's 4-bit
+    unpacking where the kernel has no decoder (a packed A next to an MN-major or k-grouped operand, a k-grouped B)."""
+    src = t if major == L.MAJOR_K else t.transpose(-2, -1)              # [..., rows, packed bytes], contiguous rows
+    rows, cols = src.size(-2), src.size(-1)
+    pitch = _align(2 * cols, 32)
+    buf = torch.empty((*src.shape[:-2], rows, pitch), dtype=torch.uint8, device=t.device)
+    if not t.is_meta:
+        stream = _stream_ptr(t.device)
+        _host_assert(src.dim() in (2, 3), 'operands have at most one leading (group) dimension')
+        for s_g, b_g in ([(src, buf)] if src.dim() == 2 else [(src[g], buf[g]) for g in range(src.size(0))]):
+            L.check(L.lib().dg_expand_fp4_launch(s_g.data_ptr(), s_g.stride(0), b_g.data_ptr(), pitch, rows, cols, stream))
+    view = buf[..., :2 * cols].view(torch.float8_e4m3fn)
+    return view if major == L.MAJOR_K else view.transpose(-2, -1)
+
+
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     """Zero-initialised scratch for split-K, one per (device, stream); the library leaves it zeroed."""
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
@@ -560,8 +577,20 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
         desc.sfa_stride, desc.sfb_stride = sfa.stride(-1), sfb.stride(-1)
         desc.sfa_group_stride = sfa.stride(0) if sfa.dim() == 3 else 0
         desc.sfb_group_stride = sfb.stride(0) if sfb.dim() == 3 else 0
-    desc.accumulate = int(c is not None and not with_bias)
     desc.gemm_type = gemm_type
+    if not bf16 and PACKED_FP4 in (a.dtype, b.dtype):
+        # packed operands the kernels cannot read as they are become E4M3 first (exact)
+        expand_a, expand_b = C.c_int(0), C.c_int(0)
+        L.check(L.lib().dg_fp4_expansion_needed(C.byref(desc), C.byref(expand_a), C.byref(expand_b)))
+        if expand_a.value:
+            a_use = _expand_fp4_operand(a_use, major_a)
+            desc.a, desc.a_dtype = _ptr(a_use), L.E4M3
+            desc.outer_stride_a, desc.group_stride_a = _outer_stride(a_use, major_a), (a_use.stride(0) if masked else 0)
+        if expand_b.value:
+            b_use = _expand_fp4_operand(b_use, major_b)
+            desc.b, desc.b_dtype = _ptr(b_use), L.E4M3
+            desc.outer_stride_b, desc.group_stride_b = _outer_stride(b_use, major_b), (b_use.stride(0) if b_use.dim() == 3 else 0)
+    desc.accumulate = int(c is not None and not with_bias)
     desc.grouped_layout = _ptr(grouped_layout) if grouped_layout is not None else None
     desc.num_groups = g
     # (for the k-grouped layout `expected_m` carries the expected K of one group, csrc/apis/gemm.hpp:35-43)
@@ -681,8 +710,8 @@ def k_grouped_fp8_gemm_tn_contiguous(a, b, d, ks_cpu, grouped_layout, c=None, re
     starting at the previous end rounded up to the 256 alignment, operand data zero in the padding);
     D[g] = A[group g]^T @ B[group g] (+ C[g] when `c` is D itself), D[g] = 0 (or kept) for an empty group."""
     (a_data, sfa), (b_data, sfb) = _transposed(a, True, 0, 1), _transposed(b, True, 0, 1)
-    _host_assert(a_data.dtype == torch.float8_e4m3fn and b_data.dtype == torch.float8_e4m3fn,
-                 'k-grouped matmul is built for FP8 operands')
+    _host_assert(a_data.dtype in (torch.float8_e4m3fn, PACKED_FP4) and b_data.dtype in (torch.float8_e4m3fn, PACKED_FP4),
+                 'Unsupported operand dtypes')
     _host_assert(d.dtype in (torch.bfloat16, torch.float32))
     _host_assert(use_psum_layout is True)
     k, g = a_data.size(-1), grouped_layout.numel()

@@ -81,9 +81,11 @@ typedef enum {
  * int16 elements between consecutive K64 columns (== MN for a dense tensor) and must be a multiple
  * of 8; sf*_group_stride is the distance between groups of scales in int16 elements.
  *
- * Operand dtype pairs (csrc/apis/gemm.hpp:22-33): E4M3 x E4M3; E4M3 x E2M1X2 (B decoded to E4M3 on the fly,
- * either major); E2M1X2 x E2M1X2 (tcgen05 kind::mxf4, K-major A and B only as in csrc/jit_kernels/fp8_gemm.hpp:81,
- * per-32 scales; every layout but the K-grouped one). E2M1X2 x E4M3 is rejected as in the reference.
+ * Operand dtype pairs (csrc/apis/gemm.hpp:22-33): E4M3 x E4M3; E4M3 x E2M1X2 (B read by the tensor cores as E2M1,
+ * either major; decoded to E4M3 on the fly when TMA cannot unpack it); E2M1X2 x E2M1X2: tcgen05 kind::mxf4 at twice
+ * the FP8 rate when A and B are K-major, kind::mxf8f6f4 with both operands read as E2M1 when one of them is MN-major
+ * or the layout is the K-grouped one (a packed A must then satisfy dg_fp4_expansion_needed). Per-32 scales.
+ * E2M1X2 x E4M3 is rejected as in the reference.
  * BF16 x BF16 (csrc/apis/gemm.hpp:412-514, launch_bf16_gemm): a_dtype = b_dtype = DG_BF16, sfa = sfb = NULL, strides in
  * BF16 elements, rows 16-byte aligned; every layout, both majors.
  */
@@ -236,6 +238,19 @@ int dg_quant_fp8_launch(const void* x, uint64_t x_stride, uint32_t tokens, uint3
  * bytes (the unaligned-K / unaligned-MN cases of tests/generators.py:491-541). */
 int dg_pad_rows_launch(const void* src, uint64_t src_pitch_bytes, void* dst, uint64_t dst_pitch_bytes,
                        uint64_t rows, uint64_t row_bytes, void* stream);
+
+/* Expand a 2-D matrix of packed E2M1 codes (two per byte along the row, low nibble first) into E4M3 bytes, exactly
+ * (every E2M1 value is an E4M3 value; the byte map of deep_gemm/include/deep_gemm/fp8_dequant_gemm.hpp:24-38). For packed
+ * operands that the GEMM cannot take as they are: a packed A (or a k-grouped packed B) whose base, strides or extent
+ * break the rules of TMA's 4-bit unpacking. dst row r holds 2 * packed_bytes bytes; dst 2-byte aligned, pitch even. */
+int dg_expand_fp4_launch(const void* src, uint64_t src_pitch_bytes, void* dst, uint64_t dst_pitch_bytes,
+                         uint64_t rows, uint64_t packed_bytes, void* stream);
+
+/* Which packed-FP4 operands of `desc` the GEMM cannot take as they are and the caller has to expand to E4M3 first
+ * (dg_expand_fp4_launch): a packed A outside the K-major x K-major FP4 kernel, or a packed B of the k-grouped layout,
+ * whose base or strides are not multiples of 32 bytes or whose contiguous extent is not a multiple of 128 elements.
+ * No reference counterpart: its kernels load packed operands in either major themselves. */
+int dg_fp4_expansion_needed(const dg_gemm_desc_t* desc, int* expand_a, int* expand_b);
 
 /* Writes a buffer larger than L2 so that the next kernel starts cold (deep_gemm/testing/bench.py:263-268). */
 int dg_l2_flush_launch(void* buffer, size_t bytes, void* stream);

@@ -268,13 +268,7 @@ def test_fp4_pair_m_grouped():
 
 
 def test_fp4_operand_rules():
-    # MN-major packed operands are not accepted for FP4 x FP4 (csrc/jit_kernels/fp8_gemm.hpp:81)
-    a4 = torch.zeros(128, 128, dtype=torch.int8, device='cuda')          # [M, K/2], K = 256
-    b4 = torch.zeros(256, 64, dtype=torch.int8, device='cuda')           # [K, N/2]: MN-major codes, N = 128
-    d4 = torch.zeros(128, 128, dtype=torch.bfloat16, device='cuda')
-    with pytest.raises(RuntimeError, match='K-major A and B only'):
-        deep_gemm.fp8_fp4_gemm_nn((a4, torch.ones(128, 8, device='cuda')), (b4, torch.ones(8, 128, device='cuda')), d4,
-                                  recipe_a=(1, 32), recipe_b=(1, 32))
+    # a packed A next to an E4M3 B stays rejected (csrc/apis/gemm.hpp:22-33); MN-major packed operands: test_gpu_fp4_majors.py
     a = torch.zeros(128, 64, dtype=torch.int8, device='cuda')
     b = torch.zeros(128, 128, dtype=torch.float8_e4m3fn, device='cuda')
     sf = torch.ones(128, 4, dtype=torch.float32, device='cuda')

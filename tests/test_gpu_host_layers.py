@@ -106,3 +106,44 @@ def test_transform_and_fp8_output_same_bits_through_both_host_layers():
         results.append((d.view(torch.uint8).clone(), sfd.clone()))
     assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
     assert deep_gemm.device_status() == 0
+
+
+@pytest.mark.parametrize('m,n,k', [(256, 384, 1024), (130, 258, 512)])
+def test_packed_fp4_with_mn_major_operands_same_bits_through_both_host_layers(m, n, k):
+    """FP4 x FP4 "tn" (both operands MN-major): read as E2M1 when TMA can unpack them, expanded to E4M3 by the host layer
+    when it cannot (the second shape); k-grouped FP8 x FP4 likewise."""
+    from helpers import uniform_fp4
+    seed_all(8)
+    a, sfa, a_ref = uniform_fp4(m, k, (1, 32), mn_major=True)
+    b, sfb, b_ref = uniform_fp4(n, k, (1, 32), mn_major=True)
+    a_arg = (a.cuda().transpose(0, 1), sfa.cuda().transpose(0, 1))
+    b_arg = (b.cuda().transpose(0, 1), sfb.cuda().transpose(0, 1))
+    outs = []
+    for fn in _both('fp8_fp4_gemm_tn'):
+        d = torch.full((m, n), float('nan'), dtype=torch.bfloat16, device='cuda')
+        fn(a_arg, b_arg, d, recipe_a=(1, 32), recipe_b=(1, 32))
+        outs.append(d)
+    assert deep_gemm.device_status() == 0
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    assert_close(outs[0], oracle.gemm_ref(a_ref, b_ref, torch.bfloat16), f'fp4xfp4 tn {m}x{n}x{k}')
+    # k-grouped: A [K, M] E4M3, B [K, N/2] packed, two groups of K
+    sizes = (k // 2, k // 2 - 40)
+    total_k, psum = oracle.make_psum_layout(list(sizes), 256)
+    a8, sfa8, _ = uniform_fp8((total_k, m), (32, 1))
+    b4, sfb4, _ = uniform_fp4(n, total_k, (1, 32), mn_major=True)
+    b4 = b4.transpose(0, 1).contiguous()                                  # [K, N/2]
+    sfb4 = sfb4.transpose(0, 1).contiguous()                              # [K/32, N]
+    for span in oracle.psum_padding_spans(psum, 256):
+        a8.view(torch.uint8)[span] = 0
+        b4[span] = 0
+    ref = oracle.k_grouped_psum_ref(oracle.dequantize(a8.float(), sfa8, 32, 1),
+                                    oracle.dequantize(oracle.decode_e2m1_packed(b4, axis=-1), sfb4, 32, 1), psum, torch.float32)
+    layout = torch.tensor(psum, dtype=torch.int32, device='cuda')
+    outs = []
+    for fn in _both('k_grouped_fp8_gemm_tn_contiguous'):
+        d = torch.full((2, m, n), float('nan'), dtype=torch.float32, device='cuda')
+        fn((a8.cuda(), sfa8.cuda()), (b4.cuda(), sfb4.cuda()), d, None, layout, recipe=(1, 1, 32))
+        outs.append(d)
+    assert deep_gemm.device_status() == 0
+    assert torch.equal(outs[0].view(torch.int32), outs[1].view(torch.int32))
+    assert_close(outs[0], ref, f'k-grouped fp8xfp4 {m}x{n}')

@@ -288,6 +288,68 @@ def test_compiled_host_layer_is_in_use_and_agrees_with_the_python_one():
     assert _api._C.get_dry_run() is True and _api.get_dry_run() is True
 
 
+def test_packed_fp4_operand_kinds_and_majors_on_meta_tensors():
+    """FP4 x FP4 with MN-major operands and the k-grouped layout with FP8 x FP4 / FP4 x FP4 operands are accepted by both
+    host layers (csrc/apis/gemm.hpp:325-384 names the three operand kinds); a packed A next to an E4M3 B is not."""
+    from deep_gemm import _api
+    layers = [_api] + ([_api._C] if _api._C is not None else [])
+    m, n, k = 256, 384, 1024
+
+    def packed(rows, kk, mn_major):         # logical [rows, kk] view of packed storage
+        t = torch.empty((kk, rows // 2) if mn_major else (rows, kk // 2), dtype=torch.int8, device='meta')
+        return t.transpose(0, 1) if mn_major else t
+
+    def scales(rows, kk, mn_major):
+        t = torch.empty((kk // 32, rows) if mn_major else (rows, kk // 32), dtype=torch.float32, device='meta')
+        return t.transpose(0, 1) if mn_major else t
+
+    d = torch.empty(m, n, dtype=torch.bfloat16, device='meta')
+    for layer in layers:
+        for trans in ('nt', 'nn', 'tn', 'tt'):
+            a = (packed(m, k, trans[0] == 't'), scales(m, k, trans[0] == 't'))
+            b = (packed(n, k, trans[1] == 'n'), scales(n, k, trans[1] == 'n'))
+            a_arg = tuple(x.transpose(0, 1) for x in a) if trans[0] == 't' else a
+            b_arg = tuple(x.transpose(0, 1) for x in b) if trans[1] == 'n' else b
+            getattr(layer, f'fp8_fp4_gemm_{trans}')(a_arg, b_arg, d, recipe_a=(1, 32), recipe_b=(1, 32))
+        layout = torch.empty(2, dtype=torch.int32, device='meta')
+        dk = torch.empty(2, m, n, dtype=torch.float32, device='meta')
+        sfa, sfb = torch.empty(k // 32, m, device='meta'), torch.empty(k // 32, n, device='meta')
+        a8 = torch.empty(k, m, dtype=torch.float8_e4m3fn, device='meta')
+        b8 = torch.empty(k, n, dtype=torch.float8_e4m3fn, device='meta')
+        a4 = torch.empty(k, m // 2, dtype=torch.int8, device='meta')
+        b4 = torch.empty(k, n // 2, dtype=torch.int8, device='meta')
+        layer.k_grouped_fp8_gemm_tn_contiguous((a8, sfa), (b4, sfb), dk, [512, 512], layout, recipe=(1, 1, 32))
+        layer.k_grouped_fp8_gemm_tn_contiguous((a4, sfa), (b4, sfb), dk, None, layout, recipe=(1, 1, 32))
+        with pytest.raises(RuntimeError, match='Unsupported operand dtypes'):
+            layer.k_grouped_fp8_gemm_tn_contiguous((a4, sfa), (b8, sfb), dk, None, layout, recipe=(1, 1, 32))
+
+
+def test_fp4_expansion_rule_of_the_c_abi():
+    """dg_fp4_expansion_needed: a packed A outside the K-major x K-major kernel, or a k-grouped packed B, must have a
+    32-byte aligned base, 32-byte strides and a contiguous extent that is a multiple of 128 elements."""
+    lib = L.lib()
+    d = L.GemmDesc()
+    d.a = d.b = d.d = d.sfa = d.sfb = 0x1000
+    d.a_dtype, d.b_dtype, d.d_dtype = L.E2M1X2, L.E2M1X2, L.BF16
+    d.m, d.n, d.k = 256, 384, 1024
+    d.major_a, d.major_b = L.MAJOR_MN, L.MAJOR_MN
+    d.outer_stride_a, d.outer_stride_b, d.outer_stride_d = 128, 192, 384        # bytes of packed storage per K row
+    ea, eb = ctypes.c_int(-1), ctypes.c_int(-1)
+    assert lib.dg_fp4_expansion_needed(ctypes.byref(d), ctypes.byref(ea), ctypes.byref(eb)) == 0
+    assert (ea.value, eb.value) == (0, 0)
+    d.m, d.outer_stride_a = 130, 65                                           # neither a 128-element extent nor a 32-byte stride
+    lib.dg_fp4_expansion_needed(ctypes.byref(d), ctypes.byref(ea), ctypes.byref(eb))
+    assert (ea.value, eb.value) == (1, 0)                                      # (B falls back to the in-kernel decoder)
+    d.m, d.outer_stride_a, d.n, d.outer_stride_b = 256, 128, 200, 100
+    d.gemm_type, d.num_groups, d.grouped_layout = L.GEMM_K_GROUPED_PSUM, 2, 0x1000
+    lib.dg_fp4_expansion_needed(ctypes.byref(d), ctypes.byref(ea), ctypes.byref(eb))
+    assert (ea.value, eb.value) == (0, 1)
+    d.major_a = d.major_b = L.MAJOR_K                                          # the kind::mxf4 kernel reads packed operands itself
+    d.gemm_type, d.n, d.outer_stride_a, d.outer_stride_b = L.GEMM_NORMAL, 200, 515, 515
+    lib.dg_fp4_expansion_needed(ctypes.byref(d), ctypes.byref(ea), ctypes.byref(eb))
+    assert (ea.value, eb.value) == (0, 0)
+
+
 def _run_bench(*argv):
     import json
     import subprocess
