@@ -162,3 +162,24 @@ def test_operand_kinds_that_stay_rejected():
     d = torch.zeros(128, 128, dtype=torch.bfloat16, device='cuda')
     with pytest.raises(RuntimeError, match='Unsupported operand dtypes'):
         deep_gemm.fp8_fp4_gemm_nt((a, sf), (b, sf), d)
+
+
+# The reference's shape lists for odd extents (tests/generators.py:466-541), which its FP4 and dequant tests run over the
+# four major combinations with FP32 accumulation. An odd extent along a packed operand's contiguous axis is doubled,
+# as the reference's generator does (two codes share a byte).
+EXTRA_SHAPES = [(4, 4, 4), (4, 4, 16384), (4, 16384, 4), (16384, 4, 4), (16384, 4, 16384), (4, 16384, 16384), (128, 128, 128),
+                (256, 512, 1024), (1024, 256, 512), (4096, 4096, 4096)]
+UNALIGNED_MN = [(4, 4, 64), (17, 4096, 4096), (4096, 17, 4096), (15, 4096, 4096), (4096, 15, 4096), (130, 257, 2048), (513, 257, 4096)]
+UNALIGNED_K = [(64, 64, 4), (1024, 2048, 17), (8192, 4096, 15), (128, 128, 234), (2048, 8192, 4095)]
+
+
+@pytest.mark.parametrize('kinds', [('fp4', 'fp4'), ('fp8', 'fp4')])
+@pytest.mark.parametrize('m,n,k', EXTRA_SHAPES + UNALIGNED_MN + UNALIGNED_K)
+def test_reference_shape_lists_with_packed_operands_all_majors(kinds, m, n, k):
+    if kinds[0] == 'fp8' and m * n * k == 4 * 16384 * 16384:
+        pytest.skip('the two 268M-element operands are generated once, for the FP4 x FP4 kind')
+    for trans in ('nt', 'nn', 'tn', 'tt'):
+        mm = m * 2 if (kinds[0] == 'fp4' and trans[0] == 't' and m % 2) else m
+        nn = n * 2 if (trans[1] == 'n' and n % 2) else n
+        kk = k * 2 if k % 2 else k
+        _dense(kinds, mm, nn, kk, trans, out=torch.float32, acc=True)
