@@ -49,11 +49,12 @@ inline bool gemm_early_return(int64_t m, int64_t n, int64_t k, const torch::Tens
 // satisfy this (K or MN not a multiple of 16, odd views) are copied once into a padded buffer.
 inline torch::Tensor tma_ready_operand(const torch::Tensor& t, int major) {
     if (t.is_meta()) return t;
+    const int64_t es = (int64_t)t.element_size();
     bool lead_ok = true;
-    for (int i = 0; i + 2 < t.dim(); ++i) lead_ok = lead_ok && t.stride(i) % 16 == 0;
-    if (reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0 && outer_stride(t, major) % 16 == 0 && lead_ok) return t;
+    for (int i = 0; i + 2 < t.dim(); ++i) lead_ok = lead_ok && t.stride(i) * es % 16 == 0;
+    if (reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0 && outer_stride(t, major) * es % 16 == 0 && lead_ok) return t;
     const auto src = major == DG_MAJOR_K ? t : t.transpose(-2, -1);
-    const int64_t rows = src.size(-2), cols = src.size(-1), pitch = align_up(cols, 16);
+    const int64_t rows = src.size(-2), cols = src.size(-1) * es, pitch = align_up(cols, 16);       // (columns in bytes)
     host_assert(src.dim() == 2 || src.dim() == 3, "operands have at most one leading (group) dimension");
     std::vector<int64_t> shape(src.sizes().begin(), src.sizes().end());
     shape.back() = pitch;
@@ -63,7 +64,7 @@ inline torch::Tensor tma_ready_operand(const torch::Tensor& t, int major) {
     for (int64_t g = 0; g < groups; ++g) {
         const auto s = src.dim() == 3 ? src[g] : src;
         const auto b = src.dim() == 3 ? buf[g] : buf;
-        check(dg_pad_rows_launch(s.data_ptr(), (uint64_t)s.stride(0), b.data_ptr(), (uint64_t)pitch, (uint64_t)rows, (uint64_t)cols, stream));
+        check(dg_pad_rows_launch(s.data_ptr(), (uint64_t)(s.stride(0) * es), b.data_ptr(), (uint64_t)pitch, (uint64_t)rows, (uint64_t)cols, stream));
     }
     auto view = buf.slice(-1, 0, cols).view(t.scalar_type());
     return major == DG_MAJOR_K ? view : view.transpose(-2, -1);
@@ -180,9 +181,8 @@ inline void run_gemm(int gemm_type, const torch::Tensor& a, const torch::Tensor&
     desc.a_dtype = dtype_code(a);
     desc.b_dtype = dtype_code(b);
     desc.d_dtype = d.scalar_type() == torch::kFloat8_e4m3fn ? DG_E4M3 : dtype_code(d);
-    // (BF16 operands are not repacked: the library answers "strides must be multiples of 16 bytes" for odd views)
-    auto a_use = bf16 ? a : tma_ready_operand(a, major_a);
-    auto b_use = bf16 ? b : tma_ready_operand(b, major_b);
+    auto a_use = tma_ready_operand(a, major_a);
+    auto b_use = tma_ready_operand(b, major_b);
     desc.a = ptr_of(a_use);
     desc.b = ptr_of(b_use);
     desc.d = ptr_of(d);
@@ -420,6 +420,28 @@ static void fp8_einsum(const std::string& expr, const TensorPair& a, const Tenso
             spec.dims, epilogue, config);
 }
 
+// ---- BF16 batched GEMM and einsum (csrc/apis/einsum.hpp:73-145): the batched scheduler with kind::f16 MMAs
+static void bf16_bmm(const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& d, const OptTensor& c,
+                     const std::string& compiled_dims, const std::shared_ptr<EpilogueClass>& epilogue, const OptConfig& config) {
+    host_assert(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "A and B must be bfloat16");
+    host_assert(d.scalar_type() == torch::kBFloat16 || d.scalar_type() == torch::kFloat32, "D must be bf16 or fp32");
+    host_assert(d.dim() == 3 && d.stride(-1) == 1, "D must be [B, M, N] and contiguous in N");
+    if (a.size(0) == 0) return;
+    run_gemm(DG_GEMM_BATCHED, a, b, d, c, resolve_epilogue(epilogue, c, d), std::nullopt, std::nullopt, std::nullopt, std::nullopt,
+             std::nullopt, std::nullopt, false, 0, config);
+}
+
+static void einsum(const std::string& expr, const torch::Tensor& a, const torch::Tensor& b, const torch::Tensor& d, const OptTensor& c,
+                   const bool& use_cublaslt, const std::shared_ptr<EpilogueClass>& epilogue, const OptConfig& config) {
+    host_assert(!use_cublaslt, "einsum: use_cublaslt is not implemented (csrc/apis/einsum.hpp:128-130)");
+    const auto perm = [](const torch::Tensor& t, std::vector<int64_t> p) { return p.empty() ? t : t.permute(p); };
+    const auto perm_c = [&](std::vector<int64_t> p) { return c.has_value() ? OptTensor(perm(c.value(), p)) : std::nullopt; };
+    if (expr == "bhr,hdr->bhd") bf16_bmm(perm(a, {1, 0, 2}), b, perm(d, {1, 0, 2}), perm_c({1, 0, 2}), "nk", epilogue, config);
+    else if (expr == "bhd,hdr->bhr") bf16_bmm(perm(a, {1, 0, 2}), perm(b, {0, 2, 1}), perm(d, {1, 0, 2}), perm_c({1, 0, 2}), "nk", epilogue, config);
+    else if (expr == "bhd,bhr->hdr") bf16_bmm(perm(a, {1, 2, 0}), perm(b, {1, 2, 0}), d, c, "mn", epilogue, config);
+    else throw std::runtime_error("Unsupported einsum expression");
+}
+
 inline void register_gemm_apis(py::module_& m) {
 #define DG_DENSE_ARGS(dims)                                                                                            \
     py::arg("a"), py::arg("b"), py::arg("d"), py::arg("c") = std::nullopt, py::arg("recipe") = std::nullopt,           \
@@ -483,6 +505,10 @@ inline void register_gemm_apis(py::module_& m) {
     m.def("fp8_bmm", &fp8_bmm, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("c") = std::nullopt,
           py::arg("recipe") = std::make_tuple(1, 1, 32), py::arg("compiled_dims") = "nk", py::arg("epilogue") = nullptr,
           py::kw_only(), py::arg("config") = std::nullopt);
+    m.def("bf16_bmm", &bf16_bmm, py::arg("a"), py::arg("b"), py::arg("d"), py::arg("c") = std::nullopt, py::arg("compiled_dims") = "nk",
+          py::arg("epilogue") = nullptr, py::kw_only(), py::arg("config") = std::nullopt);
+    m.def("einsum", &einsum, py::arg("expr"), py::arg("a"), py::arg("b"), py::arg("d"), py::arg("c") = std::nullopt,
+          py::arg("use_cublaslt") = false, py::arg("epilogue") = nullptr, py::kw_only(), py::arg("config") = std::nullopt);
     m.def("fp8_einsum", &fp8_einsum, py::arg("expr"), py::arg("a"), py::arg("b"), py::arg("d"), py::arg("c") = std::nullopt,
           py::arg("recipe") = std::make_tuple(1, 1, 32), py::arg("epilogue") = nullptr, py::kw_only(), py::arg("config") = std::nullopt);
 }

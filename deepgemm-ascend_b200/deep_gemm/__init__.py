@@ -1,7 +1,7 @@
 """deep_gemm for NVIDIA B200: block-scaled FP8 / FP8xFP4 GEMM behind the DeepGEMM-Ascend Python API.
 
 The names, arguments and error text of the hot path follow the reference's `deep_gemm/__init__.py:25-81`;
-everything else of the reference (attention, MegaMoE, BF16 einsum, ACLNN wrappers) is out of scope
+everything else of the reference (attention, MegaMoE, ACLNN wrappers) is out of scope
 and not exported. Importing this package never initialises a CUDA context.
 """
 
@@ -36,7 +36,7 @@ _HOT_PATH_NAMES = (
     'k_grouped_fp8_gemm_tn_contiguous', 'k_grouped_fp8_gemm_nt_contiguous',
     'bf16_gemm_nt', 'bf16_gemm_nn', 'bf16_gemm_tn', 'bf16_gemm_tt',
     'm_grouped_bf16_gemm_nt_contiguous', 'm_grouped_bf16_gemm_nn_contiguous', 'k_grouped_bf16_gemm_tn_contiguous',
-    'fp8_bmm', 'fp8_einsum',
+    'fp8_bmm', 'fp8_einsum', 'bf16_bmm', 'einsum',
     'transform_sf_into_required_layout', 'transform_k_grouped_sf_into_required_layout', 'get_recipe', 'npu_sleep',
 )
 _C = _api._C

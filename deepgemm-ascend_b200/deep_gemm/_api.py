@@ -441,26 +441,27 @@ def _tma_ready_operand(t: torch.Tensor, major: int) -> torch.Tensor:
     that do not satisfy this (K or MN not a multiple of 16, odd views) are copied once into a padded buffer."""
     if t.is_meta:
         return t
+    es = t.element_size()
     outer = _outer_stride(t, major)
-    lead_ok = all(t.stride(i) % 16 == 0 for i in range(t.dim() - 2))
-    if t.data_ptr() % 16 == 0 and outer % 16 == 0 and lead_ok:
+    lead_ok = all(t.stride(i) * es % 16 == 0 for i in range(t.dim() - 2))
+    if t.data_ptr() % 16 == 0 and outer * es % 16 == 0 and lead_ok:
         return t
     rows_axis = -2 if major == L.MAJOR_K else -1
     cols_axis = -1 if major == L.MAJOR_K else -2
-    rows, cols = t.size(rows_axis), t.size(cols_axis)
+    rows, cols = t.size(rows_axis), t.size(cols_axis) * es              # (columns in bytes)
     lead = t.shape[:-2]
     pitch = _align(cols, 16)
     buf = torch.empty((*lead, rows, pitch), dtype=torch.uint8, device=t.device)
-    src = t if major == L.MAJOR_K else t.transpose(-2, -1)
+    src = (t if major == L.MAJOR_K else t.transpose(-2, -1))
     # one launch per leading index keeps the source strides arbitrary
     flat_src = src.reshape(-1, rows, cols) if src.dim() > 2 and src.is_contiguous() else None
     stream = _stream_ptr(t.device)
     if src.dim() == 2:
-        L.check(L.lib().dg_pad_rows_launch(src.data_ptr(), src.stride(0), buf.data_ptr(), pitch, rows, cols, stream))
+        L.check(L.lib().dg_pad_rows_launch(src.data_ptr(), src.stride(0) * es, buf.data_ptr(), pitch, rows, cols, stream))
     else:
         _host_assert(src.dim() == 3, 'operands have at most one leading (group) dimension')
         for g in range(src.size(0)):
-            L.check(L.lib().dg_pad_rows_launch(src[g].data_ptr(), src[g].stride(0), buf[g].data_ptr(), pitch, rows, cols, stream))
+            L.check(L.lib().dg_pad_rows_launch(src[g].data_ptr(), src[g].stride(0) * es, buf[g].data_ptr(), pitch, rows, cols, stream))
     del flat_src
     view = buf[..., :cols].view(t.dtype)
     return view if major == L.MAJOR_K else view.transpose(-2, -1)
@@ -558,8 +559,7 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
                             disable_ue8m0_cast, None, True)
 
     _host_assert(a.dtype in _DTYPES and b.dtype in _DTYPES, 'Unsupported operand dtypes')
-    # (BF16 operands are not repacked: the library answers "strides must be multiples of 16 bytes" for odd views)
-    a_use, b_use = (a, b) if bf16 else (_tma_ready_operand(a, major_a), _tma_ready_operand(b, major_b))
+    a_use, b_use = _tma_ready_operand(a, major_a), _tma_ready_operand(b, major_b)
 
     desc = L.GemmDesc()
     desc.a, desc.b, desc.d = _ptr(a_use), _ptr(b_use), _ptr(d)
@@ -813,6 +813,30 @@ def fp8_einsum(expr, a, b, d, c=None, recipe=(1, 1, 32), epilogue=None, *, confi
     d_arg = (perm(d[0], pd), d[1]) if is_pair else perm(d, pd)
     fp8_bmm((perm(a[0], pa), perm(a[1], pa)), (perm(b[0], pb), perm(b[1], pb)), d_arg, perm(c, pd), recipe, dims,
             epilogue, config=config)
+
+
+def bf16_bmm(a, b, d, c=None, compiled_dims='nk', epilogue=None, *, config=None):
+    """Batched D[i] = A[i] @ B[i]^T (+ C[i]) for BF16 operands; csrc/apis/einsum.hpp:73-100. A [B,M,K], B [B,N,K] (either
+    major, any batch stride), D [B,M,N] bf16 / fp32."""
+    _host_assert(a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, 'A and B must be bfloat16')
+    _host_assert(d.dtype in (torch.bfloat16, torch.float32), 'D must be bf16 or fp32')
+    _host_assert(d.dim() == 3 and d.stride(-1) == 1, 'D must be [B, M, N] and contiguous in N')
+    if a.size(0) == 0:
+        return
+    _run_gemm(L.GEMM_BATCHED, a, b, d, c, _resolve_epilogue(epilogue, c, d), None, None, None, None, None, None,
+              compiled_dims, False, config=config)
+
+
+def einsum(expr, a, b, d, c=None, use_cublaslt=False, epilogue=None, *, config=None):
+    """BF16 einsum over the reference's three contraction strings (csrc/apis/einsum.hpp:102-145): the operands are
+    permuted (views only) into a batched BF16 GEMM."""
+    _host_assert(not use_cublaslt, 'einsum: use_cublaslt is not implemented (csrc/apis/einsum.hpp:128-130)')
+    _host_assert(expr in _BATCH_SPECS, 'Unsupported einsum expression')
+    pa, pb, pd, dims = _BATCH_SPECS[expr]
+
+    def perm(t, p):
+        return t if p is None or t is None else t.permute(p)
+    bf16_bmm(perm(a, pa), perm(b, pb), perm(d, pd), perm(c, pd), dims, epilogue, config=config)
 
 
 def device_status() -> int:

@@ -148,7 +148,55 @@ def test_argument_checks():
     with pytest.raises(RuntimeError):
         deep_gemm.bf16_gemm_nt(a, a.to(torch.float8_e4m3fn), d)
     b = torch.zeros(128, 60, dtype=torch.bfloat16, device='cuda')
-    with pytest.raises(RuntimeError):            # rows 120 bytes apart cannot be a TMA source
-        deep_gemm.bf16_gemm_nt(b, b, d)
-    deep_gemm.bf16_gemm_nt(a[:, :60], a[:, :60], d)      # the same K with 128-byte rows is fine
+    deep_gemm.bf16_gemm_nt(b, b, d)              # rows 120 bytes apart are repacked to a 16-byte pitch by the host layer
+    deep_gemm.bf16_gemm_nt(a[:, :60], a[:, :60], d)
     assert d.abs().max().item() == 0
+
+
+# tests/generators.py:491-541 through tests/test_bf16_gemm.py: extents that are not multiples of 16 bytes, every major pair
+@pytest.mark.parametrize('m,n,k', [(4, 4, 64), (17, 4096, 4096), (4096, 15, 4096), (130, 257, 2048), (513, 257, 4096),
+                                   (64, 64, 4), (1024, 2048, 17), (8192, 4096, 15), (128, 128, 234), (2048, 8192, 4095)])
+def test_reference_odd_extent_lists_all_majors(m, n, k):
+    for trans in ('nt', 'nn', 'tn', 'tt'):
+        _dense(m, n, k, trans, out=torch.float32, acc=True)
+
+
+@pytest.mark.parametrize('batch,m,n,k', [(4, 128, 256, 512), (3, 130, 200, 1000), (8, 64, 64, 64)])
+def test_bf16_bmm(batch, m, n, k):
+    seed_all(batch)
+    a, b = torch.randn(batch, m, k).bfloat16(), torch.randn(batch, n, k).bfloat16()
+    prod = torch.einsum('bmk,bnk->bmn', a.float(), b.float())
+    d = torch.full((batch, m, n), float('nan'), dtype=torch.bfloat16, device='cuda')
+    deep_gemm.bf16_bmm(a.cuda(), b.cuda(), d)
+    assert_close(d, prod.to(torch.bfloat16), f'bf16_bmm {batch}x{m}x{n}x{k}')
+    c = torch.randn(batch, m, n)
+    d32 = c.cuda()
+    deep_gemm.bf16_bmm(a.cuda(), b.cuda(), d32, c=d32)
+    assert deep_gemm.device_status() == 0
+    assert_close(d32, prod + c, f'bf16_bmm accumulate {batch}x{m}x{n}x{k}')
+
+
+@pytest.mark.parametrize('expr', ['bhr,hdr->bhd', 'bhd,hdr->bhr', 'bhd,bhr->hdr'])
+@pytest.mark.parametrize('b_,h,r,d_', [(4, 2, 2, 2), (32, 128, 512, 128), (128, 8, 4096, 1024), (4096, 8, 512, 128)])
+def test_bf16_einsum(expr, b_, h, r, d_):
+    """csrc/apis/einsum.hpp:102-145 on sizes of tests/generators.py:778-786 (inputs N(0, 0.1), the weight-gradient
+    expression accumulates into FP32, the other two write BF16)."""
+    seed_all(b_ + h)
+    shapes = {'bhr,hdr->bhd': ((b_, h, r), (h, d_, r), (b_, h, d_)), 'bhd,hdr->bhr': ((b_, h, d_), (h, d_, r), (b_, h, r)),
+              'bhd,bhr->hdr': ((b_, h, d_), (b_, h, r), (h, d_, r))}[expr]
+    a = (torch.randn(shapes[0]) * 0.1).bfloat16()
+    b = (torch.randn(shapes[1]) * 0.1).bfloat16()
+    ref = torch.einsum(expr, a.float(), b.float())
+    if expr == 'bhd,bhr->hdr':
+        c = torch.randn(shapes[2]) * 0.1
+        d = c.cuda()
+        deep_gemm.einsum(expr, a.cuda(), b.cuda(), d, c=d)
+        ref = ref + c
+    else:
+        d = torch.full(shapes[2], float('nan'), dtype=torch.bfloat16, device='cuda')
+        deep_gemm.einsum(expr, a.cuda(), b.cuda(), d)
+        ref = ref.to(torch.bfloat16)
+    assert deep_gemm.device_status() == 0
+    assert_close(d, ref, f'einsum {expr} b={b_} h={h} r={r} d={d_}')
+    with pytest.raises(RuntimeError, match='Unsupported einsum expression'):
+        deep_gemm.einsum('bh,hd->bd', a.cuda(), b.cuda(), d)
