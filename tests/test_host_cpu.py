@@ -52,6 +52,10 @@ def test_public_names_of_the_hot_path_exist():
                  'm_grouped_fp8_gemm_nt_contiguous', 'm_grouped_fp8_gemm_nn_contiguous',
                  'm_grouped_fp8_fp4_gemm_nt_contiguous', 'm_grouped_fp8_fp4_gemm_nn_contiguous',
                  'm_grouped_fp8_gemm_nt_masked', 'm_grouped_fp8_fp4_gemm_nt_masked',
+                 'k_grouped_fp8_gemm_tn_contiguous', 'k_grouped_fp8_gemm_nt_contiguous', 'k_grouped_bf16_gemm_tn_contiguous',
+                 'bf16_gemm_nt', 'bf16_gemm_nn', 'bf16_gemm_tn', 'bf16_gemm_tt', 'm_grouped_bf16_gemm_nt_contiguous',
+                 'm_grouped_bf16_gemm_nn_contiguous', 'fp8_bmm', 'fp8_einsum', 'bf16_bmm', 'einsum',
+                 'transform_k_grouped_sf_into_required_layout', 'get_recipe', 'npu_sleep',
                  'transform_sf_into_required_layout', 'get_num_sms', 'set_num_sms',
                  'get_mk_alignment_for_contiguous_layout', 'use_deterministic_algorithms', 'set_dry_run'):
         assert callable(getattr(deep_gemm, name)), name
