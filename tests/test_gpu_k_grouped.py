@@ -171,12 +171,12 @@ def test_sf_fixtures_from_the_reference_layout_model(golden):
 @pytest.mark.parametrize('dtype', [torch.float32, torch.int16])
 @pytest.mark.parametrize('gran', [1, 32, 128])
 @pytest.mark.parametrize('mn_major', [False, True])
-def test_sf_random_against_oracle(dtype, gran, mn_major):
-    """The reference's sweep shape: groups whose real size is 16 short of the alignment on odd indices
-    (tests/generators.py:716-722)."""
+@pytest.mark.parametrize('mn,num_groups,avg_k', [(4096, 16, 2048), (7168, 8, 4096), (4096, 72, 384), (7168, 128, 256)])
+def test_sf_random_against_oracle(dtype, gran, mn_major, mn, num_groups, avg_k):
+    """The reference's sweep (tests/generators.py:693-722): rows x group configurations, groups whose real size is 16
+    short of the alignment on odd indices."""
     seed_all(5)
-    mn = 4096
-    sizes = [oracle.align(int(2048 * (0.7 + 0.6 * torch.rand(()).item())), 256) - (16 if i % 2 else 0) for i in range(16)]
+    sizes = [oracle.align(int(avg_k * (0.7 + 0.6 * torch.rand(()).item())), 256) - (16 if i % 2 else 0) for i in range(num_groups)]
     k, psum = oracle.make_psum_layout(sizes, 256)
     div = 32 if dtype == torch.float32 else 64
     shape = (oracle.ceil_div(mn, gran), oracle.ceil_div(k, div))

@@ -81,3 +81,31 @@ def test_gran_k_128_expands_to_four_blocks():
         sf = (torch.randint(90, 140, (rows, oracle.ceil_div(k, 128)), dtype=torch.int32) << 23).view(torch.float32)
         out = deep_gemm.transform_sf_into_required_layout(sf.cuda(), mn, k, (gran, gran, 128), is_sfa=True)
         _check(out, oracle.required_sf_layout(sf, mn, k, gran, gran_k=128), f'gran_k=128 gran_mn={gran}')
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.int16])
+@pytest.mark.parametrize('mn_major', [False, True])
+@pytest.mark.parametrize('num_batches', [1, 2, 4])
+def test_reference_layout_product(dtype, mn_major, num_batches):
+    """tests/generators.py:682-690: (4096, 4097, 8192) rows x (128, 7168, 7296) columns of K x the three row
+    granularities, dense and batched, K-major and MN-major sources, FP32 and packed int16 sources."""
+    for mn in (4096, 4097, 8192):
+        for k in (128, 7168, 7296):
+            for gran in (1, 32, 128):
+                torch.manual_seed(mn * 7 + k + gran + num_batches)
+                div = 32 if dtype == torch.float32 else 64
+                shape = (oracle.ceil_div(mn, gran), oracle.ceil_div(k, div))
+                if num_batches > 1:
+                    shape = (num_batches, *shape)
+                if dtype == torch.float32:
+                    sf = (torch.randint(1, 255, shape, dtype=torch.int32) << 23).view(torch.float32)
+                else:
+                    sf = torch.randint(-32768, 32768, shape, dtype=torch.int16)
+                expected = oracle.required_sf_layout(sf, mn, k, gran)
+                src = sf.cuda()
+                if mn_major and shape[-1] > 1 and shape[-2] > 1:
+                    src = src.transpose(-2, -1).contiguous().transpose(-2, -1)
+                kwargs = {'num_groups': num_batches} if num_batches > 1 else {}
+                out = deep_gemm.transform_sf_into_required_layout(src, mn, k, (gran, gran, 32), is_sfa=True, **kwargs)
+                _check(out, expected, f'{dtype} mn_major={mn_major} batches={num_batches} mn={mn} k={k} gran={gran}')
+    assert deep_gemm.device_status() == 0
