@@ -26,6 +26,7 @@ def main() -> None:
     ap.add_argument('--cta-group', type=int, default=0)
     ap.add_argument('--split-k', type=int, default=0)
     ap.add_argument('--stages', type=int, default=0)
+    ap.add_argument('--raster-group', type=int, default=0, help='row blocks per group of the dense tile walk (0 = default)')
     ap.add_argument('--out', default='bf16', choices=['bf16', 'f32'])
     ap.add_argument('--fp4', action='store_true', help='both operands packed E2M1 (dense only)')
     ap.add_argument('--bf16', action='store_true', help='BF16 operands, no scale factors (dense only)')
@@ -79,7 +80,8 @@ def main() -> None:
         a_bf16 = torch.randn(rows, k, device=dev).bfloat16()
         b_bf16 = torch.randn(n, k, device=dev).bfloat16()
     config = {key: val for key, val in (('block_n', args.block_n), ('cta_group', args.cta_group),
-                                        ('split_k', args.split_k), ('num_stages', args.stages)) if val}
+                                        ('split_k', args.split_k), ('num_stages', args.stages),
+                                        ('raster_group', args.raster_group)) if val}
     layout = torch.arange(1, g + 1, dtype=torch.int32, device=dev) * m if g else None
     if args.mixed:
         b_packed = torch.randint(-128, 128, (k, n // 2), dtype=torch.int8, device=dev)
