@@ -213,3 +213,27 @@ def test_lean_gemm_after_kernels_that_dirty_shared_memory():
         torch.cuda.synchronize()
         assert deep_gemm.device_status() == 0
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f'iteration {i}'
+
+
+def test_bench_msprof_reports_the_gemm_kernel_by_name():
+    """The reference's profiler-based timer (deep_gemm/testing/bench.py:284-400) with its three return forms."""
+    from deep_gemm.testing import bench_msprof
+    seed_all(11)
+    m, n, k = 256, 512, 1024
+    a, sfa, _ = uniform_fp8((m, k), (1, 32))
+    b, sfb, _ = uniform_fp8((n, k), (1, 32))
+    a, sfa, b, sfb = a.cuda(), sfa.cuda(), b.cuda(), sfb.cuda()
+    d = torch.empty(m, n, dtype=torch.bfloat16, device='cuda')
+
+    def fn():
+        deep_gemm.fp8_gemm_nt((a, sfa), (b, sfb), d)
+    one = bench_msprof(fn, kernel_names='mx_gemm_kernel', num_warmups=2, num_tests=5)
+    assert one.iters == 5 and 0.5 < one.dur_us < 1000 and one.tflops(2.0 * m * n * k) > 0
+    both = bench_msprof(fn, kernel_names=['mx_gemm_kernel', 'transform_sf', 'no_such_kernel'], num_warmups=1, num_tests=3)
+    assert both[0] is not None and both[1] is not None and both[2] is None
+    everything = bench_msprof(fn, return_all_kernels=True, num_warmups=1, num_tests=3)
+    assert any('mx_gemm_kernel' in name for name in everything) and any('l2_flush' in name for name in everything)
+    with pytest.raises(RuntimeError, match='No unique kernel'):
+        bench_msprof(fn, kernel_names='kernel', num_warmups=0, num_tests=1)
+    with pytest.raises(ValueError):
+        bench_msprof(fn)
