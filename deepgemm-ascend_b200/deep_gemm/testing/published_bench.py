@@ -4,6 +4,8 @@ The reference measured on an Ascend 950DT with cold L2 (README.md:102); the figu
 and TFLOPS per row, kept here only to print them beside this build's numbers. The dense rows are timed like the
 shapes of the dense sweep (a CUDA graph of back-to-back launches over rotating operand sets that together exceed L2
 several times); the m-grouped rows run for a millisecond or more and are timed per launch after an untimed L2 flush.
+Every dense row is also timed the reference's way: alone, after a buffer larger than L2 has been written, its duration
+read from the profiler's activity trace (that leaves L2 full of dirty lines, whose write-back the kernel then pays for).
 Operands are synthetic: uniform E4M3 / E2M1 codes with power-of-two UE8M0 scales per 32 elements of K, already in the
 required layout, BF16 output. One sampled row block of every row is checked against the CPU oracle.
 """
@@ -19,7 +21,7 @@ import torch
 
 from .. import _api
 from .. import _lib as L
-from .bench import bench_graph
+from .bench import bench_graph, bench_msprof
 from .moe_bench import _close, _codes, _flush_timed, _scales, _unpacked_scales
 from .sharding import shard_psum_layout
 
@@ -153,10 +155,18 @@ def time_published(device, steps: int) -> dict:
         sets = [first] + [DenseRow(kinds, m, n, k, device, seed=9000 + 40 * i + j) for j in range(copies - 1)]
         us = bench_graph([(lambda sptr, s=s: s.launch(lib, sptr)) for s in sets], 3, steps).dur_us
         ok = first.verify() and ok
+        # the reference's own method (deep_gemm/testing/bench.py:284-400): the kernel alone after a buffer larger than L2
+        # has been written, its duration taken from the profiler's activity trace; None where no trace can be had
+        try:
+            sptr = torch.cuda.current_stream(device).cuda_stream
+            alone = bench_msprof(lambda: first.launch(lib, sptr), kernel_names='mx_gemm_kernel', num_warmups=2, num_tests=10).dur_us
+        except Exception:      # noqa: BLE001 - the trace is an extra; the CUDA-event figures above stand without it
+            alone = None
         rows.append({'case': 'dense %s %dx%dx%d' % (kinds, m, n, k), 'us': round(us, 2),
                      'tflops': round(first.flops / us / 1e6, 1), 'gbs': round(first.bytes / us / 1e3, 1),
                      'published_us': pub_us, 'published_tflops': pub_tf, 'published_at': where,
-                     'speedup': round(pub_us / us, 2), 'block_n': first.config['block_n'],
+                     'speedup': round(pub_us / us, 2), 'us_alone_after_written_flush': round(alone, 2) if alone else None,
+                     'block_n': first.config['block_n'],
                      'cta_group': first.config['cta_group'], 'split_k': first.config['split_k'], 'flops': first.flops})
         del sets, first
     torch.cuda.empty_cache()
