@@ -145,7 +145,7 @@ class GroupedRow:
         return ok
 
 
-def time_published(device, steps: int) -> dict:
+def time_published(device, steps: int, alone_too: bool = False) -> dict:
     """All rows on one GPU. Returns {'rows': [...], 'tflops', 'published_tflops', 'geomean_speedup', 'verified'}."""
     lib = L.lib()
     rows, ok = [], True
@@ -157,9 +157,11 @@ def time_published(device, steps: int) -> dict:
         ok = first.verify() and ok
         # the reference's own method (deep_gemm/testing/bench.py:284-400): the kernel alone after a buffer larger than L2
         # has been written, its duration taken from the profiler's activity trace; None where no trace can be had
+        alone = None
         try:
             sptr = torch.cuda.current_stream(device).cuda_stream
-            alone = bench_msprof(lambda: first.launch(lib, sptr), kernel_names='mx_gemm_kernel', num_warmups=2, num_tests=10).dur_us
+            if alone_too:
+                alone = bench_msprof(lambda: first.launch(lib, sptr), kernel_names='mx_gemm_kernel', num_warmups=2, num_tests=10).dur_us
         except Exception:      # noqa: BLE001 - the trace is an extra; the CUDA-event figures above stand without it
             alone = None
         rows.append({'case': 'dense %s %dx%dx%d' % (kinds, m, n, k), 'us': round(us, 2),
@@ -196,7 +198,7 @@ def time_published(device, steps: int) -> dict:
 
 
 def run_published(args, rank, world, device, emit=None):
-    r = time_published(device, max(3, min(args.steps, 10)))
+    r = time_published(device, max(3, min(args.steps, 10)), alone_too=True)
     if rank != 0:
         return
     line = {'metric': 'fp8_block_scaled_gemm_tflops', 'value': world * r['tflops'], 'unit': 'TFLOP/s', 'n_gpus': world,
