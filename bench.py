@@ -606,6 +606,13 @@ def run_dense(args, rank, world, device):
     emit(line)
 
 
+def oracle_checks() -> dict:
+    """The CPU oracle's checkers for the workloads of `deep_gemm.testing` (which know nothing of the oracle themselves)."""
+    from oracle import checks
+    return {'mixed': checks.mixed_case, 'grouped': checks.grouped_case, 'dense_row': checks.dense_row,
+            'grouped_row': checks.grouped_row}
+
+
 def other_config_legs(args, device, pk) -> dict:
     """Short legs for the configurations the sweep does not contain: mixed FP8xFP4 (config 3), m-grouped contiguous
     with 32 experts (config 4) and m-grouped masked 32 x 256 (config 5), verified on a row sample, with the roofline
@@ -616,27 +623,28 @@ def other_config_legs(args, device, pk) -> dict:
     fp8_peak = 2.0 * pk['bf16_tflops']
     steps = max(3, min(args.steps, 10))
     out = {}
-    r = moe_bench.time_mixed(device, steps)
+    checks = oracle_checks()
+    r = moe_bench.time_mixed(device, steps, checks['mixed'])
     out['mixed_fp8_fp4_nn_4096x7168x2048'] = {
         'us': round(r['us'], 2), 'tflops': round(r['tflops'], 1), 'verified': r['verified'], 'tiling': r['tiling'],
         'roofline': {'bound': 'tensor', 'achieved': r['tflops'], 'peak': fp8_peak, 'unit': 'TFLOP/s',
                      'frac': r['tflops'] / fp8_peak, 'frac_of_nominal': r['tflops'] / NOMINAL_FP8_TFLOPS, 'traffic': None}}
     random.seed(1234)
     sizes = [int(random.uniform(0.7, 1.3) * 8192) for _ in range(GLOBAL_EXPERTS)]
-    r = moe_bench.time_grouped(device, sizes, steps, masked=False)
+    r = moe_bench.time_grouped(device, sizes, steps, masked=False, check=checks['grouped'])
     out['m_grouped_contiguous_32_experts'] = {
         'shapes': r['shapes'], 'tflops': round(r['tflops'], 1), 'verified': r['verified'],
         'roofline': {'bound': 'tensor', 'achieved': r['tflops'], 'peak': fp8_peak, 'unit': 'TFLOP/s',
                      'frac': r['tflops'] / fp8_peak, 'frac_of_nominal': r['tflops'] / NOMINAL_FP8_TFLOPS, 'traffic': None}}
     masked = [random.randint(0, 256) for _ in range(GLOBAL_EXPERTS)]
-    r = moe_bench.time_grouped(device, masked, steps, masked=True)
+    r = moe_bench.time_grouped(device, masked, steps, masked=True, check=checks['grouped'])
     out['m_grouped_masked_32x256'] = {
         'shapes': r['shapes'], 'tflops': round(r['tflops'], 1), 'gbs': round(r['gbs'], 1), 'verified': r['verified'],
         'roofline': {'bound': 'hbm', 'achieved': r['gbs'], 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
                      'frac': r['gbs'] / pk['hbm_gbs'], 'frac_of_nominal': r['gbs'] / NOMINAL_HBM_GBS, 'traffic': None}}
     # every row of the reference's own published tables (other hardware), for the ratio a reader will want to see
     from deep_gemm.testing import published_bench
-    r = published_bench.time_published(device, steps)
+    r = published_bench.time_published(device, steps, check_dense=checks['dense_row'], check_grouped=checks['grouped_row'])
     out['reference_published_tables'] = {
         'tflops': round(r['tflops'], 1), 'published_tflops_other_hardware': round(r['published_tflops'], 1),
         'geomean_speedup_vs_published': round(r['geomean_speedup'], 2), 'verified': r['verified'], 'rows': r['rows']}
@@ -691,7 +699,7 @@ def main():
             run_dense(args, rank, world, device)
         else:
             from deep_gemm.testing import moe_bench
-            moe_bench.run(args, rank, world, device, emit, peaks())
+            moe_bench.run(args, rank, world, device, emit, peaks(), oracle_checks())
     finally:
         if world > 1:
             torch.distributed.destroy_process_group()

@@ -106,18 +106,6 @@ def _flush_timed(lib, device, launch, steps, warmup=3):
     return sum(e0.elapsed_time(e1) for e0, e1 in ev) / steps * 1e3
 
 
-def _close(out: torch.Tensor, ref: torch.Tensor) -> bool:
-    import oracle
-    out, ref = out.cpu(), ref.cpu()
-    return bool(torch.isfinite(out.float()).all()) and oracle.calc_diff(out, ref) <= 1e-3 and oracle.max_rel_err(out, ref) <= 2e-2
-
-
-def _unpacked_scales(sf16: torch.Tensor, k: int) -> torch.Tensor:
-    """Required-layout int16 scales [..., MN, K64] (any strides) -> FP32 scales [..., MN, ceil(K/32)] on the host."""
-    import oracle
-    return oracle.unpack_required_sf(sf16.cpu().contiguous(), k)
-
-
 class MixedCase:
     """FP8 x packed-FP4 GEMM "NN" (configuration 3): A [M, K] E4M3, B [K, N/2] packed E2M1 (uniform codes), per-32
     UE8M0 scales already in the required layout, BF16 out."""
@@ -141,15 +129,6 @@ class MixedCase:
     def launch(self, lib, sptr):
         L.check(lib.dg_gemm_launch(ctypes.byref(self.desc), None, None, 0, sptr))
 
-    def verify(self, rows: int = 16) -> bool:
-        import oracle
-        idx = torch.randperm(self.m, generator=torch.Generator().manual_seed(3))[:rows].sort().values
-        a_deq = oracle.dequantize(oracle.decode_e4m3(self.a[idx.to(self.a.device)].cpu()),
-                                  _unpacked_scales(self.sfa, self.k)[idx], 1, 32)
-        b_vals = oracle.decode_e2m1_packed(self.b.cpu(), axis=-1).transpose(0, 1)            # [N, K]
-        b_deq = oracle.dequantize(b_vals, _unpacked_scales(self.sfb, self.k), 1, 32)
-        return _close(self.d[idx.to(self.d.device)], oracle.gemm_ref(a_deq, b_deq, torch.bfloat16))
-
 
 def _graph_timed(lib, cases, steps) -> float:
     """Mean microseconds per launch of `cases` (same problem, operands of their own, together several times the L2
@@ -158,42 +137,16 @@ def _graph_timed(lib, cases, steps) -> float:
     return bench_graph([(lambda sptr, c=c: c.launch(lib, sptr)) for c in cases], 3, steps).dur_us
 
 
-def time_mixed(device, steps: int) -> dict:
+def time_mixed(device, steps: int, check=None) -> dict:
     lib = L.lib()
     cases = [MixedCase(device, seed=7 + i) for i in range(7)]           # 7 x 75 MB of operands and outputs
     us = _graph_timed(lib, cases, steps)
     case = cases[0]
     return {'us': us, 'tflops': case.flops / us / 1e6, 'gbs': case.bytes / us / 1e3, 'tiling': case.config,
-            'verified': case.verify()}
+            'verified': check(case) if check is not None else None}
 
 
-def _verify_grouped(case: 'GroupedCase', sizes, masked: bool, samples: int = 6) -> bool:
-    """Row blocks of a few groups against the CPU oracle: the first 64 valid rows and the last 64 of each sampled group."""
-    import oracle
-    g_all = [g for g, s in enumerate(sizes) if s > 0]
-    picks = g_all[:: max(1, len(g_all) // samples)][:samples]
-    ok = True
-    psum_start = 0
-    starts = []
-    for s in sizes:
-        starts.append(psum_start)
-        psum_start = (psum_start + s + 255) // 256 * 256
-    for g in picks:
-        rows = sizes[g]
-        b_deq = oracle.dequantize(oracle.decode_e4m3(case.b[g].cpu()), _unpacked_scales(case.sfb[g], case.k), 1, 32)
-        for lo in {0, max(0, rows - 64)}:
-            hi = min(rows, lo + 64)
-            if masked:
-                a_blk, sf_blk, d_blk = case.a[g, lo:hi], case.sfa[g, lo:hi], case.d[g, lo:hi]
-            else:
-                r0 = starts[g]
-                a_blk, sf_blk, d_blk = case.a[r0 + lo:r0 + hi], case.sfa[r0 + lo:r0 + hi], case.d[r0 + lo:r0 + hi]
-            a_deq = oracle.dequantize(oracle.decode_e4m3(a_blk.cpu()), _unpacked_scales(sf_blk, case.k), 1, 32)
-            ok = ok and _close(d_blk, oracle.gemm_ref(a_deq, b_deq, torch.bfloat16))
-    return ok
-
-
-def time_grouped(device, sizes, steps: int, masked: bool) -> dict:
+def time_grouped(device, sizes, steps: int, masked: bool, check=None) -> dict:
     """Both (N, K) of the MoE configurations on one GPU for the given per-expert row counts."""
     lib = L.lib()
     shapes, flops, us_total, nbytes, ok = [], 0.0, 0.0, 0.0, True
@@ -205,7 +158,7 @@ def time_grouped(device, sizes, steps: int, masked: bool) -> dict:
             del extra
         else:
             us = _flush_timed(lib, device, lambda sptr: case.launch(lib, sptr), steps)
-        ok = ok and _verify_grouped(case, sizes, masked)
+        ok = ok and (check(case, sizes, masked) if check is not None else True)
         shapes.append({'rows': case.rows, 'valid_rows': case.valid_rows, 'n': n, 'k': k, 'us': round(us, 1),
                        'tflops': round(case.flops / us / 1e6, 1), 'gbs': round(case.bytes / us / 1e3, 1),
                        'block_n': case.config['block_n'], 'cta_group': case.config['cta_group']})
@@ -214,12 +167,16 @@ def time_grouped(device, sizes, steps: int, masked: bool) -> dict:
         us_total += us
         del case
         torch.cuda.empty_cache()
-    return {'shapes': shapes, 'tflops': flops / us_total / 1e6, 'gbs': nbytes / us_total / 1e3, 'verified': ok}
+    return {'shapes': shapes, 'tflops': flops / us_total / 1e6, 'gbs': nbytes / us_total / 1e3,
+            'verified': ok if check is not None else None}
 
 
-def run(args, rank, world, device, emit=None, pk=None):
+def run(args, rank, world, device, emit=None, pk=None, checks=None):
+    """`checks`: optional callables that compare a timed case with a reference on the host (the benchmark passes the
+    CPU oracle's: 'mixed', 'grouped', 'dense_row', 'grouped_row'); without them the lines carry `verified: null`."""
+    checks = checks or {}
     if args.workload == 'mixed':
-        return run_mixed(args, rank, world, device, emit)
+        return run_mixed(args, rank, world, device, emit, checks.get('mixed'))
     if args.workload == 'fp4':
         return run_fp4(args, rank, world, device, emit)
     if args.workload == 'bf16':
@@ -230,11 +187,12 @@ def run(args, rank, world, device, emit=None, pk=None):
         return run_layout(args, rank, world, device, emit, pk)
     if args.workload == 'published':
         from .published_bench import run_published
-        return run_published(args, rank, world, device, emit)
-    return run_grouped(args, rank, world, device, emit, pk or {'bf16_tflops': 1590.0, 'hbm_gbs': 6650.0, 'source': 'fallback'})
+        return run_published(args, rank, world, device, emit, checks.get('dense_row'), checks.get('grouped_row'))
+    return run_grouped(args, rank, world, device, emit, pk or {'bf16_tflops': 1590.0, 'hbm_gbs': 6650.0, 'source': 'fallback'},
+                       checks.get('grouped'))
 
 
-def run_grouped(args, rank, world, device, emit, pk):
+def run_grouped(args, rank, world, device, emit, pk, check=None):
     """m-grouped contiguous (or masked) FP8 GEMM with a FIXED global expert count sharded over the ranks: every rank
     owns a contiguous block of experts (`sharding.expert_range`) and runs the single-GPU kernel on its local psum
     layout; nothing is exchanged on the data path. The NCCL all-gather of the outputs (equal, padded chunks) is timed
@@ -284,7 +242,7 @@ def run_grouped(args, rank, world, device, emit, pk):
     launches = lib.dg_kernel_launch_count() - launches0
     per_case_us = [sum(ev[s][ci][0].elapsed_time(ev[s][ci][1]) for s in range(args.steps)) / args.steps * 1e3
                    for ci in range(len(cases))]
-    verified = all(_verify_grouped(c, mine, masked, samples=2) for c in cases)
+    verified = all(check(c, mine, masked, samples=2) for c in cases) if check is not None else None
 
     def reduce_max(x):
         t = torch.tensor([x], dtype=torch.float64, device=device)
@@ -396,7 +354,7 @@ def run_grouped(args, rank, world, device, emit, pk):
     (emit or (lambda l: print(json.dumps(l), flush=True)))(line)
 
 
-def run_mixed(args, rank, world, device, emit=None):
+def run_mixed(args, rank, world, device, emit=None, check=None):
     """FP8 x packed-FP4 GEMM "NN": A [M,K] E4M3 with per-128 scales, B [K, N/2] packed E2M1 (uniform codes) with
     per-32 scales, BF16 out; M=4096, N=7168, K=2048. Normalised by the FP8 peak (the MMA runs on E4M3 operands)."""
     lib = L.lib()
@@ -410,7 +368,7 @@ def run_mixed(args, rank, world, device, emit=None):
             'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp8_e4m3 x fp4_e2m1 (kind::mxf8f6f4), ue8m0 scales',
             'data': 'synthetic',
             'config': {'workload': 'mixed FP8xFP4 GEMM NN, M=%d N=%d K=%d, BF16 out' % (m, n, k), 'l2': 'flushed, untimed'},
-            'gbs': case.bytes / us / 1e3, 'tiling': case.config, 'verified': case.verify(),
+            'gbs': case.bytes / us / 1e3, 'tiling': case.config, 'verified': check(case) if check is not None else None,
             'device_status': _api.device_status()}
     (emit or (lambda l: print(json.dumps(l), flush=True)))(line)
 

@@ -7,7 +7,8 @@ several times); the m-grouped rows run for a millisecond or more and are timed p
 Every dense row is also timed the reference's way: alone, after a buffer larger than L2 has been written, its duration
 read from the profiler's activity trace (that leaves L2 full of dirty lines, whose write-back the kernel then pays for).
 Operands are synthetic: uniform E4M3 / E2M1 codes with power-of-two UE8M0 scales per 32 elements of K, already in the
-required layout, BF16 output. One sampled row block of every row is checked against the CPU oracle.
+required layout, BF16 output. The caller may pass checkers that compare a sampled row block of every row with a reference
+on the host (the benchmark passes the CPU oracle's).
 """
 
 from __future__ import annotations
@@ -22,7 +23,7 @@ import torch
 from .. import _api
 from .. import _lib as L
 from .bench import bench_graph, bench_msprof
-from .moe_bench import _close, _codes, _flush_timed, _scales, _unpacked_scales
+from .moe_bench import _codes, _flush_timed, _scales
 from .sharding import shard_psum_layout
 
 # (operand kinds, M, N, K, published latency in us, published TFLOPS, where)
@@ -64,11 +65,6 @@ def _operand(kind: str, lead, mn: int, k: int, device, gen) -> torch.Tensor:
     return torch.randint(-128, 128, (*lead, mn, k // 2), dtype=torch.int8, device=device, generator=gen)
 
 
-def _values(kind: str, t: torch.Tensor) -> torch.Tensor:
-    import oracle
-    return oracle.decode_e4m3(t.cpu()) if kind == 'fp8' else oracle.decode_e2m1_packed(t.cpu(), axis=-1)
-
-
 class DenseRow:
     def __init__(self, kinds: str, m: int, n: int, k: int, device, seed: int):
         gen = torch.Generator(device=device).manual_seed(seed)
@@ -94,13 +90,6 @@ class DenseRow:
     def launch(self, lib, sptr):
         L.check(lib.dg_gemm_launch(ctypes.byref(self.desc), None, self.ws.data_ptr() if self.ws is not None else None,
                                    self.ws.numel() if self.ws is not None else 0, sptr))
-
-    def verify(self, rows: int = 8) -> bool:
-        import oracle
-        idx = torch.randperm(self.m, generator=torch.Generator().manual_seed(3))[:rows].sort().values
-        a_deq = oracle.dequantize(_values(self.kind_a, self.a[idx.to(self.a.device)]), _unpacked_scales(self.sfa, self.k)[idx], 1, 32)
-        b_deq = oracle.dequantize(_values(self.kind_b, self.b), _unpacked_scales(self.sfb, self.k), 1, 32)
-        return _close(self.d[idx.to(self.d.device)], oracle.gemm_ref(a_deq, b_deq, torch.bfloat16))
 
 
 class GroupedRow:
@@ -129,23 +118,8 @@ class GroupedRow:
     def launch(self, lib, sptr):
         L.check(lib.dg_gemm_launch(ctypes.byref(self.desc), None, None, 0, sptr))
 
-    def verify(self, rows: int = 16) -> bool:
-        """The first and the last `rows` valid rows of the first and of the last group against the oracle."""
-        import oracle
-        ok, start, starts = True, 0, []
-        for s in self.sizes:
-            starts.append(start)
-            start = (start + s + 255) // 256 * 256
-        for g in (0, len(self.sizes) - 1):
-            b_deq = oracle.dequantize(_values('fp4', self.b[g]), _unpacked_scales(self.sfb[g], self.k), 1, 32)
-            for lo in {0, max(0, self.sizes[g] - rows)}:
-                r = slice(starts[g] + lo, starts[g] + min(self.sizes[g], lo + rows))
-                a_deq = oracle.dequantize(_values('fp8', self.a[r]), _unpacked_scales(self.sfa[r], self.k), 1, 32)
-                ok = ok and _close(self.d[r], oracle.gemm_ref(a_deq, b_deq, torch.bfloat16))
-        return ok
 
-
-def time_published(device, steps: int, alone_too: bool = False) -> dict:
+def time_published(device, steps: int, alone_too: bool = False, check_dense=None, check_grouped=None) -> dict:
     """All rows on one GPU. Returns {'rows': [...], 'tflops', 'published_tflops', 'geomean_speedup', 'verified'}."""
     lib = L.lib()
     rows, ok = [], True
@@ -154,7 +128,7 @@ def time_published(device, steps: int, alone_too: bool = False) -> dict:
         copies = max(3, min(32, -(-512_000_000 // first.bytes)))
         sets = [first] + [DenseRow(kinds, m, n, k, device, seed=9000 + 40 * i + j) for j in range(copies - 1)]
         us = bench_graph([(lambda sptr, s=s: s.launch(lib, sptr)) for s in sets], 3, steps).dur_us
-        ok = first.verify() and ok
+        ok = (check_dense(first) if check_dense is not None else True) and ok
         # the reference's own method (deep_gemm/testing/bench.py:284-400): the kernel alone after a buffer larger than L2
         # has been written, its duration taken from the profiler's activity trace; None where no trace can be had
         alone = None
@@ -177,7 +151,7 @@ def time_published(device, steps: int, alone_too: bool = False) -> dict:
         sizes = [int(random.uniform(0.7, 1.3) * per_group) for _ in range(g)]          # tests/generators.py:212-220
         case = GroupedRow(sizes, n, k, device, seed=700 + i)
         us = _flush_timed(lib, device, lambda sptr: case.launch(lib, sptr), steps)
-        ok = case.verify() and ok
+        ok = (check_grouped(case) if check_grouped is not None else True) and ok
         # the published row is for groups x rows-per-group rows; scale its latency to the rows drawn here
         pub_scaled = pub_us * case.valid_rows / (g * per_group)
         rows.append({'case': 'm-grouped fp8xfp4 %d x %d rows (%d valid), N=%d K=%d' % (g, per_group, case.valid_rows, n, k),
@@ -193,12 +167,13 @@ def time_published(device, steps: int, alone_too: bool = False) -> dict:
     for r in rows:
         del r['flops']
     return {'rows': rows, 'tflops': flops / ours_s / 1e12, 'published_tflops': flops / theirs_s / 1e12,
-            'geomean_speedup': math.exp(sum(math.log(r['speedup']) for r in rows) / len(rows)), 'verified': ok,
+            'geomean_speedup': math.exp(sum(math.log(r['speedup']) for r in rows) / len(rows)),
+            'verified': ok if (check_dense is not None and check_grouped is not None) else None,
             'us_total': ours_s * 1e6}
 
 
-def run_published(args, rank, world, device, emit=None):
-    r = time_published(device, max(3, min(args.steps, 10)), alone_too=True)
+def run_published(args, rank, world, device, emit=None, check_dense=None, check_grouped=None):
+    r = time_published(device, max(3, min(args.steps, 10)), alone_too=True, check_dense=check_dense, check_grouped=check_grouped)
     if rank != 0:
         return
     line = {'metric': 'fp8_block_scaled_gemm_tflops', 'value': world * r['tflops'], 'unit': 'TFLOP/s', 'n_gpus': world,

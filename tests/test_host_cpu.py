@@ -354,6 +354,20 @@ def test_fp4_expansion_rule_of_the_c_abi():
     assert (ea.value, eb.value) == (0, 0)
 
 
+def test_the_shipped_package_never_refers_to_the_oracle():
+    """The oracle is test infrastructure: no module of the package (its benchmark helpers included) imports it; the
+    benchmark hands the checkers in from outside."""
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 'deepgemm-ascend_b200')
+    offenders = []
+    for folder, _, files in os.walk(root):
+        for name in files:
+            if name.endswith(('.py', '.cu', '.cuh', '.cpp', '.hpp', '.h')):
+                text = open(os.path.join(folder, name), encoding='utf-8').read()
+                if re.search(r'^\s*(import|from)\s+oracle\b', text, re.M) or 'oracle/' in text:
+                    offenders.append(os.path.join(folder, name))
+    assert offenders == []
+
+
 def _run_bench(*argv):
     import json
     import subprocess
