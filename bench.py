@@ -1,7 +1,7 @@
 """Benchmark of the block-scaled FP8 GEMM hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload auto|dense|grouped|masked|mixed|fp4|bf16|quant|layout|published]
+                    [--workload auto|dense|grouped|masked|mixed|fp4|bf16|quant|layout|published|moe_mlp]
 
 One GPU (`--workload auto` = `dense`): one "step" is one pass over the dense FP8 NT sweep the baseline names: M in
 {64, 128, 4096} times six (N, K) pairs, BF16 output, A quantised per 1x128 and B per 128x128 from N(0,1) data
@@ -610,7 +610,7 @@ def oracle_checks() -> dict:
     """The CPU oracle's checkers for the workloads of `deep_gemm.testing` (which know nothing of the oracle themselves)."""
     from oracle import checks
     return {'mixed': checks.mixed_case, 'grouped': checks.grouped_case, 'dense_row': checks.dense_row,
-            'grouped_row': checks.grouped_row}
+            'grouped_row': checks.grouped_row, 'moe_mlp': checks.moe_mlp_case}
 
 
 def other_config_legs(args, device, pk) -> dict:
@@ -671,7 +671,7 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--workload', default='auto',
-                    choices=['auto', 'dense', 'grouped', 'masked', 'mixed', 'fp4', 'bf16', 'quant', 'layout', 'published'])
+                    choices=['auto', 'dense', 'grouped', 'masked', 'mixed', 'fp4', 'bf16', 'quant', 'layout', 'published', 'moe_mlp'])
     ap.add_argument('--experts', type=int, default=0, help='grouped / masked workloads: global expert count (default 32)')
     ap.add_argument('--no-graph', action='store_true',
                     help='dense workload: plain stream launches instead of a CUDA graph (for profilers that cannot follow a capture)')

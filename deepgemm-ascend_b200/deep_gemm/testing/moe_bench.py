@@ -185,6 +185,8 @@ def run(args, rank, world, device, emit=None, pk=None, checks=None):
         return run_quant(args, rank, world, device, emit)
     if args.workload == 'layout':
         return run_layout(args, rank, world, device, emit, pk)
+    if args.workload == 'moe_mlp':
+        return run_moe_mlp(args, rank, world, device, emit, checks.get('moe_mlp'))
     if args.workload == 'published':
         from .published_bench import run_published
         return run_published(args, rank, world, device, emit, checks.get('dense_row'), checks.get('grouped_row'))
@@ -533,6 +535,78 @@ def run_bf16(args, rank, world, device, emit=None):
             'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16 x bf16, fp32 accumulate (kind::f16)', 'data': 'synthetic',
             'config': {'workload': 'BF16 GEMM NT, BF16 out: ' + str(shapes), 'l2': 'flushed before every GEMM, untimed'},
             'shapes': rows, 'device_status': _api.device_status()}
+    (emit or (lambda l: print(json.dumps(l), flush=True)))(line)
+
+
+class ExpertMlpCase:
+    """The expert MLP of an MoE layer as the reference's unfused baseline runs it (tests/test_mega_moe.py:139-145): an
+    m-grouped FP8 x FP4 GEMM to 2 * intermediate columns, SwiGLU with the routing weight applied and quantised to E4M3
+    with per-32 scales, a second m-grouped FP8 x FP4 GEMM back to `hidden` columns. Tokens sit on the 256-row psum
+    layout; every call goes through the public API."""
+
+    def __init__(self, sizes, hidden: int, intermediate: int, device, seed: int):
+        gen = torch.Generator(device=device).manual_seed(seed)
+        self.sizes, self.hidden, self.intermediate, g = list(sizes), hidden, intermediate, len(sizes)
+        local = shard_psum_layout(self.sizes, 1, 0)
+        self.rows, self.valid_rows = local['rows'], sum(sizes)
+        self.x = _codes((self.rows, hidden), device, gen)
+        self.sfx = _scales((), self.rows, hidden, device, gen)
+        self.w1 = torch.randint(-128, 128, (g, 2 * intermediate, hidden // 2), dtype=torch.int8, device=device, generator=gen)
+        self.sfw1 = _scales((g,), 2 * intermediate, hidden, device, gen)
+        self.w2 = torch.randint(-128, 128, (g, hidden, intermediate // 2), dtype=torch.int8, device=device, generator=gen)
+        self.sfw2 = _scales((g,), hidden, intermediate, device, gen)
+        self.topk_weights = torch.rand(self.rows, device=device, generator=gen) + 0.25
+        self.layout = torch.tensor(local['psum'], dtype=torch.int32, device=device)
+        self.y1 = torch.empty(self.rows, 2 * intermediate, dtype=torch.bfloat16, device=device)
+        self.y2 = torch.empty(self.rows, hidden, dtype=torch.bfloat16, device=device)
+        self.a2 = self.sfa2 = None
+        self.flops = 2.0 * self.valid_rows * (2 * intermediate * hidden + hidden * intermediate)
+        k64 = lambda k: (k + 63) // 64                                                  # noqa: E731
+        self.bytes = (self.valid_rows * (hidden + k64(hidden) * 2 + 2 * intermediate * 2)               # GEMM 1: A, SFA, D
+                      + g * 2 * intermediate * (hidden // 2 + k64(hidden) * 2)                         #         B, SFB
+                      + self.valid_rows * (2 * intermediate * 2 + 4 + intermediate + k64(intermediate) * 2)   # SwiGLU: in, weight, out, scales
+                      + self.valid_rows * (intermediate + k64(intermediate) * 2 + hidden * 2)         # GEMM 2: A, SFA, D
+                      + g * hidden * (intermediate // 2 + k64(intermediate) * 2))                      #         B, SFB
+
+    def run(self):
+        import deep_gemm
+        deep_gemm.m_grouped_fp8_fp4_gemm_nt_contiguous((self.x, self.sfx), (self.w1, self.sfw1), self.y1, self.layout)
+        self.a2, self.sfa2 = deep_gemm.swiglu_apply_weight_to_fp8(self.y1, self.topk_weights, self.layout, expert_alignment=256)
+        deep_gemm.m_grouped_fp8_fp4_gemm_nt_contiguous((self.a2, self.sfa2), (self.w2, self.sfw2), self.y2, self.layout)
+
+
+def run_moe_mlp(args, rank, world, device, emit=None, check=None):
+    """`--workload moe_mlp`: 8 experts of about 8192 tokens, hidden 7168, intermediate 2048 (the two (N, K) of the grouped
+    configuration are exactly this layer's two GEMMs). One step = the three launches; an untimed L2 flush before each
+    step, one CUDA-event pair around it."""
+    lib = L.lib()
+    stream = torch.cuda.current_stream(device)
+    flush = l2_flush_buffer(device)
+    sizes = grouped_sizes(8, False)
+    case = ExpertMlpCase(sizes, 7168, 2048, device, seed=31 + rank)
+    for _ in range(max(args.warmup, 3)):
+        case.run()
+    torch.cuda.synchronize(device)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    launches0 = lib.dg_kernel_launch_count()
+    for e0, e1 in ev:
+        L.check(lib.dg_l2_flush_launch(flush.data_ptr(), flush.numel(), stream.cuda_stream))
+        e0.record(stream)
+        case.run()
+        e1.record(stream)
+    torch.cuda.synchronize(device)
+    launches = lib.dg_kernel_launch_count() - launches0               # (the flush kernel is not counted)
+    ms = sum(e0.elapsed_time(e1) for e0, e1 in ev) / args.steps
+    if rank != 0:
+        return
+    line = {'metric': 'fp8_block_scaled_gemm_tflops', 'value': world * case.flops / ms / 1e9, 'unit': 'TFLOP/s', 'n_gpus': world,
+            'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': 'fp8_e4m3 x fp4_e2m1, ue8m0 scales, bf16 between the GEMMs', 'data': 'synthetic',
+            'config': {'workload': 'MoE expert MLP, 8 experts, %d tokens on the 256-row psum layout, hidden 7168, intermediate 2048: '
+                                   'm-grouped FP8xFP4 GEMM -> SwiGLU * routing weight -> FP8 (per-32 scales) -> m-grouped FP8xFP4 GEMM'
+                                   % case.valid_rows, 'l2': 'flushed before every step, untimed'},
+            'gbs': case.bytes / ms / 1e6, 'gpu_launches': int(launches),
+            'verified': check(case) if check is not None else None, 'device_status': _api.device_status()}
     (emit or (lambda l: print(json.dumps(l), flush=True)))(line)
 
 

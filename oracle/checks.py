@@ -81,3 +81,29 @@ def grouped_row(case, rows: int = 16) -> bool:
             a_deq = dequantize(_values('fp8', case.a[r]), _scales(case.sfa[r], case.k), 1, 32)
             ok = ok and close(case.d[r], gemm_ref(a_deq, b_deq, torch.bfloat16))
     return ok
+
+
+def moe_mlp_case(case, rows: int = 24) -> bool:
+    """The expert MLP chain (GEMM, SwiGLU * weight -> FP8, GEMM) on the first rows of the first and of the last expert:
+    the first GEMM against the oracle; the quantiser against the oracle applied to the GEMM's own BF16 output (codes
+    within one E4M3 step where the device's exp differs in the last bit, scales equal); the second GEMM against the
+    oracle applied to the quantiser's own output."""
+    from .quant import swiglu_quant_ref
+    ok, start, starts = True, 0, []
+    for s_ in case.sizes:
+        starts.append(start)
+        start = (start + s_ + 255) // 256 * 256
+    for g in (0, len(case.sizes) - 1):
+        n_rows = min(rows, case.sizes[g])
+        if n_rows == 0:
+            continue
+        r = slice(starts[g], starts[g] + n_rows)
+        x_deq = dequantize(_values('fp8', case.x[r]), _scales(case.sfx[r], case.hidden), 1, 32)
+        w1_deq = dequantize(_values('fp4', case.w1[g]), _scales(case.sfw1[g], case.hidden), 1, 32)
+        ok = ok and close(case.y1[r], gemm_ref(x_deq, w1_deq, torch.bfloat16))
+        codes, sf, _, deq = swiglu_quant_ref(case.y1[r].cpu(), case.topk_weights[r].cpu())
+        a2_deq = dequantize(_values('fp8', case.a2[r]), _scales(case.sfa2[r], case.intermediate), 1, 32)
+        ok = ok and close(a2_deq, deq)
+        w2_deq = dequantize(_values('fp4', case.w2[g]), _scales(case.sfw2[g], case.intermediate), 1, 32)
+        ok = ok and close(case.y2[r], gemm_ref(a2_deq, w2_deq, torch.bfloat16))
+    return ok

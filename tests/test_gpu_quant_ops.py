@@ -92,3 +92,15 @@ def test_output_feeds_the_gemm_without_a_relayout():
     assert deep_gemm._lib.lib().dg_kernel_launch_count() - launches <= 3
     a_deq = oracle.dequantize(a.float().cpu(), oracle.unpack_required_sf(sfa.cpu(), hidden), 1, 32)
     assert_close(d, oracle.gemm_ref(a_deq, b_ref, torch.bfloat16), 'gemm on the producer output')
+
+
+def test_expert_mlp_chain_through_the_public_api():
+    """GEMM -> SwiGLU * routing weight -> FP8 -> GEMM on a small psum layout (the unfused expert MLP of
+    tests/test_mega_moe.py:139-145), each stage checked by the oracle on the stage's own input."""
+    from deep_gemm.testing.moe_bench import ExpertMlpCase
+    from oracle import checks
+    case = ExpertMlpCase([300, 0, 513, 77], 512, 256, torch.device('cuda', 0), seed=5)
+    case.run()
+    torch.cuda.synchronize()
+    assert deep_gemm.device_status() == 0
+    assert checks.moe_mlp_case(case, rows=64)
