@@ -3,8 +3,9 @@
 // scale-factor relayout runs between the producer and the GEMM. Optionally with SwiGLU in front
 // (out = silu(x[:, :H]) * x[:, H:] * weight), which is the operator between the two expert GEMMs of an MoE layer.
 //
-// Follows third-party/tilelang_ops/swiglu_apply_weight_to_fp8.py of the reference: clamp (:156-161), SiLU by exact
-// division (:162-165), scale = 2^ceil(log2(max(amax, 1e-4) / 448)) from the bit pattern (:80-90), values times the
+// Follows third-party/tilelang_ops/swiglu_apply_weight_to_fp8.py of the reference: clamp (:156-161), SiLU = x / (1 + e^-x)
+// (:162-165; here with the fast exponential and the hardware reciprocal, each within 2 ulp of the exact operation: a value
+// on a rounding boundary of E4M3 may land on the neighbouring code, and the exact division cost a third of the run time), scale = 2^ceil(log2(max(amax, 1e-4) / 448)) from the bit pattern (:80-90), values times the
 // inverse scale rounded to E4M3 (:250-252), packed scales transposed per group of 32 tokens (:104-125), tokens in
 // the padding of a psum layout skipped (:263-268).
 //
@@ -97,7 +98,7 @@ __global__ void __launch_bounds__(kQuantThreads) quant_fp8_kernel(const QuantArg
                                     xl[k] = fminf(xl[k], a.clamp);
                                     xr[k] = fmaxf(fminf(xr[k], a.clamp), -a.clamp);
                                 }
-                                const float silu = __fdiv_rn(xl[k], 1.0f + __expf(-xl[k]));
+                                const float silu = __fdividef(xl[k], 1.0f + __expf(-xl[k]));
                                 float y = silu * xr[k];
                                 if (a.weights) y *= weight;
                                 v[i * 2 + k] = y;
