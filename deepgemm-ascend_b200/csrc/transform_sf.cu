@@ -9,6 +9,7 @@
 // HBM-bound streaming kernel. Each CTA produces a [128 rows x 32 int16 columns] output tile: the
 // source region it needs (at most 128 rows x 64 scales) is read coalesced along whichever source
 // axis is contiguous, reduced to bytes in shared memory, and written back coalesced along MN.
+#include <algorithm>
 #include <cstdlib>
 #include <cuda_runtime.h>
 #include <cstdint>
@@ -270,13 +271,21 @@ __global__ void __launch_bounds__(kTsfThreads, 4) transform_sf_stream_kernel(con
                 packed = make_uint4(lo.x & keep2, lo.y & keep2, hi.x & keep2, hi.y & keep2);
             } else {
                 const uint32_t rel0 = (kb >> a.k_repeat_shift) - s0, rel1 = ((kb + 1u) >> a.k_repeat_shift) - s0;
-                uint32_t out[8];
-                #pragma unroll
-                for (uint32_t j = 0; j < 8; ++j) {
-                    const uint32_t r = (ml0 + j) >> a.gran_shift;
-                    out[j] = r < rows ? (((uint32_t)bytes[r][rel0] | ((uint32_t)bytes[r][rel1] << 8)) & keep) : 0u;
+                if (a.gran_shift >= 3u) {
+                    // the eight rows share one source row: one look-up, replicated
+                    const uint32_t r = ml0 >> a.gran_shift;
+                    const uint32_t one = r < rows ? (((uint32_t)bytes[r][rel0] | ((uint32_t)bytes[r][rel1] << 8)) & keep) : 0u;
+                    const uint32_t two = one | (one << 16);
+                    packed = make_uint4(two, two, two, two);
+                } else {
+                    uint32_t out[8];
+                    #pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j) {
+                        const uint32_t r = (ml0 + j) >> a.gran_shift;
+                        out[j] = r < rows ? (((uint32_t)bytes[r][rel0] | ((uint32_t)bytes[r][rel1] << 8)) & keep) : 0u;
+                    }
+                    packed = make_uint4(out[0] | (out[1] << 16), out[2] | (out[3] << 16), out[4] | (out[5] << 16), out[6] | (out[7] << 16));
                 }
-                packed = make_uint4(out[0] | (out[1] << 16), out[2] | (out[3] << 16), out[4] | (out[5] << 16), out[6] | (out[7] << 16));
             }
             int16_t* dst = a.dst + batch * a.dst_batch_stride + (uint64_t)col * a.dst_col_stride + mn;
             if (mn + 8u <= a.dst_mn) {
@@ -286,6 +295,75 @@ __global__ void __launch_bounds__(kTsfThreads, 4) transform_sf_stream_kernel(con
                 for (uint32_t j = 0; mn + j < a.dst_mn; ++j) dst[j] = (int16_t)(w[j >> 1] >> (16u * (j & 1u)));
             }
         }
+    }
+    if (kFp32 && bad && a.invalid_flag != nullptr) atomicExch(a.invalid_flag, 1);
+}
+
+// An MN-major source with one scale row per operand row (gran_mn = 1) already has the destination's orientation: output
+// column c of eight consecutive rows is two runs of eight source scales (K blocks 2c and 2c + 1), so every thread moves
+// 64 (FP32) or 16 (packed) contiguous bytes in and 16 contiguous bytes out, with no staging at all. Rows in the padding
+// of a psum layout are written as zero. Needs 16-byte aligned source columns and destination columns.
+template <bool kFp32>
+__global__ void __launch_bounds__(kTsfThreads) transform_sf_mn_major_kernel(const TransformSfArgs a) {
+    const uint32_t chunks = (a.dst_mn + 7u) / 8u;
+    const uint64_t total = (uint64_t)chunks * a.dst_cols;
+    const uint32_t batch = blockIdx.y;
+    bool bad = false;
+    for (uint64_t i = blockIdx.x * (uint64_t)kTsfThreads + threadIdx.x; i < total; i += (uint64_t)gridDim.x * kTsfThreads) {
+        const uint32_t col = (uint32_t)(i / chunks), mn = (uint32_t)(i - (uint64_t)col * chunks) * 8u;
+        const uint32_t live = min(8u, a.dst_mn - mn);
+        // rows of this chunk that hold data: all of them, or those below the end of the psum group the chunk lies in
+        // (groups start on multiples of the alignment, which is a multiple of 8: a chunk never straddles two groups)
+        uint32_t valid = live;
+        if (a.psum != nullptr) {
+            uint32_t lo = 0, hi = a.num_groups;
+            while (lo < hi) {
+                const uint32_t mid = (lo + hi) / 2;
+                const uint32_t end = ((uint32_t)__ldg(a.psum + mid) + a.alignment - 1) / a.alignment * a.alignment;
+                if (end > mn) hi = mid; else lo = mid + 1;
+            }
+            const uint32_t end = lo < a.num_groups ? (uint32_t)__ldg(a.psum + lo) : 0u;
+            valid = end > mn ? min(live, end - mn) : 0u;
+        }
+        uint32_t out[4] = {0u, 0u, 0u, 0u};
+        if (valid != 0u) {
+            if constexpr (kFp32) {
+                #pragma unroll
+                for (uint32_t h = 0; h < 2; ++h) {
+                    const uint32_t kb = 2u * col + h;
+                    if (kb >= a.k32_blocks) continue;
+                    const uint32_t* src = reinterpret_cast<const uint32_t*>(a.src) + batch * a.src_batch_stride +
+                                          (uint64_t)(kb >> a.k_repeat_shift) * a.src_col_stride + mn;
+                    uint32_t v[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+                    if (live == 8u) {
+                        const uint4 x = __ldg(reinterpret_cast<const uint4*>(src)), y = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+                        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
+                    } else {
+                        for (uint32_t j = 0; j < live; ++j) v[j] = __ldg(src + j);
+                    }
+                    #pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j) {
+                        if (j >= valid) continue;
+                        if ((v[j] & 0x807fffffu) != 0u) bad = true;            // negative or not a power of two
+                        out[j >> 1] |= ((v[j] >> 23) & 0xffu) << (16u * (j & 1u) + 8u * h);
+                    }
+                }
+            } else {
+                const uint16_t* src = reinterpret_cast<const uint16_t*>(a.src) + batch * a.src_batch_stride + (uint64_t)col * a.src_col_stride + mn;
+                if (live == 8u) {
+                    const uint4 x = __ldg(reinterpret_cast<const uint4*>(src));
+                    out[0] = x.x; out[1] = x.y; out[2] = x.z; out[3] = x.w;
+                } else {
+                    for (uint32_t j = 0; j < live; ++j) out[j >> 1] |= (uint32_t)__ldg(src + j) << (16u * (j & 1u));
+                }
+                #pragma unroll
+                for (uint32_t j = 0; j < 8; ++j)
+                    if (j >= valid) out[j >> 1] &= ~(0xffffu << (16u * (j & 1u)));
+            }
+        }
+        int16_t* dst = a.dst + batch * a.dst_batch_stride + (uint64_t)col * a.dst_col_stride + mn;
+        if (live == 8u) *reinterpret_cast<uint4*>(dst) = make_uint4(out[0], out[1], out[2], out[3]);
+        else for (uint32_t j = 0; j < live; ++j) dst[j] = (int16_t)(out[j >> 1] >> (16u * (j & 1u)));
     }
     if (kFp32 && bad && a.invalid_flag != nullptr) atomicExch(a.invalid_flag, 1);
 }
@@ -356,6 +434,21 @@ extern "C" int dg_transform_sf_launch(const void* src, int src_is_fp32,
                            getenv("DG_TRANSFORM_GENERIC") == nullptr;
     auto s = static_cast<cudaStream_t>(stream);
     const bool per_row = gran_mn == 1;
+    // an MN-major per-row source (FP32 with either K granularity, or packed with per-32 scales)
+    const bool mn_major_ok = per_row && k_psum == nullptr && src_row_stride == 1 && src_cols > 1 && (src_is_fp32 || k_repeat == 1) &&
+                             (reinterpret_cast<uintptr_t>(src) & 15) == 0 && (src_col_stride * src_elem) % 16 == 0 &&
+                             (src_batch_stride * src_elem) % 16 == 0 &&
+                             (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && dst_col_stride % 8 == 0 && dst_batch_stride % 8 == 0 &&
+                             alignment % 8 == 0 && getenv("DG_TRANSFORM_GENERIC") == nullptr;
+    if (mn_major_ok) {
+        const uint64_t items = (uint64_t)((dst_mn + 7) / 8) * a.dst_cols;
+        const uint32_t grid = (uint32_t)std::min<uint64_t>((items + kTsfThreads - 1) / kTsfThreads, 148ull * 32);
+        if (src_is_fp32) transform_sf_mn_major_kernel<true><<<dim3(grid, num_batches), kTsfThreads, 0, s>>>(a);
+        else transform_sf_mn_major_kernel<false><<<dim3(grid, num_batches), kTsfThreads, 0, s>>>(a);
+        DG_CHECK_CUDA(cudaGetLastError());
+        count_kernel_launch();
+        return DG_OK;
+    }
     if (stream_ok && src_is_fp32 && per_row) transform_sf_stream_kernel<true, true><<<dim3(grid_x, num_batches), kTsfThreads, 0, s>>>(a);
     else if (stream_ok && src_is_fp32) transform_sf_stream_kernel<true, false><<<dim3(grid_x, num_batches), kTsfThreads, 0, s>>>(a);
     else if (stream_ok && per_row) transform_sf_stream_kernel<false, true><<<dim3(grid_x, num_batches), kTsfThreads, 0, s>>>(a);
