@@ -71,6 +71,16 @@ def test_group_padding_is_zeroed_even_when_poisoned(dtype, gran):
     out = deep_gemm.transform_sf_into_required_layout(poisoned.cuda(), total, k, (gran, gran, 32), is_sfa=True,
                                                       psum_layout=layout)
     _check(out, expected, f'psum {dtype} gran={gran}')
+    # the same source with the row axis contiguous (its own kernel for per-row scales); no invalid-scale report from padding
+    src = poisoned.cuda().t().contiguous().t()
+    out = deep_gemm.transform_sf_into_required_layout(src, total, k, (gran, gran, 32), is_sfa=True, psum_layout=layout)
+    if dtype == torch.int16 and gran == 1:
+        # packed per-row scales that already have the required layout come back untouched, padding included
+        # (csrc/apis/layout.hpp:37-62 decides before it looks at the psum layout)
+        assert out.data_ptr() == src.data_ptr()
+    else:
+        _check(out, expected, f'psum {dtype} gran={gran} MN-major source')
+    assert deep_gemm.device_status() == 0
 
 
 def test_gran_k_128_expands_to_four_blocks():
@@ -81,6 +91,12 @@ def test_gran_k_128_expands_to_four_blocks():
         sf = (torch.randint(90, 140, (rows, oracle.ceil_div(k, 128)), dtype=torch.int32) << 23).view(torch.float32)
         out = deep_gemm.transform_sf_into_required_layout(sf.cuda(), mn, k, (gran, gran, 128), is_sfa=True)
         _check(out, oracle.required_sf_layout(sf, mn, k, gran, gran_k=128), f'gran_k=128 gran_mn={gran}')
+        # the same scales stored with the row axis contiguous, dense and with rows that end off the 8-row vector width
+        for rows_used in (mn, mn - 3):
+            src = sf[:oracle.ceil_div(rows_used, gran)].cuda().t().contiguous().t()
+            out = deep_gemm.transform_sf_into_required_layout(src, rows_used, k, (gran, gran, 128), is_sfa=True)
+            _check(out, oracle.required_sf_layout(sf[:oracle.ceil_div(rows_used, gran)], rows_used, k, gran, gran_k=128),
+                   f'gran_k=128 gran_mn={gran} MN-major rows={rows_used}')
 
 
 @pytest.mark.parametrize('dtype', [torch.float32, torch.int16])
