@@ -627,6 +627,10 @@ def _run_gemm(gemm_type, a, b, d, c, epilogue_obj, sfa_in, sfb_in, recipe, recip
                 setattr(cfg, key, int(value))
     cfg_ptr = C.byref(cfg) if cfg is not None else None
     lib = L.lib()
+    # The descriptor only holds addresses. Callers that keep it to launch again through the C ABI (the benchmarks do) must
+    # not outlive the tensors behind it, some of which were made here (re-laid scales, repacked or expanded operands):
+    # they ride along on the returned object.
+    desc.keep_alive = (a_use, b_use, sfa, sfb, d, grouped_layout)
     if get_dry_run() or d.is_meta:
         L.check(lib.dg_gemm_dry_run(C.byref(desc), cfg_ptr))
         return desc
