@@ -55,6 +55,22 @@ static int device_sm_count() {
     return 148;    // B200; used when planning without a device (dry run)
 }
 
+// Thread-block clusters of a given size that are resident at once with one CTA per SM. A cluster lives inside one GPC,
+// so this is less than SMs / size. The table holds what cudaOccupancyMaxActiveClusters reports on a B200 (and what the
+// timings show: 33 clusters of 4 run as one wave and 34 take two; 24 of 5 run as one and 27 do not; 18 of 6 do and 24 do
+// not); the first real launch replaces it with the figures of the device at hand.
+static std::atomic<uint32_t> g_cluster_capacity[9] = {{0}, {148}, {74}, {45}, {33}, {26}, {22}, {15}, {15}};
+static void refresh_cluster_capacity() {
+    static std::once_flag once;
+    std::call_once(once, [] {
+        for (uint32_t size = 2; size <= 8; ++size) {
+            int n = 0;
+            if (query_resident_clusters(size, &n) == DG_OK && n > 0) g_cluster_capacity[size].store((uint32_t)n);
+        }
+        (void)cudaGetLastError();
+    });
+}
+
 static uint32_t effective_num_sms(const dg_gemm_desc_t& d) {
     int n = d.num_sms ? (int)d.num_sms : (g_num_sms.load() > 0 ? g_num_sms.load() : device_sm_count());
     return (uint32_t)(n < 1 ? 1 : n);
@@ -460,8 +476,13 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
                 // (a wide tile has one accumulator: ~290 cycles per 32-column chunk are not hidden behind the next tile)
                 const double t_epi = bn > 256 ? bn * 12.0 : bn * (out_fp32 ? 8.0 : 6.0);
                 const bool packed_b = d.b_dtype == DG_E2M1X2 && !is_fp4_pair(d);
-                const double main_loop = rows > kBlockM ? tile_main_cycles(cg, bn, kb_per, atoms, out_fp32 ? 4 : elem_size(d.d_dtype), packed_b, decodes_b(d))
-                                                        : kb_per * k_block_cycles(cg, bn, packed_b, decodes_b(d));
+                double main_loop = rows > kBlockM ? tile_main_cycles(cg, bn, kb_per, atoms, out_fp32 ? 4 : elem_size(d.d_dtype), packed_b, decodes_b(d))
+                                                  : kb_per * k_block_cycles(cg, bn, packed_b, decodes_b(d));
+                // One tile per CTA and that is all (a few hundred rows): the steady-state figures above do not hold, a K
+                // block was never measured under about 520 cycles (256 x 2112 x 7168 as 66 pairs of 32 columns: 18.4 us,
+                // as 66 single CTAs of 64 columns: 18.8 us; both modelled at 11-12 us without this floor, so the K splits
+                // in a cluster that take 12.2 us lost to them)
+                if (rows > kBlockM && waves == 1 && d.gemm_type == DG_GEMM_NORMAL) main_loop = std::max(main_loop, 520.0 * kb_per);
                 const double cycles = main_loop + ((single_accum || waves == 1) ? t_epi : 0.0) + 700.0;
                 double cost = (double)waves * cycles / 1.8;                   // ns at ~1.8 GHz
                 if (cost < t_hbm) cost = t_hbm + 1e-3 * cost;     // HBM-bound: the cheaper schedule still wins ties
@@ -485,11 +506,9 @@ static int select_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
             for (uint32_t bn = 32; bn <= 256; bn += 32) {
                 if (bn > 32 && bn - 32 >= d.n) continue;
                 if (max_stages_for(bn, 1, false, 2, split, atoms) < 4) continue;
-                // A cluster lives inside one GPC, so fewer clusters than SMs / split are resident at once. Assumed GPC
-                // sizes (two of 20 SMs, six of 18), consistent with what was measured: 33 clusters of 4, 45 of 3 and 18 of 6
-                // run as one wave, 18 clusters of 7 or of 8 take two.
+                // (fewer clusters than SMs / split are resident at once: g_cluster_capacity)
                 const uint64_t clusters = m_tiles * ceil_div_u32(d.n, bn);
-                const uint64_t resident = std::max<uint64_t>(1, (uint64_t)(2 * (20 / split) + 6 * (18 / split)) * num_sms / 148);
+                const uint64_t resident = std::max<uint64_t>(1, (uint64_t)g_cluster_capacity[split].load() * num_sms / 148);
                 const uint64_t waves = (clusters + resident - 1) / resident;
                 const uint32_t kb_per = ceil_div_u32(nkb, split);
                 // exchange: staging and sending the chunks a rank does not own, the cluster barrier, the summation
@@ -992,6 +1011,7 @@ int dg_gemm_launch(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config,
         g_plan_hits.fetch_add(1, std::memory_order_relaxed);
     } else {
         g_plan_misses.fetch_add(1, std::memory_order_relaxed);
+        refresh_cluster_capacity();
         if (int rc = validate(*desc)) return rc;
         if (int rc = resolve_config(*desc, config, c)) return rc;
         if (int rc = build_plan(*desc, c, workspace, workspace_bytes, /*encode=*/true, plan)) return rc;
@@ -1007,6 +1027,10 @@ int dg_fp4_expansion_needed(const dg_gemm_desc_t* desc, int* expand_a, int* expa
     *expand_a = (unpacks_fp4_a(d) && !tma_can_expand_fp4(d.a, d.outer_stride_a, d.group_stride_a, d.major_a == DG_MAJOR_K ? d.k : d.m)) ? 1 : 0;
     *expand_b = (decodes_b(d) && d.gemm_type == DG_GEMM_K_GROUPED_PSUM) ? 1 : 0;
     return DG_OK;
+}
+
+uint32_t dg_resident_clusters(uint32_t cluster_size) {
+    return cluster_size >= 1 && cluster_size <= 8 ? g_cluster_capacity[cluster_size].load() : 0u;
 }
 
 void dg_plan_cache_stats(uint64_t* hits, uint64_t* misses) {

@@ -37,5 +37,8 @@ struct LaunchPlan {
 
 int launch_gemm_kernel(const LaunchPlan& plan, cudaStream_t stream);
 int get_status_pointer(int32_t** out);
+// How many thread-block clusters of `cluster_size` single-CTA-per-SM GEMM CTAs the current device keeps resident at once
+// (a cluster must fit into one GPC). Loads the kernel: call it only where a launch is about to happen anyway.
+int query_resident_clusters(uint32_t cluster_size, int* out);
 
 }  // namespace dg

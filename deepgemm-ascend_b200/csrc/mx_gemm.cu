@@ -106,6 +106,25 @@ static KernelFn pick_kernel(int cta_group, int major_a, int major_b, bool decode
     return table[cta_group - 1][major_a][major_b][decode_b ? 1 : 0];
 }
 
+int query_resident_clusters(uint32_t cluster_size, int* out) {
+    KernelFn fn = mx_gemm_kernel<1, 0, 0, false, true>;          // the lean kernel, which is what splits K over a cluster
+    constexpr int kSmem = 200 * 1024;                             // one CTA per SM, as every tiling of that kernel has
+    DG_CHECK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(cluster_size * 148, 1, 1);
+    cfg.blockDim = dim3(kNumThreads, 1, 1);
+    cfg.dynamicSmemBytes = kSmem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster_size;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DG_CHECK_CUDA(cudaOccupancyMaxActiveClusters(out, fn, &cfg));
+    return DG_OK;
+}
+
 // Caller-owned trace buffers, one per device (see dg_debug_set_trace_buffer).
 static std::mutex g_trace_mu;
 static unsigned long long* g_trace_buf[64] = {};

@@ -252,6 +252,11 @@ int dg_expand_fp4_launch(const void* src, uint64_t src_pitch_bytes, void* dst, u
  * No reference counterpart: its kernels load packed operands in either major themselves. */
 int dg_fp4_expansion_needed(const dg_gemm_desc_t* desc, int* expand_a, int* expand_b);
 
+/* Thread-block clusters of `cluster_size` (1..8) CTAs, one CTA per SM, that the tiling heuristic assumes are resident at
+ * once when it splits K over a cluster: figures measured on B200 until the first dg_gemm_launch of the process has asked
+ * the runtime (cudaOccupancyMaxActiveClusters) for the device's own. No reference counterpart. */
+uint32_t dg_resident_clusters(uint32_t cluster_size);
+
 /* Writes a buffer larger than L2 so that the next kernel starts cold (deep_gemm/testing/bench.py:263-268). */
 int dg_l2_flush_launch(void* buffer, size_t bytes, void* stream);
 

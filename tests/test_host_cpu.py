@@ -395,3 +395,26 @@ def test_benchmark_refuses_to_run_without_a_gpu():
     proc, line = _run_bench('--steps', '1')
     assert proc.returncode != 0 and line is None
     assert 'no CPU fallback' in proc.stderr
+
+
+def test_cluster_split_never_exceeds_the_resident_clusters():
+    """A K split inside a thread-block cluster only pays when all clusters run as one wave: for a range of few-hundred-row
+    problems the heuristic's cluster tilings stay within `dg_resident_clusters` (a cluster must fit into one GPC)."""
+    lib = L.lib()
+    caps = [lib.dg_resident_clusters(s) for s in range(0, 9)]
+    assert caps[1] == 148 and caps[2] <= 74 and caps[4] <= 148 // 4 and caps[8] <= 148 // 8 and all(c > 0 for c in caps[1:])
+    for m in (1, 64, 128, 256, 384, 512, 768, 1024):
+        for n, k in ((2112, 7168), (576, 7168), (4096, 7168), (7168, 2048), (7168, 16384), (1024, 7168)):
+            d = L.GemmDesc()
+            d.a = d.b = d.d = d.sfa = d.sfb = 0x1000
+            d.a_dtype, d.b_dtype, d.d_dtype = L.E4M3, L.E4M3, L.BF16
+            d.m, d.n, d.k = m, n, k
+            d.outer_stride_a = d.outer_stride_b = k
+            d.outer_stride_d = n
+            d.sfa_stride, d.sfb_stride = (m + 7) // 8 * 8, (n + 7) // 8 * 8
+            cfg = L.GemmConfig()
+            assert lib.dg_select_config(ctypes.byref(d), ctypes.byref(cfg)) == 0, L.last_error()
+            c = cfg.as_dict()
+            if c['cluster_split']:
+                clusters = -(-m // 128) * -(-n // c['block_n'])
+                assert clusters <= caps[c['split_k']], (m, n, k, c)
