@@ -269,7 +269,8 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     const bool tma_ok = split || tma_store_ok(d);
     if (d.epilogue == DG_EPILOGUE_FP8_QUANT) c.epilogue_mode = kEpiFp8Quant;
     else if (split) c.epilogue_mode = kEpiTmaReduce;
-    else if (d.accumulate) c.epilogue_mode = tma_ok ? kEpiTmaReduce : kEpiPlainAtomic;
+    // (a BF16 D that is accumulated into is read, added in FP32 and rounded once: no reduce-add in memory)
+    else if (d.accumulate) c.epilogue_mode = d.d_dtype == DG_BF16 ? kEpiPlainStore : (tma_ok ? kEpiTmaReduce : kEpiPlainAtomic);
     else c.epilogue_mode = tma_ok ? kEpiTmaStore : kEpiPlainStore;
 
     const uint32_t gran = 32u;
@@ -633,6 +634,7 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     if (unpacks_fp4_a(d)) a.idesc |= (5u << 7);                  // kind::mxf8f6f4: A format E2M1
     a.b_tx_shift = native_fp4_b(d) ? 1u : 0u;
     a.a_tx_shift = unpacks_fp4_a(d) ? 1u : 0u;
+    a.add_c_bf16 = (d.accumulate && d.d_dtype == DG_BF16 && !split) ? 1u : 0u;
     if (is_bf16_pair(d))                                         // kind::f16: FP32 accumulator, BF16 operands, no scale fields
         a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)d.major_a << 15) | ((uint32_t)d.major_b << 16) |
                   (((c.block_n / tile_halves(c.block_n)) >> 3) << 17) | (((kBlockM * c.cta_group) >> 4) << 24);
@@ -645,7 +647,8 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     plan.bf16_pair = is_bf16_pair(d);
     plan.wide_epi = wide_epilogue(c);
     plan.lean = d.gemm_type == DG_GEMM_NORMAL && c.cta_group == 1 && !plan.decode_b && c.epilogue_mode == kEpiPlainStore &&
-                (d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_BIAS) && !plan.fp4_pair && !plan.bf16_pair && !plan.wide_epi && !feature_disabled("lean");
+                (d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_BIAS) && !plan.fp4_pair && !plan.bf16_pair && !plan.wide_epi &&
+                !a.add_c_bf16 && !feature_disabled("lean");
     a.epi_simple = (d.epilogue == DG_EPILOGUE_IDENTITY && !a.has_alpha && !a.has_bias && !a.stochastic &&
                     c.epilogue_mode <= kEpiTmaReduce && !splits_in_cluster(c) && !feature_disabled("straight")) ? 1u : 0u;
     plan.wide_tile = c.block_n > 256;

@@ -83,6 +83,7 @@ struct GemmKernelArgs {
     uint32_t b_tx_shift;              // 1 when TMA expands packed E2M1 rows of B into 16-byte containers: the barrier then
                                       // counts the packed bytes it read (half of what lands in shared memory), else 0
     uint32_t a_tx_shift;              // the same for a packed E2M1 A
+    uint32_t add_c_bf16;              // BF16 D accumulated into: the epilogue reads D, adds in FP32 and rounds once
     int32_t* status;
     unsigned long long* trace;        // debugging aid: per-CTA timestamps (8 slots each), or nullptr
 };
@@ -853,6 +854,30 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             bv = out_is_fp32() ? __ldg(reinterpret_cast<const float*>(p.bias) + col0 + i)
                                              : __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0 + i));
                         v[i] = __float_as_uint(__uint_as_float(v[i]) + bv);
+                    }
+                }
+                if (!kLean && !kSimple && p.add_c_bf16) {
+                    // D = bf16(A B + D): a reduce-add in memory would round the product to BF16 before adding, which costs
+                    // up to an ulp of the larger addend when the two nearly cancel; here the old D joins the FP32 sum.
+                    if (row < p.m) {
+                        const __nv_bfloat16* old_d = reinterpret_cast<const __nv_bfloat16*>(p.d) + (uint64_t)t.d_z * p.d_group_stride +
+                                                     (uint64_t)row * p.d_stride + col0;
+                        if (col0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(old_d) & 15u) == 0) {
+                            #pragma unroll
+                            for (uint32_t c = 0; c < 4; ++c) {
+                                const uint4 x = reinterpret_cast<const uint4*>(old_d)[c];
+                                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+                                #pragma unroll
+                                for (uint32_t j = 0; j < 4; ++j) {
+                                    v[c * 8 + 2 * j] = __float_as_uint(__uint_as_float(v[c * 8 + 2 * j]) + __uint_as_float(w[j] << 16));
+                                    v[c * 8 + 2 * j + 1] = __float_as_uint(__uint_as_float(v[c * 8 + 2 * j + 1]) + __uint_as_float(w[j] & 0xffff0000u));
+                                }
+                            }
+                        } else {
+                            #pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (col0 + i < p.n) v[i] = __float_as_uint(__uint_as_float(v[i]) + __bfloat162float(old_d[i]));
+                        }
                     }
                 }
                 if (!kLean && !kSimple && p.epilogue_mode == kEpiFp8Quant) {

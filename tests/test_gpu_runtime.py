@@ -237,3 +237,22 @@ def test_bench_msprof_reports_the_gemm_kernel_by_name():
         bench_msprof(fn, kernel_names='kernel', num_warmups=0, num_tests=1)
     with pytest.raises(ValueError):
         bench_msprof(fn)
+
+
+@pytest.mark.parametrize('m,n,k', [(256, 384, 1024), (130, 200, 512), (4096, 512, 2048), (64, 2112, 7168)])
+def test_bf16_accumulation_rounds_once(m, n, k):
+    """D (BF16) = A B + D is the FP32 sum rounded once: bit for bit the BF16 cast of the FP32-accumulated result, also
+    where product and addend nearly cancel (a reduce-add of a BF16-rounded product would be off by several ulps there)."""
+    seed_all(12)
+    a, sfa, a_ref = uniform_fp8((m, k), (1, 32))
+    b, sfb, b_ref = uniform_fp8((n, k), (1, 32))
+    prod = a_ref @ b_ref.T
+    c = (-prod * (1.0 + 0.01 * torch.randn(m, n))).to(torch.bfloat16)           # nearly cancels the product
+    a_arg, b_arg = (a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda())
+    d32 = c.float().cuda()
+    deep_gemm.fp8_gemm_nt(a_arg, b_arg, d32, c=d32)
+    d16 = c.cuda()
+    deep_gemm.fp8_gemm_nt(a_arg, b_arg, d16, c=d16)
+    assert deep_gemm.device_status() == 0
+    assert torch.equal(d16.view(torch.int16), d32.to(torch.bfloat16).view(torch.int16))
+    assert_close(d16, (prod + c.float()).to(torch.bfloat16), f'bf16 accumulate {m}x{n}x{k}')
