@@ -646,7 +646,10 @@ static int build_plan(const dg_gemm_desc_t& d, const dg_gemm_config_t& c, void* 
     plan.fp4_pair = is_fp4_pair(d);
     plan.bf16_pair = is_bf16_pair(d);
     plan.wide_epi = wide_epilogue(c);
-    plan.lean = d.gemm_type == DG_GEMM_NORMAL && c.cta_group == 1 && !plan.decode_b && c.epilogue_mode == kEpiPlainStore &&
+    // (the lean kernel is built for CTAs that have one tile each: once that tile is multiplied its producer, MMA and packer
+    //  warps turn into epilogue warps. Plain stores are also what a D that TMA cannot write gets, with any number of tiles)
+    const bool one_tile_each = (uint64_t)a.num_m_blocks * a.num_n_blocks * c.split_k <= c.num_ctas;
+    plan.lean = d.gemm_type == DG_GEMM_NORMAL && c.cta_group == 1 && !plan.decode_b && c.epilogue_mode == kEpiPlainStore && one_tile_each &&
                 (d.epilogue == DG_EPILOGUE_IDENTITY || d.epilogue == DG_EPILOGUE_BIAS) && !plan.fp4_pair && !plan.bf16_pair && !plan.wide_epi &&
                 !a.add_c_bf16 && !feature_disabled("lean");
     a.epi_simple = (d.epilogue == DG_EPILOGUE_IDENTITY && !a.has_alpha && !a.has_bias && !a.stochastic &&

@@ -535,3 +535,13 @@ def test_m_grouped_mixed_fp8_fp4(trans_b):
         for g, mg in enumerate(masked):
             if mg:
                 assert_close(d[g, :mg], ref[g, :mg], f'masked fp8xfp4 group {g}')
+
+
+@pytest.mark.parametrize('m,n,k,config', [(1152, 2742, 1408, {'block_n': 64, 'cta_group': 1}),
+                                          (1152, 2742, 1425, {'block_n': 32, 'cta_group': 1}),
+                                          (384, 32766, 512, None), (1000, 4098, 640, {'block_n': 128, 'cta_group': 1})])
+def test_dense_plain_stores_with_several_tiles_per_cta(m, n, k, config):
+    """A D whose rows TMA cannot write (N * element size not a multiple of 16 bytes) goes out through plain stores; with
+    single CTAs and three or more tiles per CTA that must not take the one-tile-per-CTA kernel."""
+    _dense(m, n, k, config=config)
+    _dense(m, n, k, config=config, out=torch.float32, acc=True)
