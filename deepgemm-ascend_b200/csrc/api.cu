@@ -263,6 +263,13 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
     const uint32_t num_sms = effective_num_sms(d);
     c.block_m = kBlockM * c.cta_group;
     c.block_k = kBlockK;
+    if (c.split_k > 1) {
+        // every split must own at least one K block: settle the split count before anything is derived from it (the
+        // reduce buffers of a cluster split grow when the count drops, e.g. 4 -> 3 splits of a 128-column tile)
+        const uint32_t nkb_all = ceil_div_u32(k_bytes(d), kBlockK);
+        DG_CHECK_ARG(c.split_k <= nkb_all, "split_k larger than the number of K blocks");
+        c.split_k = ceil_div_u32(nkb_all, ceil_div_u32(nkb_all, c.split_k));
+    }
     if (c.split_k <= 1) c.reserved[3] = 0;
     const bool split = splits_in_workspace(c);
     const bool in_cluster = splits_in_cluster(c);
@@ -349,13 +356,6 @@ static int complete_config(const dg_gemm_desc_t& d, dg_gemm_config_t& c) {
         //  a lean kernel uses)
         const uint32_t need = (c.block_n / 32) * kReduceSlabBytes + kNumEpilogueWarps * (store_bufs + 1) * kStoreBufBytes;
         DG_CHECK_ARG(ring >= need, "cluster split-K needs a pipeline of at least %u bytes, %u stages give %u", need, c.num_stages, ring);
-    }
-    if (c.split_k > 1) {
-        DG_CHECK_ARG(c.split_k <= nkb, "split_k larger than the number of K blocks");
-        // every split must own at least one K block
-        const uint32_t per = ceil_div_u32(nkb, c.split_k);
-        c.split_k = ceil_div_u32(nkb, per);
-        if (c.split_k <= 1) c.reserved[3] = 0;
     }
     // one CTA per SM: keep the dynamic shared memory above half of the SM's capacity
     const uint32_t need = make_smem_layout(c.block_n, c.num_stages, c.cta_group, decode_b, store_bufs,
@@ -1030,8 +1030,10 @@ int dg_gemm_launch(const dg_gemm_desc_t* desc, const dg_gemm_config_t* config,
 int dg_fp4_expansion_needed(const dg_gemm_desc_t* desc, int* expand_a, int* expand_b) {
     DG_CHECK_ARG(desc != nullptr && expand_a != nullptr && expand_b != nullptr, "dg_fp4_expansion_needed: null argument");
     const dg_gemm_desc_t& d = *desc;
-    *expand_a = (unpacks_fp4_a(d) && !tma_can_expand_fp4(d.a, d.outer_stride_a, d.group_stride_a, d.major_a == DG_MAJOR_K ? d.k : d.m)) ? 1 : 0;
     *expand_b = (decodes_b(d) && d.gemm_type == DG_GEMM_K_GROUPED_PSUM) ? 1 : 0;
+    // (an expanded B is E4M3, and a packed A next to an E4M3 B is not a supported pair: A follows)
+    *expand_a = (unpacks_fp4_a(d) && (*expand_b || !tma_can_expand_fp4(d.a, d.outer_stride_a, d.group_stride_a,
+                                                                        d.major_a == DG_MAJOR_K ? d.k : d.m))) ? 1 : 0;
     return DG_OK;
 }
 

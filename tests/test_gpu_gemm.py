@@ -545,3 +545,12 @@ def test_dense_plain_stores_with_several_tiles_per_cta(m, n, k, config):
     single CTAs and three or more tiles per CTA that must not take the one-tile-per-CTA kernel."""
     _dense(m, n, k, config=config)
     _dense(m, n, k, config=config, out=torch.float32, acc=True)
+
+
+def test_cluster_split_that_shrinks_to_fewer_splits():
+    """K = 551 has five K blocks: four requested splits become three (two blocks each), whose reduce buffers are larger
+    than those of four; the pipeline depth must be sized for the split count that runs."""
+    cfg = {'block_n': 128, 'cta_group': 1, 'split_k': 4, 'cluster_split': 1, 'num_stages': 6}
+    _dense(33, 128, 551, trans='tn', config=cfg, acc=True)
+    _dense(33, 128, 551, trans='nt', config=cfg)
+    _dense(128, 192, 640, config={'block_n': 64, 'cta_group': 1, 'split_k': 4, 'cluster_split': 1})

@@ -347,7 +347,11 @@ def test_fp4_expansion_rule_of_the_c_abi():
     d.m, d.outer_stride_a, d.n, d.outer_stride_b = 256, 128, 200, 100
     d.gemm_type, d.num_groups, d.grouped_layout = L.GEMM_K_GROUPED_PSUM, 2, 0x1000
     lib.dg_fp4_expansion_needed(ctypes.byref(d), ctypes.byref(ea), ctypes.byref(eb))
+    assert (ea.value, eb.value) == (1, 1)                                      # (an expanded B is E4M3: the packed A follows it)
+    d.a_dtype = L.E4M3
+    lib.dg_fp4_expansion_needed(ctypes.byref(d), ctypes.byref(ea), ctypes.byref(eb))
     assert (ea.value, eb.value) == (0, 1)
+    d.a_dtype = L.E2M1X2
     d.major_a = d.major_b = L.MAJOR_K                                          # the kind::mxf4 kernel reads packed operands itself
     d.gemm_type, d.n, d.outer_stride_a, d.outer_stride_b = L.GEMM_NORMAL, 200, 515, 515
     lib.dg_fp4_expansion_needed(ctypes.byref(d), ctypes.byref(ea), ctypes.byref(eb))
