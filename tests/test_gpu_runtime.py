@@ -256,3 +256,81 @@ def test_bf16_accumulation_rounds_once(m, n, k):
     assert deep_gemm.device_status() == 0
     assert torch.equal(d16.view(torch.int16), d32.to(torch.bfloat16).view(torch.int16))
     assert_close(d16, (prod + c.float()).to(torch.bfloat16), f'bf16 accumulate {m}x{n}x{k}')
+
+
+def _runtime_cases():
+    seed_all(21)
+    cases = []
+    for (m, n, k) in [(128, 2112, 7168), (64, 512, 8192), (1000, 1500, 1024), (4096, 1024, 512)]:
+        a, sfa, a_ref = uniform_fp8((m, k), (1, 32))
+        b, sfb, b_ref = uniform_fp8((n, k), (1, 32))
+        cases.append(((a.cuda(), sfa.cuda()), (b.cuda(), sfb.cuda()), oracle.gemm_ref(a_ref, b_ref, torch.bfloat16), (m, n, k)))
+    return cases
+
+
+def test_sm_limit_from_all_sms_down_to_one():
+    """`set_num_sms` (csrc/apis/runtime.hpp:12-24): grids, cluster splits and waves follow the limit; results do not change."""
+    cases = _runtime_cases()
+    try:
+        for sms in (148, 132, 100, 33, 8, 2, 1):
+            deep_gemm.set_num_sms(sms)
+            for a, b, ref, shape in cases:
+                d = torch.full(ref.shape, float('nan'), dtype=torch.bfloat16, device='cuda')
+                deep_gemm.fp8_gemm_nt(a, b, d)
+                assert deep_gemm.device_status() == 0
+                assert_close(d, ref, f'num_sms={sms} {shape}')
+    finally:
+        deep_gemm.set_num_sms(torch.cuda.get_device_properties(0).multi_processor_count)
+
+
+def test_threads_on_streams_of_their_own():
+    """Three host threads, each on its own stream, alternating the heuristic's tiling and a split through the FP32 scratch
+    (one scratch per stream): the ABI is thread-safe and the launches of different streams do not share state."""
+    import threading
+    cases = _runtime_cases()[:3]
+    errors = []
+
+    def worker(tid):
+        try:
+            torch.cuda.set_device(0)
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                for it in range(20):
+                    for a, b, ref, shape in cases:
+                        d = torch.full(ref.shape, float('nan'), dtype=torch.bfloat16, device='cuda')
+                        cfg = {'block_n': 128, 'cta_group': 1, 'split_k': 4} if (it + tid) % 2 else None
+                        deep_gemm.fp8_gemm_nt(a, b, d, config=cfg)
+                        stream.synchronize()
+                        assert_close(d, ref, f'thread {tid} iteration {it} {shape}')
+        except Exception as exc:        # noqa: BLE001 - collected and reported by the main thread
+            errors.append((tid, repr(exc)[:300]))
+    threads = [threading.Thread(target=worker, args=(t,)) for t in range(3)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert errors == [] and deep_gemm.device_status() == 0
+
+
+def test_api_calls_inside_a_cuda_graph():
+    """Calls with FP32 scales (two relayout kernels each) and a K split through the scratch, captured once (after a
+    first plain call, as the header asks) and replayed: same results at every replay."""
+    a, b, ref, _ = _runtime_cases()[1]
+    split = {'block_n': 128, 'cta_group': 1, 'split_k': 4}
+    d = torch.empty(ref.shape, dtype=torch.bfloat16, device='cuda')
+    deep_gemm.fp8_gemm_nt(a, b, d)
+    deep_gemm.fp8_gemm_nt(a, b, d, config=split)
+    torch.cuda.synchronize()
+    d1, d2 = torch.empty_like(d), torch.empty_like(d)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        deep_gemm.fp8_gemm_nt(a, b, d1)
+        deep_gemm.fp8_gemm_nt(a, b, d2, config=split)
+    for _ in range(3):
+        d1.fill_(float('nan'))
+        d2.fill_(float('nan'))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert_close(d1, ref, 'replayed, heuristic tiling')
+        assert_close(d2, ref, 'replayed, split through the scratch')
+    assert deep_gemm.device_status() == 0
